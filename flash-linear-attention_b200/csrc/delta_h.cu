@@ -1,0 +1,204 @@
+// State recurrence of the (gated) delta rule: the serial part of the pipeline.
+//   forward  (fla/ops/common/chunk_delta_h.py:27-119): per chunk
+//       h[t] = S;  v_new = u - (w * e^{b}) bf(S);  S <- e^{b_L} S + (k * e^{b_L-b})^T bf(v_new)
+//   backward (fla/ops/common/chunk_delta_h.py:136-237): per chunk, last to first
+//       dh[t] = D; dv2 = dv + (k * e^{b_L-b}) bf(D);
+//       D <- e^{b_L} D + (q*scale*e^{b})^T do - (w * e^{b})^T bf(dv2)
+// One CTA owns all K rows and a 64-wide slab of V columns of one (sequence, head) state; the state
+// stays in accumulator registers, its rounded copy goes through shared memory both as the operand
+// of the dependent product and as the staging buffer of the coalesced h / dh store.  Token tiles of
+// the next chunk are prefetched with cp.async while the current chunk is processed.
+#include "common.cuh"
+
+namespace flab {
+
+constexpr int DBV = 64;  // V columns per CTA
+
+template <typename T, int KP, bool BWD>
+__global__ void __launch_bounds__(128) delta_h_kernel(const flab_args a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int LDK = KP + Num<T>::pad;
+  constexpr int LDB = DBV + Num<T>::pad;
+  constexpr int MI = KP / 64;  // state rows per warp = 16 * MI
+  constexpr int NKT = BWD ? 3 : 2;  // [tokens x K] tiles per chunk: fwd (w, k); bwd (q, k, w)
+  constexpr int NVT = BWD ? 2 : 1;  // [tokens x BV] tiles per chunk: fwd (u); bwd (do, dv)
+  T *sKT = reinterpret_cast<T *>(smem_raw);        // [2][NKT][64][LDK]
+  T *sVT = sKT + 2 * NKT * C * LDK;                // [2][NVT][64][LDB]
+  T *sS = sVT + 2 * NVT * C * LDB;                 // [KP][LDB] rounded state
+  float *sG = reinterpret_cast<float *>(sS + KP * LDB);  // [2][64]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2;
+  const int v0 = blockIdx.x * DBV;
+  const int n = blockIdx.y / a.H, hd = blockIdx.y % a.H;
+  const Seq s = seq_of(a, n);
+  const int vw = min(DBV, a.V - v0);
+  const bool use_g = a.g != nullptr;
+  const size_t ks = tok_stride(a, a.K), vs = tok_stride(a, a.V), gs = tok_stride(a, 1);
+  const size_t offk = tok_off(a, s, hd, 0, a.K), offv = tok_off(a, s, hd, 0, a.V) + v0;
+  const float *G = use_g ? reinterpret_cast<const float *>(a.g) + tok_off(a, s, hd, 0, 1) : nullptr;
+  const T *kt_src[3];
+  const T *vt_src[2];
+  if (!BWD) {
+    kt_src[0] = reinterpret_cast<const T *>(a.w) + offk;
+    kt_src[1] = reinterpret_cast<const T *>(a.k) + offk;
+    kt_src[2] = nullptr;
+    vt_src[0] = reinterpret_cast<const T *>(a.u) + offv;
+    vt_src[1] = nullptr;
+  } else {
+    kt_src[0] = reinterpret_cast<const T *>(a.q) + offk;
+    kt_src[1] = reinterpret_cast<const T *>(a.k) + offk;
+    kt_src[2] = reinterpret_cast<const T *>(a.w) + offk;
+    vt_src[0] = reinterpret_cast<const T *>(a.d_o) + offv;
+    vt_src[1] = reinterpret_cast<const T *>(a.dv) + offv;
+  }
+  T *Hout = reinterpret_cast<T *>(BWD ? a.dh : a.h);
+  T *Vout = reinterpret_cast<T *>(BWD ? a.dv2 : a.v_new) + offv;
+  const float *S0 = reinterpret_cast<const float *>(BWD ? a.dht : a.h0);
+  float *S1 = reinterpret_cast<float *>(BWD ? a.dh0 : a.ht);
+
+  float acc[MI][8][4];
+  acc_zero(acc);
+  const int ms = warp * 16 * MI;  // first state row of this warp
+  const int m0 = warp * 16;       // first token row of this warp
+  const size_t st_off = ((size_t)n * a.H + hd) * a.K * a.V;
+  if (S0) {
+    FLAB_ACC_FOREACH(MI, 8, ms, 0, row, col, mi, ni, r) {
+      if (row < a.K && col < vw) acc[mi][ni][r] = S0[st_off + (size_t)row * a.V + v0 + col];
+    }
+  }
+
+  auto load = [&](int it, int buf) {
+    const int t0 = it * C, rows = min(C, s.len - t0);
+#pragma unroll
+    for (int j = 0; j < NKT; ++j)
+      tile_load<T>(sKT + (buf * NKT + j) * C * LDK, LDK, kt_src[j] + (size_t)t0 * ks, ks, rows, C, a.K, KP, tid, 128);
+#pragma unroll
+    for (int j = 0; j < NVT; ++j)
+      tile_load<T>(sVT + (buf * NVT + j) * C * LDB, LDB, vt_src[j] + (size_t)t0 * vs, vs, rows, C, vw, DBV, tid, 128);
+    if (tid < C) sG[buf * C + tid] = (use_g && tid < rows) ? G[(size_t)(t0 + tid) * gs] : 0.f;
+    cp_async_commit();
+  };
+
+  const int first = BWD ? s.nt - 1 : 0, step = BWD ? -1 : 1;
+  if (s.nt > 0) load(first, 0);
+  for (int i = 0; i < s.nt; ++i) {
+    const int it = first + i * step, cur = i & 1;
+    if (i + 1 < s.nt) {
+      load(it + step, cur ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int t0 = it * C, rows = min(C, s.len - t0), last = rows - 1;
+    T *kt = sKT + cur * NKT * C * LDK, *vt = sVT + cur * NVT * C * LDB;
+    const float *gc = sG + cur * C;
+    const float gl = gc[last];
+    // (a) rounded state -> shared; gate scaling of the token tiles in place
+    acc_to_smem<MI, 8, T>(acc, sS, LDB, ms, 0);
+    if (!BWD) {
+      if (use_g) {
+        T *w = kt, *k = kt + C * LDK;
+        for (int e = tid; e < C * KP; e += 128) {
+          int r_ = e / KP, c_ = e - r_ * KP;
+          w[r_ * LDK + c_] = Num<T>::t(Num<T>::f(w[r_ * LDK + c_]) * expf(gc[r_]));
+          k[r_ * LDK + c_] = Num<T>::t(Num<T>::f(k[r_ * LDK + c_]) * expf(gl - gc[r_]));
+        }
+      }
+    } else {
+      T *q = kt, *k = kt + C * LDK, *w = kt + 2 * C * LDK;
+      for (int e = tid; e < C * KP; e += 128) {
+        int r_ = e / KP, c_ = e - r_ * KP;
+        const float eg = use_g ? expf(gc[r_]) : 1.f;
+        q[r_ * LDK + c_] = Num<T>::t(Num<T>::f(q[r_ * LDK + c_]) * a.scale * eg);
+        w[r_ * LDK + c_] = Num<T>::t(-Num<T>::f(w[r_ * LDK + c_]) * eg);
+        if (use_g) k[r_ * LDK + c_] = Num<T>::t(Num<T>::f(k[r_ * LDK + c_]) * expf(gl - gc[r_]));
+      }
+    }
+    __syncthreads();
+    // (b) state at the chunk boundary -> global
+    {
+      const size_t hoff = ((size_t)(s.c0 + it) * a.H + hd) * a.K * a.V + v0;
+      tile_store<T>(Hout + hoff, (size_t)a.V, sS, LDB, a.K, vw, tid, 128);
+    }
+    // (c) the dependent product against the rounded state
+    {
+      float p[1][8][4];
+      acc_zero(p);
+      const T *A = BWD ? kt + C * LDK : kt;  // bwd: k~ ; fwd: w~
+      WarpGemm<1, 8, false, true, T>::run(p, A, LDK, m0, sS, LDB, 0, KP);
+      T *y = BWD ? vt + C * LDB : vt;  // bwd: dv ; fwd: u   (updated in place)
+      FLAB_ACC_FOREACH(1, 8, m0, 0, row, col, mi, ni, r) {
+        float base = Num<T>::f(y[row * LDB + col]);
+        p[mi][ni][r] = BWD ? base + p[mi][ni][r] : base - p[mi][ni][r];
+      }
+      acc_to_smem<1, 8, T>(p, y, LDB, m0, 0);
+    }
+    __syncthreads();
+    // (d) v_new / dv2 -> global
+    tile_store<T>(Vout + (size_t)t0 * vs, vs, BWD ? vt + C * LDB : vt, LDB, rows, vw, tid, 128);
+    // (e) state update
+    if (use_g) {
+      const float d = expf(gl);
+#pragma unroll
+      for (int mi = 0; mi < MI; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) acc[mi][ni][r] *= d;
+    }
+    if (!BWD) {
+      WarpGemm<MI, 8, true, true, T>::run(acc, kt + C * LDK, LDK, ms, vt, LDB, 0, C);
+    } else {
+      WarpGemm<MI, 8, true, true, T>::run(acc, kt, LDK, ms, vt, LDB, 0, C);                          // q~^T do
+      WarpGemm<MI, 8, true, true, T>::run(acc, kt + 2 * C * LDK, LDK, ms, vt + C * LDB, LDB, 0, C);  // -(w~)^T dv2
+    }
+    __syncthreads();
+  }
+  if (S1) {
+    FLAB_ACC_FOREACH(MI, 8, ms, 0, row, col, mi, ni, r) {
+      if (row < a.K && col < vw) S1[st_off + (size_t)row * a.V + v0 + col] = acc[mi][ni][r];
+    }
+  }
+  (void)g8;
+}
+
+template <typename T, int KP, bool BWD> static int launch_delta_h(const flab_args *a, cudaStream_t stream) {
+  constexpr int LDK = KP + Num<T>::pad, LDB = DBV + Num<T>::pad;
+  constexpr int NKT = BWD ? 3 : 2, NVT = BWD ? 2 : 1;
+  size_t smem = ((size_t)2 * NKT * C * LDK + (size_t)2 * NVT * C * LDB + (size_t)KP * LDB) * sizeof(T) + 2 * C * sizeof(float);
+  auto kern = delta_h_kernel<T, KP, BWD>;
+  if (int e = set_smem(kern, smem)) return e;
+  kern<<<dim3(cdiv(a->V, DBV), a->N * a->H), 128, smem, stream>>>(*a);
+  return check_launch(BWD ? "delta_bwd_dhu" : "delta_fwd_h");
+}
+
+template <bool BWD> static int dispatch_delta_h(const flab_args *a, void *stream) {
+  FLAB_REQUIRE(a->K <= 256, FLAB_E_UNSUPPORTED, "delta-rule state scan: K = %d > 256", a->K);
+  FLAB_DISPATCH_16(a->dtype, T, {
+    if (a->K <= 64) return (launch_delta_h<T, 64, BWD>(a, (cudaStream_t)stream));
+    if (a->K <= 128) return (launch_delta_h<T, 128, BWD>(a, (cudaStream_t)stream));
+    return (launch_delta_h<T, 256, BWD>(a, (cudaStream_t)stream));
+  });
+  return FLAB_OK;
+}
+
+}  // namespace flab
+
+extern "C" {
+
+int flab_delta_fwd_h(const flab_args *a, void *stream) {
+  using namespace flab;
+  if (int e = check_common(a)) return e;
+  FLAB_REQUIRE(a->k && a->w && a->u && a->h && a->v_new, FLAB_E_BADARG, "delta_fwd_h needs k, w, u, h and v_new");
+  return dispatch_delta_h<false>(a, stream);
+}
+
+int flab_delta_bwd_dhu(const flab_args *a, void *stream) {
+  using namespace flab;
+  if (int e = check_common(a)) return e;
+  FLAB_REQUIRE(a->q && a->k && a->w && a->d_o && a->dv && a->dh && a->dv2, FLAB_E_BADARG,
+               "delta_bwd_dhu needs q, k, w, d_o, dv, dh and dv2");
+  return dispatch_delta_h<true>(a, stream);
+}
+}

@@ -1,0 +1,391 @@
+// WY / UT transform of the (gated) delta rule, one CTA per (chunk, head).
+//   forward : A = (I + tril(diag(beta) K K^T [* e^{b_i-b_j}], -1))^-1,  w = Aw (beta k),  u = Au (beta v)
+//             (fla/ops/delta_rule/wy_fast.py:94-253, fla/ops/gated_delta_rule/wy_fast.py:111-317)
+//   backward: dk, dv, dbeta (, dg) from dw, du through the inverse
+//             (fla/ops/delta_rule/wy_fast.py:325-433, fla/ops/gated_delta_rule/wy_fast.py:440-562)
+// The Gram matrix and all products run on the tensor cores; the 64x64 unit-lower-triangular inverse
+// is a forward substitution in fp32 shared memory (one thread per column, one barrier per row).
+// A is rounded to the element type before it multiplies anything, as in the reference.
+// K and V are walked in tiles of 128 columns, so any head dimension works.
+#include "common.cuh"
+
+namespace flab {
+
+constexpr int WT = 128;  // column tile of k / v
+constexpr int LDL = C + 1;
+
+// forward substitution: Linv = strict lower part of (I + L)^-1 given Lo = -strict_lower(Gram).
+// `nmat` matrices are processed side by side by thread groups of 64.
+__device__ __forceinline__ void tri_inverse(const float *Lo, float *Li, int nmat, int tid) {
+  const int mat = tid >> 6, j = tid & 63;
+  const bool act = mat < nmat;
+  const float *lo = Lo + mat * C * LDL;
+  float *li = Li + mat * C * LDL;
+  if (act) li[j] = 0.f;  // row 0
+  __syncthreads();
+  for (int i = 1; i < C; ++i) {
+    if (act) {
+      float acc = 0.f;
+      if (j < i) {
+        acc = lo[i * LDL + j];
+        for (int m = j + 1; m < i; ++m) acc = fmaf(lo[i * LDL + m], li[m * LDL + j], acc);
+      }
+      li[i * LDL + j] = acc;
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T, bool GATED, bool RECOMPUTE>
+__global__ void __launch_bounds__(128) wy_fwd_kernel(const flab_args a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int LDX = WT + Num<T>::pad;
+  constexpr int LDP = C + Num<T>::pad;
+  constexpr int NM = GATED ? 2 : 1;
+  T *sX = reinterpret_cast<T *>(smem_raw);  // [64][LDX] k or v tile; reused to stage w / u
+  T *sXB = sX + C * LDX;                    // [64][LDX] beta-scaled tile
+  T *sA = sXB + C * LDX;                    // [NM][64][LDP] Aw, Au as T
+  float *sLo = reinterpret_cast<float *>(sA + NM * C * LDP);  // [NM][64][LDL]
+  float *sLi = sLo + NM * C * LDL;                            // [NM][64][LDL]
+  float *sBeta = sLi + NM * C * LDL;                          // [64]
+  float *sG = sBeta + C;                                      // [64]
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  int n, it;
+  chunk_of(a, blockIdx.x, n, it);
+  const int hd = blockIdx.y;
+  const Seq s = seq_of(a, n);
+  const int t0 = it * C, rows = min(C, s.len - t0);
+  const size_t ks = tok_stride(a, a.K), vs = tok_stride(a, a.V), as_ = tok_stride(a, C);
+  const size_t offk = tok_off(a, s, hd, t0, a.K), offv = tok_off(a, s, hd, t0, a.V), offa = tok_off(a, s, hd, t0, C);
+  const T *k = reinterpret_cast<const T *>(a.k), *v = reinterpret_cast<const T *>(a.v), *beta = reinterpret_cast<const T *>(a.beta);
+  const int m0 = warp * 16;
+
+  if (tid < C) {
+    sBeta[tid] = tid < rows ? Num<T>::f(beta[tok_off(a, s, hd, t0 + tid, 1)]) : 0.f;
+    sG[tid] = (GATED && tid < rows) ? reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + tid, 1)] : 0.f;
+  }
+
+  if (!RECOMPUTE) {
+    float gram[1][8][4];
+    acc_zero(gram);
+    for (int k0 = 0; k0 < a.K; k0 += WT) {
+      const int kw = min(WT, a.K - k0), kp = round_up(kw, 16);
+      __syncthreads();
+      tile_load<T>(sX, LDX, k + offk + k0, ks, rows, C, kw, kp, tid, 128);
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncthreads();
+      for (int e = tid; e < C * kp; e += 128) {
+        int r_ = e / kp, c_ = e - r_ * kp;
+        sXB[r_ * LDX + c_] = Num<T>::t(Num<T>::f(sX[r_ * LDX + c_]) * sBeta[r_]);
+      }
+      __syncthreads();
+      WarpGemm<1, 8, false, false, T>::run(gram, sXB, LDX, m0, sX, LDX, 0, kp);
+    }
+    FLAB_ACC_FOREACH(1, 8, m0, 0, row, col, mi, ni, r) {
+      float x = row > col ? -gram[mi][ni][r] : 0.f;
+      sLo[row * LDL + col] = x;
+      if (GATED) sLo[C * LDL + row * LDL + col] = row > col ? x * safe_exp(sG[row] - sG[col]) : 0.f;
+    }
+    __syncthreads();
+    tri_inverse(sLo, sLi, NM, tid);
+    for (int e = tid; e < NM * C * C; e += 128) {
+      int m = e / (C * C), r_ = (e / C) % C, c_ = e % C;
+      float x = sLi[m * C * LDL + r_ * LDL + c_] + (r_ == c_ ? 1.f : 0.f);
+      sA[m * C * LDP + r_ * LDP + c_] = Num<T>::t(x);
+    }
+    __syncthreads();
+    tile_store<T>(reinterpret_cast<T *>(a.aw) + offa, as_, sA, LDP, rows, C, tid, 128);
+    if (GATED) tile_store<T>(reinterpret_cast<T *>(a.au) + offa, as_, sA + C * LDP, LDP, rows, C, tid, 128);
+  } else {
+    tile_load<T>(sA, LDP, reinterpret_cast<const T *>(a.aw) + offa, as_, rows, C, C, C, tid, 128);
+    if (GATED) tile_load<T>(sA + C * LDP, LDP, reinterpret_cast<const T *>(a.au) + offa, as_, rows, C, C, C, tid, 128);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+  }
+
+  // w = Aw (beta k), u = Au (beta v), tile by tile
+  for (int pass = 0; pass < 2; ++pass) {
+    const int D = pass == 0 ? a.K : a.V;
+    const T *src = pass == 0 ? k + offk : v + offv;
+    T *dst = pass == 0 ? reinterpret_cast<T *>(a.w) + offk : reinterpret_cast<T *>(a.u) + offv;
+    const size_t st = pass == 0 ? ks : vs;
+    const T *A = (pass == 1 && GATED) ? sA + C * LDP : sA;
+    for (int d0 = 0; d0 < D; d0 += WT) {
+      const int dw_ = min(WT, D - d0);
+      __syncthreads();
+      tile_load<T>(sXB, LDX, src + d0, st, rows, C, dw_, WT, tid, 128);
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncthreads();
+      for (int e = tid; e < C * WT; e += 128) {
+        int r_ = e / WT, c_ = e - r_ * WT;
+        sXB[r_ * LDX + c_] = Num<T>::t(Num<T>::f(sXB[r_ * LDX + c_]) * sBeta[r_]);
+      }
+      __syncthreads();
+      float acc[1][16][4];
+      acc_zero(acc);
+      WarpGemm<1, 16, false, true, T>::run(acc, A, LDP, m0, sXB, LDX, 0, C);
+      acc_to_smem<1, 16, T>(acc, sX, LDX, m0, 0);
+      __syncthreads();
+      tile_store<T>(dst + d0, st, sX, LDX, rows, dw_, tid, 128);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward
+// ------------------------------------------------------------------------------------------------
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(128) wy_bwd_kernel(const flab_args a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int LDX = WT + Num<T>::pad;
+  constexpr int LDP = C + Num<T>::pad;
+  T *sX = reinterpret_cast<T *>(smem_raw);  // [64][LDX] k / v tile
+  T *sXB = sX + C * LDX;                    // [64][LDX] beta-scaled tile
+  T *sD = sXB + C * LDX;                    // [64][LDX] dw / du tile; reused to stage outputs
+  T *sAw = sD + C * LDX;                    // [64][LDP]
+  T *sAu = sAw + C * LDP;                   // [64][LDP] (gated)
+  T *sDA = sAu + (GATED ? C * LDP : 0);     // [64][LDP] staged dA
+  T *sTmp = sDA + C * LDP;                  // [64][LDP] staged intermediate product
+  float *sBeta = reinterpret_cast<float *>(sTmp + C * LDP);  // [64]
+  float *sG = sBeta + C;                                     // [64]
+  float *sDG = sG + C;                                       // [64]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2;
+  int n, it;
+  chunk_of(a, blockIdx.x, n, it);
+  const int hd = blockIdx.y;
+  const Seq s = seq_of(a, n);
+  const int t0 = it * C, rows = min(C, s.len - t0);
+  const size_t ks = tok_stride(a, a.K), vs = tok_stride(a, a.V), as_ = tok_stride(a, C);
+  const size_t offk = tok_off(a, s, hd, t0, a.K), offv = tok_off(a, s, hd, t0, a.V), offa = tok_off(a, s, hd, t0, C);
+  const T *k = reinterpret_cast<const T *>(a.k), *v = reinterpret_cast<const T *>(a.v), *beta = reinterpret_cast<const T *>(a.beta);
+  const int m0 = warp * 16;
+
+  if (tid < C) {
+    sBeta[tid] = tid < rows ? Num<T>::f(beta[tok_off(a, s, hd, t0 + tid, 1)]) : 0.f;
+    sG[tid] = (GATED && tid < rows) ? reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + tid, 1)] : 0.f;
+    sDG[tid] = 0.f;
+  }
+  tile_load<T>(sAw, LDP, reinterpret_cast<const T *>(a.aw) + offa, as_, rows, C, C, C, tid, 128);
+  if (GATED) tile_load<T>(sAu, LDP, reinterpret_cast<const T *>(a.au) + offa, as_, rows, C, C, C, tid, 128);
+  cp_async_commit();
+
+  const float b_lo = 0.f;
+  (void)b_lo;
+  float dbeta_lo = 0.f, dbeta_hi = 0.f;  // rows m0+g8, m0+g8+8 (partial over this thread's columns)
+  float dA[1][8][4], dA2[1][8][4];
+  acc_zero(dA);
+  acc_zero(dA2);
+
+  // one pass over the column tiles of (x = k or v, dx = dw or du): accumulates dAcc += dx (beta x)^T,
+  // writes dout = (A^T dx) * beta and adds sum(A^T dx * x) to dbeta.
+  auto tile_pass = [&](const T *x, const T *dx, T *dout, size_t st, int D, const T *A, float (&dAcc)[1][8][4]) {
+    for (int d0 = 0; d0 < D; d0 += WT) {
+      const int dw_ = min(WT, D - d0);
+      __syncthreads();
+      tile_load<T>(sX, LDX, x + d0, st, rows, C, dw_, WT, tid, 128);
+      tile_load<T>(sD, LDX, dx + d0, st, rows, C, dw_, WT, tid, 128);
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncthreads();
+      for (int e = tid; e < C * WT; e += 128) {
+        int r_ = e / WT, c_ = e - r_ * WT;
+        sXB[r_ * LDX + c_] = Num<T>::t(Num<T>::f(sX[r_ * LDX + c_]) * sBeta[r_]);
+      }
+      __syncthreads();
+      WarpGemm<1, 8, false, false, T>::run(dAcc, sD, LDX, m0, sXB, LDX, 0, WT);
+      float acc[1][16][4];
+      acc_zero(acc);
+      WarpGemm<1, 16, true, true, T>::run(acc, A, LDP, m0, sD, LDX, 0, C);
+      FLAB_ACC_FOREACH(1, 16, m0, 0, row, col, mi, ni, r) {
+        float xb = acc[mi][ni][r];
+        float xv = Num<T>::f(sX[row * LDX + col]);
+        if (r >> 1) dbeta_hi += xb * xv; else dbeta_lo += xb * xv;
+        acc[mi][ni][r] = xb * sBeta[row];
+      }
+      __syncthreads();  // all warps finished reading sD
+      acc_to_smem<1, 16, T>(acc, sD, LDX, m0, 0);
+      __syncthreads();
+      tile_store<T>(dout + d0, st, sD, LDX, rows, dw_, tid, 128);
+    }
+  };
+  // dA <- -strict_lower(A^T strict_lower(dA) A^T), rounded to T between products; result left in
+  // registers (rounded) and staged in sDA.
+  auto transform = [&](float (&dAcc)[1][8][4], const T *A) {
+    FLAB_ACC_FOREACH(1, 8, m0, 0, row, col, mi, ni, r) { dAcc[mi][ni][r] = row > col ? dAcc[mi][ni][r] : 0.f; }
+    __syncthreads();
+    acc_to_smem<1, 8, T>(dAcc, sDA, LDP, m0, 0);
+    __syncwarp();
+    float x1[1][8][4];
+    acc_zero(x1);
+    WarpGemm<1, 8, false, false, T>::run(x1, sDA, LDP, m0, A, LDP, 0, C);  // dA A^T
+    acc_to_smem<1, 8, T>(x1, sTmp, LDP, m0, 0);
+    __syncthreads();
+    acc_zero(dAcc);
+    WarpGemm<1, 8, true, true, T>::run(dAcc, A, LDP, m0, sTmp, LDP, 0, C);  // A^T (dA A^T)
+    FLAB_ACC_FOREACH(1, 8, m0, 0, row, col, mi, ni, r) { dAcc[mi][ni][r] = row > col ? rnd<T>(-dAcc[mi][ni][r]) : 0.f; }
+  };
+
+  cp_async_wait<0>();
+  __syncthreads();
+  T *dk = reinterpret_cast<T *>(a.dk) + offk, *dv = reinterpret_cast<T *>(a.dv) + offv;
+  const T *dw = reinterpret_cast<const T *>(a.dw) + offk, *du = reinterpret_cast<const T *>(a.du) + offv;
+  if (!GATED) {
+    tile_pass(v + offv, du, dv, vs, a.V, sAw, dA);
+    tile_pass(k + offk, dw, dk, ks, a.K, sAw, dA);
+    transform(dA, sAw);
+  } else {
+    tile_pass(k + offk, dw, dk, ks, a.K, sAw, dA);
+    transform(dA, sAw);
+    tile_pass(v + offv, du, dv, vs, a.V, sAu, dA2);
+    transform(dA2, sAu);
+    FLAB_ACC_FOREACH(1, 8, m0, 0, row, col, mi, ni, r) {
+      float x2 = dA2[mi][ni][r] * safe_exp(sG[row] - sG[col]);
+      dA2[mi][ni][r] = x2;
+      dA[mi][ni][r] = rnd<T>(dA[mi][ni][r] + x2);
+    }
+  }
+  __syncthreads();
+  acc_to_smem<1, 8, T>(dA, sDA, LDP, m0, 0);
+  __syncthreads();
+
+  // second K pass: dk += dA^T (beta k) + (dA k) * beta; dbeta += sum((dA k) * k); gated: Gram for dg
+  float gram[1][8][4];
+  acc_zero(gram);
+  for (int k0 = 0; k0 < a.K; k0 += WT) {
+    const int kw = min(WT, a.K - k0);
+    __syncthreads();
+    tile_load<T>(sX, LDX, k + offk + k0, ks, rows, C, kw, WT, tid, 128);
+    tile_load<T>(sD, LDX, dk + k0, ks, rows, C, kw, WT, tid, 128);  // first-pass dk (rounded to T)
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    for (int e = tid; e < C * WT; e += 128) {
+      int r_ = e / WT, c_ = e - r_ * WT;
+      sXB[r_ * LDX + c_] = Num<T>::t(Num<T>::f(sX[r_ * LDX + c_]) * sBeta[r_]);
+    }
+    __syncthreads();
+    if (GATED) WarpGemm<1, 8, false, false, T>::run(gram, sXB, LDX, m0, sX, LDX, 0, WT);
+    float kb2[1][16][4], acc[1][16][4];
+    acc_zero(kb2);
+    acc_zero(acc);
+    WarpGemm<1, 16, false, true, T>::run(kb2, sDA, LDP, m0, sX, LDX, 0, C);  // dA k
+    WarpGemm<1, 16, true, true, T>::run(acc, sDA, LDP, m0, sXB, LDX, 0, C);  // dA^T (beta k)
+    FLAB_ACC_FOREACH(1, 16, m0, 0, row, col, mi, ni, r) {
+      float xb = kb2[mi][ni][r];
+      float kv = Num<T>::f(sX[row * LDX + col]);
+      if (r >> 1) dbeta_hi += xb * kv; else dbeta_lo += xb * kv;
+      acc[mi][ni][r] += Num<T>::f(sD[row * LDX + col]) + xb * sBeta[row];
+    }
+    // each thread overwrites exactly the sD elements it just read
+    acc_to_smem<1, 16, T>(acc, sD, LDX, m0, 0);
+    __syncthreads();
+    tile_store<T>(dk + k0, ks, sD, LDX, rows, kw, tid, 128);
+  }
+  // dbeta
+  dbeta_lo += __shfl_xor_sync(0xffffffffu, dbeta_lo, 1);
+  dbeta_lo += __shfl_xor_sync(0xffffffffu, dbeta_lo, 2);
+  dbeta_hi += __shfl_xor_sync(0xffffffffu, dbeta_hi, 1);
+  dbeta_hi += __shfl_xor_sync(0xffffffffu, dbeta_hi, 2);
+  float *dbeta = reinterpret_cast<float *>(a.dbeta);
+  if ((lane & 3) == 0) {
+    if (m0 + g8 < rows) dbeta[tok_off(a, s, hd, t0 + m0 + g8, 1)] = dbeta_lo;
+    if (m0 + g8 + 8 < rows) dbeta[tok_off(a, s, hd, t0 + m0 + g8 + 8, 1)] = dbeta_hi;
+  }
+  if (GATED) {
+    // dg = rowsum(dA2 * Gram) - colsum(dA2 * Gram)
+    float r_lo = 0.f, r_hi = 0.f;
+#pragma unroll
+    for (int ni = 0; ni < 8; ++ni) {
+      float p0 = dA2[0][ni][0] * gram[0][ni][0], p1 = dA2[0][ni][1] * gram[0][ni][1];
+      float p2 = dA2[0][ni][2] * gram[0][ni][2], p3 = dA2[0][ni][3] * gram[0][ni][3];
+      r_lo += p0 + p1;
+      r_hi += p2 + p3;
+      float c0 = p0 + p2, c1 = p1 + p3;
+      c0 += __shfl_xor_sync(0xffffffffu, c0, 4);
+      c0 += __shfl_xor_sync(0xffffffffu, c0, 8);
+      c0 += __shfl_xor_sync(0xffffffffu, c0, 16);
+      c1 += __shfl_xor_sync(0xffffffffu, c1, 4);
+      c1 += __shfl_xor_sync(0xffffffffu, c1, 8);
+      c1 += __shfl_xor_sync(0xffffffffu, c1, 16);
+      if (g8 == 0) {
+        atomicAdd(&sDG[ni * 8 + 2 * (lane & 3)], -c0);
+        atomicAdd(&sDG[ni * 8 + 2 * (lane & 3) + 1], -c1);
+      }
+    }
+    r_lo += __shfl_xor_sync(0xffffffffu, r_lo, 1);
+    r_lo += __shfl_xor_sync(0xffffffffu, r_lo, 2);
+    r_hi += __shfl_xor_sync(0xffffffffu, r_hi, 1);
+    r_hi += __shfl_xor_sync(0xffffffffu, r_hi, 2);
+    if ((lane & 3) == 0) {
+      atomicAdd(&sDG[m0 + g8], r_lo);
+      atomicAdd(&sDG[m0 + g8 + 8], r_hi);
+    }
+    __syncthreads();
+    if (tid < rows) reinterpret_cast<float *>(a.dg)[tok_off(a, s, hd, t0 + tid, 1)] = sDG[tid];
+  }
+}
+
+template <typename T, bool GATED, bool RECOMPUTE> static int launch_wy_fwd(const flab_args *a, cudaStream_t stream) {
+  constexpr int LDX = WT + Num<T>::pad, LDP = C + Num<T>::pad, NM = GATED ? 2 : 1;
+  size_t smem = ((size_t)2 * C * LDX + (size_t)NM * C * LDP) * sizeof(T) + ((size_t)2 * NM * C * LDL + 2 * C) * sizeof(float);
+  auto kern = wy_fwd_kernel<T, GATED, RECOMPUTE>;
+  if (int e = set_smem(kern, smem)) return e;
+  kern<<<dim3(a->NT, a->H), 128, smem, stream>>>(*a);
+  return check_launch(RECOMPUTE ? "wy_recompute" : "wy_fwd");
+}
+
+template <typename T, bool GATED> static int launch_wy_bwd(const flab_args *a, cudaStream_t stream) {
+  constexpr int LDX = WT + Num<T>::pad, LDP = C + Num<T>::pad;
+  size_t smem = ((size_t)3 * C * LDX + (size_t)(GATED ? 4 : 3) * C * LDP) * sizeof(T) + 3 * C * sizeof(float);
+  auto kern = wy_bwd_kernel<T, GATED>;
+  if (int e = set_smem(kern, smem)) return e;
+  kern<<<dim3(a->NT, a->H), 128, smem, stream>>>(*a);
+  return check_launch("wy_bwd");
+}
+
+}  // namespace flab
+
+extern "C" {
+
+int flab_wy_fwd(const flab_args *a, void *stream) {
+  using namespace flab;
+  if (int e = check_common(a)) return e;
+  FLAB_REQUIRE(a->k && a->v && a->beta && a->aw && a->w && a->u, FLAB_E_BADARG, "wy_fwd needs k, v, beta, aw, w and u");
+  FLAB_REQUIRE(!a->g || a->au, FLAB_E_BADARG, "wy_fwd: g given but au is NULL");
+  FLAB_DISPATCH_16(a->dtype, T, {
+    if (a->g) return (launch_wy_fwd<T, true, false>(a, (cudaStream_t)stream));
+    return (launch_wy_fwd<T, false, false>(a, (cudaStream_t)stream));
+  });
+  return FLAB_OK;
+}
+
+int flab_wy_recompute(const flab_args *a, void *stream) {
+  using namespace flab;
+  if (int e = check_common(a)) return e;
+  FLAB_REQUIRE(a->k && a->v && a->beta && a->aw && a->w && a->u, FLAB_E_BADARG, "wy_recompute needs k, v, beta, aw, w and u");
+  FLAB_DISPATCH_16(a->dtype, T, {
+    if (a->au) return (launch_wy_fwd<T, true, true>(a, (cudaStream_t)stream));
+    return (launch_wy_fwd<T, false, true>(a, (cudaStream_t)stream));
+  });
+  return FLAB_OK;
+}
+
+int flab_wy_bwd(const flab_args *a, void *stream) {
+  using namespace flab;
+  if (int e = check_common(a)) return e;
+  FLAB_REQUIRE(a->k && a->v && a->beta && a->aw && a->dw && a->du && a->dk && a->dv && a->dbeta, FLAB_E_BADARG,
+               "wy_bwd needs k, v, beta, aw, dw, du, dk, dv and dbeta");
+  const bool gated = a->g != nullptr;
+  FLAB_REQUIRE(!gated || (a->au && a->dg), FLAB_E_BADARG, "wy_bwd: g given but au or dg is NULL");
+  FLAB_DISPATCH_16(a->dtype, T, {
+    if (gated) return (launch_wy_bwd<T, true>(a, (cudaStream_t)stream));
+    return (launch_wy_bwd<T, false>(a, (cudaStream_t)stream));
+  });
+  return FLAB_OK;
+}
+}

@@ -1,0 +1,117 @@
+# -*- coding: utf-8 -*-
+"""ctypes binding of libflab200.so (the C ABI declared in include/flab200.h).
+
+The shared library is the product: there is no Python or CPU fallback.  Importing this module
+without the built library raises immediately with the build command.
+"""
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("FLA_B200_LIB", os.path.join(_HERE, "libflab200.so"))
+
+CHUNK = 64
+
+_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+F_REVERSE = 1 << 0
+F_BETA_VECTOR = 1 << 1
+F_INPLACE_STATE = 1 << 2
+
+_PTR_FIELDS = [
+    "q", "k", "v", "g", "gk", "gv", "beta", "w", "u", "aw", "au", "h", "h0", "ht", "v_new", "o",
+    "d_o", "dh", "dht", "dh0", "dq", "dk", "dv", "dv2", "dw", "du", "dg", "dgk", "dgv", "dbeta",
+    "a", "da", "x", "y", "ws",
+]
+
+
+class FlabArgs(ctypes.Structure):
+    """Mirror of `struct flab_args` (include/flab200.h)."""
+    _fields_ = (
+        [(n, ctypes.c_int32) for n in ("B", "T", "H", "K", "V", "N", "NT", "dtype", "head_first", "flags")]
+        + [("scale", ctypes.c_float), ("S", ctypes.c_int32)]
+        + [(n, ctypes.c_void_p) for n in ("cu_seqlens", "chunk_indices", "chunk_offsets")]
+        + [(n, ctypes.c_void_p) for n in _PTR_FIELDS]
+        + [("ws_bytes", ctypes.c_size_t)]
+    )
+
+
+ENTRY_POINTS = [
+    "flab_chunk_local_cumsum_scalar", "flab_chunk_local_cumsum_vector",
+    "flab_chunk_global_cumsum_scalar", "flab_chunk_global_cumsum_vector",
+    "flab_chunk_fwd_h", "flab_chunk_bwd_dh", "flab_chunk_fwd_o", "flab_chunk_bwd_dv",
+    "flab_chunk_bwd_dv_local", "flab_chunk_bwd_dqkwg", "flab_wy_fwd", "flab_wy_recompute",
+    "flab_wy_bwd", "flab_delta_fwd_h", "flab_delta_bwd_dhu", "flab_gla_fwd_intra", "flab_gla_fwd_o",
+    "flab_gla_bwd_dav", "flab_gla_bwd_dqkg", "flab_recurrent_fwd", "flab_recurrent_bwd",
+    "flab_recurrent_delta_fwd", "flab_recurrent_delta_bwd",
+]
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once; fail loudly if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} not found. Build it with `make -C flash-linear-attention_b200/csrc` "
+            "(or `python -c 'import __graft_entry__ as g; g.build()'`). There is no fallback path.")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.flab_last_error.restype = ctypes.c_char_p
+    lib.flab_abi_version.restype = ctypes.c_int
+    for name in ENTRY_POINTS:
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.POINTER(FlabArgs), ctypes.c_void_p]
+    _lib = lib
+    return lib
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    assert t.is_contiguous(), "flab200 kernels need contiguous tensors"
+    return t.data_ptr()
+
+
+def call(entry: str, ref: torch.Tensor, *, B, T, H, K=0, V=0, N=None, NT=0, dtype=None, head_first=False,
+         flags=0, scale=1.0, S=0, varlen=None, **tensors):
+    """Launch one stage on the current stream of `ref`'s device.
+
+    `varlen` is the tuple produced by `fla_b200.utils.prepare_varlen` or None; `tensors` maps slot
+    names of `flab_args` to tensors (None = absent).
+    """
+    lib = load()
+    if not ref.is_cuda:
+        raise RuntimeError("flab200 kernels run on CUDA tensors only (no CPU fallback)")
+    a = FlabArgs()
+    a.B, a.T, a.H, a.K, a.V = B, T, H, K, V
+    a.N = N if N is not None else B
+    a.NT = NT
+    a.dtype = _DTYPES[dtype if dtype is not None else ref.dtype]
+    a.head_first = int(bool(head_first))
+    a.flags = flags
+    a.scale = float(scale)
+    a.S = S
+    if varlen is not None:
+        a.cu_seqlens = varlen.cu_seqlens.data_ptr()
+        a.chunk_indices = varlen.chunk_indices.data_ptr()
+        a.chunk_offsets = varlen.chunk_offsets.data_ptr()
+    for name, t in tensors.items():
+        if name not in _PTR_FIELDS:
+            raise KeyError(f"unknown flab_args slot {name!r}")
+        if t is not None:
+            if t.device != ref.device:
+                raise RuntimeError(f"slot {name}: tensor on {t.device}, expected {ref.device}")
+            setattr(a, name, _ptr(t))
+    with torch.cuda.device(ref.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = getattr(lib, entry)(ctypes.byref(a), ctypes.c_void_p(stream))
+    if rc != 0:
+        raise RuntimeError(f"{entry} failed ({rc}): {lib.flab_last_error().decode()}")

@@ -1,0 +1,156 @@
+# -*- coding: utf-8 -*-
+"""Stage-level launch wrappers: one Python function per C-ABI entry point, allocating outputs with
+torch and passing raw pointers.  Names follow the reference's launch wrappers in
+fla/ops/common/{chunk_h,chunk_o,chunk_delta_h}.py, fla/ops/utils/cumsum.py and the wy_fast modules."""
+
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+from .._lib import CHUNK, F_REVERSE
+from ..utils import Geometry, prepare_varlen
+
+
+def _geo(x: torch.Tensor, offsets, head_first: bool) -> Geometry:
+    """Geometry for a [B,T,H] / [B,T,H,S] tensor (cumsum entry points)."""
+    if x.dim() == 3:
+        k = x.unsqueeze(-1)
+    else:
+        k = x
+    return Geometry(k, None, offsets, head_first)
+
+
+def _cumsum(x, reverse, offsets, head_first, local, out_dtype=torch.float32):
+    x = x.contiguous()
+    if offsets is not None:
+        assert x.shape[0] == 1, "Only batch size 1 is supported when offsets are provided"
+    if x.dim() not in (3, 4):
+        raise ValueError(f"Unsupported input shape {x.shape}; expected [B,T,H] / [B,T,H,D] "
+                         f"(or the head-first permutations)")
+    geo = _geo(x, offsets, head_first)
+    y = torch.empty_like(x, dtype=torch.float32)
+    S = x.shape[-1] if x.dim() == 4 else 0
+    kind = "vector" if x.dim() == 4 else "scalar"
+    entry = f"flab_chunk_{'local' if local else 'global'}_cumsum_{kind}"
+    _lib.call(entry, x, B=geo.B, T=geo.T, H=geo.H, N=geo.N, NT=geo.NT, head_first=head_first,
+              flags=F_REVERSE if reverse else 0, S=S, varlen=geo.varlen, dtype=x.dtype, x=x, y=y)
+    return y if out_dtype in (None, torch.float32) else y.to(out_dtype)
+
+
+def chunk_local_cumsum(g: torch.Tensor, chunk_size: int = CHUNK, reverse: bool = False,
+                       offsets: Optional[torch.Tensor] = None, indices=None, head_first: bool = True) -> torch.Tensor:
+    """Per-chunk inclusive cumulative sum, fp32 result (fla/ops/utils/cumsum.py:389)."""
+    if chunk_size != CHUNK:
+        raise ValueError(f"chunk_size is fixed at {CHUNK}")
+    return _cumsum(g, reverse, offsets, head_first, True)
+
+
+def chunk_global_cumsum(s: torch.Tensor, dtype: Optional[torch.dtype] = None, reverse: bool = False,
+                        offsets: Optional[torch.Tensor] = None, head_first: bool = True) -> torch.Tensor:
+    """Whole-sequence inclusive cumulative sum (fla/ops/utils/cumsum.py:369)."""
+    return _cumsum(s, reverse, offsets, head_first, False, dtype or s.dtype)
+
+
+def _state_buffers(geo: Geometry, ref: torch.Tensor, want_final: bool):
+    h = torch.empty(geo.NT, geo.H, geo.K, geo.V, dtype=ref.dtype, device=ref.device)
+    ht = torch.empty(geo.N, geo.H, geo.K, geo.V, dtype=torch.float32, device=ref.device) if want_final else None
+    return h, ht
+
+
+def _f32(x):
+    return None if x is None else x.float().contiguous()
+
+
+def chunk_fwd_h(geo: Geometry, k, v, g=None, gk=None, h0=None, output_final_state=False):
+    """State at the start of every chunk (fla/ops/common/chunk_h.py:282). Returns (h, ht)."""
+    h, ht = _state_buffers(geo, k, output_final_state)
+    _lib.call("flab_chunk_fwd_h", k, **geo.kw(), k=k, v=v, g=g, gk=gk, h0=_f32(h0), h=h, ht=ht)
+    return h, ht
+
+
+def chunk_bwd_dh(geo: Geometry, q, do, scale, g=None, gk=None, dht=None, want_dh0=False):
+    """Reverse state-gradient scan (fla/ops/common/chunk_h.py:338). Returns (dh, dh0)."""
+    dh, dh0 = _state_buffers(geo, q, want_dh0)
+    _lib.call("flab_chunk_bwd_dh", q, **geo.kw(), scale=scale, q=q, d_o=do, g=g, gk=gk, dht=_f32(dht), dh=dh, dh0=dh0)
+    return dh, dh0
+
+
+def chunk_fwd_o(geo: Geometry, q, k, v, h, g=None, scale=1.0):
+    """Intra-chunk output (fla/ops/common/chunk_o.py:444)."""
+    o = torch.empty_like(v)
+    _lib.call("flab_chunk_fwd_o", q, **geo.kw(), scale=scale, q=q, k=k, v=v, h=h, g=g, o=o)
+    return o
+
+
+def chunk_bwd_dv(geo: Geometry, q, k, g, do, dh, scale):
+    """dv including the inter-chunk term (fla/ops/common/chunk_o.py:499)."""
+    dv = torch.empty_like(do)
+    _lib.call("flab_chunk_bwd_dv", q, **geo.kw(), scale=scale, q=q, k=k, g=g, d_o=do, dh=dh, dv=dv)
+    return dv
+
+
+def chunk_bwd_dv_local(geo: Geometry, q, k, g, do, scale):
+    """Intra-chunk part of dv (fla/ops/common/chunk_o.py:551)."""
+    dv = torch.empty_like(do)
+    _lib.call("flab_chunk_bwd_dv_local", q, **geo.kw(), scale=scale, q=q, k=k, g=g, d_o=do, dv=dv)
+    return dv
+
+
+def chunk_bwd_dqkwg(geo: Geometry, q, k, v, h, dh, do, scale, g=None, w=None, dv=None):
+    """dq, dk, dw, dg (fla/ops/common/chunk_o.py:602). dg is w.r.t. the cumsummed gate, fp32."""
+    dq, dk = torch.empty_like(q), torch.empty_like(k)
+    dw = torch.empty_like(w) if w is not None else None
+    dg = torch.empty(g.shape, dtype=torch.float32, device=g.device) if g is not None else None
+    _lib.call("flab_chunk_bwd_dqkwg", q, **geo.kw(), scale=scale, q=q, k=k, v=v, h=h, dh=dh, d_o=do, g=g, w=w,
+              dv=dv, dq=dq, dk=dk, dw=dw, dg=dg)
+    return dq, dk, dw, dg
+
+
+def fwd_prepare_wy_repr(geo: Geometry, k, v, beta, g=None):
+    """WY factors of the (gated) delta rule (fla/ops/delta_rule/wy_fast.py:436,
+    fla/ops/gated_delta_rule/wy_fast.py:320). Returns (aw, au, w, u); au is None without gates."""
+    shape_a = (*beta.shape, CHUNK)
+    aw = torch.empty(shape_a, dtype=k.dtype, device=k.device)
+    au = torch.empty(shape_a, dtype=k.dtype, device=k.device) if g is not None else None
+    w, u = torch.empty_like(k), torch.empty_like(v)
+    _lib.call("flab_wy_fwd", k, **geo.kw(), k=k, v=v, beta=beta, g=g, aw=aw, au=au, w=w, u=u)
+    return aw, au, w, u
+
+
+def fwd_recompute_w_u(geo: Geometry, k, v, beta, aw, au=None):
+    """w, u from stored inverse factors (fla/ops/delta_rule/wy_fast.py:532)."""
+    w, u = torch.empty_like(k), torch.empty_like(v)
+    _lib.call("flab_wy_recompute", k, **geo.kw(), k=k, v=v, beta=beta, aw=aw, au=au, w=w, u=u)
+    return w, u
+
+
+def bwd_prepare_wy_repr(geo: Geometry, k, v, beta, aw, dw, du, g=None, au=None):
+    """Backward of the WY transform (fla/ops/delta_rule/wy_fast.py:619,
+    fla/ops/gated_delta_rule/wy_fast.py:565). Returns (dk, dv, dbeta, dg)."""
+    dk, dv = torch.empty_like(k), torch.empty_like(v)
+    dbeta = torch.empty(beta.shape, dtype=torch.float32, device=k.device)
+    dg = torch.empty(beta.shape, dtype=torch.float32, device=k.device) if g is not None else None
+    _lib.call("flab_wy_bwd", k, **geo.kw(), k=k, v=v, beta=beta, g=g, aw=aw, au=au, dw=dw, du=du, dk=dk, dv=dv,
+              dbeta=dbeta, dg=dg)
+    return dk, dv, dbeta, dg
+
+
+def chunk_gated_delta_rule_fwd_h(geo: Geometry, k, w, u, g=None, h0=None, output_final_state=False):
+    """Delta-rule state scan (fla/ops/common/chunk_delta_h.py:248). Returns (h, v_new, ht)."""
+    h, ht = _state_buffers(geo, k, output_final_state)
+    v_new = torch.empty_like(u)
+    _lib.call("flab_delta_fwd_h", k, **geo.kw(), k=k, w=w, u=u, g=g, h0=_f32(h0), h=h, v_new=v_new, ht=ht)
+    return h, v_new, ht
+
+
+def chunk_gated_delta_rule_bwd_dhu(geo: Geometry, q, k, w, do, dv, scale, g=None, dht=None, want_dh0=False):
+    """Reverse delta-rule scan (fla/ops/common/chunk_delta_h.py:323). Returns (dh, dh0, dv2)."""
+    dh, dh0 = _state_buffers(geo, q, want_dh0)
+    dv2 = torch.empty_like(dv)
+    _lib.call("flab_delta_bwd_dhu", q, **geo.kw(), scale=scale, q=q, k=k, w=w, g=g, dht=_f32(dht), d_o=do, dv=dv,
+              dh=dh, dh0=dh0, dv2=dv2)
+    return dh, dh0, dv2
+
+
+__all__ = [n for n in dir() if n.startswith(("chunk_", "fwd_", "bwd_"))] + ["prepare_varlen", "Geometry"]

@@ -1,0 +1,116 @@
+# -*- coding: utf-8 -*-
+"""Gated DeltaNet: S_t = e^{g_t} S_{t-1} + k_t^T beta_t (v_t - k_t e^{g_t} S_{t-1}).
+Public signatures follow fla/ops/gated_delta_rule/chunk.py:258 and
+fla/ops/gated_delta_rule/fused_recurrent.py:210."""
+
+from typing import Optional, Tuple
+
+import torch
+
+from ..utils import Geometry, autocast_custom_bwd, autocast_custom_fwd, contiguous, resolve_offsets
+from . import common as C
+from .recurrent import FusedRecurrentGatedDeltaRuleFunction
+from .simple_gla import check_varlen_args
+
+
+def chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta, scale, initial_state, output_final_state):
+    """Stage order of fla/ops/gated_delta_rule/chunk.py:20-73."""
+    g = C.chunk_local_cumsum(g, offsets=geo.offsets_tensor, head_first=geo.head_first)
+    aw, au, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta, g=g)
+    h, v_new, ht = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=initial_state,
+                                                  output_final_state=output_final_state)
+    o = C.chunk_fwd_o(geo, q, k, v_new, h, g=g, scale=scale)
+    return g, o, aw, au, ht
+
+
+def chunk_gated_delta_rule_bwd(geo, q, k, v, g, beta, aw, au, scale, initial_state, do, dht):
+    """Stage order of fla/ops/gated_delta_rule/chunk.py:76-177; `g` is the chunk-local cumsum."""
+    w, u = C.fwd_recompute_w_u(geo, k, v, beta, aw, au)
+    h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=initial_state, output_final_state=False)
+    dv = C.chunk_bwd_dv_local(geo, q, k, g, do, scale)
+    dh, dh0, dv = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g, dht=dht,
+                                                   want_dh0=initial_state is not None)
+    dq, dk, dw, dg = C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=g, w=w, dv=dv)
+    dk2, dv, db, dg2 = C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv, g=g, au=au)
+    dk.add_(dk2)
+    dg.add_(dg2)
+    dg = C.chunk_local_cumsum(dg, reverse=True, offsets=geo.offsets_tensor, head_first=geo.head_first)
+    return dq, dk, dv, db, dg, dh0
+
+
+class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
+
+    @staticmethod
+    @contiguous
+    @autocast_custom_fwd
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, offsets, head_first):
+        geo = Geometry(k, v, offsets, head_first)
+        beta_k = beta.to(k.dtype)
+        g_cum, o, aw, au, ht = chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta_k, scale, initial_state,
+                                                          output_final_state)
+        ctx.save_for_backward(q, k, v, g_cum, beta_k, aw, au, initial_state)
+        ctx.geo, ctx.scale, ctx.g_dtype, ctx.beta_dtype = geo, scale, g.dtype, beta.dtype
+        return o.to(q.dtype), ht
+
+    @staticmethod
+    @contiguous
+    @autocast_custom_bwd
+    def backward(ctx, do, dht):
+        q, k, v, g_cum, beta, aw, au, initial_state = ctx.saved_tensors
+        dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(ctx.geo, q, k, v, g_cum, beta, aw, au, ctx.scale,
+                                                            initial_state, do, dht)
+        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(ctx.g_dtype), db.to(ctx.beta_dtype),
+                None, dh0, None, None, None)
+
+
+def chunk_gated_delta_rule(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    beta: torch.Tensor,
+    scale: float = None,
+    initial_state: torch.Tensor = None,
+    output_final_state: bool = False,
+    offsets: Optional[torch.LongTensor] = None,
+    head_first: bool = True,
+    cu_seqlens: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """q, k: [B,H,T,K] (or [B,T,H,K]); v: [...,V]; g (log decay), beta: [B,H,T] (or [B,T,H]). bf16/fp16 only."""
+    offsets = resolve_offsets(offsets, cu_seqlens)
+    assert q.dtype == k.dtype == v.dtype
+    assert q.dtype != torch.float32, "ChunkGatedDeltaRuleFunction does not support float32. Please use bfloat16."
+    assert len(beta.shape) == 3, "beta must be of shape [B, H, T] if head_first=True, or [B, T, H] if head_first=False."
+    check_varlen_args(q, initial_state, offsets, head_first)
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    else:
+        assert scale > 0, "Scale must be positive."
+    return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, offsets,
+                                             head_first)
+
+
+def fused_recurrent_gated_delta_rule(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    beta: torch.Tensor = None,
+    scale: float = None,
+    initial_state: torch.Tensor = None,
+    output_final_state: bool = False,
+    offsets: Optional[torch.LongTensor] = None,
+    head_first: bool = True,
+    cu_seqlens: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Decode / token-recurrent form (forward only, like the reference)."""
+    offsets = resolve_offsets(offsets, cu_seqlens)
+    check_varlen_args(q, initial_state, offsets, head_first)
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    else:
+        assert scale > 0, "scale must be positive"
+    if beta is None:
+        beta = torch.ones_like(q[..., 0])
+    return FusedRecurrentGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state,
+                                                      offsets, head_first)

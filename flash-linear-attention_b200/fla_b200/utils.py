@@ -1,0 +1,103 @@
+# -*- coding: utf-8 -*-
+"""Host-side helpers shared by the op wrappers: argument normalisation, variable-length chunk
+tables (the integer index data of this path) and the autograd decorators the reference applies
+(fla/utils.py:10-21 `contiguous`, :88-93 autocast wrappers)."""
+
+import functools
+from collections import namedtuple
+from typing import Optional
+
+import torch
+
+from ._lib import CHUNK
+
+Varlen = namedtuple("Varlen", ["cu_seqlens", "chunk_indices", "chunk_offsets", "N", "NT", "lengths"])
+
+
+def contiguous(fn):
+    """Make every tensor argument contiguous before the autograd Function body runs."""
+    @functools.wraps(fn)
+    def wrapper(ctx, *args, **kwargs):
+        return fn(ctx,
+                  *(i if not isinstance(i, torch.Tensor) else i.contiguous() for i in args),
+                  **{k: (v if not isinstance(v, torch.Tensor) else v.contiguous()) for k, v in kwargs.items()})
+    return wrapper
+
+
+autocast_custom_fwd = functools.partial(torch.amp.custom_fwd, device_type="cuda")
+autocast_custom_bwd = functools.partial(torch.amp.custom_bwd, device_type="cuda")
+
+
+def chunk_tables(lengths, chunk_size: int = CHUNK):
+    """Integer chunk tables for a list of sequence lengths.
+
+    Returns (indices, chunk_offsets): `indices[c] = (sequence id, chunk id inside that sequence)` for
+    every chunk in sequence order, and `chunk_offsets[n]` = number of chunks before sequence n
+    (length N+1).  Same values as the reference builds in
+    fla/ops/gated_delta_rule/chunk.py:204-207 and fla/ops/common/chunk_h.py:274-279.
+    """
+    indices, chunk_offsets, total = [], [0], 0
+    for n, length in enumerate(lengths):
+        nt = -(-int(length) // chunk_size)
+        indices.extend((n, i) for i in range(nt))
+        total += nt
+        chunk_offsets.append(total)
+    return indices, chunk_offsets
+
+
+_VARLEN_CACHE = {}
+
+
+def prepare_varlen(offsets: Optional[torch.Tensor], device) -> Optional[Varlen]:
+    """Device-resident int32 tables for `offsets` (int32 or int64, [N+1]); cached per tensor.
+
+    Reading `offsets` on the host costs one device-to-host copy, like the reference's `.tolist()`.
+    """
+    if offsets is None:
+        return None
+    key = (offsets.data_ptr(), tuple(offsets.shape), offsets.dtype, str(offsets.device), offsets._version, str(device))
+    hit = _VARLEN_CACHE.get(key)
+    if hit is not None:
+        return hit
+    host = [int(x) for x in offsets.tolist()]
+    if len(host) < 2 or host[0] != 0 or any(b < a for a, b in zip(host, host[1:])):
+        raise ValueError(f"`offsets` must start at 0 and be non-decreasing, got {host[:8]}...")
+    lengths = [b - a for a, b in zip(host, host[1:])]
+    indices, chunk_offsets = chunk_tables(lengths)
+    cu = torch.tensor(host, dtype=torch.int32, device=device)
+    idx = torch.tensor(indices if indices else [(0, 0)], dtype=torch.int32, device=device).reshape(-1, 2)
+    co = torch.tensor(chunk_offsets, dtype=torch.int32, device=device)
+    out = Varlen(cu, idx, co, len(lengths), len(indices), lengths)
+    if len(_VARLEN_CACHE) > 64:
+        _VARLEN_CACHE.clear()
+    _VARLEN_CACHE[key] = out
+    return out
+
+
+def resolve_offsets(offsets, cu_seqlens):
+    """`cu_seqlens=` is accepted as an alias of the reference's `offsets=` keyword."""
+    if offsets is not None and cu_seqlens is not None:
+        raise ValueError("pass either `offsets` or `cu_seqlens`, not both")
+    return offsets if offsets is not None else cu_seqlens
+
+
+class Geometry:
+    """Shape bookkeeping for one op call (seq-first or head-first, fixed or variable length)."""
+
+    def __init__(self, k: torch.Tensor, v: Optional[torch.Tensor], offsets, head_first: bool):
+        if head_first:
+            self.B, self.H, self.T, self.K = k.shape
+        else:
+            self.B, self.T, self.H, self.K = k.shape
+        self.V = v.shape[-1] if v is not None else 0
+        self.head_first = bool(head_first)
+        self.offsets_tensor = offsets
+        self.varlen = prepare_varlen(offsets, k.device)
+        if self.varlen is not None:
+            self.N, self.NT = self.varlen.N, self.varlen.NT
+        else:
+            self.N, self.NT = self.B, self.B * (-(-self.T // CHUNK))
+
+    def kw(self):
+        return dict(B=self.B, T=self.T, H=self.H, K=self.K, V=self.V, N=self.N, NT=self.NT,
+                    head_first=self.head_first, varlen=self.varlen)

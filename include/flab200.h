@@ -1,0 +1,178 @@
+/*
+ * flab200 — C ABI of the B200 (sm_100a) chunked linear-attention kernels.
+ *
+ * The reference project (flash-linear-attention) has no FFI layer: its boundary is the Python
+ * functional API in fla/ops/<family>/{chunk,fused_recurrent}.py, whose autograd Functions launch
+ * Triton kernels stage by stage.  This header defines one entry point per such stage, so a Python
+ * (ctypes) or C++ host can drive the same pipeline.  Each declaration cites the reference launch
+ * wrapper it replaces (path inside the reference repository : line).
+ *
+ * Conventions
+ *  - Every entry point returns 0 on success and a negative FLAB_E_* code otherwise;
+ *    flab_last_error() returns a thread-local, human readable message for the last failure.
+ *  - All pointers are device pointers on the current device. Nothing is allocated, freed or
+ *    synchronised by the library (except where an entry point says otherwise); kernels are
+ *    enqueued on `stream` (a cudaStream_t passed as void*).
+ *  - Token-major tensors are contiguous in either seq-first [B,T,H,D] (head_first = 0) or
+ *    head-first [B,H,T,D] (head_first = 1) layout; per-token scalars (g, beta) use D = 1.
+ *  - Variable-length batches: B = 1, T = total tokens, `cu_seqlens` (int32[N+1]) gives sequence
+ *    starts, `chunk_indices` (int32[NT][2]) = (sequence, chunk-in-sequence) per chunk and
+ *    `chunk_offsets` (int32[N+1]) = exclusive prefix sum of per-sequence chunk counts.
+ *  - The chunk length is fixed at 64 tokens. Chunk states are laid out [total_chunks, H, K, V].
+ *  - Initial/final states and their gradients are fp32 [N,H,K,V].
+ */
+#ifndef FLAB200_H
+#define FLAB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLAB_ABI_VERSION 1
+#define FLAB_CHUNK 64
+
+enum { FLAB_BF16 = 0, FLAB_FP16 = 1, FLAB_FP32 = 2 };
+
+enum {
+  FLAB_OK = 0,
+  FLAB_E_BADARG = -1,      /* NULL / inconsistent argument                    */
+  FLAB_E_UNSUPPORTED = -2, /* shape or dtype outside what the kernels handle  */
+  FLAB_E_LAUNCH = -3,      /* CUDA reported an error at launch                */
+  FLAB_E_TIMEOUT = -4      /* a bounded device-side wait ran out              */
+};
+
+enum {
+  FLAB_F_REVERSE = 1 << 0,       /* cumsum / recurrence run from the last token to the first */
+  FLAB_F_BETA_VECTOR = 1 << 1,   /* fused_recurrent_delta_rule: beta is [.., V] not scalar    */
+  FLAB_F_INPLACE_STATE = 1 << 2, /* decode: ht may alias h0                                   */
+  FLAB_F_UPPER = 1 << 3          /* reserved                                                  */
+};
+
+typedef struct flab_args {
+  /* geometry */
+  int32_t B, T, H, K, V;
+  int32_t N;          /* number of sequences (B, or len(cu_seqlens) - 1)        */
+  int32_t NT;         /* total number of 64-token chunks over all sequences     */
+  int32_t dtype;      /* FLAB_BF16 / FLAB_FP16 / FLAB_FP32: element type of q,k,v,o,... */
+  int32_t head_first; /* 0: [B,T,H,D]   1: [B,H,T,D]                            */
+  int32_t flags;      /* FLAB_F_*                                               */
+  float scale;
+  int32_t S;          /* innermost extent for the vector cumsum entry points    */
+  /* variable-length tables (NULL for fixed length) */
+  const int32_t *cu_seqlens;
+  const int32_t *chunk_indices;
+  const int32_t *chunk_offsets;
+  /* tensor slots; each entry point documents the ones it reads and writes */
+  void *q, *k, *v;
+  void *g;     /* fp32 log-gates per token/head (chunk entry points: already chunk-cumsummed) */
+  void *gk;    /* fp32 log-gates per token/head/key channel                                  */
+  void *gv;    /* fused_recurrent only: log-gates per value channel                          */
+  void *beta;
+  void *w, *u;     /* WY factors                                                    */
+  void *aw, *au;   /* [.., 64] inverse factors of the WY transform (au: gated only) */
+  void *h;         /* chunk states [NT,H,K,V], element type = dtype                 */
+  void *h0, *ht;   /* fp32 [N,H,K,V]                                                */
+  void *v_new;
+  void *o;
+  void *d_o;       /* gradient of o */
+  void *dh;        /* chunk state gradients [NT,H,K,V] */
+  void *dht, *dh0; /* fp32 [N,H,K,V] */
+  void *dq, *dk, *dv, *dv2, *dw, *du, *dg, *dgk, *dgv, *dbeta;
+  void *a, *da;    /* GLA intra-chunk score matrix [.., 64] fp32 and its gradient */
+  void *x, *y;     /* generic in / out (cumsum entry points)                      */
+  void *ws;        /* caller-provided scratch                                     */
+  size_t ws_bytes;
+} flab_args;
+
+int flab_abi_version(void);
+const char *flab_last_error(void);
+
+/* ---- gate cumulative sums ------------------------------------------------------------------
+ * x -> y (fp32). Replaces chunk_local_cumsum (fla/ops/utils/cumsum.py:389) and
+ * chunk_global_cumsum (fla/ops/utils/cumsum.py:369). x has element type `dtype`;
+ * scalar variants treat x as [B,T,H] (head_first: [B,H,T]); vector variants as [..., S].
+ * FLAB_F_REVERSE selects suffix sums. */
+int flab_chunk_local_cumsum_scalar(const flab_args *a, void *stream);
+int flab_chunk_local_cumsum_vector(const flab_args *a, void *stream);
+int flab_chunk_global_cumsum_scalar(const flab_args *a, void *stream);
+int flab_chunk_global_cumsum_vector(const flab_args *a, void *stream);
+
+/* ---- inter-chunk state recurrence for diagonal decay ---------------------------------------
+ * Replaces chunk_fwd_h (fla/ops/common/chunk_h.py:282): reads k, v, g or gk (either may be NULL),
+ * h0 (optional); writes h (state at the start of every chunk) and ht (optional). */
+int flab_chunk_fwd_h(const flab_args *a, void *stream);
+/* Replaces chunk_bwd_dh (fla/ops/common/chunk_h.py:338): reads q, d_o, g or gk, dht (optional);
+ * writes dh and dh0 (optional). */
+int flab_chunk_bwd_dh(const flab_args *a, void *stream);
+
+/* ---- intra-chunk output and its gradients ---------------------------------------------------
+ * Replaces chunk_fwd_o (fla/ops/common/chunk_o.py:444): reads q, k, v, h, g (optional); writes o. */
+int flab_chunk_fwd_o(const flab_args *a, void *stream);
+/* Replaces chunk_bwd_dv (fla/ops/common/chunk_o.py:499): reads q, k, g, d_o, dh; writes dv. */
+int flab_chunk_bwd_dv(const flab_args *a, void *stream);
+/* Replaces chunk_bwd_dv_local (fla/ops/common/chunk_o.py:551): reads q, k, g (optional), d_o;
+ * writes dv. */
+int flab_chunk_bwd_dv_local(const flab_args *a, void *stream);
+/* Replaces chunk_bwd_dqkwg (fla/ops/common/chunk_o.py:602): reads q, k, v, h, dh, d_o, g (optional),
+ * and for the delta-rule family w and dv; writes dq, dk, dg (fp32, gradient w.r.t. the cumsummed
+ * gate, when g is given) and dw (when w is given). */
+int flab_chunk_bwd_dqkwg(const flab_args *a, void *stream);
+
+/* ---- WY / UT transform of the (gated) delta rule --------------------------------------------
+ * Replaces fwd_prepare_wy_repr (fla/ops/delta_rule/wy_fast.py:436,
+ * fla/ops/gated_delta_rule/wy_fast.py:320): reads k, v, beta, g (gated only); writes aw, au (gated
+ * only), w, u. */
+int flab_wy_fwd(const flab_args *a, void *stream);
+/* Replaces fwd_recompute_w_u (fla/ops/delta_rule/wy_fast.py:532,
+ * fla/ops/gated_delta_rule/wy_fast.py:379): reads k, v, beta, aw, au (gated only); writes w, u. */
+int flab_wy_recompute(const flab_args *a, void *stream);
+/* Replaces bwd_prepare_wy_repr (fla/ops/delta_rule/wy_fast.py:619,
+ * fla/ops/gated_delta_rule/wy_fast.py:565): reads k, v, beta, g (gated only), aw, au (gated only),
+ * dw, du; writes dk, dv, dbeta (fp32) and dg (fp32, gated only). */
+int flab_wy_bwd(const flab_args *a, void *stream);
+
+/* ---- state recurrence of the (gated) delta rule ----------------------------------------------
+ * Replaces chunk_gated_delta_rule_fwd_h (fla/ops/common/chunk_delta_h.py:248): reads k, w, u,
+ * g (optional), h0 (optional); writes h, v_new, ht (optional). */
+int flab_delta_fwd_h(const flab_args *a, void *stream);
+/* Replaces chunk_gated_delta_rule_bwd_dhu (fla/ops/common/chunk_delta_h.py:323): reads q, k, w,
+ * g (optional), dht (optional), d_o, dv; writes dh, dv2, dh0 (optional). */
+int flab_delta_bwd_dhu(const flab_args *a, void *stream);
+
+/* ---- GLA (per-channel gates) -----------------------------------------------------------------
+ * Replaces chunk_gla_fwd_intra_gk (fla/ops/gla/chunk.py:840): reads q, k, gk; writes a (fp32). */
+int flab_gla_fwd_intra(const flab_args *a, void *stream);
+/* Replaces chunk_gla_fwd_o_gk (fla/ops/gla/chunk.py:941): reads q, v, gk, h, a; writes o. */
+int flab_gla_fwd_o(const flab_args *a, void *stream);
+/* Replaces chunk_gla_bwd_dA (fla/ops/gla/chunk.py:982) and chunk_gla_bwd_dv
+ * (fla/ops/gla/chunk.py:1018): reads k, v, gk, a, d_o, dh; writes da (fp32) and dv. */
+int flab_gla_bwd_dav(const flab_args *a, void *stream);
+/* Replaces chunk_gla_bwd_dqk_intra (fla/ops/gla/chunk.py:1057) and chunk_gla_bwd_dqkg
+ * (fla/ops/gla/chunk.py:1102): reads q, k, v, gk, h, dh, d_o, da; writes dq, dk, dgk (fp32,
+ * gradient w.r.t. the raw gate). */
+int flab_gla_bwd_dqkg(const flab_args *a, void *stream);
+
+/* ---- token-recurrent kernels -----------------------------------------------------------------
+ * Replaces fused_recurrent_fwd (fla/ops/common/fused_recurrent.py:322): reads q, k, v, g/gk/gv
+ * (each optional, element type `dtype` except g/gk/gv which are fp32), h0; writes o (fp32) and ht. */
+int flab_recurrent_fwd(const flab_args *a, void *stream);
+/* Replaces the kernel launch inside fused_recurrent_bwd (fla/ops/common/fused_recurrent.py:385):
+ * reads q, k, v, gates, h0, d_o, dht; writes dq, dk, dv (fp32) and dh0. Gate gradients are formed by
+ * the caller with the global cumsum entry points, as the reference does. */
+int flab_recurrent_bwd(const flab_args *a, void *stream);
+/* Replaces fused_recurrent_delta_rule_fwd (fla/ops/delta_rule/fused_recurrent.py:293) and
+ * fused_recurrent_gated_delta_rule_fwd (fla/ops/gated_delta_rule/fused_recurrent.py:113):
+ * reads q, k, v, beta, g (optional, fp32), h0; writes o (element type dtype), ht, and u (optional:
+ * the pre-beta corrected values the backward kernel needs). */
+int flab_recurrent_delta_fwd(const flab_args *a, void *stream);
+/* Replaces fused_recurrent_delta_rule_bwd (fla/ops/delta_rule/fused_recurrent.py:350): reads q, k,
+ * v, beta, h0, d_o, dht; writes dq, dk, dv (fp32), dbeta (fp32), dh0. */
+int flab_recurrent_delta_bwd(const flab_args *a, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLAB200_H */

@@ -1,0 +1,14 @@
+"""CPU restatement of the reference's linear-attention algorithms.  TEST INFRASTRUCTURE ONLY.
+
+This package is the checker the CUDA kernels are compared against (tests/, the smoke test and the
+cpu_baseline / reference arm of bench.py).  Nothing under fla_b200/ imports it, and it must never be
+used as a fallback compute path.
+
+Parity pin: every function here is checked in tests/test_oracle_golden.py against vectors produced
+by the reference's own naive PyTorch functions (tests/golden/make_golden.py, run against the
+reference checkout) - see each function's docstring for the reference file:line it restates.
+"""
+
+from .indexing import chunk_indices_ref, chunk_offsets_ref  # noqa: F401
+from .naive import (cumsum_global, cumsum_local, delta_rule, gated_delta_rule, gla, retention_log_decay,  # noqa: F401
+                    simple_gla)

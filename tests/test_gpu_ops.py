@@ -1,0 +1,441 @@
+"""GPU parity tests: the CUDA path (through the public fla.ops-style API, i.e. through the C ABI)
+against the CPU oracle on identical seeded inputs, the committed golden vectors of the reference,
+and size-independent properties.  Error metric and shape sweeps follow the reference's tests
+(tests/ops/test_{gla,simple_gla,retention,delta,gated_delta,cumsum}.py)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import oracle
+from util import assert_close, err_ratio, t
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+# relative-L2 bars: bf16/fp16 5e-3, fp32 1e-5
+TOL = {torch.bfloat16: 5e-3, torch.float16: 5e-3, torch.float32: 1e-5}
+
+
+def ops():
+    import fla_b200.ops as o
+    return o
+
+
+def rand_offsets(T, N, seed=42):
+    g0 = torch.Generator().manual_seed(seed)
+    cuts = torch.randperm(T - 1, generator=g0)[:N - 1] + 1
+    return torch.cat([torch.tensor([0]), cuts.sort()[0], torch.tensor([T])]).long()
+
+
+def build(B, T, H, K, V, dtype, seed, gate=None, beta=False, h0=False, norm=False, gate_div=1.0, N=None):
+    g0 = torch.Generator().manual_seed(seed)
+    q, k = torch.randn(B, T, H, K, generator=g0), torch.randn(B, T, H, K, generator=g0)
+    v = torch.randn(B, T, H, V, generator=g0)
+    if norm:
+        q, k = F.normalize(q, p=2, dim=-1), F.normalize(k, p=2, dim=-1)
+    d = dict(q=q.to(dtype), k=k.to(dtype), v=v.to(dtype))
+    if gate == "scalar":
+        d["g"] = F.logsigmoid(torch.randn(B, T, H, generator=g0)) / gate_div
+    if gate == "vector":
+        d["g"] = (F.logsigmoid(torch.randn(B, T, H, K, generator=g0)) / gate_div).to(dtype)
+    if beta:
+        d["beta"] = torch.rand(B, T, H, generator=g0).sigmoid().to(dtype)
+    if h0:
+        d["h0"] = torch.randn(N or B, H, K, V, generator=g0) * 0.1
+    d["do"] = torch.randn(B, T, H, V, generator=g0).to(dtype)
+    d["dht"] = torch.randn(N or B, H, K, V, generator=g0)
+    return d
+
+
+def run_both(fn_gpu, fn_ref, d, names, head_first=False, tol=None, tol_over=None, check_grads=True, **kw):
+    """Run `fn_gpu` on CUDA and `fn_ref` (oracle) on CPU fp32 with the same bits; compare o, ht, grads."""
+    dtype = d["q"].dtype
+    tol = tol or TOL[dtype]
+    tol_over = tol_over or {}
+
+    def prep(dev, cast):
+        out = {}
+        for n in names:
+            x = d[n]
+            if head_first and x.dim() >= 3 and n not in ("h0",):
+                x = x.transpose(1, 2).contiguous()
+            x = x.to(dev)
+            if cast and x.is_floating_point():
+                x = x.float()
+            out[n] = x.detach().clone().requires_grad_(check_grads)
+        return out
+
+    gi, ri = prep(DEV, False), prep("cpu", True)
+    do, dht = d["do"], d["dht"]
+    if head_first:
+        do = do.transpose(1, 2).contiguous()
+    o, ht = fn_gpu(gi, head_first=head_first, **kw)
+    o_ref, ht_ref = fn_ref(ri, head_first=head_first, **kw)
+    res = {"o": assert_close("o", o_ref, o, tol_over.get("o", tol))}
+    if ht_ref is not None:
+        res["ht"] = assert_close("ht", ht_ref, ht, tol_over.get("ht", tol))
+    if check_grads:
+        loss = (o.float() * do.to(DEV).float()).sum()
+        loss_ref = (o_ref * do.float()).sum()
+        if ht_ref is not None:
+            loss = loss + (ht * dht.to(DEV)).sum()
+            loss_ref = loss_ref + (ht_ref * dht).sum()
+        gg = torch.autograd.grad(loss, [gi[n] for n in names])
+        gr = torch.autograd.grad(loss_ref, [ri[n] for n in names])
+        for n, a, b in zip(names, gr, gg):
+            res["d" + n] = assert_close("d" + n, a, b, tol_over.get("d" + n, tol))
+    print({k_: f"{v_:.2e}" for k_, v_ in res.items()})
+    return res
+
+
+# ------------------------------------------------------------------------------------------------
+# cumsum
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("head_first", [False, True])
+@pytest.mark.parametrize("reverse", [False, True])
+@pytest.mark.parametrize("S", [0, 24])
+def test_cumsum_local_and_global(dtype, head_first, reverse, S):
+    from fla_b200.ops.common import chunk_global_cumsum, chunk_local_cumsum
+    g0 = torch.Generator().manual_seed(1)
+    shape = (2, 150, 3) + ((S,) if S else ())
+    x = torch.randn(*shape, generator=g0).to(dtype)
+    xs = x.transpose(1, 2).contiguous() if head_first else x
+    y = chunk_local_cumsum(xs.to(DEV), 64, reverse=reverse, head_first=head_first).cpu()
+    torch.testing.assert_close(y, oracle.cumsum_local(xs, 64, reverse=reverse, head_first=head_first), rtol=1e-5, atol=1e-5)
+    y = chunk_global_cumsum(xs.to(DEV), dtype=torch.float32, reverse=reverse, head_first=head_first).cpu()
+    torch.testing.assert_close(y, oracle.cumsum_global(xs, reverse=reverse, head_first=head_first), rtol=1e-5, atol=2e-5)
+
+
+def test_cumsum_varlen_and_golden(golden):
+    from fla_b200.ops.common import chunk_global_cumsum, chunk_local_cumsum
+    x = torch.randn(1, 500, 4, generator=torch.Generator().manual_seed(3))
+    for dt in (torch.int64, torch.int32):
+        off = rand_offsets(500, 5).to(dt)
+        for rev in (False, True):
+            y = chunk_local_cumsum(x.to(DEV), 64, reverse=rev, offsets=off.to(DEV), head_first=False).cpu()
+            torch.testing.assert_close(y, oracle.cumsum_local(x, 64, reverse=rev, offsets=off, head_first=False), rtol=1e-5, atol=1e-5)
+            y = chunk_global_cumsum(x.to(DEV), reverse=rev, offsets=off.to(DEV), head_first=False).cpu()
+            torch.testing.assert_close(y, oracle.cumsum_global(x, reverse=rev, offsets=off, head_first=False), rtol=1e-5, atol=2e-5)
+    for name in ("s3", "s4"):
+        xg = t(golden, f"cumsum.{name}.x")
+        y = chunk_local_cumsum(xg.to(DEV), 64, head_first=False).cpu()
+        torch.testing.assert_close(y, t(golden, f"cumsum.{name}.local"), rtol=1e-5, atol=1e-5)
+        y = chunk_global_cumsum(xg.to(DEV), reverse=True, head_first=False).cpu()
+        torch.testing.assert_close(y, t(golden, f"cumsum.{name}.glob_rev"), rtol=1e-5, atol=2e-5)
+
+
+# ------------------------------------------------------------------------------------------------
+# simple GLA / retention
+# ------------------------------------------------------------------------------------------------
+def _sgla_gpu(i, **kw):
+    return ops().chunk_simple_gla(i["q"], i["k"], i["v"], i["g"], initial_state=i.get("h0"), output_final_state=True, **kw)
+
+
+def _sgla_ref(i, scale=None, offsets=None, head_first=False, **kw):
+    return oracle.simple_gla(i["q"], i["k"], i["v"], i["g"], scale=scale, initial_state=i.get("h0"),
+                             output_final_state=True, offsets=offsets, head_first=head_first)
+
+
+@pytest.mark.parametrize("B,T,H,K,V,dtype,head_first", [
+    (2, 130, 3, 64, 64, torch.bfloat16, False),
+    (2, 256, 2, 128, 128, torch.bfloat16, False),
+    (1, 300, 2, 100, 60, torch.bfloat16, False),
+    (2, 63, 2, 32, 64, torch.float16, True),
+    (2, 200, 2, 64, 128, torch.float32, False),
+    (1, 15, 2, 64, 64, torch.float32, True),
+])
+def test_chunk_simple_gla(B, T, H, K, V, dtype, head_first):
+    d = build(B, T, H, K, V, dtype, seed=T, gate="scalar", h0=True)
+    run_both(_sgla_gpu, _sgla_ref, d, ["q", "k", "v", "g", "h0"], head_first=head_first)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_chunk_simple_gla_varlen(dtype):
+    T, N = 500, 4
+    d = build(1, T, 3, 64, 64, dtype, seed=5, gate="scalar", h0=True, N=N)
+    off = rand_offsets(T, N)
+    run_both(lambda i, **kw: _sgla_gpu(i, offsets=off.to(DEV), head_first=False),
+             lambda i, **kw: _sgla_ref(i, offsets=off), d, ["q", "k", "v", "g", "h0"])
+
+
+def test_chunk_retention_matches_oracle_and_golden(golden):
+    o_ = ops()
+    d = build(2, 200, 4, 64, 64, torch.bfloat16, seed=11)
+    g = oracle.retention_log_decay(4)[None, None, :].expand(2, 200, 4).contiguous()
+
+    def gpu(i, **kw):
+        return o_.chunk_retention(i["q"], i["k"], i["v"], output_final_state=True, head_first=False)
+
+    def ref(i, **kw):
+        return oracle.simple_gla(i["q"], i["k"], i["v"], g, output_final_state=True, head_first=False)
+    run_both(gpu, ref, d, ["q", "k", "v"])
+    # the reference's O(T^2) retention on its own seeded inputs (fp32, head-first)
+    q, k, v = (t(golden, f"retention.{n}").to(DEV) for n in ("q", "k", "v"))
+    o, _ = o_.chunk_retention(q, k, v, head_first=True)
+    assert_close("retention golden", t(golden, "retention.o"), o, 1e-5)
+    o2, _ = o_.fused_recurrent_retention(q, k, v, head_first=True)
+    assert_close("recurrent retention golden", t(golden, "retention.o"), o2, 1e-5)
+
+
+def test_chunk_simple_gla_golden(golden):
+    names = ("q", "k", "v", "g", "h0")
+    q, k, v, g, h0 = (t(golden, f"simple_gla.{n}").to(DEV).requires_grad_(True) for n in names)
+    o, ht = ops().chunk_simple_gla(q, k, v, g, initial_state=h0, output_final_state=True, head_first=True)
+    assert_close("o", t(golden, "simple_gla.o"), o, 1e-5)
+    assert_close("ht", t(golden, "simple_gla.ht"), ht, 1e-5)
+    loss = (o * t(golden, "simple_gla.do").to(DEV)).sum() + (ht * t(golden, "simple_gla.dht").to(DEV)).sum()
+    for n, gx in zip(("dq", "dk", "dv", "dg", "dh0"), torch.autograd.grad(loss, (q, k, v, g, h0))):
+        assert_close(n, t(golden, f"simple_gla.{n}"), gx, 1e-5)
+
+
+# ------------------------------------------------------------------------------------------------
+# GLA
+# ------------------------------------------------------------------------------------------------
+def _gla_gpu(i, **kw):
+    return ops().chunk_gla(i["q"], i["k"], i["v"], i["g"], initial_state=i.get("h0"), output_final_state=True, **kw)
+
+
+def _gla_ref(i, scale=None, offsets=None, head_first=False, **kw):
+    return oracle.gla(i["q"], i["k"], i["v"], gk=i["g"], scale=scale, initial_state=i.get("h0"), output_final_state=True,
+                      offsets=offsets, head_first=head_first)
+
+
+@pytest.mark.parametrize("B,T,H,K,V,dtype,head_first,gate_div", [
+    (2, 512, 4, 64, 64, torch.float32, False, 16.0),   # the fp32 configuration of the build spec
+    (2, 130, 2, 64, 64, torch.float32, True, 1.0),
+    (2, 200, 2, 128, 128, torch.bfloat16, False, 1.0),
+    (1, 300, 2, 100, 100, torch.bfloat16, False, 20.0),
+    (1, 70, 2, 32, 64, torch.float16, False, 1.0),
+])
+def test_chunk_gla(B, T, H, K, V, dtype, head_first, gate_div):
+    d = build(B, T, H, K, V, dtype, seed=T, gate="vector", h0=True, gate_div=gate_div)
+    run_both(_gla_gpu, _gla_ref, d, ["q", "k", "v", "g", "h0"], head_first=head_first)
+
+
+def test_chunk_gla_varlen():
+    T, N = 400, 4
+    d = build(1, T, 2, 64, 64, torch.float32, seed=8, gate="vector", h0=True, N=N)
+    off = rand_offsets(T, N)
+    run_both(lambda i, **kw: _gla_gpu(i, offsets=off.to(DEV), head_first=False),
+             lambda i, **kw: _gla_ref(i, offsets=off), d, ["q", "k", "v", "g", "h0"])
+
+
+def test_chunk_gla_golden(golden):
+    names = ("q", "k", "v", "gk", "h0")
+    q, k, v, gk, h0 = (t(golden, f"gla.{n}").to(DEV).requires_grad_(True) for n in names)
+    o, ht = ops().chunk_gla(q, k, v, gk, initial_state=h0, output_final_state=True, head_first=True)
+    assert_close("o", t(golden, "gla.o"), o, 1e-5)
+    assert_close("ht", t(golden, "gla.ht"), ht, 1e-5)
+    loss = (o * t(golden, "gla.do").to(DEV)).sum() + (ht * t(golden, "gla.dht").to(DEV)).sum()
+    for n, gx in zip(("dq", "dk", "dv", "dgk", "dh0"), torch.autograd.grad(loss, (q, k, v, gk, h0))):
+        assert_close(n, t(golden, f"gla.{n}"), gx, 1e-5)
+
+
+# ------------------------------------------------------------------------------------------------
+# delta rule / gated delta rule
+# ------------------------------------------------------------------------------------------------
+def _delta_gpu(i, **kw):
+    return ops().chunk_delta_rule(i["q"], i["k"], i["v"], i["beta"], initial_state=i.get("h0"), output_final_state=True, **kw)
+
+
+def _delta_ref(i, scale=None, offsets=None, head_first=False, **kw):
+    return oracle.delta_rule(i["q"], i["k"], i["v"], i["beta"], scale=scale, initial_state=i.get("h0"),
+                             output_final_state=True, offsets=offsets, head_first=head_first)
+
+
+def _gdelta_gpu(i, **kw):
+    return ops().chunk_gated_delta_rule(i["q"], i["k"], i["v"], i["g"], i["beta"], initial_state=i.get("h0"),
+                                        output_final_state=True, **kw)
+
+
+def _gdelta_ref(i, scale=None, offsets=None, head_first=False, **kw):
+    return oracle.gated_delta_rule(i["q"], i["k"], i["v"], i["beta"], g=i["g"], scale=scale, initial_state=i.get("h0"),
+                                   output_final_state=True, offsets=offsets, head_first=head_first)
+
+
+# the reference's own bars for these two families (tests/ops/test_delta.py:74-93,
+# tests/ops/test_gated_delta.py:282-294): o/ht 5e-3, dq/dk/dv/dh0 7e-3..8e-3, dbeta/dg 2e-2
+DELTA_TOL = {"dq": 8e-3, "dk": 8e-3, "dv": 8e-3, "dh0": 8e-3, "dbeta": 2e-2, "dg": 2e-2}
+
+
+@pytest.mark.parametrize("B,T,H,K,V,dtype,head_first", [
+    (2, 130, 2, 64, 64, torch.bfloat16, False),
+    (2, 256, 2, 128, 128, torch.bfloat16, False),
+    (1, 300, 2, 100, 60, torch.bfloat16, False),
+    (2, 63, 2, 32, 64, torch.float16, True),
+    (1, 7, 2, 64, 64, torch.bfloat16, False),
+])
+def test_chunk_delta_rule(B, T, H, K, V, dtype, head_first):
+    d = build(B, T, H, K, V, dtype, seed=T, beta=True, h0=True, norm=True)
+    run_both(_delta_gpu, _delta_ref, d, ["q", "k", "v", "beta", "h0"], head_first=head_first, tol_over=DELTA_TOL)
+
+
+@pytest.mark.parametrize("B,T,H,K,V,dtype,head_first,gate_div", [
+    (2, 130, 2, 64, 64, torch.bfloat16, False, 1.0),
+    (2, 256, 2, 128, 128, torch.bfloat16, False, 1.0),
+    (1, 300, 2, 100, 60, torch.bfloat16, False, 1.0),
+    (2, 63, 2, 32, 64, torch.float16, True, 1.0),
+    (2, 200, 2, 64, 64, torch.bfloat16, False, 10.0),
+])
+def test_chunk_gated_delta_rule(B, T, H, K, V, dtype, head_first, gate_div):
+    d = build(B, T, H, K, V, dtype, seed=T, gate="scalar", beta=True, h0=True, norm=True, gate_div=gate_div)
+    run_both(_gdelta_gpu, _gdelta_ref, d, ["q", "k", "v", "g", "beta", "h0"], head_first=head_first, tol_over=DELTA_TOL)
+
+
+@pytest.mark.parametrize("odt", [torch.int64, torch.int32])
+def test_chunk_gated_delta_rule_varlen(odt):
+    T, N = 700, 5
+    d = build(1, T, 2, 64, 64, torch.bfloat16, seed=9, gate="scalar", beta=True, h0=True, norm=True, N=N)
+    off = rand_offsets(T, N).to(odt)
+    run_both(lambda i, **kw: _gdelta_gpu(i, cu_seqlens=off.to(DEV), head_first=False),
+             lambda i, **kw: _gdelta_ref(i, offsets=off), d, ["q", "k", "v", "g", "beta", "h0"], tol_over=DELTA_TOL)
+
+
+def test_chunk_delta_rule_varlen():
+    T, N = 600, 4
+    d = build(1, T, 2, 64, 64, torch.bfloat16, seed=10, beta=True, h0=True, norm=True, N=N)
+    off = rand_offsets(T, N)
+    run_both(lambda i, **kw: _delta_gpu(i, offsets=off.to(DEV), head_first=False),
+             lambda i, **kw: _delta_ref(i, offsets=off), d, ["q", "k", "v", "beta", "h0"], tol_over=DELTA_TOL)
+
+
+def test_delta_families_on_reference_golden_inputs(golden):
+    """Reference fp32 vectors, cast to bf16 for the chunk kernels (which reject fp32 like the reference)."""
+    o_ = ops()
+    q, k, v, beta, g, h0 = (t(golden, f"gated_delta.{n}") for n in ("q", "k", "v", "beta", "g", "h0"))
+    scale = float(golden["gated_delta.scale"])
+    bf = lambda x: x.to(DEV).bfloat16()  # noqa: E731
+    o, ht = o_.chunk_gated_delta_rule(bf(q), bf(k), bf(v), g.to(DEV), bf(beta), scale=scale, initial_state=h0.to(DEV),
+                                      output_final_state=True, head_first=False)
+    assert_close("gated o", t(golden, "gated_delta.o"), o, 8e-3)
+    assert_close("gated ht", t(golden, "gated_delta.ht"), ht, 8e-3)
+    o, ht = o_.fused_recurrent_gated_delta_rule(q.to(DEV), k.to(DEV), v.to(DEV), g.to(DEV), beta.to(DEV), scale=scale,
+                                                initial_state=h0.to(DEV), output_final_state=True, head_first=False)
+    assert_close("recurrent gated o", t(golden, "gated_delta.o"), o, 1e-5)
+    assert_close("recurrent gated ht", t(golden, "gated_delta.ht"), ht, 1e-5)
+    q, k, v, beta, h0 = (t(golden, f"delta.{n}") for n in ("q", "k", "v", "beta", "h0"))
+    o, ht = o_.chunk_delta_rule(bf(q), bf(k), bf(v), bf(beta), initial_state=h0.to(DEV), output_final_state=True, head_first=True)
+    assert_close("delta o", t(golden, "delta.o"), o, 8e-3)
+    assert_close("delta ht", t(golden, "delta.ht"), ht, 8e-3)
+
+
+# ------------------------------------------------------------------------------------------------
+# token-recurrent kernels
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("K,V", [(64, 64), (100, 60), (200, 128)])
+@pytest.mark.parametrize("reverse", [False, True])
+def test_fused_recurrent_gla(dtype, K, V, reverse):
+    d = build(2, 70, 2, K, V, dtype, seed=K + V, gate="vector", h0=True)
+    d["gv"] = F.logsigmoid(torch.randn(2, 70, 2, V, generator=torch.Generator().manual_seed(1))).to(dtype)
+    d["dht"] = d["dht"] * 0  # the reference forbids a final-state gradient together with gate gradients
+    tol = 1e-5 if dtype == torch.float32 else 5e-3
+
+    def gpu(i, **kw):
+        return ops().fused_recurrent_gla(i["q"], i["k"], i["v"], gk=i["g"], gv=i["gv"], initial_state=i["h0"],
+                                         output_final_state=True, reverse=reverse, head_first=False)
+
+    def ref(i, **kw):
+        return oracle.gla(i["q"], i["k"], i["v"], gk=i["g"], gv=i["gv"], initial_state=i["h0"], output_final_state=True,
+                          reverse=reverse, head_first=False)
+    run_both(gpu, ref, d, ["q", "k", "v", "g", "gv", "h0"], tol=tol)
+
+
+def test_fused_recurrent_simple_gla_varlen_and_golden(golden):
+    T, N = 200, 3
+    d = build(1, T, 2, 64, 64, torch.float32, seed=3, gate="scalar", h0=True, N=N)
+    d["dht"] = d["dht"] * 0
+    off = rand_offsets(T, N)
+
+    def gpu(i, **kw):
+        return ops().fused_recurrent_simple_gla(i["q"], i["k"], i["v"], i["g"], initial_state=i["h0"],
+                                                output_final_state=True, offsets=off.to(DEV), head_first=False)
+    run_both(gpu, lambda i, **kw: _sgla_ref(i, offsets=off), d, ["q", "k", "v", "g", "h0"])
+    names = ("q", "k", "v", "gk", "h0")
+    q, k, v, gk, h0 = (t(golden, f"gla.{n}").to(DEV) for n in names)
+    o, ht = ops().fused_recurrent_gla(q, k, v, gk=gk, initial_state=h0, output_final_state=True, head_first=True)
+    assert_close("o", t(golden, "gla.o"), o, 1e-5)
+    assert_close("ht", t(golden, "gla.ht"), ht, 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("K,V,vec_beta", [(64, 64, False), (100, 60, True), (200, 128, False)])
+def test_fused_recurrent_delta_rule(dtype, K, V, vec_beta):
+    d = build(2, 70, 2, K, V, dtype, seed=K, beta=True, h0=True, norm=True)
+    if vec_beta:
+        d["beta"] = torch.rand(2, 70, 2, V, generator=torch.Generator().manual_seed(2)).sigmoid().to(dtype)
+    tol = 2e-5 if dtype == torch.float32 else 6e-3
+
+    def gpu(i, **kw):
+        return ops().fused_recurrent_delta_rule(i["q"], i["k"], i["v"], i["beta"], initial_state=i["h0"],
+                                                output_final_state=True, head_first=False)
+    run_both(gpu, _delta_ref, d, ["q", "k", "v", "beta", "h0"], tol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_recurrent_gated_delta_rule_decode(dtype):
+    """Decode: one token per call, state carried call to call, against the oracle run over the whole sequence."""
+    B, T, H, K, V = 3, 9, 2, 128, 128
+    d = build(B, T, H, K, V, dtype, seed=4, gate="scalar", beta=True, h0=True, norm=True)
+    i = {n: x.to(DEV) for n, x in d.items()}
+    S = i["h0"].float()
+    outs = []
+    for s in range(T):
+        sl = slice(s, s + 1)
+        o, S = ops().fused_recurrent_gated_delta_rule(i["q"][:, sl], i["k"][:, sl], i["v"][:, sl], i["g"][:, sl],
+                                                      i["beta"][:, sl], initial_state=S, output_final_state=True,
+                                                      head_first=False)
+        outs.append(o)
+    o = torch.cat(outs, 1)
+    r = {n: (x.float() if x.is_floating_point() else x) for n, x in d.items()}
+    o_ref, ht_ref = oracle.gated_delta_rule(r["q"], r["k"], r["v"], r["beta"], g=r["g"], initial_state=r["h0"],
+                                            output_final_state=True, head_first=False)
+    tol = 2e-5 if dtype == torch.float32 else 5e-3
+    assert_close("o", o_ref, o, tol)
+    assert_close("ht", ht_ref, S, tol)
+    with pytest.raises(NotImplementedError):
+        q = i["q"].clone().requires_grad_(True)
+        o, _ = ops().fused_recurrent_gated_delta_rule(q, i["k"], i["v"], i["g"], i["beta"], head_first=False)
+        o.sum().backward()
+
+
+# ------------------------------------------------------------------------------------------------
+# properties that do not depend on an oracle (usable at full benchmark sizes)
+# ------------------------------------------------------------------------------------------------
+def test_state_handoff_equals_one_shot():
+    """Running T tokens in two halves, passing ht -> h0, gives the one-shot result (checkpoint/resume semantics)."""
+    d = build(2, 512, 4, 128, 128, torch.bfloat16, seed=21, gate="scalar", beta=True, norm=True)
+    i = {n: x.to(DEV) for n, x in d.items()}
+    o_ = ops()
+    o, ht = o_.chunk_gated_delta_rule(i["q"], i["k"], i["v"], i["g"], i["beta"], output_final_state=True, head_first=False)
+    h = 256
+    o1, s1 = o_.chunk_gated_delta_rule(i["q"][:, :h], i["k"][:, :h], i["v"][:, :h], i["g"][:, :h], i["beta"][:, :h],
+                                       output_final_state=True, head_first=False)
+    o2, s2 = o_.chunk_gated_delta_rule(i["q"][:, h:], i["k"][:, h:], i["v"][:, h:], i["g"][:, h:], i["beta"][:, h:],
+                                       initial_state=s1, output_final_state=True, head_first=False)
+    assert err_ratio(o, torch.cat([o1, o2], 1)) < 1e-6
+    assert err_ratio(ht, s2) < 1e-6
+
+
+def test_chunk_equals_recurrent_at_benchmark_shape_and_is_deterministic():
+    """B=2 slice of the headline shape (H=16, K=V=128, T=4096): chunk kernels vs the recurrent kernel, twice."""
+    d = build(2, 4096, 16, 128, 128, torch.bfloat16, seed=33, gate="scalar", beta=True, h0=True, norm=True)
+    i = {n: x.to(DEV) for n, x in d.items()}
+    o_ = ops()
+    args = (i["q"], i["k"], i["v"], i["g"], i["beta"])
+    o1, h1 = o_.chunk_gated_delta_rule(*args, initial_state=i["h0"], output_final_state=True, head_first=False)
+    o2, h2 = o_.chunk_gated_delta_rule(*args, initial_state=i["h0"], output_final_state=True, head_first=False)
+    assert torch.equal(o1, o2) and torch.equal(h1, h2)
+    o3, h3 = o_.fused_recurrent_gated_delta_rule(*args, initial_state=i["h0"], output_final_state=True, head_first=False)
+    assert_close("o chunk vs recurrent", o3, o1, 5e-3)
+    assert_close("ht chunk vs recurrent", h3, h1, 5e-3)
+
+
+def test_linearity_in_v_at_benchmark_shape():
+    """o is linear in v for fixed q, k, g, beta: f(v1 + v2) = f(v1) + f(v2) up to rounding."""
+    d = build(1, 4096, 16, 128, 128, torch.bfloat16, seed=34, gate="scalar", beta=True, norm=True)
+    i = {n: x.to(DEV) for n, x in d.items()}
+    v2 = torch.randn_like(i["v"])
+    f = lambda v: ops().chunk_gated_delta_rule(i["q"], i["k"], v, i["g"], i["beta"], head_first=False)[0].float()  # noqa: E731
+    assert err_ratio(f(i["v"]) + f(v2), f(i["v"] + v2)) < 1e-2

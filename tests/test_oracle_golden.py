@@ -1,0 +1,98 @@
+"""CPU: the oracle restatement against vectors produced by the reference's own naive functions
+(tests/golden/make_golden.py).  This is what pins the oracle."""
+import torch
+
+import oracle
+from util import assert_close, t
+
+TOL = 2e-5  # fp32 recurrences evaluated in a different association order
+
+
+def _grads(outs, douts, inputs):
+    loss = sum((o * d).sum() for o, d in zip(outs, douts))
+    return torch.autograd.grad(loss, inputs)
+
+
+def test_gla_matches_reference_naive(golden):
+    q, k, v, gk, h0 = (t(golden, f"gla.{n}").requires_grad_(True) for n in ("q", "k", "v", "gk", "h0"))
+    o, ht = oracle.gla(q, k, v, gk=gk, initial_state=h0, output_final_state=True, head_first=True)
+    assert_close("o", t(golden, "gla.o"), o, TOL)
+    assert_close("ht", t(golden, "gla.ht"), ht, TOL)
+    gr = _grads((o, ht), (t(golden, "gla.do"), t(golden, "gla.dht")), (q, k, v, gk, h0))
+    for name, gx in zip(("dq", "dk", "dv", "dgk", "dh0"), gr):
+        assert_close(name, t(golden, f"gla.{name}"), gx, TOL)
+
+
+def test_simple_gla_matches_reference_naive(golden):
+    q, k, v, g, h0 = (t(golden, f"simple_gla.{n}").requires_grad_(True) for n in ("q", "k", "v", "g", "h0"))
+    o, ht = oracle.simple_gla(q, k, v, g, initial_state=h0, output_final_state=True, head_first=True)
+    assert_close("o", t(golden, "simple_gla.o"), o, TOL)
+    assert_close("ht", t(golden, "simple_gla.ht"), ht, TOL)
+    gr = _grads((o, ht), (t(golden, "simple_gla.do"), t(golden, "simple_gla.dht")), (q, k, v, g, h0))
+    for name, gx in zip(("dq", "dk", "dv", "dg", "dh0"), gr):
+        assert_close(name, t(golden, f"simple_gla.{name}"), gx, TOL)
+
+
+def test_retention_matches_reference_naive(golden):
+    q, k, v = (t(golden, f"retention.{n}") for n in ("q", "k", "v"))
+    H = q.shape[1]
+    g = oracle.retention_log_decay(H)[None, :, None].expand(q.shape[0], H, q.shape[2])
+    o, _ = oracle.simple_gla(q, k, v, g, head_first=True)
+    assert_close("o", t(golden, "retention.o"), o, TOL)
+
+
+def test_delta_rule_matches_reference_naive(golden):
+    q, k, v, beta, h0 = (t(golden, f"delta.{n}").requires_grad_(True) for n in ("q", "k", "v", "beta", "h0"))
+    o, ht = oracle.delta_rule(q, k, v, beta, initial_state=h0, output_final_state=True, head_first=True)
+    assert_close("o", t(golden, "delta.o"), o, TOL)
+    assert_close("ht", t(golden, "delta.ht"), ht, TOL)
+    gr = _grads((o, ht), (t(golden, "delta.do"), t(golden, "delta.dht")), (q, k, v, beta, h0))
+    for name, gx in zip(("dq", "dk", "dv", "dbeta", "dh0"), gr):
+        assert_close(name, t(golden, f"delta.{name}"), gx, TOL)
+
+
+def test_gated_delta_rule_matches_reference_refs(golden):
+    names = ("q", "k", "v", "beta", "g", "h0")
+    q, k, v, beta, g, h0 = (t(golden, f"gated_delta.{n}").requires_grad_(True) for n in names)
+    scale = float(golden["gated_delta.scale"])
+    o, ht = oracle.gated_delta_rule(q, k, v, beta, g=g, scale=scale, initial_state=h0, output_final_state=True,
+                                    head_first=False)
+    assert_close("o", t(golden, "gated_delta.o"), o, TOL)
+    assert_close("ht", t(golden, "gated_delta.ht"), ht, TOL)
+    # the reference's chunked restatement agrees with its recurrent one to fp32 round-off
+    assert_close("o_chunk", t(golden, "gated_delta.o_chunk"), o, 1e-4)
+    gr = _grads((o, ht), (t(golden, "gated_delta.do"), t(golden, "gated_delta.dht")), (q, k, v, beta, g, h0))
+    for name, gx in zip(("dq", "dk", "dv", "dbeta", "dg", "dh0"), gr):
+        assert_close(name, t(golden, f"gated_delta.{name}"), gx, TOL)
+
+
+def test_cumsum_matches_reference(golden):
+    for name in ("s3", "s4"):
+        x = t(golden, f"cumsum.{name}.x")
+        for key, kw in (("local", dict(reverse=False)), ("local_rev", dict(reverse=True))):
+            y = oracle.cumsum_local(x, 64, head_first=False, **kw)
+            torch.testing.assert_close(y, t(golden, f"cumsum.{name}.{key}"))
+        for key, kw in (("glob", dict(reverse=False)), ("glob_rev", dict(reverse=True))):
+            y = oracle.cumsum_global(x, head_first=False, **kw)
+            torch.testing.assert_close(y, t(golden, f"cumsum.{name}.{key}"))
+
+
+def test_varlen_tables_bit_exact(golden):
+    offsets = t(golden, "varlen.offsets")
+    assert torch.equal(oracle.chunk_indices_ref(offsets), t(golden, "varlen.indices"))
+    assert torch.equal(oracle.chunk_offsets_ref(offsets), t(golden, "varlen.chunk_offsets"))
+
+
+def test_oracle_varlen_equals_per_sequence_runs():
+    g0 = torch.Generator().manual_seed(7)
+    T, H, K, V = 50, 2, 8, 8
+    q, k, v = torch.randn(1, T, H, K, generator=g0), torch.randn(1, T, H, K, generator=g0), torch.randn(1, T, H, V, generator=g0)
+    g = -torch.rand(1, T, H, generator=g0)
+    beta = torch.rand(1, T, H, generator=g0)
+    offsets = torch.tensor([0, 13, 13 + 30, 50])
+    o, ht = oracle.gated_delta_rule(q, k, v, beta, g=g, offsets=offsets, output_final_state=True, head_first=False)
+    for n, (a, b) in enumerate(zip(offsets[:-1].tolist(), offsets[1:].tolist())):
+        on, hn = oracle.gated_delta_rule(q[:, a:b], k[:, a:b], v[:, a:b], beta[:, a:b], g=g[:, a:b],
+                                         output_final_state=True, head_first=False)
+        torch.testing.assert_close(o[:, a:b], on)
+        torch.testing.assert_close(ht[n:n + 1], hn)
