@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Benchmark of the chunked linear-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one forward + backward pass of the op over one synthetic batch.  The default
+workload is the configuration the headline metric is quoted on: chunk_gated_delta_rule, bf16,
+B=8 T=4096 H=16 K=V=128, initial state given, final state requested.  With N > 1 (torchrun, one
+rank per GPU) every rank runs the same per-GPU batch (sequences and heads are independent, so the
+path shards with no data-path collective): weak scaling, value = tokens of all ranks / max time.
+
+Prints ONE JSON line (rank 0).  `value` = tokens/s with inputs resident in HBM; `e2e` = the same
+step with host (pinned) input buffers copied in and every result copied back inside the timed
+region; `roofline` = the dominant kernel timed on its own with CUDA events; `cpu_baseline` = the
+CPU oracle (a port of the reference's naive recurrence) on a bounded sample.
+`--impl reference` times that CPU path only (it is the reference's own CPU implementation of the
+path, restated; the reference checkout does not travel to the GPU box).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "flash-linear-attention_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+import torch.nn.functional as F  # noqa: E402
+
+METRIC = "chunk fwd+bwd tokens/s (GDN H=16 D=128 T=4K bf16)"
+UNIT = "tokens/s"
+
+WORKLOADS = {
+    # name: (op, B, T, H, K, V)
+    "gdn": ("gated_delta", 8, 4096, 16, 128, 128),
+    "delta": ("delta", 8, 4096, 16, 128, 128),
+    "retention": ("simple_gla", 8, 4096, 16, 128, 128),
+    "gla_fp32": ("gla", 2, 512, 4, 64, 64),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+def make_inputs(op, B, T, H, K, V, seed, dtype):
+    """Seeded synthetic inputs (CPU generator, so every implementation sees identical bits)."""
+    g0 = torch.Generator().manual_seed(seed)
+    q, k = torch.randn(B, T, H, K, generator=g0), torch.randn(B, T, H, K, generator=g0)
+    v = torch.randn(B, T, H, V, generator=g0)
+    d = {}
+    if op in ("gated_delta", "delta"):
+        q, k = F.normalize(q, p=2, dim=-1), F.normalize(k, p=2, dim=-1)
+        d["beta"] = torch.randn(B, T, H, generator=g0).sigmoid().to(dtype)
+        d["h0"] = torch.randn(B, H, K, V, generator=g0) * 0.1
+    if op == "gated_delta":
+        d["g"] = F.logsigmoid(torch.randn(B, T, H, generator=g0))
+    if op == "simple_gla":
+        # per-head decay log(1 - 2^(-5 - h*7/16)), constant along T
+        s = (1 - torch.tensor(2.).pow(-5. - torch.arange(H, dtype=torch.float) * 7 / 16)).log()
+        d["g"] = s[None, None, :].expand(B, T, H).contiguous()
+    if op == "gla":
+        d["g"] = F.logsigmoid(torch.randn(B, T, H, K, generator=g0)) / 16
+        d["h0"] = torch.zeros(B, H, K, V)
+    d.update(q=q.to(dtype), k=k.to(dtype), v=v.to(dtype))
+    d["do"] = torch.randn(B, T, H, V, generator=g0).to(dtype)
+    if "h0" in d:
+        d["dht"] = torch.randn(B, H, K, V, generator=g0)
+    return d
+
+
+GRAD_NAMES = {"gated_delta": ["q", "k", "v", "g", "beta", "h0"], "delta": ["q", "k", "v", "beta", "h0"],
+              "simple_gla": ["q", "k", "v", "g"], "gla": ["q", "k", "v", "g", "h0"]}
+
+
+def call_op(op, i, mod):
+    """mod = fla_b200.ops (CUDA) or the oracle (CPU)."""
+    st = "h0" in i
+    if mod == "oracle":
+        import oracle
+        if op == "gated_delta":
+            return oracle.gated_delta_rule(i["q"], i["k"], i["v"], i["beta"], g=i["g"], initial_state=i["h0"], output_final_state=True, head_first=False)
+        if op == "delta":
+            return oracle.delta_rule(i["q"], i["k"], i["v"], i["beta"], initial_state=i["h0"], output_final_state=True, head_first=False)
+        if op == "simple_gla":
+            return oracle.simple_gla(i["q"], i["k"], i["v"], i["g"], head_first=False)
+        return oracle.gla(i["q"], i["k"], i["v"], gk=i["g"], initial_state=i["h0"], output_final_state=True, head_first=False)
+    import fla_b200.ops as o
+    if op == "gated_delta":
+        return o.chunk_gated_delta_rule(i["q"], i["k"], i["v"], i["g"], i["beta"], initial_state=i["h0"], output_final_state=st, head_first=False)
+    if op == "delta":
+        return o.chunk_delta_rule(i["q"], i["k"], i["v"], i["beta"], initial_state=i["h0"], output_final_state=st, head_first=False)
+    if op == "simple_gla":
+        return o.chunk_simple_gla(i["q"], i["k"], i["v"], i["g"], head_first=False)
+    return o.chunk_gla(i["q"], i["k"], i["v"], i["g"], initial_state=i["h0"], output_final_state=st, head_first=False)
+
+
+def fwd_bwd(op, i, mod="ours"):
+    for n in GRAD_NAMES[op]:
+        i[n].grad = None
+    o, ht = call_op(op, i, mod)
+    outs, gouts = [o], [i["do"]]
+    if ht is not None:
+        outs.append(ht)
+        gouts.append(i["dht"])
+    torch.autograd.backward(outs, gouts)
+    return o, ht
+
+
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.stop_flag, self.thread = index, [], False, None
+
+    def _run(self):
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.1)
+
+    def __enter__(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop_flag = True
+        self.thread.join(timeout=6)
+
+    def summary(self):
+        mhz = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples for n, val in zip(names, s[2:6]) if val.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def time_stage(fn, reps=10, warm=3):
+    """Average device time of fn() in ms (CUDA events on the current stream)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def stage_breakdown(op, i):
+    """Times every stage of the gated-delta-rule forward+backward on its own; returns
+    {stage: (ms, launches per step, algorithmic bytes, algorithmic flops)} for the roofline entry."""
+    from fla_b200.ops import common as C
+    from fla_b200.utils import Geometry
+    if op != "gated_delta":
+        return {}
+    q, k, v, g, beta, h0, do, dht = (i[n].detach() for n in ("q", "k", "v", "g", "beta", "h0", "do", "dht"))
+    geo = Geometry(k, v, None, False)
+    B, T, H, K, V = geo.B, geo.T, geo.H, geo.K, geo.V
+    TH = B * T * H
+    scale = K ** -0.5
+    gc = C.chunk_local_cumsum(g, head_first=False)
+    aw, au, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta, g=gc)
+    h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=gc, h0=h0, output_final_state=True)
+    dv = C.chunk_bwd_dv_local(geo, q, k, gc, do, scale)
+    dh, dh0, dv2 = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=gc, dht=dht, want_dh0=True)
+    dq, dk, dw, dg = C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=gc, w=w, dv=dv2)
+    e = 2  # bytes per bf16 element
+    st = K * V * e / 64  # chunk-state bytes per token*head
+    # algorithmic (compulsory) traffic and dense-tile flops per token*head of each stage
+    table = {
+        "cumsum": (lambda: C.chunk_local_cumsum(g, head_first=False), 2, 8, 0),
+        "wy_fwd": (lambda: C.fwd_prepare_wy_repr(geo, k, v, beta, g=gc), 1, (2 * K + 2 * V) * e + 2 * 64 * e + 6, 2 * 64 * K + 2 * 64 * (K + V) + 2 * 64 * 64),
+        "wy_recompute": (lambda: C.fwd_recompute_w_u(geo, k, v, beta, aw, au), 1, (2 * K + 2 * V) * e + 2 * 64 * e + 2, 2 * 64 * (K + V)),
+        "delta_fwd_h": (lambda: C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=gc, h0=h0, output_final_state=True), 2, (2 * K + 2 * V) * e + 4 + st, 4 * K * V),
+        "chunk_fwd_o": (lambda: C.chunk_fwd_o(geo, q, k, v_new, h, g=gc, scale=scale), 1, (2 * K + 2 * V) * e + 4 + st, 2 * K * V + 2 * 64 * K + 2 * 64 * V),
+        "dv_local": (lambda: C.chunk_bwd_dv_local(geo, q, k, gc, do, scale), 1, (2 * K + 2 * V) * e + 4, 2 * 64 * K + 2 * 64 * V),
+        "delta_bwd_dhu": (lambda: C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=gc, dht=dht, want_dh0=True), 1, (3 * K + 3 * V) * e + 4 + st, 6 * K * V),
+        "dqkwg": (lambda: C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=gc, w=w, dv=dv2), 1, (6 * K + 3 * V) * e + 8 + 2 * st, 6 * K * V + 2 * 64 * V + 6 * 64 * K),
+        "wy_bwd": (lambda: C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv2, g=gc, au=au), 1, (4 * K + 4 * V) * e + 2 * 64 * e + 14, 8 * 64 * K + 4 * 64 * V + 8 * 64 * 64),
+    }
+    out = {}
+    for name, (fn, launches, bytes_th, flops_th) in table.items():
+        ms = time_stage(fn)
+        out[name] = dict(ms=ms, launches_per_step=launches, bytes=bytes_th * TH, flops=flops_th * TH)
+    return out
+
+
+def cpu_sample(op, B, T, H, K, V, dtype, steps=1, warmup=0):
+    """Oracle (CPU port of the reference's naive recurrence) forward+backward on a T-truncated sample."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    Ts = min(T, 128 if op != "gla" else T)
+    i = make_inputs(op, B, Ts, H, K, V, 0, dtype)
+    i = {n: x.float() for n, x in i.items()}
+    for n in GRAD_NAMES[op]:
+        i[n].requires_grad_(True)
+    times = []
+    for s in range(warmup + steps):
+        t0 = time.perf_counter()
+        fwd_bwd(op, i, "oracle")
+        if s >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return dict(value=B * Ts / sec, unit=UNIT, cores=cores, kind="port",
+                sample=f"{op} fwd+bwd via the oracle, fp32, B={B} T={Ts} (of {T}) H={H} K={K} V={V}, {len(times)} pass(es) of {sec:.2f} s"), sec
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gdn", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-extras", action="store_true", help="skip e2e / roofline / cpu_baseline legs")
+    args = ap.parse_args()
+    op, B, T, H, K, V = WORKLOADS[args.workload]
+    dtype = torch.float32 if args.workload == "gla_fp32" else torch.bfloat16
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    config = {"workload": f"chunk_{op} fwd+bwd {str(dtype).split('.')[-1]} B={B} T={T} H={H} K={K} V={V} seq-first, "
+              f"initial_state given, output_final_state=True, per GPU", "timing": "inputs (>600 MB) larger than the 126 MB L2",
+              "parallelism": f"{world} independent per-GPU batches (sequence x head shards, no collective)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        base, sec = cpu_sample(op, B, T, H, K, V, dtype, steps=max(1, min(args.steps, 3)), warmup=min(args.warmup, 1))
+        line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                "cpu_baseline": base, "gpu_launches": 0,
+                "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    from fla_b200 import _lib
+
+    host = make_inputs(op, B, T, H, K, V, 1000 + rank, dtype)
+    pinned = {n: x.pin_memory() for n, x in host.items()}
+    i = {n: x.to(dev) for n, x in host.items()}
+    for n in GRAD_NAMES[op]:
+        i[n].requires_grad_(True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        fwd_bwd(op, i)
+    barrier()
+    launches0 = _lib.LAUNCHES
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        a.record()
+        for _ in range(args.steps):
+            fwd_bwd(op, i)
+        b.record()
+        barrier()
+    ms_total = a.elapsed_time(b)
+    launches = (_lib.LAUNCHES - launches0) // args.steps
+    if world > 1:
+        tmax = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms_total = tmax.item()
+    ms_step = ms_total / args.steps
+    tokens = B * T * world
+    value = tokens / (ms_step * 1e-3)
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic", "config": config,
+            "clocks": clk.summary(), "gpu_launches": launches}
+
+    # ---- end to end: host buffers in, every result back to the host, inside the timed region
+    if not args.no_extras:
+        grads_host = {n: torch.empty_like(host[n], dtype=(torch.float32 if n in ("g", "h0") else host[n].dtype)).pin_memory()
+                      for n in GRAD_NAMES[op]}
+        o_host = torch.empty_like(host["do"]).pin_memory()
+        ht_host = torch.empty(B, H, K, V).pin_memory() if "h0" in host else None
+
+        def e2e_step():
+            j = {n: x.to(dev, non_blocking=True) for n, x in pinned.items()}
+            for n in GRAD_NAMES[op]:
+                j[n].requires_grad_(True)
+            o, ht = fwd_bwd(op, j)
+            o_host.copy_(o.detach(), non_blocking=True)
+            if ht is not None:
+                ht_host.copy_(ht.detach(), non_blocking=True)
+            for n in GRAD_NAMES[op]:
+                grads_host[n].copy_(j[n].grad, non_blocking=True)
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        a.record()
+        for _ in range(args.steps):
+            e2e_step()
+        b.record()
+        barrier()
+        e_ms = a.elapsed_time(b)
+        if world > 1:
+            tmax = torch.tensor([e_ms], device=dev)
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            e_ms = tmax.item()
+        h2d = sum(x.numel() * x.element_size() for x in pinned.values())
+        d2h = o_host.numel() * o_host.element_size() + (ht_host.numel() * 4 if ht_host is not None else 0) + \
+            sum(x.numel() * x.element_size() for x in grads_host.values())
+        line["e2e"] = {"value": tokens / (e_ms / args.steps * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                       "d2h_bytes_per_step": d2h}
+
+    if rank == 0 and not args.no_extras:
+        pk = peaks()
+        stages = stage_breakdown(op, i)
+        if stages:
+            top = max(stages, key=lambda s: stages[s]["ms"] * stages[s]["launches_per_step"])
+            s = stages[top]
+            t_hbm = s["bytes"] / (pk["hbm_gbs"] * 1e9)
+            t_tc = s["flops"] / (pk["bf16_tflops"] * 1e12)
+            if t_hbm >= t_tc:
+                ach, peak, unit, bound = s["bytes"] / (s["ms"] * 1e-3) / 1e9, pk["hbm_gbs"], "GB/s", "hbm"
+            else:
+                ach, peak, unit, bound = s["flops"] / (s["ms"] * 1e-3) / 1e12, pk["bf16_tflops"], "TFLOP/s", "tensor"
+            line["roofline"] = {"kernel": top, "bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+                                "traffic": None, "peak_source": pk["source"], "ms_per_launch": s["ms"],
+                                "tensor_frac": s["flops"] / (s["ms"] * 1e-3) / 1e12 / pk["bf16_tflops"]}
+            line["stages_ms"] = {k_: round(v_["ms"] * v_["launches_per_step"], 4) for k_, v_ in stages.items()}
+        line["cpu_baseline"], _ = cpu_sample(op, B, T, H, K, V, dtype)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

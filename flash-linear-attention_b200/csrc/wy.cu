@@ -63,7 +63,8 @@ __global__ void __launch_bounds__(128) wy_fwd_kernel(const flab_args a) {
 
   if (tid < C) {
     sBeta[tid] = tid < rows ? Num<T>::f(beta[tok_off(a, s, hd, t0 + tid, 1)]) : 0.f;
-    sG[tid] = (GATED && tid < rows) ? reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + tid, 1)] : 0.f;
+    // the gate only enters through the Gram decay, which the recompute path does not rebuild
+    sG[tid] = (GATED && !RECOMPUTE && tid < rows) ? reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + tid, 1)] : 0.f;
   }
 
   if (!RECOMPUTE) {

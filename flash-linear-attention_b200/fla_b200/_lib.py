@@ -51,6 +51,7 @@ ENTRY_POINTS = [
 ]
 
 _lib = None
+LAUNCHES = 0  # kernels launched through this module (one per successful call)
 
 
 def load() -> ctypes.CDLL:
@@ -115,3 +116,5 @@ def call(entry: str, ref: torch.Tensor, *, B, T, H, K=0, V=0, N=None, NT=0, dtyp
         rc = getattr(lib, entry)(ctypes.byref(a), ctypes.c_void_p(stream))
     if rc != 0:
         raise RuntimeError(f"{entry} failed ({rc}): {lib.flab_last_error().decode()}")
+    global LAUNCHES
+    LAUNCHES += 1

@@ -4,6 +4,7 @@ tables (the integer index data of this path) and the autograd decorators the ref
 (fla/utils.py:10-21 `contiguous`, :88-93 autocast wrappers)."""
 
 import functools
+import weakref
 from collections import namedtuple
 from typing import Optional
 
@@ -45,20 +46,23 @@ def chunk_tables(lengths, chunk_size: int = CHUNK):
     return indices, chunk_offsets
 
 
-_VARLEN_CACHE = {}
+_VARLEN_CACHE = {}  # id(offsets tensor) -> (weakref to it, its version counter, Varlen)
 
 
 def prepare_varlen(offsets: Optional[torch.Tensor], device) -> Optional[Varlen]:
-    """Device-resident int32 tables for `offsets` (int32 or int64, [N+1]); cached per tensor.
+    """Device-resident int32 tables for `offsets` (int32 or int64, [N+1]).
 
     Reading `offsets` on the host costs one device-to-host copy, like the reference's `.tolist()`.
+    The result is cached per tensor OBJECT (validated through a weak reference and the tensor's
+    version counter), never per address: the allocator reuses addresses, and a table built for
+    another batch would silently index the wrong tokens.
     """
     if offsets is None:
         return None
-    key = (offsets.data_ptr(), tuple(offsets.shape), offsets.dtype, str(offsets.device), offsets._version, str(device))
+    key = id(offsets)
     hit = _VARLEN_CACHE.get(key)
-    if hit is not None:
-        return hit
+    if hit is not None and hit[0]() is offsets and hit[1] == offsets._version and hit[2].cu_seqlens.device == torch.device(device):
+        return hit[2]
     host = [int(x) for x in offsets.tolist()]
     if len(host) < 2 or host[0] != 0 or any(b < a for a, b in zip(host, host[1:])):
         raise ValueError(f"`offsets` must start at 0 and be non-decreasing, got {host[:8]}...")
@@ -70,7 +74,7 @@ def prepare_varlen(offsets: Optional[torch.Tensor], device) -> Optional[Varlen]:
     out = Varlen(cu, idx, co, len(lengths), len(indices), lengths)
     if len(_VARLEN_CACHE) > 64:
         _VARLEN_CACHE.clear()
-    _VARLEN_CACHE[key] = out
+    _VARLEN_CACHE[key] = (weakref.ref(offsets), offsets._version, out)
     return out
 
 
