@@ -58,28 +58,27 @@ __global__ void __launch_bounds__(128) chunk_h_kernel(const flab_args a) {
   };
 
   const int first = BWD ? s.nt - 1 : 0, step = BWD ? -1 : 1;
-  load(first, 0);
+  if (s.nt > 0) load(first, 0);
   for (int i = 0; i < s.nt; ++i) {
     const int it = first + i * step, cur = i & 1;
-    if (i + 1 < s.nt) {
-      load(it + step, cur ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+    cp_async_wait<0>();
+    __syncthreads();  // tiles of this chunk have landed; every warp is done with the previous chunk
+    if (i + 1 < s.nt) load(it + step, cur ^ 1);
     T *x = sX + cur * C * LD, *y = sY + cur * C * LD;
     const int rows = min(C, s.len - it * C);
     const int last = rows - 1;
     // stage the state at the chunk boundary for the store
     acc_to_smem<1, 8, T>(acc, sStage, LD, m0, 0);
-    // operand pre-scaling in shared memory (rounded to the element type like the reference does)
+    // operand pre-scaling in shared memory (rounded to the element type like the reference does);
+    // scalar gate: thread = (token row, half of the 64 columns), one exp per thread
     if (!BWD) {
       if (GATE == 1) {
-        const float gl = sG[cur * C + last];
-        for (int e = tid; e < C * HB; e += 128) {
-          int r_ = e / HB, c_ = e - r_ * HB;
-          y[r_ * LD + c_] = Num<T>::t(Num<T>::f(y[r_ * LD + c_]) * expf(gl - sG[cur * C + r_]));
+        const int r_ = tid >> 1, c0 = (tid & 1) * (HB / 2);
+        const float f = expf(sG[cur * C + last] - sG[cur * C + r_]);
+#pragma unroll 4
+        for (int c_ = c0; c_ < c0 + HB / 2; c_ += 2) {
+          T *p = y + r_ * LD + c_;
+          st_pair<T>(p, Num<T>::f(p[0]) * f, Num<T>::f(p[1]) * f);
         }
       } else if (GATE == 2) {
         const float *gk = sGK + cur * C * LDG;
@@ -89,13 +88,21 @@ __global__ void __launch_bounds__(128) chunk_h_kernel(const flab_args a) {
         }
       }
     } else {
-      const float *gk = sGK + cur * C * LDG;
-      for (int e = tid; e < C * HB; e += 128) {
-        int r_ = e / HB, c_ = e - r_ * HB;
-        float qv = rnd<T>(Num<T>::f(x[r_ * LD + c_]) * a.scale);
-        if (GATE == 1) qv *= expf(sG[cur * C + r_]);
-        if (GATE == 2) qv *= expf(gk[r_ * LDG + c_]);
-        x[r_ * LD + c_] = Num<T>::t(qv);
+      if (GATE == 2) {
+        const float *gk = sGK + cur * C * LDG;
+        for (int e = tid; e < C * HB; e += 128) {
+          int r_ = e / HB, c_ = e - r_ * HB;
+          float qv = rnd<T>(Num<T>::f(x[r_ * LD + c_]) * a.scale) * expf(gk[r_ * LDG + c_]);
+          x[r_ * LD + c_] = Num<T>::t(qv);
+        }
+      } else {
+        const int r_ = tid >> 1, c0 = (tid & 1) * (HB / 2);
+        const float f = GATE == 1 ? expf(sG[cur * C + r_]) : 1.f;
+#pragma unroll 4
+        for (int c_ = c0; c_ < c0 + HB / 2; c_ += 2) {
+          T *p = x + r_ * LD + c_;
+          st_pair<T>(p, rnd<T>(Num<T>::f(p[0]) * a.scale) * f, rnd<T>(Num<T>::f(p[1]) * a.scale) * f);
+        }
       }
     }
     __syncthreads();
@@ -122,7 +129,6 @@ __global__ void __launch_bounds__(128) chunk_h_kernel(const flab_args a) {
       }
     }
     WarpGemm<1, 8, true, true, T>::run(acc, x, LD, m0, y, LD, 0, C);
-    __syncthreads();
   }
   if (S1) {
     FLAB_ACC_FOREACH(1, 8, m0, 0, row, col, mi, ni, r) {

@@ -137,27 +137,31 @@ template <typename T, int MODE> static int launch_chunk_o(const flab_args *a, cu
 }
 
 // ------------------------------------------------------------------------------------------------
-// dqkwg.  grid = (NT, H); 8 warps: warp = (row block rb of 16 tokens, column half ch).
-// The K extent is walked in tiles of BKT columns; per tile the inter-chunk terms contract over V
-// against the h / dh tiles and the intra-chunk terms contract over the 64 tokens against ds.
+// dqkwg.  grid = (NT, H); 8 warps: warp = (row block rb of 16 tokens, column half ch of a 64-wide
+// K tile).  K is walked in tiles of 64 channels.  Per tile, phase 1 contracts do / v / dv over V
+// against the h / dh tiles (inter-chunk terms); the q / k / w tiles are then fetched into the same
+// buffers and phase 2 adds the intra-chunk terms (contraction over the 64 tokens against ds).
+// Re-using the buffers keeps the CTA under half of the SM's shared memory, so two CTAs overlap
+// each other's load and compute phases.
 // ------------------------------------------------------------------------------------------------
-template <typename T, int BKT, bool USE_DW>
+constexpr int QB = 64;  // K tile
+
+template <typename T, bool USE_DW>
 __global__ void __launch_bounds__(256) chunk_dqkwg_kernel(const flab_args a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int VP = round_up(a.V, 16);
   const int LDV = VP + Num<T>::pad;
-  constexpr int LDK = BKT + Num<T>::pad;
+  constexpr int LDK = QB + Num<T>::pad;
   constexpr int LDP = C + Num<T>::pad;
+  constexpr int NT3 = USE_DW ? 3 : 2;
   T *sV = reinterpret_cast<T *>(smem_raw);  // [64][LDV]
   T *sDO = sV + C * LDV;                    // [64][LDV]
   T *sDV = sDO + C * LDV;                   // [64][LDV]   (USE_DW)
-  const int HSZ = max(BKT * LDV, C * LDK);
-  T *sH = sDV + (USE_DW ? C * LDV : 0);     // [BKT][LDV]  later reused to stage dq as [64][LDK]
-  T *sDH = sH + HSZ;                        // [BKT][LDV]  later reused to stage dk as [64][LDK]
-  T *sQ = sDH + HSZ;                        // [64][LDK]
-  T *sK = sQ + C * LDK;                     // [64][LDK]
-  T *sW = sK + C * LDK;                     // [64][LDK]   (USE_DW) later reused to stage dw
-  T *sDS = sW + (USE_DW ? C * LDK : 0);     // [64][LDP]
+  T *sU = sDV + (USE_DW ? C * LDV : 0);     // union: phase 1 {h, dh}[64][LDV]; phase 2 {q, k, w}[64][LDK]
+  const int usz = max(2 * QB * LDV, NT3 * C * LDK);
+  T *sH = sU, *sDH = sU + QB * LDV;
+  T *sQ = sU, *sK = sU + C * LDK, *sW = sU + 2 * C * LDK;
+  T *sDS = sU + usz;                                     // [64][LDP]
   float *sG = reinterpret_cast<float *>(sDS + C * LDP);  // [64]
   float *sDG = sG + C;                                   // [64]
   float *sRed = sDG + C;                                 // [2]: sum(h*dh), sum(dk*k)
@@ -172,10 +176,16 @@ __global__ void __launch_bounds__(256) chunk_dqkwg_kernel(const flab_args a) {
   const size_t ks = tok_stride(a, a.K), vs = tok_stride(a, a.V);
   const size_t offk = tok_off(a, s, hd, t0, a.K), offv = tok_off(a, s, hd, t0, a.V);
   const bool use_g = a.g != nullptr;
+  const size_t hbase = ((size_t)(s.c0 + it) * a.H + hd) * a.K * a.V;
 
   tile_load<T>(sV, LDV, reinterpret_cast<const T *>(a.v) + offv, vs, rows, C, a.V, VP, tid, 256);
   tile_load<T>(sDO, LDV, reinterpret_cast<const T *>(a.d_o) + offv, vs, rows, C, a.V, VP, tid, 256);
   if (USE_DW) tile_load<T>(sDV, LDV, reinterpret_cast<const T *>(a.dv) + offv, vs, rows, C, a.V, VP, tid, 256);
+  {
+    const int kw0 = min(QB, a.K);
+    tile_load<T>(sH, LDV, reinterpret_cast<const T *>(a.h) + hbase, (size_t)a.V, kw0, QB, a.V, VP, tid, 256);
+    tile_load<T>(sDH, LDV, reinterpret_cast<const T *>(a.dh) + hbase, (size_t)a.V, kw0, QB, a.V, VP, tid, 256);
+  }
   if (tid < C) {
     float gv = 0.f;
     if (use_g && tid < rows) gv = reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + tid, 1)];
@@ -188,51 +198,62 @@ __global__ void __launch_bounds__(256) chunk_dqkwg_kernel(const flab_args a) {
   __syncthreads();
 
   const int rb = warp & 3, ch = warp >> 2;
-  const int m0 = rb * 16;
+  const int m0 = rb * 16, n0 = ch * 32;
   // ds = do v^T, masked / decayed / scaled once; kept in fp32 registers and as T in shared memory
   float ds[1][4][4];
   acc_zero(ds);
-  WarpGemm<1, 4, false, false, T>::run(ds, sDO, LDV, m0, sV, LDV, ch * 32, VP);
-  FLAB_ACC_FOREACH(1, 4, m0, ch * 32, row, col, mi, ni, r) {
+  WarpGemm<1, 4, false, false, T>::run(ds, sDO, LDV, m0, sV, LDV, n0, VP);
+  FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
     float x = ds[mi][ni][r];
     x = (row >= col) ? (use_g ? x * safe_exp(sG[row] - sG[col]) : x) * a.scale : 0.f;
     ds[mi][ni][r] = x;
   }
-  acc_to_smem<1, 4, T>(ds, sDS, LDP, m0, ch * 32);
+  acc_to_smem<1, 4, T>(ds, sDS, LDP, m0, n0);
 
   const float e_lo = use_g ? expf(sG[m0 + g8]) : 1.f, e_hi = use_g ? expf(sG[m0 + g8 + 8]) : 1.f;
   const float f_lo = use_g ? safe_exp(sG[last] - sG[m0 + g8]) : 1.f, f_hi = use_g ? safe_exp(sG[last] - sG[m0 + g8 + 8]) : 1.f;
   float dg_lo = 0.f, dg_hi = 0.f;  // per-row partial of dg for rows m0+g8 and m0+g8+8
   float hdh = 0.f, dkk = 0.f;
 
-  constexpr int NI = BKT / 16;
-  const int nk = cdiv(a.K, BKT);
+  const int nk = cdiv(a.K, QB);
   for (int kt = 0; kt < nk; ++kt) {
-    const int k0 = kt * BKT, kw = min(BKT, a.K - k0);
-    __syncthreads();  // previous tile fully consumed (also orders sDS writes before the first use)
-    {
-      const size_t hoff = ((size_t)(s.c0 + it) * a.H + hd) * a.K * a.V + (size_t)k0 * a.V;
-      tile_load<T>(sH, LDV, reinterpret_cast<const T *>(a.h) + hoff, (size_t)a.V, kw, BKT, a.V, VP, tid, 256);
-      tile_load<T>(sDH, LDV, reinterpret_cast<const T *>(a.dh) + hoff, (size_t)a.V, kw, BKT, a.V, VP, tid, 256);
-      tile_load<T>(sQ, LDK, reinterpret_cast<const T *>(a.q) + offk + k0, ks, rows, C, kw, BKT, tid, 256);
-      tile_load<T>(sK, LDK, reinterpret_cast<const T *>(a.k) + offk + k0, ks, rows, C, kw, BKT, tid, 256);
-      if (USE_DW) tile_load<T>(sW, LDK, reinterpret_cast<const T *>(a.w) + offk + k0, ks, rows, C, kw, BKT, tid, 256);
+    const int k0 = kt * QB, kw = min(QB, a.K - k0);
+    if (kt > 0) {
+      __syncthreads();  // previous tile's staged outputs have been read
+      tile_load<T>(sH, LDV, reinterpret_cast<const T *>(a.h) + hbase + (size_t)k0 * a.V, (size_t)a.V, kw, QB, a.V, VP, tid, 256);
+      tile_load<T>(sDH, LDV, reinterpret_cast<const T *>(a.dh) + hbase + (size_t)k0 * a.V, (size_t)a.V, kw, QB, a.V, VP, tid, 256);
       cp_async_commit();
       cp_async_wait<0>();
+      __syncthreads();
     }
-    __syncthreads();
-    const int n0 = ch * (BKT / 2);
-    float dq[1][NI][4], dk[1][NI][4];
+    // ---- phase 1: inter-chunk terms
+    float dq[1][4][4], dk[1][4][4], dw[1][4][4];
     acc_zero(dq);
     acc_zero(dk);
-    WarpGemm<1, NI, false, false, T>::run(dq, sDO, LDV, m0, sH, LDV, n0, VP);
-    WarpGemm<1, NI, false, false, T>::run(dk, sV, LDV, m0, sDH, LDV, n0, VP);
+    WarpGemm<1, 4, false, false, T>::run(dq, sDO, LDV, m0, sH, LDV, n0, VP);
+    WarpGemm<1, 4, false, false, T>::run(dk, sV, LDV, m0, sDH, LDV, n0, VP);
     if (USE_DW) {
-      float dw[1][NI][4];
       acc_zero(dw);
-      WarpGemm<1, NI, false, false, T>::run(dw, sDV, LDV, m0, sH, LDV, n0, VP);
-      // dw = -(dv h^T) * e^{b_i}; dg_i -= <w_i, dw_i> (before the sign flip)
-      FLAB_ACC_FOREACH(1, NI, m0, n0, row, col, mi, ni, r) {
+      WarpGemm<1, 4, false, false, T>::run(dw, sDV, LDV, m0, sH, LDV, n0, VP);
+    }
+    if (use_g) {
+      for (int e = tid; e < kw * (VP / 2); e += 256) {
+        const int r_ = e / (VP / 2), c_ = (e - r_ * (VP / 2)) * 2;
+        hdh += Num<T>::f(sH[r_ * LDV + c_]) * Num<T>::f(sDH[r_ * LDV + c_]) +
+               Num<T>::f(sH[r_ * LDV + c_ + 1]) * Num<T>::f(sDH[r_ * LDV + c_ + 1]);
+      }
+    }
+    __syncthreads();  // every warp is done with h / dh
+    tile_load<T>(sQ, LDK, reinterpret_cast<const T *>(a.q) + offk + k0, ks, rows, C, kw, QB, tid, 256);
+    tile_load<T>(sK, LDK, reinterpret_cast<const T *>(a.k) + offk + k0, ks, rows, C, kw, QB, tid, 256);
+    if (USE_DW) tile_load<T>(sW, LDK, reinterpret_cast<const T *>(a.w) + offk + k0, ks, rows, C, kw, QB, tid, 256);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    // ---- phase 2: gates, dg contributions, intra-chunk terms
+    if (USE_DW) {
+      // dw = -(dv h^T) * e^{b_i}; dg_i -= <w_i, dw_i> (dw before the sign flip)
+      FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
         float x = dw[mi][ni][r] * ((r >> 1) ? e_hi : e_lo);
         if (use_g) {
           float wv = Num<T>::f(sW[row * LDK + col]);
@@ -240,18 +261,8 @@ __global__ void __launch_bounds__(256) chunk_dqkwg_kernel(const flab_args a) {
         }
         dw[mi][ni][r] = -x;
       }
-      __syncthreads();  // every warp is done reading sW as an input? (sW is only read above) -> stage dw in place
-      acc_to_smem<1, NI, T>(dw, sW, LDK, m0, n0);
     }
-    if (use_g) {
-      // sum(h * dh) over the tile
-      for (int e = tid; e < kw * a.V; e += 256) {
-        int r_ = e / a.V, c_ = e - r_ * a.V;
-        hdh += Num<T>::f(sH[r_ * LDV + c_]) * Num<T>::f(sDH[r_ * LDV + c_]);
-      }
-    }
-    // gating of the inter-chunk terms and their dg contributions
-    FLAB_ACC_FOREACH(1, NI, m0, n0, row, col, mi, ni, r) {
+    FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
       const bool hi = r >> 1;
       float xq = dq[mi][ni][r] * (hi ? e_hi : e_lo) * a.scale;
       float xk = dk[mi][ni][r] * (hi ? f_hi : f_lo);
@@ -268,37 +279,35 @@ __global__ void __launch_bounds__(256) chunk_dqkwg_kernel(const flab_args a) {
       // ds2 = ds * (q k^T): row sums add to dg, column sums subtract
       float qk[1][4][4];
       acc_zero(qk);
-      WarpGemm<1, 4, false, false, T>::run(qk, sQ, LDK, m0, sK, LDK, ch * 32, BKT);
-      float colsum[4][2];
+      WarpGemm<1, 4, false, false, T>::run(qk, sQ, LDK, m0, sK, LDK, n0, QB);
 #pragma unroll
       for (int ni = 0; ni < 4; ++ni) {
         float p0 = ds[0][ni][0] * qk[0][ni][0], p1 = ds[0][ni][1] * qk[0][ni][1];
         float p2 = ds[0][ni][2] * qk[0][ni][2], p3 = ds[0][ni][3] * qk[0][ni][3];
         dg_lo += p0 + p1;
         dg_hi += p2 + p3;
-        colsum[ni][0] = p0 + p2;
-        colsum[ni][1] = p1 + p3;
-      }
-#pragma unroll
-      for (int ni = 0; ni < 4; ++ni)
-#pragma unroll
-        for (int c_ = 0; c_ < 2; ++c_) {
-          float x = colsum[ni][c_];
-          x += __shfl_xor_sync(0xffffffffu, x, 4);
-          x += __shfl_xor_sync(0xffffffffu, x, 8);
-          x += __shfl_xor_sync(0xffffffffu, x, 16);
-          if (g8 == 0) atomicAdd(&sDG[ch * 32 + ni * 8 + 2 * (lane & 3) + c_], -x);
+        float c0 = p0 + p2, c1 = p1 + p3;
+        c0 += __shfl_xor_sync(0xffffffffu, c0, 4);
+        c0 += __shfl_xor_sync(0xffffffffu, c0, 8);
+        c0 += __shfl_xor_sync(0xffffffffu, c0, 16);
+        c1 += __shfl_xor_sync(0xffffffffu, c1, 4);
+        c1 += __shfl_xor_sync(0xffffffffu, c1, 8);
+        c1 += __shfl_xor_sync(0xffffffffu, c1, 16);
+        if (g8 == 0) {
+          atomicAdd(&sDG[n0 + ni * 8 + 2 * (lane & 3)], -c0);
+          atomicAdd(&sDG[n0 + ni * 8 + 2 * (lane & 3) + 1], -c1);
         }
+      }
     }
-    // intra-chunk terms
-    WarpGemm<1, NI, false, true, T>::run(dq, sDS, LDP, m0, sK, LDK, n0, C);
-    WarpGemm<1, NI, true, true, T>::run(dk, sDS, LDP, m0, sQ, LDK, n0, C);
-    __syncthreads();  // all warps done with sH / sDH / sQ / sK
-    acc_to_smem<1, NI, T>(dq, sH, LDK, m0, n0);
-    acc_to_smem<1, NI, T>(dk, sDH, LDK, m0, n0);
+    WarpGemm<1, 4, false, true, T>::run(dq, sDS, LDP, m0, sK, LDK, n0, C);
+    WarpGemm<1, 4, true, true, T>::run(dk, sDS, LDP, m0, sQ, LDK, n0, C);
+    __syncthreads();  // all warps done reading q / k / w
+    acc_to_smem<1, 4, T>(dq, sQ, LDK, m0, n0);
+    acc_to_smem<1, 4, T>(dk, sK, LDK, m0, n0);
+    if (USE_DW) acc_to_smem<1, 4, T>(dw, sW, LDK, m0, n0);
     __syncthreads();
-    tile_store<T>(reinterpret_cast<T *>(a.dq) + offk + k0, ks, sH, LDK, rows, kw, tid, 256);
-    tile_store<T>(reinterpret_cast<T *>(a.dk) + offk + k0, ks, sDH, LDK, rows, kw, tid, 256);
+    tile_store<T>(reinterpret_cast<T *>(a.dq) + offk + k0, ks, sQ, LDK, rows, kw, tid, 256);
+    tile_store<T>(reinterpret_cast<T *>(a.dk) + offk + k0, ks, sK, LDK, rows, kw, tid, 256);
     if (USE_DW) tile_store<T>(reinterpret_cast<T *>(a.dw) + offk + k0, ks, sW, LDK, rows, kw, tid, 256);
   }
   if (use_g) {
@@ -325,13 +334,14 @@ __global__ void __launch_bounds__(256) chunk_dqkwg_kernel(const flab_args a) {
   }
 }
 
-template <typename T, int BKT, bool USE_DW> static int launch_dqkwg(const flab_args *a, cudaStream_t stream) {
+template <typename T, bool USE_DW> static int launch_dqkwg(const flab_args *a, cudaStream_t stream) {
   const int VP = round_up(a->V, 16);
-  const int LDV = VP + Num<T>::pad, LDK = BKT + Num<T>::pad, LDP = C + Num<T>::pad;
-  const size_t hsz = (size_t)(BKT * LDV > C * LDK ? BKT * LDV : C * LDK);
-  size_t elems = (size_t)(USE_DW ? 3 : 2) * C * LDV + 2 * hsz + (size_t)(USE_DW ? 3 : 2) * C * LDK + (size_t)C * LDP;
+  const int LDV = VP + Num<T>::pad, LDK = QB + Num<T>::pad, LDP = C + Num<T>::pad;
+  const int nt3 = USE_DW ? 3 : 2;
+  const size_t usz = (size_t)(2 * QB * LDV > nt3 * C * LDK ? 2 * QB * LDV : nt3 * C * LDK);
+  size_t elems = (size_t)nt3 * C * LDV + usz + (size_t)C * LDP;
   size_t smem = elems * sizeof(T) + (2 * C + 4) * sizeof(float);
-  auto kern = chunk_dqkwg_kernel<T, BKT, USE_DW>;
+  auto kern = chunk_dqkwg_kernel<T, USE_DW>;
   if (int e = set_smem(kern, smem)) return e;
   dim3 grid(a->NT, a->H);
   kern<<<grid, 256, smem, stream>>>(*a);
@@ -379,20 +389,9 @@ int flab_chunk_bwd_dqkwg(const flab_args *a, void *stream) {
   const bool use_dw = a->w != nullptr;
   if (use_dw) {
     FLAB_REQUIRE(a->dv && a->dw, FLAB_E_BADARG, "chunk_bwd_dqkwg: w given but dv or dw is NULL");
-    FLAB_REQUIRE(a->V <= 128, FLAB_E_UNSUPPORTED, "chunk_bwd_dqkwg (delta rule): V = %d > 128", a->V);
-    FLAB_DISPATCH_16(a->dtype, T, {
-      if (a->K > 64) return (launch_dqkwg<T, 128, true>(a, (cudaStream_t)stream));
-      return (launch_dqkwg<T, 64, true>(a, (cudaStream_t)stream));
-    });
+    FLAB_DISPATCH_16(a->dtype, T, return (launch_dqkwg<T, true>(a, (cudaStream_t)stream)));
   } else {
-    if (a->dtype == FLAB_FP32) {
-      FLAB_REQUIRE(a->V <= 128, FLAB_E_UNSUPPORTED, "chunk_bwd_dqkwg (fp32): V = %d > 128", a->V);
-      return launch_dqkwg<float, 64, false>(a, (cudaStream_t)stream);
-    }
-    FLAB_DISPATCH_16(a->dtype, T, {
-      if (a->K > 64) return (launch_dqkwg<T, 128, false>(a, (cudaStream_t)stream));
-      return (launch_dqkwg<T, 64, false>(a, (cudaStream_t)stream));
-    });
+    FLAB_DISPATCH_ALL(a->dtype, T, return (launch_dqkwg<T, false>(a, (cudaStream_t)stream)));
   }
   return FLAB_OK;
 }

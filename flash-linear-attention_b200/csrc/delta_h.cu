@@ -4,30 +4,39 @@
 //   backward (fla/ops/common/chunk_delta_h.py:136-237): per chunk, last to first
 //       dh[t] = D; dv2 = dv + (k * e^{b_L-b}) bf(D);
 //       D <- e^{b_L} D + (q*scale*e^{b})^T do - (w * e^{b})^T bf(dv2)
-// One CTA owns all K rows and a 64-wide slab of V columns of one (sequence, head) state; the state
-// stays in accumulator registers, its rounded copy goes through shared memory both as the operand
-// of the dependent product and as the staging buffer of the coalesced h / dh store.  Token tiles of
-// the next chunk are prefetched with cp.async while the current chunk is processed.
+// One CTA (8 warps) owns all K rows and a 64-wide slab of V columns of one (sequence, head) state.
+// The state stays in accumulator registers; its rounded copy goes through shared memory both as the
+// operand of the dependent product and as the staging buffer of the coalesced h / dh store.
+// The per-token gate factors are applied to the rows of the small [64 x 64] product / operand tiles
+// (e^{b_i} (w S) instead of (e^{b_i} w) S, and k^T (e^{b_L-b_i} v_new) instead of (e^{b_L-b_i} k)^T v_new),
+// so the [64 x K] token tiles are consumed exactly as cp.async delivered them and nothing but the two
+// dependent products, two small conversions and four barriers sit on the serial path.
 #include "common.cuh"
 
 namespace flab {
 
 constexpr int DBV = 64;  // V columns per CTA
+constexpr int DTH = 256;
 
 template <typename T, int KP, bool BWD>
-__global__ void __launch_bounds__(128) delta_h_kernel(const flab_args a) {
+__global__ void __launch_bounds__(DTH) delta_h_kernel(const flab_args a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LDK = KP + Num<T>::pad;
   constexpr int LDB = DBV + Num<T>::pad;
-  constexpr int MI = KP / 64;  // state rows per warp = 16 * MI
+  // state tile KP x 64 over 8 warps
+  constexpr int SR = KP >= 128 ? KP / 8 : 16;  // state rows per warp
+  constexpr int SMI = SR / 16;
+  constexpr int SNI = KP >= 128 ? 8 : 4;       // 64 or 32 columns per warp
   constexpr int NKT = BWD ? 3 : 2;  // [tokens x K] tiles per chunk: fwd (w, k); bwd (q, k, w)
   constexpr int NVT = BWD ? 2 : 1;  // [tokens x BV] tiles per chunk: fwd (u); bwd (do, dv)
   T *sKT = reinterpret_cast<T *>(smem_raw);        // [2][NKT][64][LDK]
   T *sVT = sKT + 2 * NKT * C * LDK;                // [2][NVT][64][LDB]
   T *sS = sVT + 2 * NVT * C * LDB;                 // [KP][LDB] rounded state
-  float *sG = reinterpret_cast<float *>(sS + KP * LDB);  // [2][64]
+  T *sOp = sS + KP * LDB;                          // [64][LDB] gate-scaled operand of the state update
+  float *sG = reinterpret_cast<float *>(sOp + C * LDB);  // [2][64] gates; [64] e^{b}; [64] e^{b_L-b}
+  float *sE1 = sG + 2 * C, *sE2 = sE1 + C;
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int v0 = blockIdx.x * DBV;
   const int n = blockIdx.y / a.H, hd = blockIdx.y % a.H;
   const Seq s = seq_of(a, n);
@@ -56,13 +65,16 @@ __global__ void __launch_bounds__(128) delta_h_kernel(const flab_args a) {
   const float *S0 = reinterpret_cast<const float *>(BWD ? a.dht : a.h0);
   float *S1 = reinterpret_cast<float *>(BWD ? a.dh0 : a.ht);
 
-  float acc[MI][8][4];
+  float acc[SMI][SNI][4];
   acc_zero(acc);
-  const int ms = warp * 16 * MI;  // first state row of this warp
-  const int m0 = warp * 16;       // first token row of this warp
+  // warp tile of the state: rows [ms, ms + SR), columns [ns, ns + 8*SNI)
+  const int ms = KP >= 128 ? warp * SR : (warp & 3) * 16;
+  const int ns = KP >= 128 ? 0 : (warp >> 2) * 32;
+  // warp tile of the [64 tokens x 64] product: rows [m0, m0+16), columns [n0, n0+32)
+  const int m0 = (warp & 3) * 16, n0 = (warp >> 2) * 32;
   const size_t st_off = ((size_t)n * a.H + hd) * a.K * a.V;
   if (S0) {
-    FLAB_ACC_FOREACH(MI, 8, ms, 0, row, col, mi, ni, r) {
+    FLAB_ACC_FOREACH(SMI, SNI, ms, ns, row, col, mi, ni, r) {
       if (row < a.K && col < vw) acc[mi][ni][r] = S0[st_off + (size_t)row * a.V + v0 + col];
     }
   }
@@ -71,10 +83,10 @@ __global__ void __launch_bounds__(128) delta_h_kernel(const flab_args a) {
     const int t0 = it * C, rows = min(C, s.len - t0);
 #pragma unroll
     for (int j = 0; j < NKT; ++j)
-      tile_load<T>(sKT + (buf * NKT + j) * C * LDK, LDK, kt_src[j] + (size_t)t0 * ks, ks, rows, C, a.K, KP, tid, 128);
+      tile_load<T>(sKT + (buf * NKT + j) * C * LDK, LDK, kt_src[j] + (size_t)t0 * ks, ks, rows, C, a.K, KP, tid, DTH);
 #pragma unroll
     for (int j = 0; j < NVT; ++j)
-      tile_load<T>(sVT + (buf * NVT + j) * C * LDB, LDB, vt_src[j] + (size_t)t0 * vs, vs, rows, C, vw, DBV, tid, 128);
+      tile_load<T>(sVT + (buf * NVT + j) * C * LDB, LDB, vt_src[j] + (size_t)t0 * vs, vs, rows, C, vw, DBV, tid, DTH);
     if (tid < C) sG[buf * C + tid] = (use_g && tid < rows) ? G[(size_t)(t0 + tid) * gs] : 0.f;
     cp_async_commit();
   };
@@ -83,93 +95,91 @@ __global__ void __launch_bounds__(128) delta_h_kernel(const flab_args a) {
   if (s.nt > 0) load(first, 0);
   for (int i = 0; i < s.nt; ++i) {
     const int it = first + i * step, cur = i & 1;
-    if (i + 1 < s.nt) {
-      load(it + step, cur ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+    cp_async_wait<0>();
+    __syncthreads();  // (1) tiles of this chunk have landed; every warp is done with the previous chunk
+    if (i + 1 < s.nt) load(it + step, cur ^ 1);  // prefetch into the buffer the previous chunk used
     const int t0 = it * C, rows = min(C, s.len - t0), last = rows - 1;
     T *kt = sKT + cur * NKT * C * LDK, *vt = sVT + cur * NVT * C * LDB;
     const float *gc = sG + cur * C;
     const float gl = gc[last];
-    // (a) rounded state -> shared; gate scaling of the token tiles in place
-    acc_to_smem<MI, 8, T>(acc, sS, LDB, ms, 0);
-    if (!BWD) {
-      if (use_g) {
-        T *w = kt, *k = kt + C * LDK;
-        for (int e = tid; e < C * KP; e += 128) {
-          int r_ = e / KP, c_ = e - r_ * KP;
-          w[r_ * LDK + c_] = Num<T>::t(Num<T>::f(w[r_ * LDK + c_]) * expf(gc[r_]));
-          k[r_ * LDK + c_] = Num<T>::t(Num<T>::f(k[r_ * LDK + c_]) * expf(gl - gc[r_]));
-        }
-      }
-    } else {
-      T *q = kt, *k = kt + C * LDK, *w = kt + 2 * C * LDK;
-      for (int e = tid; e < C * KP; e += 128) {
-        int r_ = e / KP, c_ = e - r_ * KP;
-        const float eg = use_g ? expf(gc[r_]) : 1.f;
-        q[r_ * LDK + c_] = Num<T>::t(Num<T>::f(q[r_ * LDK + c_]) * a.scale * eg);
-        w[r_ * LDK + c_] = Num<T>::t(-Num<T>::f(w[r_ * LDK + c_]) * eg);
-        if (use_g) k[r_ * LDK + c_] = Num<T>::t(Num<T>::f(k[r_ * LDK + c_]) * expf(gl - gc[r_]));
+    // (a) rounded state -> shared; per-token gate factors; bwd: do' = do * e^{b} * scale in place
+    acc_to_smem<SMI, SNI, T>(acc, sS, LDB, ms, ns);
+    if (tid < C) {
+      sE1[tid] = use_g ? expf(gc[tid]) : 1.f;
+      sE2[tid] = use_g ? expf(gl - gc[tid]) : 1.f;
+    }
+    if (BWD) {
+      for (int e = tid; e < C * (DBV / 2); e += DTH) {
+        const int r_ = e / (DBV / 2), c_ = (e - r_ * (DBV / 2)) * 2;
+        const float f = (use_g ? expf(gc[r_]) : 1.f) * a.scale;
+        T *p = vt + r_ * LDB + c_;
+        st_pair<T>(p, Num<T>::f(p[0]) * f, Num<T>::f(p[1]) * f);
       }
     }
-    __syncthreads();
-    // (b) state at the chunk boundary -> global
+    __syncthreads();  // (2)
+    // (b) state at the chunk boundary -> global (coalesced, off the critical path)
     {
       const size_t hoff = ((size_t)(s.c0 + it) * a.H + hd) * a.K * a.V + v0;
-      tile_store<T>(Hout + hoff, (size_t)a.V, sS, LDB, a.K, vw, tid, 128);
+      tile_store<T>(Hout + hoff, (size_t)a.V, sS, LDB, a.K, vw, tid, DTH);
     }
-    // (c) the dependent product against the rounded state
+    // (c) the dependent product against the rounded state, gate applied to its rows
     {
-      float p[1][8][4];
+      float p[1][4][4];
       acc_zero(p);
-      const T *A = BWD ? kt + C * LDK : kt;  // bwd: k~ ; fwd: w~
-      WarpGemm<1, 8, false, true, T>::run(p, A, LDK, m0, sS, LDB, 0, KP);
-      T *y = BWD ? vt + C * LDB : vt;  // bwd: dv ; fwd: u   (updated in place)
-      FLAB_ACC_FOREACH(1, 8, m0, 0, row, col, mi, ni, r) {
-        float base = Num<T>::f(y[row * LDB + col]);
-        p[mi][ni][r] = BWD ? base + p[mi][ni][r] : base - p[mi][ni][r];
+      const T *A = BWD ? kt + C * LDK : kt;  // bwd: k ; fwd: w
+      WarpGemm<1, 4, false, true, T>::run(p, A, LDK, m0, sS, LDB, n0, KP);
+      T *y = BWD ? vt + C * LDB : vt;  // bwd: dv ; fwd: u   (replaced in place by dv2 / v_new)
+      float op[1][4][4];
+      FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
+        const float base = Num<T>::f(y[row * LDB + col]);
+        float x;
+        if (!BWD) {
+          x = rnd<T>(base - sE1[row] * p[mi][ni][r]);  // v_new
+          op[mi][ni][r] = x * sE2[row];                // e^{b_L-b} v_new
+        } else {
+          x = rnd<T>(base + sE2[row] * p[mi][ni][r]);  // dv2
+          op[mi][ni][r] = -x * sE1[row];               // -e^{b} dv2
+        }
+        p[mi][ni][r] = x;
       }
-      acc_to_smem<1, 8, T>(p, y, LDB, m0, 0);
+      acc_to_smem<1, 4, T>(p, y, LDB, m0, n0);
+      acc_to_smem<1, 4, T>(op, sOp, LDB, m0, n0);
     }
-    __syncthreads();
+    __syncthreads();  // (3)
     // (d) v_new / dv2 -> global
-    tile_store<T>(Vout + (size_t)t0 * vs, vs, BWD ? vt + C * LDB : vt, LDB, rows, vw, tid, 128);
+    tile_store<T>(Vout + (size_t)t0 * vs, vs, BWD ? vt + C * LDB : vt, LDB, rows, vw, tid, DTH);
     // (e) state update
     if (use_g) {
       const float d = expf(gl);
 #pragma unroll
-      for (int mi = 0; mi < MI; ++mi)
+      for (int mi = 0; mi < SMI; ++mi)
 #pragma unroll
-        for (int ni = 0; ni < 8; ++ni)
+        for (int ni = 0; ni < SNI; ++ni)
 #pragma unroll
           for (int r = 0; r < 4; ++r) acc[mi][ni][r] *= d;
     }
     if (!BWD) {
-      WarpGemm<MI, 8, true, true, T>::run(acc, kt + C * LDK, LDK, ms, vt, LDB, 0, C);
+      WarpGemm<SMI, SNI, true, true, T>::run(acc, kt + C * LDK, LDK, ms, sOp, LDB, ns, C);  // k^T (e^{b_L-b} v_new)
     } else {
-      WarpGemm<MI, 8, true, true, T>::run(acc, kt, LDK, ms, vt, LDB, 0, C);                          // q~^T do
-      WarpGemm<MI, 8, true, true, T>::run(acc, kt + 2 * C * LDK, LDK, ms, vt + C * LDB, LDB, 0, C);  // -(w~)^T dv2
+      WarpGemm<SMI, SNI, true, true, T>::run(acc, kt, LDK, ms, vt, LDB, ns, C);                 // q^T (scale e^{b} do)
+      WarpGemm<SMI, SNI, true, true, T>::run(acc, kt + 2 * C * LDK, LDK, ms, sOp, LDB, ns, C);  // w^T (-e^{b} dv2)
     }
-    __syncthreads();
   }
   if (S1) {
-    FLAB_ACC_FOREACH(MI, 8, ms, 0, row, col, mi, ni, r) {
+    FLAB_ACC_FOREACH(SMI, SNI, ms, ns, row, col, mi, ni, r) {
       if (row < a.K && col < vw) S1[st_off + (size_t)row * a.V + v0 + col] = acc[mi][ni][r];
     }
   }
-  (void)g8;
 }
 
 template <typename T, int KP, bool BWD> static int launch_delta_h(const flab_args *a, cudaStream_t stream) {
   constexpr int LDK = KP + Num<T>::pad, LDB = DBV + Num<T>::pad;
   constexpr int NKT = BWD ? 3 : 2, NVT = BWD ? 2 : 1;
-  size_t smem = ((size_t)2 * NKT * C * LDK + (size_t)2 * NVT * C * LDB + (size_t)KP * LDB) * sizeof(T) + 2 * C * sizeof(float);
+  size_t smem = ((size_t)2 * NKT * C * LDK + (size_t)2 * NVT * C * LDB + (size_t)KP * LDB + (size_t)C * LDB) * sizeof(T) +
+                4 * C * sizeof(float);
   auto kern = delta_h_kernel<T, KP, BWD>;
   if (int e = set_smem(kern, smem)) return e;
-  kern<<<dim3(cdiv(a->V, DBV), a->N * a->H), 128, smem, stream>>>(*a);
+  kern<<<dim3(cdiv(a->V, DBV), a->N * a->H), DTH, smem, stream>>>(*a);
   return check_launch(BWD ? "delta_bwd_dhu" : "delta_fwd_h");
 }
 

@@ -14,26 +14,82 @@ namespace flab {
 constexpr int WT = 128;  // column tile of k / v
 constexpr int LDL = C + 1;
 
-// forward substitution: Linv = strict lower part of (I + L)^-1 given Lo = -strict_lower(Gram).
-// `nmat` matrices are processed side by side by thread groups of 64.
-__device__ __forceinline__ void tri_inverse(const float *Lo, float *Li, int nmat, int tid) {
-  const int mat = tid >> 6, j = tid & 63;
-  const bool act = mat < nmat;
-  const float *lo = Lo + mat * C * LDL;
-  float *li = Li + mat * C * LDL;
-  if (act) li[j] = 0.f;  // row 0
+// Inverse of the unit lower-triangular M = I - N for `nmat` 64x64 matrices held side by side in
+// shared memory (N = Lo, the negated strict lower part of the Gram matrix).  Result X = M^-1
+// (with its unit diagonal) is written to Xo.  Blocked scheme:
+//   1. the four 16x16 diagonal blocks: forward substitution in registers, one half-warp per block
+//      (lane = column, coefficients broadcast with shuffles);
+//   2. 32x32 level:  X21 = X22 N21 X11 for both 32-blocks;
+//   3. 64x64 level:  X_BA = X_BB N_BA X_AA.
+// Levels 2 and 3 are small fp32 FFMA tile products (true fp32, like the reference's tl.dot with
+// allow_tf32=False).  Scr is scratch of nmat * 32 * 33 floats.  All 128 threads must call this.
+__device__ __forceinline__ void tri_inverse(const float *Lo, float *Xo, float *Scr, int nmat, int tid) {
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int e = tid; e < nmat * C * LDL; e += 128) Xo[e] = 0.f;
   __syncthreads();
-  for (int i = 1; i < C; ++i) {
-    if (act) {
-      float acc = 0.f;
-      if (j < i) {
-        acc = lo[i * LDL + j];
-        for (int m = j + 1; m < i; ++m) acc = fmaf(lo[i * LDL + m], li[m * LDL + j], acc);
-      }
-      li[i * LDL + j] = acc;
+  // ---- level 0: 16x16 diagonal blocks; warp w -> diagonal block w, half-warp -> matrix
+  {
+    const int half = lane >> 4, j = lane & 15, mat = half < nmat ? half : 0;
+    const float *n = Lo + mat * C * LDL + (16 * warp) * LDL + 16 * warp;
+    float nc[16], x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) nc[i] = n[i * LDL + j];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float acc = nc[i];
+#pragma unroll
+      for (int m = 0; m < i; ++m) acc = fmaf(__shfl_sync(0xffffffffu, nc[i], (lane & 16) + m), x[m], acc);
+      x[i] = (j < i) ? acc : 0.f;
+    }
+    if (half < nmat) {
+      float *xo = Xo + mat * C * LDL + (16 * warp) * LDL + 16 * warp;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) xo[i * LDL + j] = x[i] + (i == j ? 1.f : 0.f);
+    }
+  }
+  __syncthreads();
+  // ---- level 1: warp -> (matrix, 32-block); X21 = X22 (N21 X11)
+  {
+    const int mat = warp >> 1, blk = warp & 1;
+    if (mat < nmat) {
+      const int o = 32 * blk;
+      const float *N21 = Lo + mat * C * LDL + (o + 16) * LDL + o;
+      float *X = Xo + mat * C * LDL;
+      float *scr = Scr + warp * 16 * 17;
+      float t1[1][2][4];
+      acc_zero(t1);
+      WarpGemm<1, 2, false, true, float>::run(t1, N21, LDL, 0, X + o * LDL + o, LDL, 0, 16);
+      FLAB_ACC_FOREACH(1, 2, 0, 0, row, col, mi, ni, r) { scr[row * 17 + col] = t1[mi][ni][r]; }
+      __syncwarp();
+      float t2[1][2][4];
+      acc_zero(t2);
+      WarpGemm<1, 2, false, true, float>::run(t2, X + (o + 16) * LDL + o + 16, LDL, 0, scr, 17, 0, 16);
+      __syncwarp();
+      FLAB_ACC_FOREACH(1, 2, 0, 0, row, col, mi, ni, r) { X[(o + 16 + row) * LDL + o + col] = t2[mi][ni][r]; }
+    }
+  }
+  __syncthreads();
+  // ---- level 2: X_BA = X_BB (N_BA X_AA); warp -> 16x16 tile of the 32x32 result, per matrix
+  {
+    const int m0 = 16 * (warp & 1), n0 = 16 * (warp >> 1);
+    for (int mat = 0; mat < nmat; ++mat) {
+      const float *N = Lo + mat * C * LDL + 32 * LDL;  // rows 32.., cols 0..
+      const float *X = Xo + mat * C * LDL;
+      float t1[1][2][4];
+      acc_zero(t1);
+      WarpGemm<1, 2, false, true, float>::run(t1, N, LDL, m0, X, LDL, n0, 32);
+      FLAB_ACC_FOREACH(1, 2, m0, n0, row, col, mi, ni, r) { Scr[mat * 32 * 33 + row * 33 + col] = t1[mi][ni][r]; }
     }
     __syncthreads();
+    for (int mat = 0; mat < nmat; ++mat) {
+      float *X = Xo + mat * C * LDL;
+      float t2[1][2][4];
+      acc_zero(t2);
+      WarpGemm<1, 2, false, true, float>::run(t2, X + 32 * LDL + 32, LDL, m0, Scr + mat * 32 * 33, 33, n0, 32);
+      FLAB_ACC_FOREACH(1, 2, m0, n0, row, col, mi, ni, r) { X[(32 + row) * LDL + col] = t2[mi][ni][r]; }
+    }
   }
+  __syncthreads();
 }
 
 template <typename T, bool GATED, bool RECOMPUTE>
@@ -45,10 +101,13 @@ __global__ void __launch_bounds__(128) wy_fwd_kernel(const flab_args a) {
   T *sX = reinterpret_cast<T *>(smem_raw);  // [64][LDX] k or v tile; reused to stage w / u
   T *sXB = sX + C * LDX;                    // [64][LDX] beta-scaled tile
   T *sA = sXB + C * LDX;                    // [NM][64][LDP] Aw, Au as T
-  float *sLo = reinterpret_cast<float *>(sA + NM * C * LDP);  // [NM][64][LDL]
-  float *sLi = sLo + NM * C * LDL;                            // [NM][64][LDL]
-  float *sBeta = sLi + NM * C * LDL;                          // [64]
-  float *sG = sBeta + C;                                      // [64]
+  float *sBeta = reinterpret_cast<float *>(sA + NM * C * LDP);  // [64]
+  float *sG = sBeta + C;                                        // [64]
+  float *sLi = sG + C;                                          // [NM][64][LDL] inverse (not for RECOMPUTE)
+  float *sScr = sLi + NM * C * LDL;                             // [NM][32][33] scratch of the inverse
+  // the negated Gram matrices live in the (by then idle) k tile buffers while they are inverted
+  float *sLo = reinterpret_cast<float *>(smem_raw);             // [NM][64][LDL]
+  static_assert(2 * C * LDX * sizeof(T) >= (size_t)NM * C * LDL * sizeof(float), "Gram alias does not fit");
 
   const int tid = threadIdx.x, warp = tid >> 5;
   int n, it;
@@ -84,17 +143,17 @@ __global__ void __launch_bounds__(128) wy_fwd_kernel(const flab_args a) {
       __syncthreads();
       WarpGemm<1, 8, false, false, T>::run(gram, sXB, LDX, m0, sX, LDX, 0, kp);
     }
+    __syncthreads();  // every warp is done reading the k tiles before the Gram matrices overwrite them
     FLAB_ACC_FOREACH(1, 8, m0, 0, row, col, mi, ni, r) {
       float x = row > col ? -gram[mi][ni][r] : 0.f;
       sLo[row * LDL + col] = x;
       if (GATED) sLo[C * LDL + row * LDL + col] = row > col ? x * safe_exp(sG[row] - sG[col]) : 0.f;
     }
     __syncthreads();
-    tri_inverse(sLo, sLi, NM, tid);
+    tri_inverse(sLo, sLi, sScr, NM, tid);
     for (int e = tid; e < NM * C * C; e += 128) {
       int m = e / (C * C), r_ = (e / C) % C, c_ = e % C;
-      float x = sLi[m * C * LDL + r_ * LDL + c_] + (r_ == c_ ? 1.f : 0.f);
-      sA[m * C * LDP + r_ * LDP + c_] = Num<T>::t(x);
+      sA[m * C * LDP + r_ * LDP + c_] = Num<T>::t(sLi[m * C * LDL + r_ * LDL + c_]);
     }
     __syncthreads();
     tile_store<T>(reinterpret_cast<T *>(a.aw) + offa, as_, sA, LDP, rows, C, tid, 128);
@@ -333,7 +392,8 @@ __global__ void __launch_bounds__(128) wy_bwd_kernel(const flab_args a) {
 
 template <typename T, bool GATED, bool RECOMPUTE> static int launch_wy_fwd(const flab_args *a, cudaStream_t stream) {
   constexpr int LDX = WT + Num<T>::pad, LDP = C + Num<T>::pad, NM = GATED ? 2 : 1;
-  size_t smem = ((size_t)2 * C * LDX + (size_t)NM * C * LDP) * sizeof(T) + ((size_t)2 * NM * C * LDL + 2 * C) * sizeof(float);
+  size_t smem = ((size_t)2 * C * LDX + (size_t)NM * C * LDP) * sizeof(T) + 2 * C * sizeof(float);
+  if (!RECOMPUTE) smem += ((size_t)NM * C * LDL + (size_t)NM * 32 * 33) * sizeof(float);
   auto kern = wy_fwd_kernel<T, GATED, RECOMPUTE>;
   if (int e = set_smem(kern, smem)) return e;
   kern<<<dim3(a->NT, a->H), 128, smem, stream>>>(*a);

@@ -6,7 +6,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from ..utils import Geometry, autocast_custom_bwd, autocast_custom_fwd, contiguous, resolve_offsets
+from ..utils import SAVE_STATES, Geometry, autocast_custom_bwd, autocast_custom_fwd, contiguous, resolve_offsets
 from . import common as C
 from .recurrent import FusedRecurrentDeltaRuleFunction
 from .simple_gla import check_varlen_args
@@ -16,13 +16,17 @@ def chunk_delta_rule_fwd(geo, q, k, v, beta, scale, initial_state, output_final_
     aw, _, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta)
     h, v_new, ht = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, h0=initial_state, output_final_state=output_final_state)
     o = C.chunk_fwd_o(geo, q, k, v_new, h, scale=scale)
-    return o, aw, ht
+    return o, aw, ht, (w, h, v_new)
 
 
-def chunk_delta_rule_bwd(geo, q, k, v, beta, aw, scale, initial_state, do, dht):
-    """Same stage order as fla/ops/delta_rule/chunk.py:70-163."""
-    w, u = C.fwd_recompute_w_u(geo, k, v, beta, aw)
-    h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, h0=initial_state, output_final_state=False)
+def chunk_delta_rule_bwd(geo, q, k, v, beta, aw, scale, initial_state, do, dht, saved=None):
+    """Same stage order as fla/ops/delta_rule/chunk.py:70-163. `saved` = (w, h, v_new) kept from
+    forward; None recomputes them like the reference."""
+    if saved is not None:
+        w, h, v_new = saved
+    else:
+        w, u = C.fwd_recompute_w_u(geo, k, v, beta, aw)
+        h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, h0=initial_state, output_final_state=False)
     dv = C.chunk_bwd_dv_local(geo, q, k, None, do, scale)
     dh, dh0, dv = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, dht=dht,
                                                    want_dh0=initial_state is not None)
@@ -40,8 +44,8 @@ class ChunkDeltaRuleFunction(torch.autograd.Function):
     def forward(ctx, q, k, v, beta, scale, initial_state, output_final_state, offsets, head_first):
         geo = Geometry(k, v, offsets, head_first)
         beta_k = beta.to(k.dtype)
-        o, aw, ht = chunk_delta_rule_fwd(geo, q, k, v, beta_k, scale, initial_state, output_final_state)
-        ctx.save_for_backward(q, k, v, beta_k, aw, initial_state)
+        o, aw, ht, states = chunk_delta_rule_fwd(geo, q, k, v, beta_k, scale, initial_state, output_final_state)
+        ctx.save_for_backward(q, k, v, beta_k, aw, initial_state, *(states if SAVE_STATES else ()))
         ctx.geo, ctx.scale, ctx.beta_dtype = geo, scale, beta.dtype
         return o.to(q.dtype), ht
 
@@ -49,8 +53,9 @@ class ChunkDeltaRuleFunction(torch.autograd.Function):
     @contiguous
     @autocast_custom_bwd
     def backward(ctx, do, dht):
-        q, k, v, beta, aw, initial_state = ctx.saved_tensors
-        dq, dk, dv, db, dh0 = chunk_delta_rule_bwd(ctx.geo, q, k, v, beta, aw, ctx.scale, initial_state, do, dht)
+        q, k, v, beta, aw, initial_state, *states = ctx.saved_tensors
+        dq, dk, dv, db, dh0 = chunk_delta_rule_bwd(ctx.geo, q, k, v, beta, aw, ctx.scale, initial_state, do, dht,
+                                                   saved=states or None)
         return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), db.to(ctx.beta_dtype), None, dh0, None, None, None
 
 

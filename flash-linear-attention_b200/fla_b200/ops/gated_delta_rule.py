@@ -7,7 +7,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from ..utils import Geometry, autocast_custom_bwd, autocast_custom_fwd, contiguous, resolve_offsets
+from ..utils import SAVE_STATES, Geometry, autocast_custom_bwd, autocast_custom_fwd, contiguous, resolve_offsets
 from . import common as C
 from .recurrent import FusedRecurrentGatedDeltaRuleFunction
 from .simple_gla import check_varlen_args
@@ -20,13 +20,17 @@ def chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta, scale, initial_state, outp
     h, v_new, ht = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=initial_state,
                                                   output_final_state=output_final_state)
     o = C.chunk_fwd_o(geo, q, k, v_new, h, g=g, scale=scale)
-    return g, o, aw, au, ht
+    return g, o, aw, au, ht, (w, h, v_new)
 
 
-def chunk_gated_delta_rule_bwd(geo, q, k, v, g, beta, aw, au, scale, initial_state, do, dht):
-    """Stage order of fla/ops/gated_delta_rule/chunk.py:76-177; `g` is the chunk-local cumsum."""
-    w, u = C.fwd_recompute_w_u(geo, k, v, beta, aw, au)
-    h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=initial_state, output_final_state=False)
+def chunk_gated_delta_rule_bwd(geo, q, k, v, g, beta, aw, au, scale, initial_state, do, dht, saved=None):
+    """Stage order of fla/ops/gated_delta_rule/chunk.py:76-177; `g` is the chunk-local cumsum.
+    `saved` = (w, h, v_new) kept from forward; None recomputes them like the reference."""
+    if saved is not None:
+        w, h, v_new = saved
+    else:
+        w, u = C.fwd_recompute_w_u(geo, k, v, beta, aw, au)
+        h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=initial_state, output_final_state=False)
     dv = C.chunk_bwd_dv_local(geo, q, k, g, do, scale)
     dh, dh0, dv = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g, dht=dht,
                                                    want_dh0=initial_state is not None)
@@ -46,9 +50,10 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, offsets, head_first):
         geo = Geometry(k, v, offsets, head_first)
         beta_k = beta.to(k.dtype)
-        g_cum, o, aw, au, ht = chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta_k, scale, initial_state,
-                                                          output_final_state)
-        ctx.save_for_backward(q, k, v, g_cum, beta_k, aw, au, initial_state)
+        g_cum, o, aw, au, ht, states = chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta_k, scale, initial_state,
+                                                                  output_final_state)
+        ctx.n_saved_states = len(states) if SAVE_STATES else 0
+        ctx.save_for_backward(q, k, v, g_cum, beta_k, aw, au, initial_state, *(states if SAVE_STATES else ()))
         ctx.geo, ctx.scale, ctx.g_dtype, ctx.beta_dtype = geo, scale, g.dtype, beta.dtype
         return o.to(q.dtype), ht
 
@@ -56,9 +61,9 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @contiguous
     @autocast_custom_bwd
     def backward(ctx, do, dht):
-        q, k, v, g_cum, beta, aw, au, initial_state = ctx.saved_tensors
+        q, k, v, g_cum, beta, aw, au, initial_state, *states = ctx.saved_tensors
         dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(ctx.geo, q, k, v, g_cum, beta, aw, au, ctx.scale,
-                                                            initial_state, do, dht)
+                                                            initial_state, do, dht, saved=states or None)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(ctx.g_dtype), db.to(ctx.beta_dtype),
                 None, dh0, None, None, None)
 

@@ -7,7 +7,7 @@ from typing import Optional, Tuple
 import torch
 
 from .. import _lib
-from ..utils import Geometry, contiguous, resolve_offsets
+from ..utils import SAVE_STATES, Geometry, contiguous, resolve_offsets
 from . import common as C
 from .recurrent import fused_recurrent
 from .simple_gla import check_varlen_args
@@ -35,9 +35,10 @@ def chunk_gla_fwd(geo, q, k, v, g, scale, initial_state, output_final_state):
     return g_cum, a, h, ht, o
 
 
-def chunk_gla_bwd(geo, q, k, v, g_cum, scale, initial_state, a, do, dht):
+def chunk_gla_bwd(geo, q, k, v, g_cum, scale, initial_state, a, do, dht, h=None):
     """Stage order of fla/ops/gla/chunk.py:1217-1320; the returned dg is w.r.t. the raw gate."""
-    h, _ = C.chunk_fwd_h(geo, k, v, gk=g_cum, h0=initial_state, output_final_state=False)
+    if h is None:
+        h, _ = C.chunk_fwd_h(geo, k, v, gk=g_cum, h0=initial_state, output_final_state=False)
     dh, dh0 = C.chunk_bwd_dh(geo, q, do, scale, gk=g_cum, dht=dht, want_dh0=initial_state is not None)
     da = torch.empty_like(a)
     dv = torch.empty_like(v)
@@ -56,16 +57,17 @@ class ChunkGLAFunction(torch.autograd.Function):
     @contiguous
     def forward(ctx, q, k, v, g, scale, initial_state, output_final_state, offsets, head_first):
         geo = Geometry(k, v, offsets, head_first)
-        g_cum, a, _, ht, o = chunk_gla_fwd(geo, q, k, v, g, scale, initial_state, output_final_state)
-        ctx.save_for_backward(q, k, v, g_cum, initial_state, a)
+        g_cum, a, h, ht, o = chunk_gla_fwd(geo, q, k, v, g, scale, initial_state, output_final_state)
+        ctx.save_for_backward(q, k, v, g_cum, initial_state, a, *((h,) if SAVE_STATES else ()))
         ctx.geo, ctx.scale, ctx.g_dtype = geo, scale, g.dtype
         return o, ht
 
     @staticmethod
     @contiguous
     def backward(ctx, do, dht):
-        q, k, v, g_cum, initial_state, a = ctx.saved_tensors
-        dq, dk, dv, dg, dh0 = chunk_gla_bwd(ctx.geo, q, k, v, g_cum, ctx.scale, initial_state, a, do, dht)
+        q, k, v, g_cum, initial_state, a, *states = ctx.saved_tensors
+        dq, dk, dv, dg, dh0 = chunk_gla_bwd(ctx.geo, q, k, v, g_cum, ctx.scale, initial_state, a, do, dht,
+                                            h=states[0] if states else None)
         return dq.to(q), dk.to(k), dv.to(v), dg.to(ctx.g_dtype), None, dh0, None, None, None
 
 

@@ -7,7 +7,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from ..utils import Geometry, autocast_custom_bwd, autocast_custom_fwd, contiguous, resolve_offsets
+from ..utils import SAVE_STATES, Geometry, autocast_custom_bwd, autocast_custom_fwd, contiguous, resolve_offsets
 from . import common as C
 from .recurrent import fused_recurrent
 
@@ -16,11 +16,12 @@ def chunk_simple_gla_fwd(geo, q, k, v, g, scale, initial_state, output_final_sta
     g_cum = C.chunk_local_cumsum(g, offsets=_off(geo), head_first=geo.head_first) if g is not None else None
     h, ht = C.chunk_fwd_h(geo, k, v, g=g_cum, h0=initial_state, output_final_state=output_final_state)
     o = C.chunk_fwd_o(geo, q, k, v, h, g=g_cum, scale=scale)
-    return g_cum, o, ht
+    return g_cum, o, ht, h
 
 
-def chunk_simple_gla_bwd(geo, q, k, v, g_cum, initial_state, do, dht, scale):
-    h, _ = C.chunk_fwd_h(geo, k, v, g=g_cum, h0=initial_state, output_final_state=False)
+def chunk_simple_gla_bwd(geo, q, k, v, g_cum, initial_state, do, dht, scale, h=None):
+    if h is None:  # recompute the chunk states like the reference (fla/ops/simple_gla/chunk.py:73-86)
+        h, _ = C.chunk_fwd_h(geo, k, v, g=g_cum, h0=initial_state, output_final_state=False)
     dh, dh0 = C.chunk_bwd_dh(geo, q, do, scale, g=g_cum, dht=dht, want_dh0=initial_state is not None)
     dq, dk, _, dg = C.chunk_bwd_dqkwg(geo, q, k, v, h, dh, do, scale, g=g_cum)
     dv = C.chunk_bwd_dv(geo, q, k, g_cum, do, dh, scale)
@@ -39,8 +40,8 @@ class ChunkSimpleGLAFunction(torch.autograd.Function):
     def forward(ctx, q, k, v, g, scale, initial_state, output_final_state, offsets, head_first):
         geo = Geometry(k, v, offsets, head_first)
         geo.offsets_tensor = offsets
-        g_cum, o, ht = chunk_simple_gla_fwd(geo, q, k, v, g, scale, initial_state, output_final_state)
-        ctx.save_for_backward(q, k, v, g_cum, initial_state)
+        g_cum, o, ht, h = chunk_simple_gla_fwd(geo, q, k, v, g, scale, initial_state, output_final_state)
+        ctx.save_for_backward(q, k, v, g_cum, initial_state, *((h,) if SAVE_STATES else ()))
         ctx.geo, ctx.scale = geo, scale
         ctx.g_dtype = g.dtype if g is not None else None
         return o.to(q.dtype), ht
@@ -49,9 +50,10 @@ class ChunkSimpleGLAFunction(torch.autograd.Function):
     @contiguous
     @autocast_custom_bwd
     def backward(ctx, do, dht):
-        q, k, v, g_cum, initial_state = ctx.saved_tensors
+        q, k, v, g_cum, initial_state, *states = ctx.saved_tensors
         geo = ctx.geo
-        dq, dk, dv, dg, dh0 = chunk_simple_gla_bwd(geo, q, k, v, g_cum, initial_state, do, dht, ctx.scale)
+        dq, dk, dv, dg, dh0 = chunk_simple_gla_bwd(geo, q, k, v, g_cum, initial_state, do, dht, ctx.scale,
+                                                   h=states[0] if states else None)
         if g_cum is not None:
             dg = C.chunk_local_cumsum(dg, reverse=True, offsets=geo.offsets_tensor,
                                       head_first=geo.head_first).to(ctx.g_dtype)

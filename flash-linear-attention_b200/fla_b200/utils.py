@@ -4,6 +4,7 @@ tables (the integer index data of this path) and the autograd decorators the ref
 (fla/utils.py:10-21 `contiguous`, :88-93 autocast wrappers)."""
 
 import functools
+import os
 import weakref
 from collections import namedtuple
 from typing import Optional
@@ -11,6 +12,11 @@ from typing import Optional
 import torch
 
 from ._lib import CHUNK
+
+# Keep the chunk states (and the WY factors) computed in forward for backward instead of recomputing
+# them as the reference does: costs ~4 extra [B,T,H,D] activations, saves two kernel launches and a
+# full serial state scan in backward.  FLA_B200_SAVE_STATES=0 restores the recomputing behaviour.
+SAVE_STATES = os.environ.get("FLA_B200_SAVE_STATES", "1") != "0"
 
 Varlen = namedtuple("Varlen", ["cu_seqlens", "chunk_indices", "chunk_offsets", "N", "NT", "lengths"])
 
