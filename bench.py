@@ -236,8 +236,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gdn", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip e2e / roofline / cpu_baseline legs")
+    ap.add_argument("--seq-len", type=int, default=0, help="override T (small cases for profiler captures)")
     args = ap.parse_args()
     op, B, T, H, K, V = WORKLOADS[args.workload]
+    T = args.seq_len or T
     dtype = torch.float32 if args.workload == "gla_fp32" else torch.bfloat16
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
