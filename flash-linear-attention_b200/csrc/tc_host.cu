@@ -1,0 +1,47 @@
+// Host-side TMA tensor-map construction.  cuTensorMapEncodeTiled is fetched through the runtime's
+// driver entry point query, so the library has no link-time dependency on libcuda and still loads on
+// a machine without a driver (where only the CPU-side tests run).
+#include "tc.cuh"
+
+namespace flab {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// rank <= 4; dims[0] is the contiguous extent; strides_bytes[i] is the stride of dims[i+1].
+// 128-byte swizzle, zero fill outside the tensor.
+int make_tensor_map_bf16(CUtensorMap *map, const void *base, int rank, const uint64_t *dims, const uint64_t *strides_bytes,
+                         const uint32_t *box, int elem_fp16) {
+  EncodeTiledFn fn = encode_fn();
+  FLAB_REQUIRE(fn != nullptr, FLAB_E_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[4];
+  cuuint64_t gstr[4];
+  cuuint32_t bx[4], es[4];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) gstr[i] = strides_bytes[i];
+  }
+  CUresult r = fn(map, elem_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
+                  const_cast<void *>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FLAB_REQUIRE(r == CUDA_SUCCESS, FLAB_E_BADARG, "cuTensorMapEncodeTiled failed with code %d (base %p must be 16-byte aligned, strides multiples of 16)",
+               (int)r, base);
+  return 0;
+}
+
+}  // namespace flab

@@ -172,6 +172,14 @@ int flab_recurrent_delta_fwd(const flab_args *a, void *stream);
  * v, beta, h0, d_o, dht; writes dq, dk, dv (fp32), dbeta (fp32), dh0. */
 int flab_recurrent_delta_bwd(const flab_args *a, void *stream);
 
+/* ---- diagnostics -----------------------------------------------------------------------------
+ * No counterpart in the reference. Runs four small bf16 products through the TMA + tcgen05 + TMEM
+ * path (every shared-memory operand form the kernels use) and writes them to `out`
+ * (fp32: [64x64] A B^T, [64x128] A H, [128x64] A^T V, [64x64] bf16(A B^T) V) for the caller to compare
+ * with a plain matmul. a, b: [64x128], h: [128x128], v: [64x64], row-major bf16. *status = 0 on
+ * success, else the index of the bounded wait that ran out. */
+int flab_tc_selftest(const void *a, const void *b, const void *h, const void *v, float *out, int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
