@@ -5,6 +5,8 @@
 //   dqkwg    : dq, dk, dw, dg                                                     (fla/ops/common/chunk_o.py:118-273)
 // One CTA per (chunk, head).  All operands of a chunk are staged in shared memory once; the 64x64
 // score tile is rounded to the element type in shared memory between its two contractions.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace flab {
@@ -348,6 +350,17 @@ template <typename T, bool USE_DW> static int launch_dqkwg(const flab_args *a, c
   return check_launch("chunk_bwd_dqkwg");
 }
 
+// tcgen05 / TMA kernels for the shapes they cover (tc_chunk_o.cu); 1 = handled, 0 = not applicable
+template <int MODE> int tc_chunk_o_try(const flab_args *a, cudaStream_t stream, const char *name);
+static bool tc_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("FLA_B200_NO_TC");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 }  // namespace flab
 
 extern "C" {
@@ -357,6 +370,10 @@ int flab_chunk_fwd_o(const flab_args *a, void *stream) {
   if (int e = check_common(a)) return e;
   FLAB_REQUIRE(a->q && a->k && a->v && a->h && a->o, FLAB_E_BADARG, "chunk_fwd_o needs q, k, v, h and o");
   FLAB_REQUIRE(a->K <= 256, FLAB_E_UNSUPPORTED, "chunk_fwd_o: K = %d > 256", a->K);
+  if (tc_enabled()) {
+    int r = tc_chunk_o_try<MODE_O>(a, (cudaStream_t)stream, "chunk_fwd_o(tc)");
+    if (r != 0) return r < 0 ? r : FLAB_OK;
+  }
   FLAB_DISPATCH_ALL(a->dtype, T, return (launch_chunk_o<T, MODE_O>(a, (cudaStream_t)stream, "chunk_fwd_o")));
   return FLAB_OK;
 }
@@ -366,6 +383,10 @@ int flab_chunk_bwd_dv(const flab_args *a, void *stream) {
   if (int e = check_common(a)) return e;
   FLAB_REQUIRE(a->q && a->k && a->d_o && a->dh && a->dv, FLAB_E_BADARG, "chunk_bwd_dv needs q, k, d_o, dh and dv");
   FLAB_REQUIRE(a->K <= 256, FLAB_E_UNSUPPORTED, "chunk_bwd_dv: K = %d > 256", a->K);
+  if (tc_enabled()) {
+    int r = tc_chunk_o_try<MODE_DV>(a, (cudaStream_t)stream, "chunk_bwd_dv(tc)");
+    if (r != 0) return r < 0 ? r : FLAB_OK;
+  }
   FLAB_DISPATCH_ALL(a->dtype, T, return (launch_chunk_o<T, MODE_DV>(a, (cudaStream_t)stream, "chunk_bwd_dv")));
   return FLAB_OK;
 }
@@ -375,6 +396,10 @@ int flab_chunk_bwd_dv_local(const flab_args *a, void *stream) {
   if (int e = check_common(a)) return e;
   FLAB_REQUIRE(a->q && a->k && a->d_o && a->dv, FLAB_E_BADARG, "chunk_bwd_dv_local needs q, k, d_o and dv");
   FLAB_REQUIRE(a->K <= 256, FLAB_E_UNSUPPORTED, "chunk_bwd_dv_local: K = %d > 256", a->K);
+  if (tc_enabled()) {
+    int r = tc_chunk_o_try<MODE_DV_LOCAL>(a, (cudaStream_t)stream, "chunk_bwd_dv_local(tc)");
+    if (r != 0) return r < 0 ? r : FLAB_OK;
+  }
   FLAB_DISPATCH_ALL(a->dtype, T, return (launch_chunk_o<T, MODE_DV_LOCAL>(a, (cudaStream_t)stream, "chunk_bwd_dv_local")));
   return FLAB_OK;
 }

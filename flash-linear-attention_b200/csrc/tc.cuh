@@ -68,6 +68,12 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, u
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -140,15 +146,28 @@ __device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, float (&r)[32
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, float (&r)[16]) {
+  uint32_t *u = reinterpret_cast<uint32_t *>(r);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+        "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Load a [16 x 8*NI] block (NI multiple of 8) into acc[NI][4]; taddr = lane/column of its corner.
+// Load a [16 x 8*NI] block (NI multiple of 4) into acc[NI][4]; taddr = lane/column of its corner.
 template <int NI> __device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, float (&acc)[NI][4]) {
-  static_assert(NI % 8 == 0, "NI must be a multiple of 8");
+  static_assert(NI % 4 == 0, "NI must be a multiple of 4");
 #pragma unroll
   for (int j = 0; j < NI / 8; ++j) {
     float(&blk)[32] = *reinterpret_cast<float(*)[32]>(&acc[8 * j][0]);
     tmem_ld_16x256b_x8(taddr + 64u * j, blk);
+  }
+  if (NI % 8 != 0) {
+    float(&blk)[16] = *reinterpret_cast<float(*)[16]>(&acc[NI - 4][0]);
+    tmem_ld_16x256b_x4(taddr + 8u * (NI - 4), blk);
   }
 }
 
@@ -158,7 +177,34 @@ __device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
   return (uint32_t)row * 128u + ((((uint32_t)col >> 3) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)col & 7u) << 1);
 }
 
+// barrier among a subset of the CTA's warps (id 1..15, nthreads multiple of 32)
+__device__ __forceinline__ void named_barrier(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Each translation unit with tcgen05 kernels defines its own device error word with this macro; a
+// kernel whose bounded wait ran out stores an id of the wait there, and flab_tc_error_state() reads
+// every unit's word through the generated host getter.
+#define FLAB_TC_DEFINE_ERROR_WORD(getter)                                            \
+  namespace {                                                                        \
+  __device__ int tu_tc_error = 0;                                                    \
+  }                                                                                  \
+  namespace flab {                                                                   \
+  int getter() {                                                                     \
+    int v = 0;                                                                       \
+    if (cudaMemcpyFromSymbol(&v, tu_tc_error, sizeof(int)) != cudaSuccess) return -1000; \
+    return v;                                                                        \
+  }                                                                                  \
+  }
+
 }  // namespace tc
+
+// Tensor map over a token-major tensor with inner extent D (multiple of 64): 4-D, 64-column boxes of
+// 64 tokens.  seq-first [B,T,H,D]: dims (D, H, T, B), coordinates (d, h, t, b);
+// head-first [B,H,T,D]: dims (D, T, H, B), coordinates (d, t, h, b).  Rows past T are zero-filled.
+int make_token_map(CUtensorMap *map, const void *base, const flab_args *a, int D);
+// Tensor map over chunk states [rows = NT*H*K][V], boxes of 64 columns x `box_rows` rows.
+int make_state_map(CUtensorMap *map, const void *base, const flab_args *a, int box_rows);
 
 // host: tensor-map construction without linking libcuda (entry point fetched from the runtime)
 int make_tensor_map_bf16(CUtensorMap *map, const void *base, int rank, const uint64_t *dims, const uint64_t *strides_bytes,

@@ -1,0 +1,318 @@
+// tcgen05 / TMA version of the chunk-parallel output kernels (bf16 / fp16, K in {64,128}, V % 64 == 0):
+//   fwd_o    : o  = scale * [(q h) * e^{b_i} + tril(q k^T * e^{b_i-b_j}) v]      (fla/ops/common/chunk_o.py:23-101)
+//   bwd_dv   : dv = (k dh) * e^{b_L-b_j} + triu(k q^T * e^{b_i-b_j}) * scale do  (fla/ops/common/chunk_o.py:289-364)
+//   dv_local : second term of bwd_dv only                                         (fla/ops/common/chunk_o.py:379-441)
+//
+// Persistent kernel, one CTA per SM, work item = (chunk, head, 128-wide V tile).  Eighteen warps:
+//   warp 16 : TMA producer  - streams the item's tiles (x1, x2, y, state) into a ring of stages
+//   warp 17 : MMA issuer    - S = x1 x2^T and O = x1 state into TMEM, later O = P y
+//   warps 0-7 / 8-15: two epilogue groups working on even / odd items (ping-pong); inside a group
+//                     warp = (TMEM lane quadrant = 16 token rows, column half)
+//                           - S -> mask / decay -> P (bf16, swizzled shared memory); O -> gate -> out
+// The epilogue arithmetic (one exponential per score element, packing, swizzled stores) is what
+// bounds the kernel, hence 16 epilogue warps for one MMA-issuing thread.
+// TMEM holds two stages of [S: 64 columns | O: 128 columns] (M = 64 rows = lanes 0-15 of each warp's
+// quadrant), one per epilogue group, so the tensor core and the other group work on item i+1 while
+// one group finishes item i.  The inter-chunk
+// product O1 = x1 state is pulled into registers and gated there; the intra-chunk product re-uses
+// its TMEM columns, so no accumulator is written back.
+// All waits are bounded; a timeout records an id in the unit's error word and every role drains out.
+#include "tc.cuh"
+
+FLAB_TC_DEFINE_ERROR_WORD(tc_chunk_o_error)
+
+namespace flab {
+
+enum { TMODE_O = 0, TMODE_DV = 1, TMODE_DV_LOCAL = 2 };
+
+struct TcOParams {
+  flab_args a;
+  int n_items;   // NT * H * (V / BV)
+  int v_tiles;   // V / BV
+  int ab_fmt;    // 1 bf16, 0 fp16
+};
+
+template <int KB /*K/64*/, int VB /*BV/64*/, int MODE, int NS /*smem stages*/>
+__global__ void __launch_bounds__(576, 1)
+tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_constant__ CUtensorMap mapX2,
+                  const __grid_constant__ CUtensorMap mapY, const __grid_constant__ CUtensorMap mapH, const TcOParams p) {
+  using namespace tc;
+  constexpr int K = 64 * KB, BV = 64 * VB;
+  constexpr bool HAS_H = MODE != TMODE_DV_LOCAL;
+  constexpr uint32_t X_BYTES = KB * 8192, Y_BYTES = VB * 8192, H_BYTES = HAS_H ? VB * K * 128 : 0;
+  constexpr uint32_t STAGE_BYTES = 2 * X_BYTES + Y_BYTES + H_BYTES;
+  constexpr int LDO = BV + 8;  // padded staging rows for the coalesced store
+  constexpr uint32_t TM_STAGE = 256, TM_S = 0, TM_O = 64;
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char *sStage = base;                         // [NS][STAGE_BYTES]
+  unsigned char *sP = sStage + NS * STAGE_BYTES;         // [2][8192] score tiles (swizzled K-major)
+  bf16 *sOutAll = reinterpret_cast<bf16 *>(sP + 2 * 8192);  // [2][64][LDO]
+  float *sG = reinterpret_cast<float *>(sOutAll + 2 * C * LDO);  // [2][64]
+  __shared__ uint64_t full[NS], empty[NS], s_done[2], p_ready[2], o_done[2], t_free[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile int abort_flag;
+  __shared__ volatile int abort_snap[2];
+
+  const flab_args &a = p.a;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_done[i], 1);
+      mbar_init(&p_ready[i], 256);
+      mbar_init(&o_done[i], 1);
+      mbar_init(&t_free[i], 256);
+    }
+    abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 0) tmem_alloc(&tmem_base_s, 512);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = tmem_base_s;
+  const bool use_g = a.g != nullptr;
+  const int n_local = p.n_items > (int)blockIdx.x ? (p.n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+  auto fail = [&](int code) {
+    abort_flag = 1;
+    atomicCAS(&tu_tc_error, 0, code);
+  };
+  // item -> (chunk, head, v tile)
+  auto decode = [&](int item, int &c, int &hd, int &vt) {
+    vt = item % p.v_tiles;
+    const int ch = item / p.v_tiles;
+    hd = ch % a.H;
+    c = ch / a.H;
+  };
+
+  if (warp == 16) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int i = 0; i < n_local && !abort_flag; ++i) {
+        const int st = i % NS, ph = (i / NS) & 1;
+        if (!mbar_wait(&empty[st], ph ^ 1)) { fail(1); break; }
+        int c, hd, vt, n, it;
+        decode(blockIdx.x + i * gridDim.x, c, hd, vt);
+        chunk_of(a, c, n, it);
+        const Seq s = seq_of(a, n);
+        const int t0 = s.bos + it * C;
+        unsigned char *x1 = sStage + st * STAGE_BYTES, *x2 = x1 + X_BYTES, *y = x2 + X_BYTES, *hh = y + Y_BYTES;
+        mbar_expect_tx(&full[st], STAGE_BYTES);
+        const int c1 = a.head_first ? t0 : hd, c2 = a.head_first ? hd : t0;
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+          tma_load_4d(x1 + j * 8192, &mapX1, &full[st], 64 * j, c1, c2, s.b);
+          tma_load_4d(x2 + j * 8192, &mapX2, &full[st], 64 * j, c1, c2, s.b);
+        }
+#pragma unroll
+        for (int j = 0; j < VB; ++j) {
+          tma_load_4d(y + j * 8192, &mapY, &full[st], vt * BV + 64 * j, c1, c2, s.b);
+          if (HAS_H) tma_load_2d(hh + j * (K * 128), &mapH, &full[st], vt * BV + 64 * j, ((s.c0 + it) * a.H + hd) * K);
+        }
+      }
+    }
+  } else if (warp == 17) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = instr_desc(64, 64, p.ab_fmt, 0, 0);
+      const uint32_t idesc_h = instr_desc(64, BV, p.ab_fmt, 0, 1);
+      auto issue12 = [&](int i) -> bool {
+        const int st = i % NS, ph = (i / NS) & 1, ts = i & 1, tph = (i >> 1) & 1;
+        if (!mbar_wait(&full[st], ph)) { fail(2); return false; }
+        if (!mbar_wait(&t_free[ts], tph ^ 1)) { fail(3); return false; }
+        fence_after_sync();
+        const uint32_t x1 = smem_u32(sStage + st * STAGE_BYTES), x2 = x1 + X_BYTES, hh = x2 + X_BYTES + Y_BYTES;
+        const uint32_t t = tmem + ts * TM_STAGE;
+#pragma unroll
+        for (int s = 0; s < 4 * KB; ++s) umma(t + TM_S, desc_kmajor(x1, s, 8192), desc_kmajor(x2, s, 8192), idesc_s, s > 0);
+        if (HAS_H) {
+#pragma unroll
+          for (int s = 0; s < 4 * KB; ++s) umma(t + TM_O, desc_kmajor(x1, s, 8192), desc_mnmajor(hh, s, K * 128), idesc_h, s > 0);
+        }
+        umma_commit(&s_done[ts]);
+        return true;
+      };
+      bool ok = n_local > 0 ? issue12(0) : true;
+      for (int i = 0; i < n_local && ok && !abort_flag; ++i) {
+        const int st = i % NS, ts = i & 1, tph = (i >> 1) & 1;
+        if (i + 1 < n_local) ok = issue12(i + 1);
+        if (!ok) break;
+        if (!mbar_wait(&p_ready[ts], tph)) { fail(4); break; }
+        fence_after_sync();
+        const uint32_t y = smem_u32(sStage + st * STAGE_BYTES) + 2 * X_BYTES, pp = smem_u32(sP + ts * 8192);
+        const uint32_t t = tmem + ts * TM_STAGE;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) umma(t + TM_O, desc_kmajor(pp, s, 8192), desc_mnmajor(y, s, 8192), idesc_h, s > 0);
+        umma_commit(&o_done[ts]);
+        umma_commit(&empty[st]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue groups (warps 0-7, 8-15)
+    const int grp = warp >> 3, gw = warp & 7, wq = gw & 3, chh = gw >> 2, etid = tid & 255;
+    const int g8 = lane >> 2, t4 = lane & 3;
+    const int m0 = wq * 16;
+    const uint32_t lane_base = (uint32_t)(32 * wq) << 16;
+    constexpr int NIO = 4 * VB;  // accumulator n-tiles of this warp's half of the O columns
+    bf16 *sOut = sOutAll + grp * C * LDO;
+    const int row_lo = m0 + g8, row_hi = row_lo + 8;
+    for (int i = grp; i < n_local; i += 2) {
+      const int st = grp, ph = (i >> 1) & 1;
+      int c, hd, vt, n, it;
+      decode(blockIdx.x + i * gridDim.x, c, hd, vt);
+      chunk_of(a, c, n, it);
+      const Seq s = seq_of(a, n);
+      const int t0 = it * C, rows = min(C, s.len - t0), last = rows - 1;
+      float *gs = sG + st * C;
+      if (etid < C) gs[etid] = (use_g && etid < rows) ? reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + etid, 1)] : 0.f;
+      if (etid == 0) abort_snap[grp] = abort_flag;  // one thread samples the flag so that the whole group leaves together
+      named_barrier(1 + grp, 256);
+      if (abort_snap[grp]) break;
+      if (!mbar_wait(&s_done[st], ph)) { fail(5); break; }
+      fence_after_sync();
+      const uint32_t t = tmem + st * TM_STAGE + lane_base;
+      const float g_lo = gs[row_lo], g_hi = gs[row_hi];
+      // ---- S -> P : this warp's 16 rows x 32 columns
+      {
+        float sc[4][4];
+        tmem_ld_frag<4>(t + TM_S + 32 * chh, sc);
+        tmem_ld_wait();
+        unsigned char *pp = sP + st * 8192;
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni) {
+          const int col = 32 * chh + 8 * ni + 2 * t4;
+          const float gc0 = gs[col], gc1 = gs[col + 1];
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            const int row = hf ? row_hi : row_lo;
+            const float gr = hf ? g_hi : g_lo;
+            float x0 = sc[ni][2 * hf], x1 = sc[ni][2 * hf + 1];
+            if (MODE == TMODE_O) {
+              x0 = (row >= col) ? (use_g ? x0 * __expf(fminf(gr - gc0, 0.f)) : x0) : 0.f;
+              x1 = (row >= col + 1) ? (use_g ? x1 * __expf(fminf(gr - gc1, 0.f)) : x1) : 0.f;
+            } else {
+              x0 = (row <= col && col < rows) ? (use_g ? x0 * __expf(fminf(gc0 - gr, 0.f)) : x0) * a.scale : 0.f;
+              x1 = (row <= col + 1 && col + 1 < rows) ? (use_g ? x1 * __expf(fminf(gc1 - gr, 0.f)) : x1) * a.scale : 0.f;
+            }
+            const uint32_t off = (uint32_t)row * 128u + ((uint32_t)((4 * chh + ni) ^ (row & 7)) << 4) + 4u * t4;
+            if (p.ab_fmt) *reinterpret_cast<__nv_bfloat162 *>(pp + off) = __floats2bfloat162_rn(x0, x1);
+            else *reinterpret_cast<__half2 *>(pp + off) = __floats2half2_rn(x0, x1);
+          }
+        }
+      }
+      // ---- O1 = x1 state -> registers, gated : 16 rows x BV/2 columns
+      float o1[NIO][4];
+      if (HAS_H) {
+        tmem_ld_frag<NIO>(t + TM_O + (BV / 2) * chh, o1);
+        tmem_ld_wait();
+        if (use_g) {
+          float s_lo, s_hi;
+          if (MODE == TMODE_O) {
+            s_lo = __expf(g_lo);
+            s_hi = __expf(g_hi);
+          } else {
+            s_lo = __expf(fminf(gs[last] - g_lo, 0.f));
+            s_hi = __expf(fminf(gs[last] - g_hi, 0.f));
+          }
+#pragma unroll
+          for (int ni = 0; ni < NIO; ++ni) {
+            o1[ni][0] *= s_lo;
+            o1[ni][1] *= s_lo;
+            o1[ni][2] *= s_hi;
+            o1[ni][3] *= s_hi;
+          }
+        }
+      }
+      fence_proxy_async();
+      fence_before_sync();
+      mbar_arrive(&p_ready[st]);
+      // ---- O2 = P y
+      if (!mbar_wait(&o_done[st], ph)) { fail(6); break; }
+      fence_after_sync();
+      float o2[NIO][4];
+      tmem_ld_frag<NIO>(t + TM_O + (BV / 2) * chh, o2);
+      tmem_ld_wait();
+      fence_before_sync();
+      mbar_arrive(&t_free[st]);
+      named_barrier(1 + grp, 256);  // this group's previous store has drained sOut
+      const float osc = MODE == TMODE_O ? a.scale : 1.f;
+#pragma unroll
+      for (int ni = 0; ni < NIO; ++ni)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int row = hf ? row_hi : row_lo, col = (BV / 2) * chh + 8 * ni + 2 * t4;
+          const float x0 = (o2[ni][2 * hf] + (HAS_H ? o1[ni][2 * hf] : 0.f)) * osc;
+          const float x1 = (o2[ni][2 * hf + 1] + (HAS_H ? o1[ni][2 * hf + 1] : 0.f)) * osc;
+          if (p.ab_fmt) *reinterpret_cast<__nv_bfloat162 *>(sOut + row * LDO + col) = __floats2bfloat162_rn(x0, x1);
+          else *reinterpret_cast<__half2 *>(sOut + row * LDO + col) = __floats2half2_rn(x0, x1);
+        }
+      named_barrier(1 + grp, 256);
+      bf16 *out = reinterpret_cast<bf16 *>(MODE == TMODE_O ? a.o : a.dv) + tok_off(a, s, hd, t0, a.V) + vt * BV;
+      tile_store<bf16>(out, tok_stride(a, a.V), sOut, LDO, rows, BV, etid, 256);
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+template <int KB, int VB, int MODE, int NS> static int launch_tc_o(const flab_args *a, cudaStream_t stream, const char *name) {
+  constexpr int K = 64 * KB, BV = 64 * VB;
+  CUtensorMap mX1, mX2, mY, mH;
+  const void *x1 = MODE == TMODE_O ? a->q : a->k, *x2 = MODE == TMODE_O ? a->k : a->q;
+  const void *y = MODE == TMODE_O ? a->v : a->d_o, *hs = MODE == TMODE_O ? a->h : a->dh;
+  if (int e = make_token_map(&mX1, x1, a, a->K)) return e;
+  if (int e = make_token_map(&mX2, x2, a, a->K)) return e;
+  if (int e = make_token_map(&mY, y, a, a->V)) return e;
+  if (MODE != TMODE_DV_LOCAL) {
+    if (int e = make_state_map(&mH, hs, a, K)) return e;
+  } else {
+    mH = mY;
+  }
+  TcOParams p;
+  p.a = *a;
+  p.v_tiles = a->V / BV;
+  p.n_items = a->NT * a->H * p.v_tiles;
+  p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
+  constexpr uint32_t STAGE = 2 * KB * 8192 + VB * 8192 + (MODE != TMODE_DV_LOCAL ? VB * K * 128 : 0);
+  const size_t smem = 1024 + NS * (size_t)STAGE + 2 * 8192 + 2 * (size_t)C * (BV + 8) * 2 + 2 * C * sizeof(float);
+  auto kern = tc_chunk_o_kernel<KB, VB, MODE, NS>;
+  if (int e = set_smem(kern, smem)) return e;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = p.n_items < sms ? p.n_items : sms;
+  kern<<<grid, 576, smem, stream>>>(mX1, mX2, mY, mH, p);
+  return check_launch(name);
+}
+
+// Returns 1 if the tcgen05 kernel took the call, 0 if the shape is outside its domain, < 0 on error.
+template <int MODE> int tc_chunk_o_try(const flab_args *a, cudaStream_t stream, const char *name) {
+  if (a->dtype != FLAB_BF16 && a->dtype != FLAB_FP16) return 0;
+  if ((a->K != 64 && a->K != 128) || a->V % 64 != 0) return 0;
+  const void *ptrs[4] = {a->q, a->k, MODE == TMODE_O ? a->v : a->d_o, MODE == TMODE_O ? a->h : (MODE == TMODE_DV ? a->dh : a->q)};
+  for (int i = 0; i < 4; ++i)
+    if (reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return 0;
+  // shared-memory stages: as many as fit next to the two score tiles and the two staging buffers
+  constexpr bool L = MODE == TMODE_DV_LOCAL;
+  int rc;
+  if (a->K == 64) {
+    rc = (a->V % 128 == 0) ? launch_tc_o<1, 2, MODE, 4>(a, stream, name) : launch_tc_o<1, 1, MODE, 4>(a, stream, name);
+  } else {
+    rc = (a->V % 128 == 0) ? launch_tc_o<2, 2, MODE, L ? 3 : 2>(a, stream, name) : launch_tc_o<2, 1, MODE, L ? 4 : 3>(a, stream, name);
+  }
+  return rc < 0 ? rc : 1;
+}
+
+template int tc_chunk_o_try<TMODE_O>(const flab_args *, cudaStream_t, const char *);
+template int tc_chunk_o_try<TMODE_DV>(const flab_args *, cudaStream_t, const char *);
+template int tc_chunk_o_try<TMODE_DV_LOCAL>(const flab_args *, cudaStream_t, const char *);
+
+}  // namespace flab

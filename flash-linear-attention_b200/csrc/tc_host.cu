@@ -26,6 +26,13 @@ static EncodeTiledFn encode_fn() {
 int make_tensor_map_bf16(CUtensorMap *map, const void *base, int rank, const uint64_t *dims, const uint64_t *strides_bytes,
                          const uint32_t *box, int elem_fp16) {
   EncodeTiledFn fn = encode_fn();
+  // A driver-API call needs a current context; a thread that has only used the runtime lazily (an
+  // autograd worker thread, say) may not have bound the primary context yet.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(0);
+    bound = true;
+  }
   FLAB_REQUIRE(fn != nullptr, FLAB_E_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gdim[4];
   cuuint64_t gstr[4];
@@ -44,4 +51,30 @@ int make_tensor_map_bf16(CUtensorMap *map, const void *base, int rank, const uin
   return 0;
 }
 
+
+int make_token_map(CUtensorMap *map, const void *base, const flab_args *a, int D) {
+  const uint64_t e = 2;
+  if (!a->head_first) {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a->H, (uint64_t)a->T, (uint64_t)a->B};
+    const uint64_t str[3] = {(uint64_t)D * e, (uint64_t)a->H * D * e, (uint64_t)a->T * a->H * D * e};
+    const uint32_t box[4] = {64, 1, 64, 1};
+    return make_tensor_map_bf16(map, base, 4, dims, str, box, a->dtype == FLAB_FP16);
+  }
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a->T, (uint64_t)a->H, (uint64_t)a->B};
+  const uint64_t str[3] = {(uint64_t)D * e, (uint64_t)a->T * D * e, (uint64_t)a->H * a->T * D * e};
+  const uint32_t box[4] = {64, 64, 1, 1};
+  return make_tensor_map_bf16(map, base, 4, dims, str, box, a->dtype == FLAB_FP16);
+}
+
+int make_state_map(CUtensorMap *map, const void *base, const flab_args *a, int box_rows) {
+  const uint64_t dims[2] = {(uint64_t)a->V, (uint64_t)a->NT * a->H * a->K};
+  const uint64_t str[1] = {(uint64_t)a->V * 2};
+  const uint32_t box[2] = {64, (uint32_t)box_rows};
+  return make_tensor_map_bf16(map, base, 2, dims, str, box, a->dtype == FLAB_FP16);
+}
+
+int tc_chunk_o_error();
+
 }  // namespace flab
+
+extern "C" int flab_tc_error_state(void) { return flab::tc_chunk_o_error(); }

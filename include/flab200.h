@@ -178,6 +178,9 @@ int flab_recurrent_delta_bwd(const flab_args *a, void *stream);
  * (fp32: [64x64] A B^T, [64x128] A H, [128x64] A^T V, [64x64] bf16(A B^T) V) for the caller to compare
  * with a plain matmul. a, b: [64x128], h: [128x128], v: [64x64], row-major bf16. *status = 0 on
  * success, else the index of the bounded wait that ran out. */
+/* No counterpart in the reference. 0 if no tcgen05 kernel of this process has had a bounded wait run
+ * out so far (synchronises the device); otherwise the id of the first wait that did. */
+int flab_tc_error_state(void);
 int flab_tc_selftest(const void *a, const void *b, const void *h, const void *v, float *out, int *status, void *stream);
 
 #ifdef __cplusplus

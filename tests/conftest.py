@@ -17,3 +17,15 @@ def pytest_configure(config):
 def golden():
     import numpy as np
     return np.load(os.path.join(ROOT, "tests", "golden", "ref_vectors.npz"))
+
+
+@pytest.fixture(scope="session", autouse=True)
+def tc_error_word_stays_clear():
+    """After the whole session: no tcgen05 kernel may have recorded a timed-out wait."""
+    yield
+    import torch
+    if torch.cuda.is_available():
+        from fla_b200 import _lib
+        lib = _lib.load()
+        torch.cuda.synchronize()
+        assert lib.flab_tc_error_state() == 0, f"a bounded device-side wait ran out: id {lib.flab_tc_error_state()}"
