@@ -170,37 +170,55 @@ def time_stage(fn, reps=10, warm=3):
 
 
 def stage_breakdown(op, i):
-    """Times every stage of the gated-delta-rule forward+backward on its own; returns
-    {stage: (ms, launches per step, algorithmic bytes, algorithmic flops)} for the roofline entry."""
+    """Times every stage of the op's forward+backward on its own; returns
+    {stage: dict(ms, launches_per_step, bytes, flops)} (algorithmic bytes / dense-tile flops per launch)."""
     from fla_b200.ops import common as C
     from fla_b200.utils import Geometry
-    if op != "gated_delta":
+    if op not in ("gated_delta", "delta", "simple_gla"):
         return {}
-    q, k, v, g, beta, h0, do, dht = (i[n].detach() for n in ("q", "k", "v", "g", "beta", "h0", "do", "dht"))
+    q, k, v, do = (i[n].detach() for n in ("q", "k", "v", "do"))
     geo = Geometry(k, v, None, False)
     B, T, H, K, V = geo.B, geo.T, geo.H, geo.K, geo.V
     TH = B * T * H
     scale = K ** -0.5
-    gc = C.chunk_local_cumsum(g, head_first=False)
-    aw, au, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta, g=gc)
-    h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=gc, h0=h0, output_final_state=True)
-    dv = C.chunk_bwd_dv_local(geo, q, k, gc, do, scale)
-    dh, dh0, dv2 = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=gc, dht=dht, want_dh0=True)
-    dq, dk, dw, dg = C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=gc, w=w, dv=dv2)
     e = 2  # bytes per bf16 element
     st = K * V * e / 64  # chunk-state bytes per token*head
-    # algorithmic (compulsory) traffic and dense-tile flops per token*head of each stage
-    table = {
-        "cumsum": (lambda: C.chunk_local_cumsum(g, head_first=False), 2, 8, 0),
-        "wy_fwd": (lambda: C.fwd_prepare_wy_repr(geo, k, v, beta, g=gc), 1, (2 * K + 2 * V) * e + 2 * 64 * e + 6, 2 * 64 * K + 2 * 64 * (K + V) + 2 * 64 * 64),
-        "wy_recompute": (lambda: C.fwd_recompute_w_u(geo, k, v, beta, aw, au), 1, (2 * K + 2 * V) * e + 2 * 64 * e + 2, 2 * 64 * (K + V)),
-        "delta_fwd_h": (lambda: C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=gc, h0=h0, output_final_state=True), 2, (2 * K + 2 * V) * e + 4 + st, 4 * K * V),
-        "chunk_fwd_o": (lambda: C.chunk_fwd_o(geo, q, k, v_new, h, g=gc, scale=scale), 1, (2 * K + 2 * V) * e + 4 + st, 2 * K * V + 2 * 64 * K + 2 * 64 * V),
-        "dv_local": (lambda: C.chunk_bwd_dv_local(geo, q, k, gc, do, scale), 1, (2 * K + 2 * V) * e + 4, 2 * 64 * K + 2 * 64 * V),
-        "delta_bwd_dhu": (lambda: C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=gc, dht=dht, want_dh0=True), 1, (3 * K + 3 * V) * e + 4 + st, 6 * K * V),
-        "dqkwg": (lambda: C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=gc, w=w, dv=dv2), 1, (6 * K + 3 * V) * e + 8 + 2 * st, 6 * K * V + 2 * 64 * V + 6 * 64 * K),
-        "wy_bwd": (lambda: C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv2, g=gc, au=au), 1, (4 * K + 4 * V) * e + 2 * 64 * e + 14, 8 * 64 * K + 4 * 64 * V + 8 * 64 * 64),
-    }
+    table = {}
+    if op == "simple_gla":
+        g = i["g"].detach()
+        gc = C.chunk_local_cumsum(g, head_first=False)
+        h, _ = C.chunk_fwd_h(geo, k, v, g=gc)
+        dh, _ = C.chunk_bwd_dh(geo, q, do, scale, g=gc)
+        table = {
+            "cumsum": (lambda: C.chunk_local_cumsum(g, head_first=False), 2, 8, 0),
+            "chunk_fwd_h": (lambda: C.chunk_fwd_h(geo, k, v, g=gc), 1, (K + V) * e + 4 + st, 2 * K * V),
+            "chunk_fwd_o": (lambda: C.chunk_fwd_o(geo, q, k, v, h, g=gc, scale=scale), 1, (2 * K + 2 * V) * e + 4 + st, 2 * K * V + 2 * 64 * K + 2 * 64 * V),
+            "chunk_bwd_dh": (lambda: C.chunk_bwd_dh(geo, q, do, scale, g=gc), 1, (K + V) * e + 4 + st, 2 * K * V),
+            "dqkwg": (lambda: C.chunk_bwd_dqkwg(geo, q, k, v, h, dh, do, scale, g=gc), 1, (4 * K + 2 * V) * e + 8 + 2 * st, 4 * K * V + 2 * 64 * V + 6 * 64 * K),
+            "chunk_bwd_dv": (lambda: C.chunk_bwd_dv(geo, q, k, gc, do, dh, scale), 1, (2 * K + 2 * V) * e + 4 + st, 2 * K * V + 2 * 64 * K + 2 * 64 * V),
+        }
+    else:
+        beta, h0, dht = (i[n].detach() for n in ("beta", "h0", "dht"))
+        gated = op == "gated_delta"
+        gc = C.chunk_local_cumsum(i["g"].detach(), head_first=False) if gated else None
+        aw, au, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta, g=gc)
+        h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=gc, h0=h0, output_final_state=True)
+        dv = C.chunk_bwd_dv_local(geo, q, k, gc, do, scale)
+        dh, dh0, dv2 = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=gc, dht=dht, want_dh0=True)
+        dq, dk, dw, dg = C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=gc, w=w, dv=dv2)
+        na = 2 if gated else 1
+        table = {
+            "wy_fwd": (lambda: C.fwd_prepare_wy_repr(geo, k, v, beta, g=gc), 1, (2 * K + 2 * V) * e + na * 64 * e + 6, 2 * 64 * K + 2 * 64 * (K + V) + 2 * 64 * 64),
+            "delta_fwd_h": (lambda: C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=gc, h0=h0, output_final_state=True), 1, (2 * K + 2 * V) * e + 4 + st, 4 * K * V),
+            "chunk_fwd_o": (lambda: C.chunk_fwd_o(geo, q, k, v_new, h, g=gc, scale=scale), 1, (2 * K + 2 * V) * e + 4 + st, 2 * K * V + 2 * 64 * K + 2 * 64 * V),
+            "dv_local": (lambda: C.chunk_bwd_dv_local(geo, q, k, gc, do, scale), 1, (2 * K + 2 * V) * e + 4, 2 * 64 * K + 2 * 64 * V),
+            "delta_bwd_dhu": (lambda: C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=gc, dht=dht, want_dh0=True), 1, (3 * K + 3 * V) * e + 4 + st, 6 * K * V),
+            "dqkwg": (lambda: C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=gc, w=w, dv=dv2), 1, (6 * K + 3 * V) * e + 8 + 2 * st, 6 * K * V + 2 * 64 * V + 6 * 64 * K),
+            "wy_bwd": (lambda: C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv2, g=gc, au=au), 1, (4 * K + 4 * V) * e + na * 64 * e + 14, 8 * 64 * K + 4 * 64 * V + 8 * 64 * 64),
+        }
+        if gated:
+            g = i["g"].detach()
+            table["cumsum"] = (lambda: C.chunk_local_cumsum(g, head_first=False), 2, 8, 0)
     out = {}
     for name, (fn, launches, bytes_th, flops_th) in table.items():
         ms = time_stage(fn)

@@ -47,7 +47,7 @@ ENTRY_POINTS = [
     "flab_chunk_bwd_dv_local", "flab_chunk_bwd_dqkwg", "flab_wy_fwd", "flab_wy_recompute",
     "flab_wy_bwd", "flab_delta_fwd_h", "flab_delta_bwd_dhu", "flab_gla_fwd_intra", "flab_gla_fwd_o",
     "flab_gla_bwd_dav", "flab_gla_bwd_dqkg", "flab_recurrent_fwd", "flab_recurrent_bwd",
-    "flab_recurrent_delta_fwd", "flab_recurrent_delta_bwd",
+    "flab_recurrent_delta_fwd", "flab_recurrent_delta_bwd", "flab_gated_delta_rule_fwd",
 ]
 
 _lib = None
@@ -70,6 +70,9 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.POINTER(FlabArgs), ctypes.c_void_p]
+    lib.flab_gated_delta_rule_fwd_workspace.restype = ctypes.c_size_t
+    lib.flab_gated_delta_rule_fwd_workspace.argtypes = [ctypes.POINTER(FlabArgs)]
+    lib.flab_tc_error_state.restype = ctypes.c_int
     _lib = lib
     return lib
 
@@ -81,17 +84,11 @@ def _ptr(t: Optional[torch.Tensor]):
     return t.data_ptr()
 
 
-def call(entry: str, ref: torch.Tensor, *, B, T, H, K=0, V=0, N=None, NT=0, dtype=None, head_first=False,
-         flags=0, scale=1.0, S=0, varlen=None, **tensors):
-    """Launch one stage on the current stream of `ref`'s device.
-
-    `varlen` is the tuple produced by `fla_b200.utils.prepare_varlen` or None; `tensors` maps slot
-    names of `flab_args` to tensors (None = absent).
-    """
-    lib = load()
-    if not ref.is_cuda:
-        raise RuntimeError("flab200 kernels run on CUDA tensors only (no CPU fallback)")
+def fill_args(ref: torch.Tensor, *, B, T, H, K=0, V=0, N=None, NT=0, dtype=None, head_first=False,
+              flags=0, scale=1.0, S=0, varlen=None, ws_bytes=0, **tensors) -> FlabArgs:
+    """Build a `flab_args` struct; `tensors` maps slot names to tensors (None = absent)."""
     a = FlabArgs()
+    a.ws_bytes = ws_bytes
     a.B, a.T, a.H, a.K, a.V = B, T, H, K, V
     a.N = N if N is not None else B
     a.NT = NT
@@ -111,6 +108,18 @@ def call(entry: str, ref: torch.Tensor, *, B, T, H, K=0, V=0, N=None, NT=0, dtyp
             if t.device != ref.device:
                 raise RuntimeError(f"slot {name}: tensor on {t.device}, expected {ref.device}")
             setattr(a, name, _ptr(t))
+    return a
+
+
+def call(entry: str, ref: torch.Tensor, **kw):
+    """Launch one entry point on the current stream of `ref`'s device (see `fill_args`).
+
+    `varlen` is the tuple produced by `fla_b200.utils.prepare_varlen` or None.
+    """
+    lib = load()
+    if not ref.is_cuda:
+        raise RuntimeError("flab200 kernels run on CUDA tensors only (no CPU fallback)")
+    a = fill_args(ref, **kw)
     with torch.cuda.device(ref.device):
         stream = torch.cuda.current_stream().cuda_stream
         rc = getattr(lib, entry)(ctypes.byref(a), ctypes.c_void_p(stream))

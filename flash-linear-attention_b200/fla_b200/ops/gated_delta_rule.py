@@ -23,6 +23,21 @@ def chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta, scale, initial_state, outp
     return g, o, aw, au, ht, (w, h, v_new)
 
 
+def chunk_gated_delta_rule_fwd_fused(geo, q, k, v, g, beta, scale, initial_state, output_final_state):
+    """Forward only, as ONE call into the library (flab_gated_delta_rule_fwd): the four stages are
+    enqueued back to back with their intermediates in a workspace tensor. Used when no gradient is
+    needed (prefill / evaluation); same results as the staged forward."""
+    from .. import _lib
+    o = torch.empty_like(v)
+    ht = torch.empty(geo.N, geo.H, geo.K, geo.V, dtype=torch.float32, device=q.device) if output_final_state else None
+    probe = _lib.fill_args(q, **geo.kw())
+    need = _lib.load().flab_gated_delta_rule_fwd_workspace(probe)
+    ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+    _lib.call("flab_gated_delta_rule_fwd", q, **geo.kw(), scale=scale, q=q, k=k, v=v, g=g.float().contiguous(), beta=beta,
+              h0=None if initial_state is None else initial_state.float().contiguous(), o=o, ht=ht, ws=ws, ws_bytes=need)
+    return o, ht
+
+
 def chunk_gated_delta_rule_bwd(geo, q, k, v, g, beta, aw, au, scale, initial_state, do, dht, saved=None):
     """Stage order of fla/ops/gated_delta_rule/chunk.py:76-177; `g` is the chunk-local cumsum.
     `saved` = (w, h, v_new) kept from forward; None recomputes them like the reference."""
@@ -91,6 +106,13 @@ def chunk_gated_delta_rule(
         scale = k.shape[-1] ** -0.5
     else:
         assert scale > 0, "Scale must be positive."
+    needs_grad = torch.is_grad_enabled() and any(
+        x is not None and x.requires_grad for x in (q, k, v, g, beta, initial_state))
+    if not needs_grad and not torch.is_autocast_enabled():
+        q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
+        geo = Geometry(k, v, offsets, head_first)
+        return chunk_gated_delta_rule_fwd_fused(geo, q, k, v, g, beta.to(k.dtype), scale, initial_state,
+                                                output_final_state)
     return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, offsets,
                                              head_first)
 

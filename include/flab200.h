@@ -172,6 +172,13 @@ int flab_recurrent_delta_fwd(const flab_args *a, void *stream);
  * v, beta, h0, d_o, dht; writes dq, dk, dv (fp32), dbeta (fp32), dh0. */
 int flab_recurrent_delta_bwd(const flab_args *a, void *stream);
 
+/* ---- whole-forward entry points --------------------------------------------------------------
+ * Replaces chunk_gated_delta_rule_fwd (fla/ops/gated_delta_rule/chunk.py:20-73): the four stages
+ * (gate cumsum, WY factors, state scan, output) enqueued by one call. Reads q, k, v, g (the RAW fp32
+ * log gate, not cumsummed), beta, h0 (optional); writes o and ht (optional). Intermediates go to
+ * `ws` (256-byte aligned, at least flab_gated_delta_rule_fwd_workspace(a) bytes in ws_bytes). */
+size_t flab_gated_delta_rule_fwd_workspace(const flab_args *a);
+int flab_gated_delta_rule_fwd(const flab_args *a, void *stream);
 /* ---- diagnostics -----------------------------------------------------------------------------
  * No counterpart in the reference. Runs four small bf16 products through the TMA + tcgen05 + TMEM
  * path (every shared-memory operand form the kernels use) and writes them to `out`

@@ -463,3 +463,20 @@ def test_recompute_path_matches_saved_state_path(monkeypatch):
     for mod in (gdr, sg):
         for a_, b_ in zip(grads(mod, True), grads(mod, False)):
             assert err_ratio(a_, b_) < 1e-5  # dg is reduced with shared-memory float atomics: last-bit order effects
+
+
+def test_fused_forward_entry_equals_staged_forward():
+    """flab_gated_delta_rule_fwd (one call, workspace) against the stage-by-stage forward, fixed and varlen."""
+    o_ = ops()
+    for T, N in ((300, None), (500, 4)):
+        B = 2 if N is None else 1
+        d = build(B, T, 3, 128, 128, torch.bfloat16, seed=T, gate="scalar", beta=True, h0=True, norm=True, N=N)
+        i = {n: x.to(DEV) for n, x in d.items()}
+        off = None if N is None else rand_offsets(T, N).to(DEV)
+        with torch.no_grad():  # no gradient needed -> fused entry
+            o1, h1 = o_.chunk_gated_delta_rule(i["q"], i["k"], i["v"], i["g"], i["beta"], initial_state=i["h0"],
+                                               output_final_state=True, offsets=off, head_first=False)
+        q = i["q"].clone().requires_grad_(True)  # gradient needed -> staged autograd path
+        o2, h2 = o_.chunk_gated_delta_rule(q, i["k"], i["v"], i["g"], i["beta"], initial_state=i["h0"],
+                                           output_final_state=True, offsets=off, head_first=False)
+        assert torch.equal(o1, o2) and torch.equal(h1, h2)
