@@ -1,7 +1,10 @@
 // Whole-forward entry points of chunk_gated_delta_rule: cumsum -> WY -> state scan -> output as one
 // C call (four kernel launches, no host work in between).  Intermediates (cumsummed gate, Aw, Au, w, u,
-// chunk states, v_new) live in caller-provided scratch memory.
+// chunk states, v_new) live in scratch memory: caller-provided for flab_gated_delta_rule_fwd, a
+// file-scope device array for flab_gated_delta_rule_fwd_noalloc.
 // Stage order follows chunk_gated_delta_rule_fwd (fla/ops/gated_delta_rule/chunk.py:20-73).
+#include <mutex>
+
 #include "common.cuh"
 
 extern "C" size_t flab_gated_delta_rule_fwd_workspace(const flab_args *a);
@@ -62,6 +65,33 @@ static int check_fwd_args(const flab_args *a, const char *who) {
   return 0;
 }
 
+// ---- scratch that nobody allocates -----------------------------------------------------------------
+// 16 MiB per GPU that loads the library, held until the process exits.  It covers B*T*H <= 8192
+// token-heads at K = V = 128 (for example one 512-token prompt of a 16-head layer).
+constexpr size_t NOALLOC_BYTES = 16u << 20;
+static __device__ __align__(256) unsigned char g_fwd_scratch[NOALLOC_BYTES];
+
+// In host code `g_fwd_scratch` is only a stand-in for the device array: its device address has to be
+// asked for, once per device, with that device current.
+static std::mutex g_scratch_mutex;
+static unsigned char *g_scratch_ptr[64] = {nullptr};
+
+static int scratch_device_pointer(unsigned char **out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  FLAB_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, FLAB_E_LAUNCH, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_ptr[dev]) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_fwd_scratch);
+    FLAB_REQUIRE(e == cudaSuccess && p != nullptr, FLAB_E_LAUNCH, "cudaGetSymbolAddress(g_fwd_scratch) failed: %s",
+                 cudaGetErrorString(e));
+    g_scratch_ptr[dev] = static_cast<unsigned char *>(p);
+  }
+  *out = g_scratch_ptr[dev];
+  return 0;
+}
+
 }  // namespace flab
 
 extern "C" {
@@ -81,4 +111,16 @@ int flab_gated_delta_rule_fwd(const flab_args *a, void *stream) {
   return run_fwd(a, static_cast<unsigned char *>(a->ws), stream);
 }
 
+int flab_gated_delta_rule_fwd_noalloc(const flab_args *a, void *stream) {
+  using namespace flab;
+  if (int e = check_fwd_args(a, "gated_delta_rule_fwd_noalloc")) return e;
+  const size_t need = scratch_layout(a).total;
+  FLAB_REQUIRE(need <= NOALLOC_BYTES, FLAB_E_UNSUPPORTED,
+               "gated_delta_rule_fwd_noalloc: this problem needs %zu bytes of scratch, the built-in scratch holds %zu "
+               "(B*T*H <= 8192 at K = V = 128); use flab_gated_delta_rule_fwd with a caller workspace",
+               need, (size_t)NOALLOC_BYTES);
+  unsigned char *ws = nullptr;
+  if (int e = scratch_device_pointer(&ws)) return e;
+  return run_fwd(a, ws, stream);
+}
 }

@@ -48,6 +48,7 @@ ENTRY_POINTS = [
     "flab_wy_bwd", "flab_delta_fwd_h", "flab_delta_bwd_dhu", "flab_gla_fwd_intra", "flab_gla_fwd_o",
     "flab_gla_bwd_dav", "flab_gla_bwd_dqkg", "flab_recurrent_fwd", "flab_recurrent_bwd",
     "flab_recurrent_delta_fwd", "flab_recurrent_delta_bwd", "flab_gated_delta_rule_fwd",
+    "flab_gated_delta_rule_fwd_noalloc",
 ]
 
 _lib = None

@@ -179,6 +179,22 @@ int flab_recurrent_delta_bwd(const flab_args *a, void *stream);
  * `ws` (256-byte aligned, at least flab_gated_delta_rule_fwd_workspace(a) bytes in ws_bytes). */
 size_t flab_gated_delta_rule_fwd_workspace(const flab_args *a);
 int flab_gated_delta_rule_fwd(const flab_args *a, void *stream);
+/* No counterpart in the reference. Same computation and arguments as flab_gated_delta_rule_fwd
+ * (ws / ws_bytes ignored), for callers that must not allocate device memory at all: code running
+ * while a stream is being captured into a CUDA graph, inside a pre-sized serving arena, or in a
+ * host callback, where cudaMalloc (or torch's allocator growing its pool) is either illegal or
+ * would stall the device. The intermediates live in a 16 MiB device array that is part of the
+ * library image: every GPU that loads the library holds those 16 MiB until the process exits.
+ * Limits and rules:
+ *  - problems whose scratch exceeds the 16 MiB (B*T*H > 8192 token-heads at K = V = 128) are
+ *    rejected with FLAB_E_UNSUPPORTED and a message, nothing is launched;
+ *  - the first call on each device looks up the array's device address (no allocation, but a
+ *    runtime query): make that first call before any stream capture begins;
+ *  - all calls share the one array and it keeps the previous call's contents; every call fully
+ *    overwrites what it reads, so nothing needs clearing, but two calls that overlap on the GPU
+ *    (different streams, or two threads) race on it: serialise them. */
+int flab_gated_delta_rule_fwd_noalloc(const flab_args *a, void *stream);
+
 /* ---- diagnostics -----------------------------------------------------------------------------
  * No counterpart in the reference. Runs four small bf16 products through the TMA + tcgen05 + TMEM
  * path (every shared-memory operand form the kernels use) and writes them to `out`
