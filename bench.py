@@ -42,7 +42,16 @@ WORKLOADS = {
     "delta": ("delta", 8, 4096, 16, 128, 128),
     "retention": ("simple_gla", 8, 4096, 16, 128, 128),
     "gla_fp32": ("gla", 2, 512, 4, 64, 64),
+    # 64 sequences of 256..8192 tokens (seeded), packed into one row with cu_seqlens, H=32
+    "varlen": ("gated_delta_varlen", 1, 0, 32, 128, 128),
+    # one decode step of 256 sequences: fused_recurrent_gated_delta_rule, T = 1, fp32 state carried
+    "decode": ("decode", 256, 1, 16, 128, 128),
 }
+
+
+def varlen_lengths():
+    g0 = torch.Generator().manual_seed(0)
+    return torch.randint(256, 8193, (64,), generator=g0)
 
 
 def peaks():
@@ -59,6 +68,14 @@ def make_inputs(op, B, T, H, K, V, seed, dtype):
     q, k = torch.randn(B, T, H, K, generator=g0), torch.randn(B, T, H, K, generator=g0)
     v = torch.randn(B, T, H, V, generator=g0)
     d = {}
+    if op in ("gated_delta_varlen", "decode"):
+        q, k = F.normalize(q, p=2, dim=-1), F.normalize(k, p=2, dim=-1)
+        d["beta"] = torch.randn(B, T, H, generator=g0).sigmoid().to(dtype)
+        d["g"] = F.logsigmoid(torch.randn(B, T, H, generator=g0))
+        n_seq = 64 if op == "gated_delta_varlen" else B
+        d["h0"] = torch.randn(n_seq, H, K, V, generator=g0) * 0.1
+        if op == "gated_delta_varlen":
+            d["offsets"] = torch.cat([torch.zeros(1, dtype=torch.long), varlen_lengths().cumsum(0)]).int()
     if op in ("gated_delta", "delta"):
         q, k = F.normalize(q, p=2, dim=-1), F.normalize(k, p=2, dim=-1)
         d["beta"] = torch.randn(B, T, H, generator=g0).sigmoid().to(dtype)
@@ -75,11 +92,12 @@ def make_inputs(op, B, T, H, K, V, seed, dtype):
     d.update(q=q.to(dtype), k=k.to(dtype), v=v.to(dtype))
     d["do"] = torch.randn(B, T, H, V, generator=g0).to(dtype)
     if "h0" in d:
-        d["dht"] = torch.randn(B, H, K, V, generator=g0)
+        d["dht"] = torch.randn(d["h0"].shape, generator=g0)
     return d
 
 
-GRAD_NAMES = {"gated_delta": ["q", "k", "v", "g", "beta", "h0"], "delta": ["q", "k", "v", "beta", "h0"],
+GRAD_NAMES = {"gated_delta_varlen": ["q", "k", "v", "g", "beta", "h0"], "decode": [],
+              "gated_delta": ["q", "k", "v", "g", "beta", "h0"], "delta": ["q", "k", "v", "beta", "h0"],
               "simple_gla": ["q", "k", "v", "g"], "gla": ["q", "k", "v", "g", "h0"]}
 
 
@@ -96,6 +114,12 @@ def call_op(op, i, mod):
             return oracle.simple_gla(i["q"], i["k"], i["v"], i["g"], head_first=False)
         return oracle.gla(i["q"], i["k"], i["v"], gk=i["g"], initial_state=i["h0"], output_final_state=True, head_first=False)
     import fla_b200.ops as o
+    if op == "gated_delta_varlen":
+        return o.chunk_gated_delta_rule(i["q"], i["k"], i["v"], i["g"], i["beta"], initial_state=i["h0"], output_final_state=True,
+                                        cu_seqlens=i["offsets"], head_first=False)
+    if op == "decode":
+        return o.fused_recurrent_gated_delta_rule(i["q"], i["k"], i["v"], i["g"], i["beta"], initial_state=i["h0"],
+                                                  output_final_state=True, head_first=False)
     if op == "gated_delta":
         return o.chunk_gated_delta_rule(i["q"], i["k"], i["v"], i["g"], i["beta"], initial_state=i["h0"], output_final_state=st, head_first=False)
     if op == "delta":
@@ -106,6 +130,10 @@ def call_op(op, i, mod):
 
 
 def fwd_bwd(op, i, mod="ours"):
+    if op == "decode":  # forward only; the new state replaces the old one
+        o, ht = call_op(op, i, mod)
+        i["h0"] = ht
+        return o, ht
     for n in GRAD_NAMES[op]:
         i[n].grad = None
     o, ht = call_op(op, i, mod)
@@ -258,10 +286,14 @@ def main():
     args = ap.parse_args()
     op, B, T, H, K, V = WORKLOADS[args.workload]
     T = args.seq_len or T
+    if op == "gated_delta_varlen":
+        T = int(varlen_lengths().sum())
     dtype = torch.float32 if args.workload == "gla_fp32" else torch.bfloat16
+    if op in ("gated_delta_varlen", "decode"):
+        args.no_extras = True  # side workloads: device-resident timing (and the decode roofline) only
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
-    config = {"workload": f"chunk_{op} fwd+bwd {str(dtype).split('.')[-1]} B={B} T={T} H={H} K={K} V={V} seq-first, "
+    config = {"workload": f"{'fused_recurrent_gated_delta_rule decode step' if op == 'decode' else 'chunk_' + op + ' fwd+bwd'} {str(dtype).split('.')[-1]} B={B} T={T} H={H} K={K} V={V} seq-first, "
               f"initial_state given, output_final_state=True, per GPU", "timing": "inputs (>600 MB) larger than the 126 MB L2",
               "parallelism": f"{world} independent per-GPU batches (sequence x head shards, no collective)"}
 
@@ -322,6 +354,21 @@ def main():
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic", "config": config,
             "clocks": clk.summary(), "gpu_launches": launches}
+
+    if op == "decode" and rank == 0:
+        # the decode kernel alone (the public-API step above also pays Python / launch overhead per call)
+        from fla_b200.ops.recurrent import recurrent_delta_fwd
+        from fla_b200.utils import Geometry
+        geo = Geometry(i["k"], i["v"], None, False)
+        h0 = i["h0"].float().contiguous()
+        ms_k = time_stage(lambda: recurrent_delta_fwd(geo, i["q"], i["k"], i["v"], i["beta"], i["g"], K ** -0.5, h0, True, False),
+                          reps=50, warm=5)
+        pk = peaks()
+        nbytes = B * H * (2 * K * V * 4 + (2 * K + 2 * V) * 2 + 8)
+        ach = nbytes / (ms_k * 1e-3) / 1e9
+        line["roofline"] = {"kernel": "recurrent_fwd_kernel (decode)", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
+                            "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                            "ms_per_launch": ms_k}
 
     # ---- end to end: host buffers in, every result back to the host, inside the timed region
     if not args.no_extras:

@@ -1,48 +1,65 @@
 // Token-recurrent kernels (decode and the reference's test oracles).
 //
-// Forward: one thread owns one value column of the [K x V] state and keeps its K entries in
-// registers, so the per-token reductions over K (o = S^T q, the delta-rule correction S^T k) are
-// thread-local; a warp reads 32 adjacent columns, i.e. one 128-byte row segment of the fp32 state
-// per load.  The state is read once and written once per call - decode (T = 1) is a pure stream
-// over the state and runs at HBM speed.
+// Forward: the [K x V] state is register resident, rows split over the warps and 4 columns per lane
+// (512-byte row segments per warp access).  The state is read once and written once per call -
+// decode (T = 1) is a pure stream over the state and runs at HBM speed.
 //   generic gates g / gk / gv:  fla/ops/common/fused_recurrent.py:27-128
 //   delta rule (optional scalar gate): fla/ops/delta_rule/fused_recurrent.py:19-109,
 //                                      fla/ops/gated_delta_rule/fused_recurrent.py:19-110
 // Backward (training-time check path): the state lives in shared memory and every token does row
 // and column reductions over it (fla/ops/common/fused_recurrent.py:145-319,
 // fla/ops/delta_rule/fused_recurrent.py:118-290).
-#include "common.cuh"
+#include "tc.cuh"
+
+FLAB_TC_DEFINE_ERROR_WORD(recurrent_error)
 
 namespace flab {
 
-constexpr int RC_COLS = 32;  // value columns per CTA in the forward kernels (one warp wide)
+constexpr int RC_V = 128;     // value columns per CTA
+constexpr int RC_WARPS = 16;  // the K rows of the state are split over the warps
 
 // ------------------------------------------------------------------------------------------------
-// forward
+// forward.  CTA = (sequence, head, 128-wide V tile), 16 warps.  Warp w owns RPW consecutive state rows,
+// lane l owns 4 consecutive columns, so a warp instruction moves one full 512-byte row segment and a warp
+// streams RPW * 512 contiguous bytes of the fp32 state: decode (T = 1) is one coalesced pass over it.
+// The reductions over K (o = S^T q and the delta-rule correction S^T k) are thread-local over the
+// warp's rows, then summed across the warps through shared memory (one barrier pair per token).
+// The delta rule needs both reductions before the rank-1 update; using
+//   o = (S + k v'^T)^T q = S^T q + v' (k.q)
+// both are taken in the same pass over the (decayed) state.
 // ------------------------------------------------------------------------------------------------
-template <typename T, int KPT, bool DELTA>
-__global__ void __launch_bounds__(RC_COLS * 2) recurrent_fwd_kernel(const flab_args a) {
-  // blockDim = (32, KG): KG groups split K when K > KPT
+template <typename T, int RPW, bool DELTA>
+__global__ void __launch_bounds__(RC_WARPS * 32, (RPW <= 8 ? 2 : 1)) recurrent_fwd_kernel(const flab_args a) {
   __shared__ float sQ[256], sK[256], sE[256];  // q*scale, k, exp(gk) of the current token
-  __shared__ float sRed[2][2][RC_COLS];        // cross-group partial sums
-  const int KG = blockDim.y, kg = threadIdx.y, lane = threadIdx.x;
-  const int tid = kg * RC_COLS + lane, nthr = RC_COLS * KG;
+  __shared__ float sRed[2][RC_WARPS][RC_V];    // cross-warp partial sums
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = blockIdx.y / a.H, hd = blockIdx.y % a.H;
   const Seq s = seq_of(a, n);
-  const int col = blockIdx.x * RC_COLS + lane;
-  const bool cok = col < a.V;
-  const int kbase = kg * KPT;
   const int K = a.K, V = a.V;
+  const int c0 = blockIdx.x * RC_V + 4 * lane;  // first of this lane's 4 columns
+  const int r0 = warp * RPW;
   const bool rev = (a.flags & FLAB_F_REVERSE) != 0;
   const bool beta_vec = (a.flags & FLAB_F_BETA_VECTOR) != 0;
+  const bool vec4 = (V % 4 == 0);  // rows of h0 / ht are then 16-byte aligned at every c0
 
-  float S[KPT];
+  float S[RPW][4];
   const size_t st_off = ((size_t)n * a.H + hd) * K * V;
   const float *h0 = reinterpret_cast<const float *>(a.h0);
 #pragma unroll
-  for (int i = 0; i < KPT; ++i) {
-    int kk = kbase + i;
-    S[i] = (h0 && cok && kk < K) ? h0[st_off + (size_t)kk * V + col] : 0.f;
+  for (int i = 0; i < RPW; ++i) {
+    const int kk = r0 + i;
+    S[i][0] = S[i][1] = S[i][2] = S[i][3] = 0.f;
+    if (h0 && kk < K) {
+      const float *p = h0 + st_off + (size_t)kk * V + c0;
+      if (vec4 && c0 + 3 < V) {
+        const float4 x = *reinterpret_cast<const float4 *>(p);
+        S[i][0] = x.x, S[i][1] = x.y, S[i][2] = x.z, S[i][3] = x.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (c0 + j < V) S[i][j] = p[j];
+      }
+    }
   }
   const T *q = reinterpret_cast<const T *>(a.q), *k = reinterpret_cast<const T *>(a.k), *v = reinterpret_cast<const T *>(a.v);
   const float *g = reinterpret_cast<const float *>(a.g), *gk = reinterpret_cast<const float *>(a.gk),
@@ -52,85 +69,334 @@ __global__ void __launch_bounds__(RC_COLS * 2) recurrent_fwd_kernel(const flab_a
   for (int i_t = 0; i_t < s.len; ++i_t) {
     const int t = rev ? s.len - 1 - i_t : i_t;
     const size_t ok_ = tok_off(a, s, hd, t, K), ov = tok_off(a, s, hd, t, V), o1 = tok_off(a, s, hd, t, 1);
-    __syncthreads();
-    for (int i = tid; i < K; i += nthr) {
+    __syncthreads();  // previous token's shared vectors and partial sums are consumed
+    for (int i = tid; i < K; i += RC_WARPS * 32) {
       sQ[i] = Num<T>::f(q[ok_ + i]) * a.scale;
       sK[i] = Num<T>::f(k[ok_ + i]);
       if (gk) sE[i] = expf(gk[ok_ + i]);
     }
+    float vv[4], dec[4], bb[4];
+    const float eg = g ? expf(g[o1]) : 1.f;
+    const float bs = (DELTA && beta && !beta_vec) ? Num<T>::f(beta[o1]) : 1.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool ok = c0 + j < V;
+      vv[j] = ok ? Num<T>::f(v[ov + c0 + j]) : 0.f;
+      dec[j] = (gv && ok) ? eg * expf(gv[ov + c0 + j]) : eg;
+      bb[j] = (DELTA && beta && beta_vec) ? (ok ? Num<T>::f(beta[ov + c0 + j]) : 0.f) : bs;
+    }
     __syncthreads();
-    float vv = cok ? Num<T>::f(v[ov + col]) : 0.f;
-    float dec = 1.f;
-    if (g) dec = expf(g[o1]);
-    if (gv && cok) dec *= expf(gv[ov + col]);
-    float o_acc = 0.f;
+    float pq[4] = {0.f, 0.f, 0.f, 0.f}, pk[4] = {0.f, 0.f, 0.f, 0.f};
     if (!DELTA) {
 #pragma unroll
-      for (int i = 0; i < KPT; ++i) {
-        int kk = kbase + i;
+      for (int i = 0; i < RPW; ++i) {
+        const int kk = r0 + i;
         if (kk < K) {
-          float e = gk ? dec * sE[kk] : dec;
-          S[i] = S[i] * e + sK[kk] * vv;
-          o_acc = fmaf(S[i], sQ[kk], o_acc);
+          const float e = gk ? sE[kk] : 1.f, kv = sK[kk], qv = sQ[kk];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            S[i][j] = S[i][j] * (e * dec[j]) + kv * vv[j];
+            pq[j] = fmaf(S[i][j], qv, pq[j]);
+          }
         }
       }
     } else {
-      float p = 0.f;
 #pragma unroll
-      for (int i = 0; i < KPT; ++i) {
-        int kk = kbase + i;
+      for (int i = 0; i < RPW; ++i) {
+        const int kk = r0 + i;
         if (kk < K) {
-          S[i] *= dec;
-          p = fmaf(S[i], sK[kk], p);
-        }
-      }
-      if (KG > 1) {
-        sRed[0][kg][lane] = p;
-        __syncthreads();
-        p = sRed[0][0][lane] + sRed[0][1][lane];
-      }
-      float u_ = vv - p;
-      if (a.u && cok && kg == 0) reinterpret_cast<T *>(a.u)[ov + col] = Num<T>::t(u_);
-      float b = 1.f;
-      if (beta) b = beta_vec ? (cok ? Num<T>::f(beta[ov + col]) : 0.f) : Num<T>::f(beta[o1]);
-      float vn = u_ * b;
+          const float kv = sK[kk], qv = sQ[kk];
 #pragma unroll
-      for (int i = 0; i < KPT; ++i) {
-        int kk = kbase + i;
-        if (kk < K) {
-          S[i] = fmaf(sK[kk], vn, S[i]);
-          o_acc = fmaf(S[i], sQ[kk], o_acc);
+          for (int j = 0; j < 4; ++j) {
+            S[i][j] *= dec[j];
+            pk[j] = fmaf(S[i][j], kv, pk[j]);
+            pq[j] = fmaf(S[i][j], qv, pq[j]);
+          }
         }
       }
     }
-    if (KG > 1) {
-      sRed[1][kg][lane] = o_acc;
-      __syncthreads();
-      o_acc = sRed[1][0][lane] + sRed[1][1][lane];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sRed[0][warp][4 * lane + j] = pq[j];
+      if (DELTA) sRed[1][warp][4 * lane + j] = pk[j];
     }
-    if (cok && kg == 0) {
-      if (DELTA) reinterpret_cast<T *>(a.o)[ov + col] = Num<T>::t(o_acc);
-      else reinterpret_cast<float *>(a.o)[ov + col] = o_acc;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float x = 0.f, y = 0.f;
+#pragma unroll
+      for (int w = 0; w < RC_WARPS; ++w) {
+        x += sRed[0][w][4 * lane + j];
+        if (DELTA) y += sRed[1][w][4 * lane + j];
+      }
+      pq[j] = x;
+      pk[j] = y;
+    }
+    if (DELTA) {
+      // k . q over all K (every warp computes it; q is already scaled)
+      float kq = 0.f;
+      for (int i = lane; i < K; i += 32) kq = fmaf(sK[i], sQ[i], kq);
+      kq = warp_sum(kq);
+      float vn[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float u_ = vv[j] - pk[j];
+        if (a.u && warp == 0 && c0 + j < V) reinterpret_cast<T *>(a.u)[ov + c0 + j] = Num<T>::t(u_);
+        vn[j] = u_ * bb[j];
+        pq[j] = fmaf(vn[j], kq, pq[j]);
+      }
+#pragma unroll
+      for (int i = 0; i < RPW; ++i) {
+        const int kk = r0 + i;
+        if (kk < K) {
+          const float kv = sK[kk];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) S[i][j] = fmaf(kv, vn[j], S[i][j]);
+        }
+      }
+    }
+    if (warp == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c0 + j < V) {
+          if (DELTA) reinterpret_cast<T *>(a.o)[ov + c0 + j] = Num<T>::t(pq[j]);
+          else reinterpret_cast<float *>(a.o)[ov + c0 + j] = pq[j];
+        }
     }
   }
   float *ht = reinterpret_cast<float *>(a.ht);
-  if (ht && cok) {
+  if (ht) {
 #pragma unroll
-    for (int i = 0; i < KPT; ++i) {
-      int kk = kbase + i;
-      if (kk < K) ht[st_off + (size_t)kk * V + col] = S[i];
+    for (int i = 0; i < RPW; ++i) {
+      const int kk = r0 + i;
+      if (kk < K) {
+        float *p = ht + st_off + (size_t)kk * V + c0;
+        if (vec4 && c0 + 3 < V) {
+          *reinterpret_cast<float4 *>(p) = make_float4(S[i][0], S[i][1], S[i][2], S[i][3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (c0 + j < V) p[j] = S[i][j];
+        }
+      }
     }
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Streaming variant of the delta-rule recurrence for V == 128, K <= 128 with an initial state (the
+// decode configuration).  Persistent CTAs, one per SM, 8 consumer warps + 1 producer warp:
+//  * the 64 KB fp32 state tile of each (sequence, head) arrives through a 3-deep ring of bulk async
+//    copies (one cp.async.bulk per tile, completion on an mbarrier); the producer refills a slot as
+//    soon as the 8 consumer warps have drained it into registers (an "empty" mbarrier, no CTA barrier);
+//  * a consumer warp owns 16 state rows, a lane 4 columns; the k / q values of the warp's rows sit in
+//    one register per lane (lanes 0-15: k, lanes 16-31: q*scale) and are broadcast with shuffles; they
+//    and v, g, beta are fetched one token ahead, so no global-load latency is exposed;
+//  * one named barrier per token (the cross-warp reduction of S^T k, S^T q and k.q, double buffered);
+//  * the new state goes straight from registers to global memory with 512-byte warp stores.
+// ------------------------------------------------------------------------------------------------
+constexpr int RS_STAGES = 3;
+
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   tc::smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(tc::smem_u32(bar))
+               : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(288, 1) recurrent_stream_kernel(const flab_args a, int n_items) {
+  using namespace tc;
+  constexpr int RPW = 16;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  float *sState = reinterpret_cast<float *>(smem_raw);  // [RS_STAGES][128][128]
+  __shared__ __align__(16) float sRed[2][2][8][RC_V];   // [parity][S^T q | S^T k][warp][column]
+  __shared__ float sKQ[2][8];
+  __shared__ uint64_t full[RS_STAGES], empty[RS_STAGES];
+  __shared__ volatile int fail_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int K = a.K, V = a.V;  // V == 128
+  const uint32_t tile_bytes = (uint32_t)K * RC_V * sizeof(float);
+  const float *h0 = reinterpret_cast<const float *>(a.h0);
+  float *ht = reinterpret_cast<float *>(a.ht);
+  const T *q = reinterpret_cast<const T *>(a.q), *k = reinterpret_cast<const T *>(a.k), *v = reinterpret_cast<const T *>(a.v);
+  const float *g = reinterpret_cast<const float *>(a.g);
+  const T *beta = reinterpret_cast<const T *>(a.beta);
+  const bool beta_vec = (a.flags & FLAB_F_BETA_VECTOR) != 0;
+  const int n_local = n_items > (int)blockIdx.x ? (n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  if (tid == 0) {
+    for (int i = 0; i < RS_STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 8);
+    }
+    fail_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+  if (warp == 8) {
+    // -------------------------------------------------------------------------------- producer
+    if (lane == 0) {
+      for (int i = 0; i < n_local && !fail_flag; ++i) {
+        const int st = i % RS_STAGES;
+        if (!mbar_wait(&empty[st], ((i / RS_STAGES) & 1) ^ 1)) {
+          atomicCAS(&tu_tc_error, 0, 21);
+          fail_flag = 1;
+          break;
+        }
+        const int item = blockIdx.x + i * gridDim.x;
+        mbar_expect_tx(&full[st], tile_bytes);
+        bulk_load(sState + (size_t)st * 128 * RC_V, h0 + (size_t)item * K * V, tile_bytes, &full[st]);
+      }
+    }
+    return;
+  }
+  // ---------------------------------------------------------------------------------- consumers
+  const int c0 = 4 * lane, r0 = warp * RPW;
+  float n_kq = 0.f, n_v[4] = {0.f, 0.f, 0.f, 0.f}, n_b[4] = {1.f, 1.f, 1.f, 1.f}, n_eg = 1.f;
+  auto fetch = [&](int li, int i_t) {  // vectors of token i_t of local item li -> registers
+    if (li >= n_local) return;
+    const int item = blockIdx.x + li * gridDim.x;
+    const int n = item / a.H, hd = item % a.H;
+    const Seq s = seq_of(a, n);
+    if (i_t >= s.len) return;
+    const size_t ok_ = tok_off(a, s, hd, i_t, K), ov = tok_off(a, s, hd, i_t, V), o1 = tok_off(a, s, hd, i_t, 1);
+    const int row = r0 + (lane & 15);
+    n_kq = 0.f;
+    if (row < K) n_kq = lane < 16 ? Num<T>::f(k[ok_ + row]) : Num<T>::f(q[ok_ + row]) * a.scale;
+    n_eg = g ? expf(g[o1]) : 1.f;
+    const float bs = (beta && !beta_vec) ? Num<T>::f(beta[o1]) : 1.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      n_v[j] = Num<T>::f(v[ov + c0 + j]);
+      n_b[j] = (beta && beta_vec) ? Num<T>::f(beta[ov + c0 + j]) : bs;
+    }
+  };
+  fetch(0, 0);
+  int par = 0;
+  for (int i = 0; i < n_local; ++i) {
+    const int item = blockIdx.x + i * gridDim.x;
+    const int n = item / a.H, hd = item % a.H;
+    const Seq s = seq_of(a, n);
+    const int st = i % RS_STAGES;
+    if (fail_flag) break;
+    if (!mbar_wait(&full[st], (i / RS_STAGES) & 1)) {
+      atomicCAS(&tu_tc_error, 0, 20);
+      fail_flag = 1;
+      break;
+    }
+    float S[RPW][4];
+    const float *tile = sState + (size_t)st * 128 * RC_V;
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      const int kk = r0 + r;
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (kk < K) x = *reinterpret_cast<const float4 *>(tile + (size_t)kk * RC_V + c0);
+      S[r][0] = x.x, S[r][1] = x.y, S[r][2] = x.z, S[r][3] = x.w;
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[st]);  // this warp has drained the slot
+
+    for (int i_t = 0; i_t < s.len; ++i_t) {
+      const size_t ov = tok_off(a, s, hd, i_t, V);
+      const float kq_reg = n_kq, eg = n_eg;
+      float vv[4], bb[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) vv[j] = n_v[j], bb[j] = n_b[j];
+      if (i_t + 1 < s.len) fetch(i, i_t + 1); else fetch(i + 1, 0);
+      float pq[4] = {0.f, 0.f, 0.f, 0.f}, pk[4] = {0.f, 0.f, 0.f, 0.f}, kq_part = 0.f;
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        const float kv = __shfl_sync(0xffffffffu, kq_reg, r), qv = __shfl_sync(0xffffffffu, kq_reg, 16 + r);
+        kq_part = fmaf(kv, qv, kq_part);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          S[r][j] *= eg;
+          pk[j] = fmaf(S[r][j], kv, pk[j]);
+          pq[j] = fmaf(S[r][j], qv, pq[j]);
+        }
+      }
+      *reinterpret_cast<float4 *>(&sRed[par][0][warp][c0]) = make_float4(pq[0], pq[1], pq[2], pq[3]);
+      *reinterpret_cast<float4 *>(&sRed[par][1][warp][c0]) = make_float4(pk[0], pk[1], pk[2], pk[3]);
+      if (lane == 0) sKQ[par][warp] = kq_part;
+      named_barrier(1, 256);
+      float kq = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pq[j] = pk[j] = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const float4 x = *reinterpret_cast<const float4 *>(&sRed[par][0][w][c0]);
+        const float4 y = *reinterpret_cast<const float4 *>(&sRed[par][1][w][c0]);
+        pq[0] += x.x, pq[1] += x.y, pq[2] += x.z, pq[3] += x.w;
+        pk[0] += y.x, pk[1] += y.y, pk[2] += y.z, pk[3] += y.w;
+        kq += sKQ[par][w];
+      }
+      par ^= 1;
+      float vn[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float u_ = vv[j] - pk[j];
+        if (a.u && warp == 0) reinterpret_cast<T *>(a.u)[ov + c0 + j] = Num<T>::t(u_);
+        vn[j] = u_ * bb[j];
+        pq[j] = fmaf(vn[j], kq, pq[j]);
+      }
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        const float kv = __shfl_sync(0xffffffffu, kq_reg, r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) S[r][j] = fmaf(kv, vn[j], S[r][j]);
+      }
+      if (warp == 0) {
+        if (sizeof(T) == 2) {
+          uint2 pkd;
+          if (Num<T>::id == FLAB_BF16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(pq[0], pq[1]), hi = __floats2bfloat162_rn(pq[2], pq[3]);
+            pkd.x = *reinterpret_cast<uint32_t *>(&lo), pkd.y = *reinterpret_cast<uint32_t *>(&hi);
+          } else {
+            __half2 lo = __floats2half2_rn(pq[0], pq[1]), hi = __floats2half2_rn(pq[2], pq[3]);
+            pkd.x = *reinterpret_cast<uint32_t *>(&lo), pkd.y = *reinterpret_cast<uint32_t *>(&hi);
+          }
+          *reinterpret_cast<uint2 *>(reinterpret_cast<T *>(a.o) + ov + c0) = pkd;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) reinterpret_cast<T *>(a.o)[ov + c0 + j] = Num<T>::t(pq[j]);
+        }
+      }
+    }
+    if (ht) {
+      float *dst = ht + (size_t)item * K * V;
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        const int kk = r0 + r;
+        if (kk < K) *reinterpret_cast<float4 *>(dst + (size_t)kk * V + c0) = make_float4(S[r][0], S[r][1], S[r][2], S[r][3]);
+      }
+    }
+  }
+}
+
+template <typename T> static int launch_recurrent_stream(const flab_args *a, cudaStream_t stream) {
+  const size_t smem = (size_t)RS_STAGES * 128 * RC_V * sizeof(float);
+  auto kern = recurrent_stream_kernel<T>;
+  if (int e = set_smem(kern, smem)) return e;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int n_items = a->N * a->H;
+  kern<<<n_items < sms ? n_items : sms, 288, smem, stream>>>(*a, n_items);
+  return check_launch("recurrent_delta_fwd(stream)");
+}
+
 template <typename T, bool DELTA> static int launch_recurrent_fwd(const flab_args *a, cudaStream_t stream) {
-  dim3 grid(cdiv(a->V, RC_COLS), a->N * a->H);
+  if (DELTA && a->V == RC_V && a->K <= 128 && a->K % 4 == 0 && a->h0 && reinterpret_cast<uintptr_t>(a->h0) % 16 == 0 &&
+      (!a->ht || reinterpret_cast<uintptr_t>(a->ht) % 16 == 0) && reinterpret_cast<uintptr_t>(a->o) % 8 == 0)
+    return launch_recurrent_stream<T>(a, stream);
+  dim3 grid(cdiv(a->V, RC_V), a->N * a->H);
   if (a->K <= 64) {
-    recurrent_fwd_kernel<T, 64, DELTA><<<grid, dim3(RC_COLS, 1), 0, stream>>>(*a);
+    recurrent_fwd_kernel<T, 4, DELTA><<<grid, RC_WARPS * 32, 0, stream>>>(*a);
   } else if (a->K <= 128) {
-    recurrent_fwd_kernel<T, 128, DELTA><<<grid, dim3(RC_COLS, 1), 0, stream>>>(*a);
+    recurrent_fwd_kernel<T, 8, DELTA><<<grid, RC_WARPS * 32, 0, stream>>>(*a);
   } else {
-    recurrent_fwd_kernel<T, 128, DELTA><<<grid, dim3(RC_COLS, 2), 0, stream>>>(*a);
+    recurrent_fwd_kernel<T, 16, DELTA><<<grid, RC_WARPS * 32, 0, stream>>>(*a);
   }
   return check_launch(DELTA ? "recurrent_delta_fwd" : "recurrent_fwd");
 }
