@@ -1,0 +1,134 @@
+# -*- coding: utf-8 -*-
+"""Multi-GPU use of the path (one process per GPU, torch.distributed).
+
+* Units of work are (sequence, head) pairs with no data flow between them, so batches shard with no
+  collective at all: `shard_batch_heads` (fixed length) and `shard_sequences` (packed variable length,
+  token-balanced) only plan who owns what.
+* One very long sequence is split along T ("sequence parallel"): every recurrence on this path is affine in
+  the state, S_out = M S_in + b with M a [K,K] matrix per head that does not depend on S_in.  A rank
+  obtains (M, b) of its slab from ONE extra state scan whose value dimension is widened by K identity
+  columns, the boundary states are then passed rank to rank (point-to-point send/recv, [H,K,V] fp32 = 1 MiB
+  at H=16, K=V=128), and a local correction pass recomputes the slab with its true initial state.
+  The reference has no such mode; its unused two-level scan (fla/ops/common/chunk_h_split.py:164-260) only
+  covers diagonal decay.
+"""
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+# ---------------------------------------------------------------------------------------------
+# planners (pure host logic)
+# ---------------------------------------------------------------------------------------------
+def shard_batch_heads(B: int, H: int, world: int, rank: int) -> Tuple[slice, slice]:
+    """Slices of the batch and head axes owned by `rank`: the batch is split first, heads only when there are
+    more ranks than batch rows. Every (row, head) pair is owned by exactly one rank."""
+    if world <= B:
+        lo, hi = (B * rank) // world, (B * (rank + 1)) // world
+        return slice(lo, hi), slice(0, H)
+    if world % B != 0 or H % (world // B) != 0:
+        raise ValueError(f"cannot split B={B}, H={H} evenly over {world} ranks")
+    per_row = world // B
+    b, part = rank // per_row, rank % per_row
+    hs = H // per_row
+    return slice(b, b + 1), slice(part * hs, (part + 1) * hs)
+
+
+def shard_sequences(lengths: Sequence[int], world: int) -> List[List[int]]:
+    """Token-balanced partition of whole sequences (longest-processing-time greedy). Returns, per rank, the
+    ids of its sequences in ascending order."""
+    order = sorted(range(len(lengths)), key=lambda i: -int(lengths[i]))
+    load = [0] * world
+    owned: List[List[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (load[j], j))
+        owned[r].append(i)
+        load[r] += int(lengths[i])
+    return [sorted(o) for o in owned]
+
+
+def rebased_offsets(lengths: Sequence[int], ids: Sequence[int]) -> torch.Tensor:
+    """`offsets` ([len(ids)+1], int64) of the packed batch made of the sequences `ids`."""
+    out = [0]
+    for i in ids:
+        out.append(out[-1] + int(lengths[i]))
+    return torch.tensor(out, dtype=torch.long)
+
+
+def gather_packed(x: torch.Tensor, offsets: Sequence[int], ids: Sequence[int]) -> torch.Tensor:
+    """Rows of the packed tensor x [1, T, ...] that belong to the sequences `ids`, re-packed."""
+    return torch.cat([x[:, int(offsets[i]):int(offsets[i + 1])] for i in ids], dim=1)
+
+
+# ---------------------------------------------------------------------------------------------
+# sequence parallel state hand-off
+# ---------------------------------------------------------------------------------------------
+def handoff_states(M: torch.Tensor, b: torch.Tensor, S0: Optional[torch.Tensor], group=None,
+                   reverse: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Chain S_out = M S_in + b across the ranks of `group`.
+
+    M: [H,K,K], b: [H,K,V] fp32 of THIS rank's slab. The chain starts at rank 0 (at the last rank when
+    `reverse`) with S0 (zeros when None). Returns (S_in, S_out) of this rank. One blocking recv and one send per
+    rank; on GPUs this is NCCL point-to-point over NVLink.
+    """
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    first, step = (world - 1, -1) if reverse else (0, 1)
+    prev, nxt = rank - step, rank + step
+    if rank == first:
+        S_in = torch.zeros_like(b) if S0 is None else S0.to(b.dtype).reshape(b.shape).contiguous()
+    else:
+        S_in = torch.empty_like(b)
+        dist.recv(S_in, src=dist.get_global_rank(group, prev) if group is not None else prev, group=group)
+    S_out = torch.baddbmm(b, M, S_in)
+    if 0 <= nxt < world:
+        dist.send(S_out, dst=dist.get_global_rank(group, nxt) if group is not None else nxt, group=group)
+    return S_in, S_out
+
+
+def broadcast_from(x: torch.Tensor, src_rank: int, group=None) -> torch.Tensor:
+    dist.broadcast(x, src=dist.get_global_rank(group, src_rank) if group is not None else src_rank, group=group)
+    return x
+
+
+def _fwd_slab(q, k, v, g, beta, scale, S_in_of):
+    """Forward of one rank's slab. `S_in_of(M, b)` maps the slab's transition to its true initial state (this is
+    where the communication happens). Returns (o, S_out, saved tensors for backward)."""
+    from .ops import common as C
+    from .utils import Geometry
+    geo = Geometry(k, v, None, False)
+    H, K, V = geo.H, geo.K, geo.V
+    g_cum = C.chunk_local_cumsum(g, head_first=False)
+    aw, au, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta, g=g_cum)
+    # one widened scan: value columns [u | 0], initial state [0 | I]  ->  final state [b | M]
+    u_ext = torch.cat([u, torch.zeros_like(k)], dim=-1)
+    h0_ext = torch.cat([torch.zeros(1, H, K, V, device=k.device), torch.eye(K, device=k.device).expand(1, H, K, K)], dim=-1)
+    geo_ext = Geometry(k, u_ext, None, False)
+    _, _, ht_ext = C.chunk_gated_delta_rule_fwd_h(geo_ext, k, w, u_ext, g=g_cum, h0=h0_ext.contiguous(), output_final_state=True)
+    b, M = ht_ext[0, :, :, :V].contiguous(), ht_ext[0, :, :, V:].contiguous()
+    S_in, S_out = S_in_of(M, b)
+    # correction pass with the true initial state
+    h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g_cum, h0=S_in.unsqueeze(0), output_final_state=False)
+    o = C.chunk_fwd_o(geo, q, k, v_new, h, g=g_cum, scale=scale)
+    return o, S_out, (g_cum, aw, au, w, h, v_new, geo)
+
+
+def sp_chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, group=None):
+    """Forward of chunk_gated_delta_rule for ONE sequence split along T over the ranks of `group`.
+
+    Every rank passes its own contiguous slab (seq-first, B = 1, slab length a multiple of 64 except on the last
+    rank); rank r's slab follows rank r-1's. `initial_state` ([1,H,K,V]) is read on rank 0. Returns (o of the
+    slab, final state of the whole sequence on every rank or None). Forward only.
+    """
+    assert q.shape[0] == 1, "sequence parallel mode takes one sequence (B = 1) per call"
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    assert rank == world - 1 or q.shape[1] % 64 == 0, "slabs before the last one must be multiples of 64 tokens"
+    scale = k.shape[-1] ** -0.5 if scale is None else scale
+    q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
+    S0 = None if initial_state is None else initial_state.float()[0]
+    o, S_out, _ = _fwd_slab(q, k, v, g.float(), beta.to(k.dtype), scale, lambda M, b: handoff_states(M, b, S0, group))
+    ht = None
+    if output_final_state:
+        ht = broadcast_from(S_out.clone(), world - 1, group).unsqueeze(0)
+    return o, ht

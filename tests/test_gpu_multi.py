@@ -1,0 +1,51 @@
+"""GPU (needs >= 2 devices): sequence-parallel forward over NCCL against the single-GPU result."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+import torch.nn.functional as F
+
+from util import err_ratio
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from fla_b200.ops import chunk_gated_delta_rule
+        from fla_b200.parallel import sp_chunk_gated_delta_rule_fwd
+        g0 = torch.Generator().manual_seed(11)
+        T, H, K, V = 1024 * world + 37, 4, 128, 128   # ragged tail on the last rank
+        q = F.normalize(torch.randn(1, T, H, K, generator=g0), dim=-1).bfloat16().cuda()
+        k = F.normalize(torch.randn(1, T, H, K, generator=g0), dim=-1).bfloat16().cuda()
+        v = torch.randn(1, T, H, V, generator=g0).bfloat16().cuda()
+        g = F.logsigmoid(torch.randn(1, T, H, generator=g0)).cuda()
+        beta = torch.rand(1, T, H, generator=g0).sigmoid().bfloat16().cuda()
+        h0 = (torch.randn(1, H, K, V, generator=g0) * 0.1).cuda()
+        with torch.no_grad():
+            o_ref, ht_ref = chunk_gated_delta_rule(q, k, v, g, beta, initial_state=h0, output_final_state=True, head_first=False)
+        lo, hi = 1024 * rank, (1024 * (rank + 1) if rank < world - 1 else T)
+        sl = slice(lo, hi)
+        o, ht = sp_chunk_gated_delta_rule_fwd(q[:, sl], k[:, sl], v[:, sl], g[:, sl], beta[:, sl], initial_state=h0,
+                                              output_final_state=True)
+        torch.cuda.synchronize()
+        ret[rank] = (err_ratio(o_ref[:, sl], o), err_ratio(ht_ref, ht))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sequence_parallel_forward_matches_single_gpu():
+    world = min(torch.cuda.device_count(), 4)
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker, args=(world, 29700, ret), nprocs=world, join=True)
+        for r in range(world):
+            eo, eh = ret[r]
+            print(f"rank {r}: o {eo:.2e} ht {eh:.2e}")
+            assert eo < 5e-3 and eh < 5e-3
