@@ -148,10 +148,10 @@ template <typename T, int MODE> static int launch_chunk_o(const flab_args *a, cu
 // ------------------------------------------------------------------------------------------------
 constexpr int QB = 64;  // K tile
 
-template <typename T, bool USE_DW>
-__global__ void __launch_bounds__(256) chunk_dqkwg_kernel(const flab_args a) {
+template <typename T, bool USE_DW, int VPT /* padded V known at compile time, or 0 */>
+__global__ void __launch_bounds__(256, 2) chunk_dqkwg_kernel(const flab_args a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int VP = round_up(a.V, 16);
+  const int VP = VPT > 0 ? VPT : round_up(a.V, 16);
   const int LDV = VP + Num<T>::pad;
   constexpr int LDK = QB + Num<T>::pad;
   constexpr int LDP = C + Num<T>::pad;
@@ -207,13 +207,13 @@ __global__ void __launch_bounds__(256) chunk_dqkwg_kernel(const flab_args a) {
   WarpGemm<1, 4, false, false, T>::run(ds, sDO, LDV, m0, sV, LDV, n0, VP);
   FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
     float x = ds[mi][ni][r];
-    x = (row >= col) ? (use_g ? x * safe_exp(sG[row] - sG[col]) : x) * a.scale : 0.f;
+    x = (row >= col) ? (use_g ? x * safe_fexp<T>(sG[row] - sG[col]) : x) * a.scale : 0.f;
     ds[mi][ni][r] = x;
   }
   acc_to_smem<1, 4, T>(ds, sDS, LDP, m0, n0);
 
-  const float e_lo = use_g ? expf(sG[m0 + g8]) : 1.f, e_hi = use_g ? expf(sG[m0 + g8 + 8]) : 1.f;
-  const float f_lo = use_g ? safe_exp(sG[last] - sG[m0 + g8]) : 1.f, f_hi = use_g ? safe_exp(sG[last] - sG[m0 + g8 + 8]) : 1.f;
+  const float e_lo = use_g ? fexp<T>(sG[m0 + g8]) : 1.f, e_hi = use_g ? fexp<T>(sG[m0 + g8 + 8]) : 1.f;
+  const float f_lo = use_g ? safe_fexp<T>(sG[last] - sG[m0 + g8]) : 1.f, f_hi = use_g ? safe_fexp<T>(sG[last] - sG[m0 + g8 + 8]) : 1.f;
   float dg_lo = 0.f, dg_hi = 0.f;  // per-row partial of dg for rows m0+g8 and m0+g8+8
   float hdh = 0.f, dkk = 0.f;
 
@@ -238,13 +238,7 @@ __global__ void __launch_bounds__(256) chunk_dqkwg_kernel(const flab_args a) {
       acc_zero(dw);
       WarpGemm<1, 4, false, false, T>::run(dw, sDV, LDV, m0, sH, LDV, n0, VP);
     }
-    if (use_g) {
-      for (int e = tid; e < kw * (VP / 2); e += 256) {
-        const int r_ = e / (VP / 2), c_ = (e - r_ * (VP / 2)) * 2;
-        hdh += Num<T>::f(sH[r_ * LDV + c_]) * Num<T>::f(sDH[r_ * LDV + c_]) +
-               Num<T>::f(sH[r_ * LDV + c_ + 1]) * Num<T>::f(sDH[r_ * LDV + c_ + 1]);
-      }
-    }
+    if (use_g) hdh += tile_dot<T>(sH, sDH, LDV, kw, VP, tid, 256);
     __syncthreads();  // every warp is done with h / dh
     tile_load<T>(sQ, LDK, reinterpret_cast<const T *>(a.q) + offk + k0, ks, rows, C, kw, QB, tid, 256);
     tile_load<T>(sK, LDK, reinterpret_cast<const T *>(a.k) + offk + k0, ks, rows, C, kw, QB, tid, 256);
@@ -343,10 +337,15 @@ template <typename T, bool USE_DW> static int launch_dqkwg(const flab_args *a, c
   const size_t usz = (size_t)(2 * QB * LDV > nt3 * C * LDK ? 2 * QB * LDV : nt3 * C * LDK);
   size_t elems = (size_t)nt3 * C * LDV + usz + (size_t)C * LDP;
   size_t smem = elems * sizeof(T) + (2 * C + 4) * sizeof(float);
-  auto kern = chunk_dqkwg_kernel<T, USE_DW>;
-  if (int e = set_smem(kern, smem)) return e;
   dim3 grid(a->NT, a->H);
-  kern<<<grid, 256, smem, stream>>>(*a);
+#define FLAB_LAUNCH_DQKWG(VPT)                                   \
+  {                                                              \
+    auto kern = chunk_dqkwg_kernel<T, USE_DW, VPT>;              \
+    if (int e = set_smem(kern, smem)) return e;                  \
+    kern<<<grid, 256, smem, stream>>>(*a);                       \
+  }
+  if (VP == 128) FLAB_LAUNCH_DQKWG(128) else if (VP == 64) FLAB_LAUNCH_DQKWG(64) else FLAB_LAUNCH_DQKWG(0)
+#undef FLAB_LAUNCH_DQKWG
   return check_launch("chunk_bwd_dqkwg");
 }
 

@@ -115,17 +115,27 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 // when r < rows_valid and c < D and is zero otherwise.  Uses 16-byte cp.async when addresses allow,
 // scalar loads otherwise; the caller must cp_async_commit / wait and __syncthreads before use.
 template <typename T>
-__device__ __forceinline__ void tile_load(T *s, int ld, const T *g, size_t rstride, int rows_valid,
-                                          int rows_total, int D, int DP, int tid, int nthreads) {
+__device__ __forceinline__ void tile_load(T *s, int ld, const T *g, size_t rstride, int rows_valid, int rows_total, int D,
+                                          int DP, int tid, int nthreads) {
   constexpr int EPV = 16 / sizeof(T);
   const bool vec = (D % EPV == 0) && ((rstride * sizeof(T)) % 16 == 0) && (((uintptr_t)g) % 16 == 0);
   if (vec) {
     const int cpr = DP / EPV;  // 16-byte pieces per row
-    for (int i = tid; i < rows_total * cpr; i += nthreads) {
-      int r = i / cpr, c = (i - r * cpr) * EPV;
-      bool ok = (r < rows_valid) && (c < D);
-      const T *src = ok ? (g + (size_t)r * rstride + c) : g;
-      cp_async16(s + r * ld + c, src, ok);
+    if ((cpr & (cpr - 1)) == 0) {
+      // power-of-two row length (the common case): shifts instead of divisions
+      const int sh = 31 - __clz(cpr);
+      for (int i = tid; i < (rows_total << sh); i += nthreads) {
+        const int r = i >> sh, c = (i & (cpr - 1)) * EPV;
+        const bool ok = (r < rows_valid) && (c < D);
+        cp_async16(s + r * ld + c, ok ? (g + (size_t)r * rstride + c) : g, ok);
+      }
+    } else {
+      for (int i = tid; i < rows_total * cpr; i += nthreads) {
+        int r = i / cpr, c = (i - r * cpr) * EPV;
+        bool ok = (r < rows_valid) && (c < D);
+        const T *src = ok ? (g + (size_t)r * rstride + c) : g;
+        cp_async16(s + r * ld + c, src, ok);
+      }
     }
   } else {
     for (int i = tid; i < rows_total * DP; i += nthreads) {
@@ -139,15 +149,23 @@ __device__ __forceinline__ void tile_load(T *s, int ld, const T *g, size_t rstri
 
 // Store rows_valid rows x D columns from s to g (16-byte vectors when possible).
 template <typename T>
-__device__ __forceinline__ void tile_store(T *g, size_t rstride, const T *s, int ld, int rows_valid, int D,
-                                           int tid, int nthreads) {
+__device__ __forceinline__ void tile_store(T *g, size_t rstride, const T *s, int ld, int rows_valid, int D, int tid,
+                                           int nthreads) {
   constexpr int EPV = 16 / sizeof(T);
   const bool vec = (D % EPV == 0) && ((rstride * sizeof(T)) % 16 == 0) && (((uintptr_t)g) % 16 == 0);
   if (vec) {
     const int cpr = D / EPV;
-    for (int i = tid; i < rows_valid * cpr; i += nthreads) {
-      int r = i / cpr, c = (i - r * cpr) * EPV;
-      *reinterpret_cast<int4 *>(g + (size_t)r * rstride + c) = *reinterpret_cast<const int4 *>(s + r * ld + c);
+    if ((cpr & (cpr - 1)) == 0) {
+      const int sh = 31 - __clz(cpr);
+      for (int i = tid; i < (rows_valid << sh); i += nthreads) {
+        const int r = i >> sh, c = (i & (cpr - 1)) * EPV;
+        *reinterpret_cast<int4 *>(g + (size_t)r * rstride + c) = *reinterpret_cast<const int4 *>(s + r * ld + c);
+      }
+    } else {
+      for (int i = tid; i < rows_valid * cpr; i += nthreads) {
+        int r = i / cpr, c = (i - r * cpr) * EPV;
+        *reinterpret_cast<int4 *>(g + (size_t)r * rstride + c) = *reinterpret_cast<const int4 *>(s + r * ld + c);
+      }
     }
   } else {
     for (int i = tid; i < rows_valid * D; i += nthreads) {
@@ -155,6 +173,27 @@ __device__ __forceinline__ void tile_store(T *g, size_t rstride, const T *s, int
       g[(size_t)r * rstride + c] = s[r * ld + c];
     }
   }
+}
+
+// exp for gate factors: accurate expf for fp32 inputs (1e-5 parity bar), hardware exp2 path otherwise
+template <typename T> __device__ __forceinline__ float fexp(float x) { return sizeof(T) == 4 ? expf(x) : __expf(x); }
+template <typename T> __device__ __forceinline__ float safe_fexp(float x) { return x <= 0.f ? fexp<T>(x) : 0.f; }
+
+// sum over a [rows x cols] window of a[r][c] * b[r][c] for two shared-memory tiles with the same leading
+// dimension; cols and ld must be multiples of 16 bytes worth of elements (true for padded tiles)
+template <typename T>
+__device__ __forceinline__ float tile_dot(const T *a, const T *b, int ld, int rows, int cols, int tid, int nthreads) {
+  constexpr int EPV = 16 / sizeof(T);
+  const int cpr = cols / EPV;
+  float acc = 0.f;
+  for (int i = tid; i < rows * cpr; i += nthreads) {
+    const int r = i / cpr, c = (i - r * cpr) * EPV;
+    const int4 xa = *reinterpret_cast<const int4 *>(a + r * ld + c), xb = *reinterpret_cast<const int4 *>(b + r * ld + c);
+    const T *pa = reinterpret_cast<const T *>(&xa), *pb = reinterpret_cast<const T *>(&xb);
+#pragma unroll
+    for (int j = 0; j < EPV; ++j) acc = fmaf(Num<T>::f(pa[j]), Num<T>::f(pb[j]), acc);
+  }
+  return acc;
 }
 
 // 64 per-token scalars (fp32) of one chunk -> shared; rows past the sequence end read as `fill`.
