@@ -303,6 +303,54 @@ template <int MI, int NI, bool A_T, bool B_KN> struct WarpGemm<MI, NI, A_T, B_KN
   }
 };
 
+// fp32 tile product with the contraction length known at compile time (fully unrolled, so the
+// shared-memory operand loads of later steps overlap the FMAs of earlier ones)
+template <int MI, int NI, int KD, bool A_T, bool B_KN>
+__device__ __forceinline__ void warp_gemm_f32(float (&acc)[MI][NI][4], const float *A, int lda, int m0, const float *B, int ldb,
+                                              int n0) {
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+  for (int k = 0; k < KD; ++k) {
+    float a_lo[MI], a_hi[MI];
+#pragma unroll
+    for (int mi = 0; mi < MI; ++mi) {
+      const int m = m0 + mi * 16 + g;
+      a_lo[mi] = A_T ? A[k * lda + m] : A[m * lda + k];
+      a_hi[mi] = A_T ? A[k * lda + m + 8] : A[(m + 8) * lda + k];
+    }
+#pragma unroll
+    for (int ni = 0; ni < NI; ++ni) {
+      const int n = n0 + ni * 8 + 2 * t4;
+      const float b0 = B_KN ? B[k * ldb + n] : B[n * ldb + k];
+      const float b1 = B_KN ? B[k * ldb + n + 1] : B[(n + 1) * ldb + k];
+#pragma unroll
+      for (int mi = 0; mi < MI; ++mi) {
+        acc[mi][ni][0] = fmaf(a_lo[mi], b0, acc[mi][ni][0]);
+        acc[mi][ni][1] = fmaf(a_lo[mi], b1, acc[mi][ni][1]);
+        acc[mi][ni][2] = fmaf(a_hi[mi], b0, acc[mi][ni][2]);
+        acc[mi][ni][3] = fmaf(a_hi[mi], b1, acc[mi][ni][3]);
+      }
+    }
+  }
+}
+
+// dst[r][c] = T(src[r][c] * f[r]) over a [64 x cols] tile, 16 bytes per thread step (dst may equal src)
+template <typename T>
+__device__ __forceinline__ void tile_scale_rows(T *dst, const T *src, int ld, int cols, const float *f, int tid, int nthreads) {
+  constexpr int EPV = 16 / sizeof(T);
+  const int cpr = cols / EPV;
+  for (int i = tid; i < C * cpr; i += nthreads) {
+    const int r = i / cpr, c = (i - r * cpr) * EPV;
+    int4 x = *reinterpret_cast<const int4 *>(src + r * ld + c);
+    T *px = reinterpret_cast<T *>(&x);
+    const float fr = f[r];
+#pragma unroll
+    for (int j = 0; j < EPV; ++j) px[j] = Num<T>::t(Num<T>::f(px[j]) * fr);
+    *reinterpret_cast<int4 *>(dst + r * ld + c) = x;
+  }
+}
+
 template <int MI, int NI> __device__ __forceinline__ void acc_zero(float (&acc)[MI][NI][4]) {
 #pragma unroll
   for (int mi = 0; mi < MI; ++mi)

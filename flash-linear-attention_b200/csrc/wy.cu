@@ -25,7 +25,15 @@ constexpr int LDL = C + 1;
 // allow_tf32=False).  Scr is scratch of nmat * 32 * 33 floats.  All 128 threads must call this.
 __device__ __forceinline__ void tri_inverse(const float *Lo, float *Xo, float *Scr, int nmat, int tid) {
   const int warp = tid >> 5, lane = tid & 31;
-  for (int e = tid; e < nmat * C * LDL; e += 128) Xo[e] = 0.f;
+  // only the blocks above the block diagonal are read before they are written: zero those
+  for (int e = tid; e < nmat * 32 * 32; e += 128) {
+    const int m = e >> 10, r = (e >> 5) & 31, c = e & 31;
+    Xo[m * C * LDL + r * LDL + 32 + c] = 0.f;                                  // rows 0..31, cols 32..63
+    if ((r < 16) && (c >= 16)) {
+      Xo[m * C * LDL + r * LDL + c] = 0.f;                                     // rows 0..15, cols 16..31
+      Xo[m * C * LDL + (32 + r) * LDL + 32 + c] = 0.f;                         // rows 32..47, cols 48..63
+    }
+  }
   __syncthreads();
   // ---- level 0: 16x16 diagonal blocks; warp w -> diagonal block w, half-warp -> matrix
   {
@@ -58,12 +66,12 @@ __device__ __forceinline__ void tri_inverse(const float *Lo, float *Xo, float *S
       float *scr = Scr + warp * 16 * 17;
       float t1[1][2][4];
       acc_zero(t1);
-      WarpGemm<1, 2, false, true, float>::run(t1, N21, LDL, 0, X + o * LDL + o, LDL, 0, 16);
+      warp_gemm_f32<1, 2, 16, false, true>(t1, N21, LDL, 0, X + o * LDL + o, LDL, 0);
       FLAB_ACC_FOREACH(1, 2, 0, 0, row, col, mi, ni, r) { scr[row * 17 + col] = t1[mi][ni][r]; }
       __syncwarp();
       float t2[1][2][4];
       acc_zero(t2);
-      WarpGemm<1, 2, false, true, float>::run(t2, X + (o + 16) * LDL + o + 16, LDL, 0, scr, 17, 0, 16);
+      warp_gemm_f32<1, 2, 16, false, true>(t2, X + (o + 16) * LDL + o + 16, LDL, 0, scr, 17, 0);
       __syncwarp();
       FLAB_ACC_FOREACH(1, 2, 0, 0, row, col, mi, ni, r) { X[(o + 16 + row) * LDL + o + col] = t2[mi][ni][r]; }
     }
@@ -77,7 +85,7 @@ __device__ __forceinline__ void tri_inverse(const float *Lo, float *Xo, float *S
       const float *X = Xo + mat * C * LDL;
       float t1[1][2][4];
       acc_zero(t1);
-      WarpGemm<1, 2, false, true, float>::run(t1, N, LDL, m0, X, LDL, n0, 32);
+      warp_gemm_f32<1, 2, 32, false, true>(t1, N, LDL, m0, X, LDL, n0);
       FLAB_ACC_FOREACH(1, 2, m0, n0, row, col, mi, ni, r) { Scr[mat * 32 * 33 + row * 33 + col] = t1[mi][ni][r]; }
     }
     __syncthreads();
@@ -85,7 +93,7 @@ __device__ __forceinline__ void tri_inverse(const float *Lo, float *Xo, float *S
       float *X = Xo + mat * C * LDL;
       float t2[1][2][4];
       acc_zero(t2);
-      WarpGemm<1, 2, false, true, float>::run(t2, X + 32 * LDL + 32, LDL, m0, Scr + mat * 32 * 33, 33, n0, 32);
+      warp_gemm_f32<1, 2, 32, false, true>(t2, X + 32 * LDL + 32, LDL, m0, Scr + mat * 32 * 33, 33, n0);
       FLAB_ACC_FOREACH(1, 2, m0, n0, row, col, mi, ni, r) { X[(32 + row) * LDL + col] = t2[mi][ni][r]; }
     }
   }
@@ -136,10 +144,7 @@ __global__ void __launch_bounds__(128) wy_fwd_kernel(const flab_args a) {
       cp_async_commit();
       cp_async_wait<0>();
       __syncthreads();
-      for (int e = tid; e < C * kp; e += 128) {
-        int r_ = e / kp, c_ = e - r_ * kp;
-        sXB[r_ * LDX + c_] = Num<T>::t(Num<T>::f(sX[r_ * LDX + c_]) * sBeta[r_]);
-      }
+      tile_scale_rows<T>(sXB, sX, LDX, kp, sBeta, tid, 128);
       __syncthreads();
       WarpGemm<1, 8, false, false, T>::run(gram, sXB, LDX, m0, sX, LDX, 0, kp);
     }
@@ -147,13 +152,18 @@ __global__ void __launch_bounds__(128) wy_fwd_kernel(const flab_args a) {
     FLAB_ACC_FOREACH(1, 8, m0, 0, row, col, mi, ni, r) {
       float x = row > col ? -gram[mi][ni][r] : 0.f;
       sLo[row * LDL + col] = x;
-      if (GATED) sLo[C * LDL + row * LDL + col] = row > col ? x * safe_exp(sG[row] - sG[col]) : 0.f;
+      if (GATED) sLo[C * LDL + row * LDL + col] = row > col ? x * safe_fexp<T>(sG[row] - sG[col]) : 0.f;
     }
     __syncthreads();
     tri_inverse(sLo, sLi, sScr, NM, tid);
-    for (int e = tid; e < NM * C * C; e += 128) {
-      int m = e / (C * C), r_ = (e / C) % C, c_ = e % C;
-      sA[m * C * LDP + r_ * LDP + c_] = Num<T>::t(sLi[m * C * LDL + r_ * LDL + c_]);
+    for (int e = tid; e < NM * C * 8; e += 128) {  // 8 elements (16 bytes of T) per step
+      const int m = e >> 9, r_ = (e >> 3) & 63, c_ = (e & 7) * 8;
+      const float *src = sLi + m * C * LDL + r_ * LDL + c_;
+      int4 x;
+      T *px = reinterpret_cast<T *>(&x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) px[j] = Num<T>::t(src[j]);
+      *reinterpret_cast<int4 *>(sA + m * C * LDP + r_ * LDP + c_) = x;
     }
     __syncthreads();
     tile_store<T>(reinterpret_cast<T *>(a.aw) + offa, as_, sA, LDP, rows, C, tid, 128);
@@ -180,10 +190,7 @@ __global__ void __launch_bounds__(128) wy_fwd_kernel(const flab_args a) {
       cp_async_commit();
       cp_async_wait<0>();
       __syncthreads();
-      for (int e = tid; e < C * WT; e += 128) {
-        int r_ = e / WT, c_ = e - r_ * WT;
-        sXB[r_ * LDX + c_] = Num<T>::t(Num<T>::f(sXB[r_ * LDX + c_]) * sBeta[r_]);
-      }
+      tile_scale_rows<T>(sXB, sXB, LDX, WT, sBeta, tid, 128);
       __syncthreads();
       float acc[1][16][4];
       acc_zero(acc);
@@ -252,10 +259,7 @@ __global__ void __launch_bounds__(128) wy_bwd_kernel(const flab_args a) {
       cp_async_commit();
       cp_async_wait<0>();
       __syncthreads();
-      for (int e = tid; e < C * WT; e += 128) {
-        int r_ = e / WT, c_ = e - r_ * WT;
-        sXB[r_ * LDX + c_] = Num<T>::t(Num<T>::f(sX[r_ * LDX + c_]) * sBeta[r_]);
-      }
+      tile_scale_rows<T>(sXB, sX, LDX, WT, sBeta, tid, 128);
       __syncthreads();
       WarpGemm<1, 8, false, false, T>::run(dAcc, sD, LDX, m0, sXB, LDX, 0, WT);
       float acc[1][16][4];
@@ -304,7 +308,7 @@ __global__ void __launch_bounds__(128) wy_bwd_kernel(const flab_args a) {
     tile_pass(v + offv, du, dv, vs, a.V, sAu, dA2);
     transform(dA2, sAu);
     FLAB_ACC_FOREACH(1, 8, m0, 0, row, col, mi, ni, r) {
-      float x2 = dA2[mi][ni][r] * safe_exp(sG[row] - sG[col]);
+      float x2 = dA2[mi][ni][r] * safe_fexp<T>(sG[row] - sG[col]);
       dA2[mi][ni][r] = x2;
       dA[mi][ni][r] = rnd<T>(dA[mi][ni][r] + x2);
     }
@@ -324,10 +328,7 @@ __global__ void __launch_bounds__(128) wy_bwd_kernel(const flab_args a) {
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    for (int e = tid; e < C * WT; e += 128) {
-      int r_ = e / WT, c_ = e - r_ * WT;
-      sXB[r_ * LDX + c_] = Num<T>::t(Num<T>::f(sX[r_ * LDX + c_]) * sBeta[r_]);
-    }
+    tile_scale_rows<T>(sXB, sX, LDX, WT, sBeta, tid, 128);
     __syncthreads();
     if (GATED) WarpGemm<1, 8, false, false, T>::run(gram, sXB, LDX, m0, sX, LDX, 0, WT);
     float kb2[1][16][4], acc[1][16][4];
