@@ -15,11 +15,14 @@
 
 namespace flab {
 
-constexpr int DBV = 64;  // V columns per CTA
-constexpr int DTH = 256;
+constexpr int DBV = 64;  // V columns per slab (8 warps)
 
-template <typename T, int KP, bool BWD>
-__global__ void __launch_bounds__(DTH) delta_h_kernel(const flab_args a) {
+// NSLAB = 1: the CTA owns one 64-column slab of V.  NSLAB = 2: sixteen warps own two adjacent slabs
+// and share the [tokens x K] tiles, so a K = V = 128 head is ONE CTA: with 128 (sequence, head) chains
+// the whole scan is a single wave over the SMs instead of two.
+template <typename T, int KP, bool BWD, int NSLAB>
+__global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a) {
+  constexpr int DTH = 256 * NSLAB;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LDK = KP + Num<T>::pad;
   constexpr int LDB = DBV + Num<T>::pad;
@@ -29,18 +32,19 @@ __global__ void __launch_bounds__(DTH) delta_h_kernel(const flab_args a) {
   constexpr int SNI = KP >= 128 ? 8 : 4;       // 64 or 32 columns per warp
   constexpr int NKT = BWD ? 3 : 2;  // [tokens x K] tiles per chunk: fwd (w, k); bwd (q, k, w)
   constexpr int NVT = BWD ? 2 : 1;  // [tokens x BV] tiles per chunk: fwd (u); bwd (do, dv)
-  T *sKT = reinterpret_cast<T *>(smem_raw);        // [2][NKT][64][LDK]
-  T *sVT = sKT + 2 * NKT * C * LDK;                // [2][NVT][64][LDB]
-  T *sS = sVT + 2 * NVT * C * LDB;                 // [KP][LDB] rounded state
-  T *sOp = sS + KP * LDB;                          // [64][LDB] gate-scaled operand of the state update
-  float *sG = reinterpret_cast<float *>(sOp + C * LDB);  // [2][64] gates; [64] e^{b}; [64] e^{b_L-b}
+  const int tid = threadIdx.x, slab = tid >> 8, stid = tid & 255, warp = stid >> 5;
+  T *sKT = reinterpret_cast<T *>(smem_raw);        // [2][NKT][64][LDK]               shared by the slabs
+  T *sVTall = sKT + 2 * NKT * C * LDK;             // [NSLAB][2][NVT][64][LDB]
+  T *sSall = sVTall + NSLAB * 2 * NVT * C * LDB;   // [NSLAB][KP][LDB] rounded state
+  T *sOpall = sSall + NSLAB * KP * LDB;            // [NSLAB][64][LDB] gate-scaled operand of the state update
+  float *sG = reinterpret_cast<float *>(sOpall + NSLAB * C * LDB);  // [2][64] gates; [64] e^{b}; [64] e^{b_L-b}
   float *sE1 = sG + 2 * C, *sE2 = sE1 + C;
+  T *sVT = sVTall + slab * 2 * NVT * C * LDB, *sS = sSall + slab * KP * LDB, *sOp = sOpall + slab * C * LDB;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int v0 = blockIdx.x * DBV;
+  const int v0 = (blockIdx.x * NSLAB + slab) * DBV;
   const int n = blockIdx.y / a.H, hd = blockIdx.y % a.H;
   const Seq s = seq_of(a, n);
-  const int vw = min(DBV, a.V - v0);
+  const int vw = max(0, min(DBV, a.V - v0));
   const bool use_g = a.g != nullptr;
   const size_t ks = tok_stride(a, a.K), vs = tok_stride(a, a.V), gs = tok_stride(a, 1);
   const size_t offk = tok_off(a, s, hd, 0, a.K), offv = tok_off(a, s, hd, 0, a.V) + v0;
@@ -86,7 +90,7 @@ __global__ void __launch_bounds__(DTH) delta_h_kernel(const flab_args a) {
       tile_load<T>(sKT + (buf * NKT + j) * C * LDK, LDK, kt_src[j] + (size_t)t0 * ks, ks, rows, C, a.K, KP, tid, DTH);
 #pragma unroll
     for (int j = 0; j < NVT; ++j)
-      tile_load<T>(sVT + (buf * NVT + j) * C * LDB, LDB, vt_src[j] + (size_t)t0 * vs, vs, rows, C, vw, DBV, tid, DTH);
+      tile_load<T>(sVT + (buf * NVT + j) * C * LDB, LDB, vt_src[j] + (size_t)t0 * vs, vs, rows, C, vw, DBV, stid, 256);
     if (tid < C) sG[buf * C + tid] = (use_g && tid < rows) ? G[(size_t)(t0 + tid) * gs] : 0.f;
     cp_async_commit();
   };
@@ -105,13 +109,13 @@ __global__ void __launch_bounds__(DTH) delta_h_kernel(const flab_args a) {
     // (a) rounded state -> shared; per-token gate factors; bwd: do' = do * e^{b} * scale in place
     acc_to_smem<SMI, SNI, T>(acc, sS, LDB, ms, ns);
     if (tid < C) {
-      sE1[tid] = use_g ? expf(gc[tid]) : 1.f;
-      sE2[tid] = use_g ? expf(gl - gc[tid]) : 1.f;
+      sE1[tid] = use_g ? fexp<T>(gc[tid]) : 1.f;
+      sE2[tid] = use_g ? fexp<T>(gl - gc[tid]) : 1.f;
     }
     if (BWD) {
-      for (int e = tid; e < C * (DBV / 2); e += DTH) {
+      for (int e = stid; e < C * (DBV / 2); e += 256) {
         const int r_ = e / (DBV / 2), c_ = (e - r_ * (DBV / 2)) * 2;
-        const float f = (use_g ? expf(gc[r_]) : 1.f) * a.scale;
+        const float f = (use_g ? fexp<T>(gc[r_]) : 1.f) * a.scale;
         T *p = vt + r_ * LDB + c_;
         st_pair<T>(p, Num<T>::f(p[0]) * f, Num<T>::f(p[1]) * f);
       }
@@ -120,7 +124,7 @@ __global__ void __launch_bounds__(DTH) delta_h_kernel(const flab_args a) {
     // (b) state at the chunk boundary -> global (coalesced, off the critical path)
     {
       const size_t hoff = ((size_t)(s.c0 + it) * a.H + hd) * a.K * a.V + v0;
-      tile_store<T>(Hout + hoff, (size_t)a.V, sS, LDB, a.K, vw, tid, DTH);
+      tile_store<T>(Hout + hoff, (size_t)a.V, sS, LDB, a.K, vw, stid, 256);
     }
     // (c) the dependent product against the rounded state, gate applied to its rows
     {
@@ -147,10 +151,10 @@ __global__ void __launch_bounds__(DTH) delta_h_kernel(const flab_args a) {
     }
     __syncthreads();  // (3)
     // (d) v_new / dv2 -> global
-    tile_store<T>(Vout + (size_t)t0 * vs, vs, BWD ? vt + C * LDB : vt, LDB, rows, vw, tid, DTH);
+    tile_store<T>(Vout + (size_t)t0 * vs, vs, BWD ? vt + C * LDB : vt, LDB, rows, vw, stid, 256);
     // (e) state update
     if (use_g) {
-      const float d = expf(gl);
+      const float d = fexp<T>(gl);
 #pragma unroll
       for (int mi = 0; mi < SMI; ++mi)
 #pragma unroll
@@ -172,23 +176,25 @@ __global__ void __launch_bounds__(DTH) delta_h_kernel(const flab_args a) {
   }
 }
 
-template <typename T, int KP, bool BWD> static int launch_delta_h(const flab_args *a, cudaStream_t stream) {
+template <typename T, int KP, bool BWD, int NSLAB> static int launch_delta_h(const flab_args *a, cudaStream_t stream) {
   constexpr int LDK = KP + Num<T>::pad, LDB = DBV + Num<T>::pad;
   constexpr int NKT = BWD ? 3 : 2, NVT = BWD ? 2 : 1;
-  size_t smem = ((size_t)2 * NKT * C * LDK + (size_t)2 * NVT * C * LDB + (size_t)KP * LDB + (size_t)C * LDB) * sizeof(T) +
+  size_t smem = ((size_t)2 * NKT * C * LDK + NSLAB * ((size_t)2 * NVT * C * LDB + (size_t)KP * LDB + (size_t)C * LDB)) * sizeof(T) +
                 4 * C * sizeof(float);
-  auto kern = delta_h_kernel<T, KP, BWD>;
+  auto kern = delta_h_kernel<T, KP, BWD, NSLAB>;
   if (int e = set_smem(kern, smem)) return e;
-  kern<<<dim3(cdiv(a->V, DBV), a->N * a->H), DTH, smem, stream>>>(*a);
+  kern<<<dim3(cdiv(a->V, DBV * NSLAB), a->N * a->H), 256 * NSLAB, smem, stream>>>(*a);
   return check_launch(BWD ? "delta_bwd_dhu" : "delta_fwd_h");
 }
 
 template <bool BWD> static int dispatch_delta_h(const flab_args *a, void *stream) {
   FLAB_REQUIRE(a->K <= 256, FLAB_E_UNSUPPORTED, "delta-rule state scan: K = %d > 256", a->K);
+  // two slabs per CTA when V has at least two of them and the doubled per-slab buffers still fit (forward, K <= 128)
+  const bool two = !BWD && a->K <= 128 && a->V > DBV;
   FLAB_DISPATCH_16(a->dtype, T, {
-    if (a->K <= 64) return (launch_delta_h<T, 64, BWD>(a, (cudaStream_t)stream));
-    if (a->K <= 128) return (launch_delta_h<T, 128, BWD>(a, (cudaStream_t)stream));
-    return (launch_delta_h<T, 256, BWD>(a, (cudaStream_t)stream));
+    if (a->K <= 64) return two ? (launch_delta_h<T, 64, BWD, BWD ? 1 : 2>(a, (cudaStream_t)stream)) : (launch_delta_h<T, 64, BWD, 1>(a, (cudaStream_t)stream));
+    if (a->K <= 128) return two ? (launch_delta_h<T, 128, BWD, BWD ? 1 : 2>(a, (cudaStream_t)stream)) : (launch_delta_h<T, 128, BWD, 1>(a, (cudaStream_t)stream));
+    return (launch_delta_h<T, 256, BWD, 1>(a, (cudaStream_t)stream));
   });
   return FLAB_OK;
 }
