@@ -32,9 +32,14 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
   constexpr int SNI = KP >= 128 ? 8 : 4;       // 64 or 32 columns per warp
   constexpr int NKT = BWD ? 3 : 2;  // [tokens x K] tiles per chunk: fwd (w, k); bwd (q, k, w)
   constexpr int NVT = BWD ? 2 : 1;  // [tokens x BV] tiles per chunk: fwd (u); bwd (do, dv)
+  // Staggered buffering (backward, two slabs): k is needed only by the dependent product (c) and is kept in ONE
+  // buffer that is refilled as soon as every warp has left (c); q and w, needed by the state update (e), stay
+  // double-buffered. This is what lets two slabs fit in shared memory.
+  constexpr bool STAG = BWD && NSLAB == 2;
+  constexpr int NKBUF = STAG ? 5 : 2 * NKT;  // [tokens x K] tile buffers
   const int tid = threadIdx.x, slab = tid >> 8, stid = tid & 255, warp = stid >> 5;
-  T *sKT = reinterpret_cast<T *>(smem_raw);        // [2][NKT][64][LDK]               shared by the slabs
-  T *sVTall = sKT + 2 * NKT * C * LDK;             // [NSLAB][2][NVT][64][LDB]
+  T *sKT = reinterpret_cast<T *>(smem_raw);        // [2][NKT][64][LDK] (staggered: k, then [2][q, w]); shared by the slabs
+  T *sVTall = sKT + NKBUF * C * LDK;               // [NSLAB][2][NVT][64][LDB]
   T *sSall = sVTall + NSLAB * 2 * NVT * C * LDB;   // [NSLAB][KP][LDB] rounded state
   T *sOpall = sSall + NSLAB * KP * LDB;            // [NSLAB][64][LDB] gate-scaled operand of the state update
   float *sG = reinterpret_cast<float *>(sOpall + NSLAB * C * LDB);  // [2][64] gates; [64] e^{b}; [64] e^{b_L-b}
@@ -83,27 +88,47 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
     }
   }
 
-  auto load = [&](int it, int buf) {
+  // buffer of [tokens x K] tile j of the chunk held in stage `buf`
+  auto ktile = [&](int j, int buf) -> T * {
+    if (!STAG) return sKT + (buf * NKT + j) * C * LDK;
+    return j == 1 ? sKT : sKT + (1 + buf * 2 + (j >> 1)) * C * LDK;
+  };
+  // tiles read by the dependent product (fwd: w, bwd: k), the [tokens x BV] tiles and the gates
+  auto load_early = [&](int it, int buf) {
     const int t0 = it * C, rows = min(C, s.len - t0);
-#pragma unroll
-    for (int j = 0; j < NKT; ++j)
-      tile_load<T>(sKT + (buf * NKT + j) * C * LDK, LDK, kt_src[j] + (size_t)t0 * ks, ks, rows, C, a.K, KP, tid, DTH);
+    constexpr int je = BWD ? 1 : 0;
+    tile_load<T>(ktile(je, buf), LDK, kt_src[je] + (size_t)t0 * ks, ks, rows, C, a.K, KP, tid, DTH);
 #pragma unroll
     for (int j = 0; j < NVT; ++j)
       tile_load<T>(sVT + (buf * NVT + j) * C * LDB, LDB, vt_src[j] + (size_t)t0 * vs, vs, rows, C, vw, DBV, stid, 256);
     if (tid < C) sG[buf * C + tid] = (use_g && tid < rows) ? G[(size_t)(t0 + tid) * gs] : 0.f;
     cp_async_commit();
   };
+  // tiles read by the state update (fwd: k, bwd: q and w)
+  auto load_late = [&](int it, int buf) {
+    const int t0 = it * C, rows = min(C, s.len - t0);
+#pragma unroll
+    for (int j = 0; j < NKT; ++j)
+      if (j != (BWD ? 1 : 0))
+        tile_load<T>(ktile(j, buf), LDK, kt_src[j] + (size_t)t0 * ks, ks, rows, C, a.K, KP, tid, DTH);
+    cp_async_commit();
+  };
 
   const int first = BWD ? s.nt - 1 : 0, step = BWD ? -1 : 1;
-  if (s.nt > 0) load(first, 0);
+  if (s.nt > 0) {
+    load_late(first, 0);
+    load_early(first, 0);
+  }
   for (int i = 0; i < s.nt; ++i) {
     const int it = first + i * step, cur = i & 1;
     cp_async_wait<0>();
     __syncthreads();  // (1) tiles of this chunk have landed; every warp is done with the previous chunk
-    if (i + 1 < s.nt) load(it + step, cur ^ 1);  // prefetch into the buffer the previous chunk used
+    if (i + 1 < s.nt) {  // prefetch into the buffers the previous chunk used
+      load_late(it + step, cur ^ 1);
+      if (!STAG) load_early(it + step, cur ^ 1);
+    }
     const int t0 = it * C, rows = min(C, s.len - t0), last = rows - 1;
-    T *kt = sKT + cur * NKT * C * LDK, *vt = sVT + cur * NVT * C * LDB;
+    T *vt = sVT + cur * NVT * C * LDB;
     const float *gc = sG + cur * C;
     const float gl = gc[last];
     // (a) rounded state -> shared; per-token gate factors; bwd: do' = do * e^{b} * scale in place
@@ -130,7 +155,7 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
     {
       float p[1][4][4];
       acc_zero(p);
-      const T *A = BWD ? kt + C * LDK : kt;  // bwd: k ; fwd: w
+      const T *A = ktile(BWD ? 1 : 0, cur);  // bwd: k ; fwd: w
       WarpGemm<1, 4, false, true, T>::run(p, A, LDK, m0, sS, LDB, n0, KP);
       T *y = BWD ? vt + C * LDB : vt;  // bwd: dv ; fwd: u   (replaced in place by dv2 / v_new)
       float op[1][4][4];
@@ -150,6 +175,7 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
       acc_to_smem<1, 4, T>(op, sOp, LDB, m0, n0);
     }
     __syncthreads();  // (3)
+    if (STAG && i + 1 < s.nt) load_early(it + step, cur ^ 1);  // every warp has left (c): the k buffer is free
     // (d) v_new / dv2 -> global
     tile_store<T>(Vout + (size_t)t0 * vs, vs, BWD ? vt + C * LDB : vt, LDB, rows, vw, stid, 256);
     // (e) state update
@@ -163,10 +189,10 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
           for (int r = 0; r < 4; ++r) acc[mi][ni][r] *= d;
     }
     if (!BWD) {
-      WarpGemm<SMI, SNI, true, true, T>::run(acc, kt + C * LDK, LDK, ms, sOp, LDB, ns, C);  // k^T (e^{b_L-b} v_new)
+      WarpGemm<SMI, SNI, true, true, T>::run(acc, ktile(1, cur), LDK, ms, sOp, LDB, ns, C);  // k^T (e^{b_L-b} v_new)
     } else {
-      WarpGemm<SMI, SNI, true, true, T>::run(acc, kt, LDK, ms, vt, LDB, ns, C);                 // q^T (scale e^{b} do)
-      WarpGemm<SMI, SNI, true, true, T>::run(acc, kt + 2 * C * LDK, LDK, ms, sOp, LDB, ns, C);  // w^T (-e^{b} dv2)
+      WarpGemm<SMI, SNI, true, true, T>::run(acc, ktile(0, cur), LDK, ms, vt, LDB, ns, C);              // q^T (scale e^{b} do)
+      WarpGemm<SMI, SNI, true, true, T>::run(acc, ktile(2, cur), LDK, ms, sOp, LDB, ns, C);  // w^T (-e^{b} dv2)
     }
   }
   if (S1) {
@@ -179,7 +205,8 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
 template <typename T, int KP, bool BWD, int NSLAB> static int launch_delta_h(const flab_args *a, cudaStream_t stream) {
   constexpr int LDK = KP + Num<T>::pad, LDB = DBV + Num<T>::pad;
   constexpr int NKT = BWD ? 3 : 2, NVT = BWD ? 2 : 1;
-  size_t smem = ((size_t)2 * NKT * C * LDK + NSLAB * ((size_t)2 * NVT * C * LDB + (size_t)KP * LDB + (size_t)C * LDB)) * sizeof(T) +
+  constexpr int NKBUF = (BWD && NSLAB == 2) ? 5 : 2 * NKT;
+  size_t smem = ((size_t)NKBUF * C * LDK + NSLAB * ((size_t)2 * NVT * C * LDB + (size_t)KP * LDB + (size_t)C * LDB)) * sizeof(T) +
                 4 * C * sizeof(float);
   auto kern = delta_h_kernel<T, KP, BWD, NSLAB>;
   if (int e = set_smem(kern, smem)) return e;
@@ -189,11 +216,11 @@ template <typename T, int KP, bool BWD, int NSLAB> static int launch_delta_h(con
 
 template <bool BWD> static int dispatch_delta_h(const flab_args *a, void *stream) {
   FLAB_REQUIRE(a->K <= 256, FLAB_E_UNSUPPORTED, "delta-rule state scan: K = %d > 256", a->K);
-  // two slabs per CTA when V has at least two of them and the doubled per-slab buffers still fit (forward, K <= 128)
-  const bool two = !BWD && a->K <= 128 && a->V > DBV;
+  // two slabs per CTA when V has at least two of them and the doubled per-slab buffers still fit (K <= 128)
+  const bool two = a->K <= 128 && a->V > DBV;
   FLAB_DISPATCH_16(a->dtype, T, {
-    if (a->K <= 64) return two ? (launch_delta_h<T, 64, BWD, BWD ? 1 : 2>(a, (cudaStream_t)stream)) : (launch_delta_h<T, 64, BWD, 1>(a, (cudaStream_t)stream));
-    if (a->K <= 128) return two ? (launch_delta_h<T, 128, BWD, BWD ? 1 : 2>(a, (cudaStream_t)stream)) : (launch_delta_h<T, 128, BWD, 1>(a, (cudaStream_t)stream));
+    if (a->K <= 64) return two ? (launch_delta_h<T, 64, BWD, 2>(a, (cudaStream_t)stream)) : (launch_delta_h<T, 64, BWD, 1>(a, (cudaStream_t)stream));
+    if (a->K <= 128) return two ? (launch_delta_h<T, 128, BWD, 2>(a, (cudaStream_t)stream)) : (launch_delta_h<T, 128, BWD, 1>(a, (cudaStream_t)stream));
     return (launch_delta_h<T, 256, BWD, 1>(a, (cudaStream_t)stream));
   });
   return FLAB_OK;
