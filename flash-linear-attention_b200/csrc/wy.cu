@@ -202,6 +202,174 @@ __global__ void __launch_bounds__(128) wy_fwd_kernel(const flab_args a) {
   }
 }
 
+// In-place variant for 256 threads: X holds NMAT negated strict-lower Gram matrices ([64][LDL] fp32 each, zero
+// on and above the diagonal) and leaves their inverses (unit diagonal included). Same blocked scheme as
+// tri_inverse; every level reads a block into registers or scratch before it is overwritten. Scr is scratch of
+// NMAT * 32 * 33 floats. All 256 threads must call this.
+template <int NMAT> __device__ __forceinline__ void tri_inverse8(float *X, float *Scr, int tid) {
+  const int warp = tid >> 5, lane = tid & 31;
+  // ---- level 0: warps 0..3 -> diagonal block, half-warp -> matrix
+  if (warp < 4) {
+    const int half = lane >> 4, j = lane & 15, mat = half < NMAT ? half : 0;
+    float *n = X + mat * C * LDL + (16 * warp) * (LDL + 1);
+    float nc[16], x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) nc[i] = n[i * LDL + j];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float acc = nc[i];
+#pragma unroll
+      for (int m = 0; m < i; ++m) acc = fmaf(__shfl_sync(0xffffffffu, nc[i], (lane & 16) + m), x[m], acc);
+      x[i] = (j < i) ? acc : 0.f;
+    }
+    __syncwarp();
+    if (half < NMAT) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) n[i * LDL + j] = x[i] + (i == j ? 1.f : 0.f);
+    }
+  }
+  __syncthreads();
+  // ---- level 1: X21 = X22 (N21 X11); warp -> (matrix, 32-block, 8-column half of the 16x16 result)
+  {
+    const int mat = (warp >> 1) & 1, blk = warp & 1, n0 = 8 * (warp >> 2);
+    const bool on = mat < NMAT;
+    const int o = 32 * blk;
+    float *Xm = X + (on ? mat : 0) * C * LDL;
+    float *scr = Scr + ((on ? mat : 0) * 2 + blk) * 16 * 17;
+    if (on) {
+      float t1[1][1][4];
+      acc_zero(t1);
+      warp_gemm_f32<1, 1, 16, false, true>(t1, Xm + (o + 16) * LDL + o, LDL, 0, Xm + o * LDL + o, LDL, n0);
+      FLAB_ACC_FOREACH(1, 1, 0, n0, row, col, mi, ni, r) { scr[row * 17 + col] = t1[mi][ni][r]; }
+    }
+    __syncthreads();
+    if (on) {
+      float t2[1][1][4];
+      acc_zero(t2);
+      warp_gemm_f32<1, 1, 16, false, true>(t2, Xm + (o + 16) * LDL + o + 16, LDL, 0, scr, 17, n0);
+      FLAB_ACC_FOREACH(1, 1, 0, n0, row, col, mi, ni, r) { Xm[(o + 16 + row) * LDL + o + col] = t2[mi][ni][r]; }
+    }
+  }
+  __syncthreads();
+  // ---- level 2: X_BA = X_BB (N_BA X_AA); two matrices: warp -> (matrix, 16x16 tile); one: warp -> 16x8 tile
+  {
+    constexpr int NI2 = NMAT == 2 ? 2 : 1;
+    const int mat = NMAT == 2 ? (warp >> 2) : 0, tile = NMAT == 2 ? (warp & 3) : warp;
+    const int m0 = 16 * (tile & 1), n0 = 8 * NI2 * (tile >> 1);
+    float *Xm = X + mat * C * LDL;
+    float *scr = Scr + mat * 32 * 33;
+    float t1[1][NI2][4];
+    acc_zero(t1);
+    warp_gemm_f32<1, NI2, 32, false, true>(t1, Xm + 32 * LDL, LDL, m0, Xm, LDL, n0);
+    FLAB_ACC_FOREACH(1, NI2, m0, n0, row, col, mi, ni, r) { scr[row * 33 + col] = t1[mi][ni][r]; }
+    __syncthreads();
+    float t2[1][NI2][4];
+    acc_zero(t2);
+    warp_gemm_f32<1, NI2, 32, false, true>(t2, Xm + 32 * LDL + 32, LDL, m0, scr, 33, n0);
+    FLAB_ACC_FOREACH(1, NI2, m0, n0, row, col, mi, ni, r) { Xm[(32 + row) * LDL + col] = t2[mi][ni][r]; }
+  }
+  __syncthreads();
+}
+
+// Forward for 16-bit element types with K, V <= 128: eight warps, the whole k and v tiles of the chunk resident
+// in shared memory (loaded once, v while the Gram matrix is built and inverted), three CTAs per SM.
+//   * beta enters the Gram matrix as a row factor of the fp32 product and enters w, u as a COLUMN factor of A
+//     (A diag(beta)) x = A (beta x), so no beta-scaled copy of k or v is made;
+//   * the gated Gram matrix is the similarity transform D N D^-1 of the ungated one (D = diag(e^b)), hence
+//     Au = D Aw D^-1, i.e. Au_ij = Aw_ij e^{b_i - b_j}: ONE inverse serves both;
+//   * the scaled copies are derived from the rounded A, so the recompute entry (which reads the stored A)
+//     produces bit-identical w and u.
+template <typename T, bool GATED, bool RECOMPUTE>
+__global__ void __launch_bounds__(256, 3) wy_fwd16_kernel(const flab_args a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int LDX = WT + Num<T>::pad;
+  constexpr int LDP = C + Num<T>::pad;
+  constexpr int NM = GATED ? 2 : 1;
+  T *sK = reinterpret_cast<T *>(smem_raw);  // [64][LDX] k, replaced in place by w
+  T *sV = sK + C * LDX;                     // [64][LDX] v, replaced in place by u
+  T *sAb = sV + C * LDX;                    // [NM][64][LDP] Aw diag(beta), Au diag(beta)
+  float *sBeta = reinterpret_cast<float *>(sAb + NM * C * LDP);  // [64]
+  float *sG = sBeta + C;                                         // [64]
+  float *sF = sG + C;                                            // [64][LDL] negated Gram matrix, inverted in place
+  float *sScr = reinterpret_cast<float *>(sAb);                  // scratch of the inverse (sAb still idle)
+  static_assert((size_t)NM * C * LDP * sizeof(T) >= (size_t)32 * 33 * sizeof(float), "inverse scratch does not fit");
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  int n, it;
+  chunk_of(a, blockIdx.x, n, it);
+  const int hd = blockIdx.y;
+  const Seq s = seq_of(a, n);
+  const int t0 = it * C, rows = min(C, s.len - t0);
+  const size_t ks = tok_stride(a, a.K), vs = tok_stride(a, a.V), as_ = tok_stride(a, C);
+  const size_t offk = tok_off(a, s, hd, t0, a.K), offv = tok_off(a, s, hd, t0, a.V), offa = tok_off(a, s, hd, t0, C);
+  const T *k = reinterpret_cast<const T *>(a.k), *v = reinterpret_cast<const T *>(a.v), *beta = reinterpret_cast<const T *>(a.beta);
+  const int m0 = (warp & 3) * 16, nh = warp >> 2;
+
+  tile_load<T>(sK, LDX, k + offk, ks, rows, C, a.K, WT, tid, 256);
+  if (RECOMPUTE) {
+    tile_load<T>(sAb, LDP, reinterpret_cast<const T *>(a.aw) + offa, as_, rows, C, C, C, tid, 256);
+    if (GATED) tile_load<T>(sAb + C * LDP, LDP, reinterpret_cast<const T *>(a.au) + offa, as_, rows, C, C, C, tid, 256);
+  }
+  cp_async_commit();
+  tile_load<T>(sV, LDX, v + offv, vs, rows, C, a.V, WT, tid, 256);
+  cp_async_commit();
+  if (tid < C) {
+    sBeta[tid] = tid < rows ? Num<T>::f(beta[tok_off(a, s, hd, t0 + tid, 1)]) : 0.f;
+    // the gate only enters through the decay of A, which the recompute path does not rebuild
+    sG[tid] = (GATED && !RECOMPUTE && tid < rows) ? reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + tid, 1)] : 0.f;
+  }
+  cp_async_wait<1>();
+  __syncthreads();  // k (and the stored A) have landed
+
+  if (!RECOMPUTE) {
+    float gram[1][4][4];
+    acc_zero(gram);
+    WarpGemm<1, 4, false, false, T>::run(gram, sK, LDX, m0, sK, LDX, nh * 32, round_up(a.K, 16));
+    FLAB_ACC_FOREACH(1, 4, m0, nh * 32, row, col, mi, ni, r) {
+      sF[row * LDL + col] = row > col ? -gram[mi][ni][r] * sBeta[row] : 0.f;
+    }
+    __syncthreads();
+    tri_inverse8<1>(sF, sScr, tid);
+  }
+  // A (forward: rounded and written to global from registers) and A diag(beta), 8 elements per step
+  for (int e = tid; e < C * 8; e += 256) {
+    const int r_ = e >> 3, c_ = (e & 7) * 8;
+#pragma unroll
+    for (int m = 0; m < NM; ++m) {
+      T *pab = sAb + m * C * LDP + r_ * LDP + c_;
+      int4 x;
+      T *px = reinterpret_cast<T *>(&x);
+      if (!RECOMPUTE) {
+        const float *src = sF + r_ * LDL + c_;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) px[j] = Num<T>::t(m == 0 ? src[j] : src[j] * safe_fexp<T>(sG[r_] - sG[c_ + j]));
+        if (r_ < rows) *reinterpret_cast<int4 *>(reinterpret_cast<T *>(m == 0 ? a.aw : a.au) + offa + (size_t)r_ * as_ + c_) = x;
+      } else {
+        x = *reinterpret_cast<const int4 *>(pab);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) px[j] = Num<T>::t(Num<T>::f(px[j]) * sBeta[c_ + j]);
+      *reinterpret_cast<int4 *>(pab) = x;
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // A diag(beta) and v are in place
+  // w = (Aw diag(beta)) k, then u = (Au diag(beta)) v; warp tile 16 rows x 64 columns, results replace k and v
+  const bool do_w = nh * 64 < a.K, do_u = nh * 64 < a.V;
+  float acc[1][8][4];
+  acc_zero(acc);
+  if (do_w) WarpGemm<1, 8, false, true, T>::run(acc, sAb, LDP, m0, sK, LDX, nh * 64, C);
+  __syncthreads();  // every warp has read k
+  if (do_w) acc_to_smem<1, 8, T>(acc, sK, LDX, m0, nh * 64);
+  acc_zero(acc);
+  if (do_u) WarpGemm<1, 8, false, true, T>::run(acc, GATED ? sAb + C * LDP : sAb, LDP, m0, sV, LDX, nh * 64, C);
+  __syncthreads();  // every warp has read v; w is complete
+  if (do_u) acc_to_smem<1, 8, T>(acc, sV, LDX, m0, nh * 64);
+  tile_store<T>(reinterpret_cast<T *>(a.w) + offk, ks, sK, LDX, rows, a.K, tid, 256);
+  __syncthreads();
+  tile_store<T>(reinterpret_cast<T *>(a.u) + offv, vs, sV, LDX, rows, a.V, tid, 256);
+}
+
 // ------------------------------------------------------------------------------------------------
 // backward
 // ------------------------------------------------------------------------------------------------
@@ -393,6 +561,14 @@ __global__ void __launch_bounds__(128) wy_bwd_kernel(const flab_args a) {
 
 template <typename T, bool GATED, bool RECOMPUTE> static int launch_wy_fwd(const flab_args *a, cudaStream_t stream) {
   constexpr int LDX = WT + Num<T>::pad, LDP = C + Num<T>::pad, NM = GATED ? 2 : 1;
+  if (sizeof(T) == 2 && a->K <= WT && a->V <= WT) {
+    size_t smem = ((size_t)2 * C * LDX + (size_t)NM * C * LDP) * sizeof(T) + 2 * C * sizeof(float);
+    if (!RECOMPUTE) smem += (size_t)C * LDL * sizeof(float);
+    auto kern = wy_fwd16_kernel<T, GATED, RECOMPUTE>;
+    if (int e = set_smem(kern, smem)) return e;
+    kern<<<dim3(a->NT, a->H), 256, smem, stream>>>(*a);
+    return check_launch(RECOMPUTE ? "wy_recompute" : "wy_fwd");
+  }
   size_t smem = ((size_t)2 * C * LDX + (size_t)NM * C * LDP) * sizeof(T) + 2 * C * sizeof(float);
   if (!RECOMPUTE) smem += ((size_t)NM * C * LDL + (size_t)NM * 32 * 33) * sizeof(float);
   auto kern = wy_fwd_kernel<T, GATED, RECOMPUTE>;
