@@ -372,6 +372,16 @@ template <> __device__ __forceinline__ void st_pair<float>(float *p, float x, fl
   *reinterpret_cast<float2 *>(p) = make_float2(x, y);
 }
 
+// load two adjacent elements as floats
+template <typename T> __device__ __forceinline__ float2 ld_pair(const T *p);
+template <> __device__ __forceinline__ float2 ld_pair<bf16>(const bf16 *p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+}
+template <> __device__ __forceinline__ float2 ld_pair<__half>(const __half *p) {
+  return __half22float2(*reinterpret_cast<const __half2 *>(p));
+}
+template <> __device__ __forceinline__ float2 ld_pair<float>(const float *p) { return *reinterpret_cast<const float2 *>(p); }
+
 // accumulator fragment -> shared tile (element type T), rows m0.., cols n0..
 template <int MI, int NI, typename T>
 __device__ __forceinline__ void acc_to_smem(const float (&acc)[MI][NI][4], T *s, int ld, int m0, int n0) {

@@ -559,6 +559,205 @@ __global__ void __launch_bounds__(128) wy_bwd_kernel(const flab_args a) {
   }
 }
 
+// Backward for 16-bit element types with K, V <= 128: eight warps; k, v, dw, du of the chunk are loaded once
+// and stay resident (dk and dv are built in place over dw and du), two CTAs per SM. beta is applied to fp32
+// accumulators (as a column factor of dw k^T, a row factor of k k^T) or to the 64x64 matrix dA instead of
+// to a copy of k or v.
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256, 2) wy_bwd16_kernel(const flab_args a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int LDX = WT + Num<T>::pad;
+  constexpr int LDP = C + Num<T>::pad;
+  T *sK = reinterpret_cast<T *>(smem_raw);  // [64][LDX] k
+  T *sV = sK + C * LDX;                     // [64][LDX] v
+  T *sDW = sV + C * LDX;                    // [64][LDX] dw, replaced in place by dk
+  T *sDU = sDW + C * LDX;                   // [64][LDX] du, replaced in place by dv
+  T *sAw = sDU + C * LDX;                   // [64][LDP]
+  T *sAu = sAw + C * LDP;                   // [64][LDP] (gated)
+  T *sDA = sAu + (GATED ? C * LDP : 0);     // [64][LDP] staged dA
+  T *sTmp = sDA + C * LDP;                  // [64][LDP] staged intermediate product; later diag(beta) dA
+  float *sBeta = reinterpret_cast<float *>(sTmp + C * LDP);  // [64]
+  float *sG = sBeta + C;                                     // [64]
+  float *sDG = sG + C;                                       // [64]
+  float *sDB = sDG + C;                                      // [64]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
+  int n, it;
+  chunk_of(a, blockIdx.x, n, it);
+  const int hd = blockIdx.y;
+  const Seq s = seq_of(a, n);
+  const int t0 = it * C, rows = min(C, s.len - t0);
+  const size_t ks = tok_stride(a, a.K), vs = tok_stride(a, a.V), as_ = tok_stride(a, C);
+  const size_t offk = tok_off(a, s, hd, t0, a.K), offv = tok_off(a, s, hd, t0, a.V), offa = tok_off(a, s, hd, t0, C);
+  const T *beta = reinterpret_cast<const T *>(a.beta);
+  const int m0 = (warp & 3) * 16, n32 = (warp >> 2) * 32, n64 = (warp >> 2) * 64;
+
+  tile_load<T>(sAw, LDP, reinterpret_cast<const T *>(a.aw) + offa, as_, rows, C, C, C, tid, 256);
+  tile_load<T>(sK, LDX, reinterpret_cast<const T *>(a.k) + offk, ks, rows, C, a.K, WT, tid, 256);
+  tile_load<T>(sDW, LDX, reinterpret_cast<const T *>(a.dw) + offk, ks, rows, C, a.K, WT, tid, 256);
+  cp_async_commit();
+  if (GATED) tile_load<T>(sAu, LDP, reinterpret_cast<const T *>(a.au) + offa, as_, rows, C, C, C, tid, 256);
+  tile_load<T>(sV, LDX, reinterpret_cast<const T *>(a.v) + offv, vs, rows, C, a.V, WT, tid, 256);
+  tile_load<T>(sDU, LDX, reinterpret_cast<const T *>(a.du) + offv, vs, rows, C, a.V, WT, tid, 256);
+  cp_async_commit();
+  if (tid < C) {
+    sBeta[tid] = tid < rows ? Num<T>::f(beta[tok_off(a, s, hd, t0 + tid, 1)]) : 0.f;
+    sG[tid] = (GATED && tid < rows) ? reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + tid, 1)] : 0.f;
+    sDG[tid] = 0.f;
+    sDB[tid] = 0.f;
+  }
+
+  float dbeta_lo = 0.f, dbeta_hi = 0.f;  // rows m0+g8, m0+g8+8 (partial over this thread's columns)
+  float dA[1][4][4], dA2[1][4][4];
+  acc_zero(dA);
+  acc_zero(dA2);
+
+  // one pass over (x = k or v, dx = dw or du): dAcc += dx x^T (beta is applied by `transform`), dx is replaced
+  // in place by (A^T dx) * beta and sum(A^T dx * x) is added to dbeta.
+  auto pass = [&](const T *sX, T *sDX, const T *A, int D, float (&dAcc)[1][4][4]) {
+    WarpGemm<1, 4, false, false, T>::run(dAcc, sDX, LDX, m0, sX, LDX, n32, round_up(D, 16));
+    const bool on = n64 < D;
+    float acc[1][8][4];
+    acc_zero(acc);
+    if (on) {
+      WarpGemm<1, 8, true, true, T>::run(acc, A, LDP, m0, sDX, LDX, n64, C);
+      const float b_lo = sBeta[m0 + g8], b_hi = sBeta[m0 + g8 + 8];
+#pragma unroll
+      for (int ni = 0; ni < 8; ++ni) {
+        const int col = n64 + ni * 8 + 2 * t4;
+        const float2 x_lo = ld_pair<T>(sX + (m0 + g8) * LDX + col), x_hi = ld_pair<T>(sX + (m0 + g8 + 8) * LDX + col);
+        dbeta_lo += acc[0][ni][0] * x_lo.x + acc[0][ni][1] * x_lo.y;
+        dbeta_hi += acc[0][ni][2] * x_hi.x + acc[0][ni][3] * x_hi.y;
+        acc[0][ni][0] *= b_lo;
+        acc[0][ni][1] *= b_lo;
+        acc[0][ni][2] *= b_hi;
+        acc[0][ni][3] *= b_hi;
+      }
+    }
+    __syncthreads();  // every warp has read dx
+    if (on) acc_to_smem<1, 8, T>(acc, sDX, LDX, m0, n64);
+  };
+  // dAcc <- -strict_lower(A^T strict_lower(dAcc diag(beta)) A^T), rounded to T between products; the result
+  // stays in registers (rounded).
+  auto transform = [&](float (&dAcc)[1][4][4], const T *A) {
+    FLAB_ACC_FOREACH(1, 4, m0, n32, row, col, mi, ni, r) { dAcc[mi][ni][r] = row > col ? dAcc[mi][ni][r] * sBeta[col] : 0.f; }
+    acc_to_smem<1, 4, T>(dAcc, sDA, LDP, m0, n32);
+    __syncthreads();
+    float x1[1][4][4];
+    acc_zero(x1);
+    WarpGemm<1, 4, false, false, T>::run(x1, sDA, LDP, m0, A, LDP, n32, C);  // dA A^T
+    acc_to_smem<1, 4, T>(x1, sTmp, LDP, m0, n32);
+    __syncthreads();
+    acc_zero(dAcc);
+    WarpGemm<1, 4, true, true, T>::run(dAcc, A, LDP, m0, sTmp, LDP, n32, C);  // A^T (dA A^T)
+    FLAB_ACC_FOREACH(1, 4, m0, n32, row, col, mi, ni, r) { dAcc[mi][ni][r] = row > col ? rnd<T>(-dAcc[mi][ni][r]) : 0.f; }
+  };
+
+  cp_async_wait<1>();
+  __syncthreads();  // Aw, k, dw have landed
+  if (!GATED) {
+    pass(sK, sDW, sAw, a.K, dA);
+    cp_async_wait<0>();
+    __syncthreads();  // v, du have landed
+    pass(sV, sDU, sAw, a.V, dA);
+    transform(dA, sAw);
+  } else {
+    pass(sK, sDW, sAw, a.K, dA);
+    transform(dA, sAw);
+    cp_async_wait<0>();
+    __syncthreads();  // Au, v, du have landed; every warp is done with the staging buffers
+    pass(sV, sDU, sAu, a.V, dA2);
+    transform(dA2, sAu);
+    FLAB_ACC_FOREACH(1, 4, m0, n32, row, col, mi, ni, r) {
+      const float x2 = dA2[mi][ni][r] * safe_fexp<T>(sG[row] - sG[col]);
+      dA2[mi][ni][r] = x2;
+      dA[mi][ni][r] = rnd<T>(dA[mi][ni][r] + x2);
+    }
+  }
+  __syncthreads();  // dv is complete in sDU; the staging buffers are idle
+  tile_store<T>(reinterpret_cast<T *>(a.dv) + offv, vs, sDU, LDX, rows, a.V, tid, 256);
+  acc_to_smem<1, 4, T>(dA, sDA, LDP, m0, n32);
+  {
+    float dAb[1][4][4];
+    FLAB_ACC_FOREACH(1, 4, m0, n32, row, col, mi, ni, r) { dAb[mi][ni][r] = dA[mi][ni][r] * sBeta[row]; }
+    acc_to_smem<1, 4, T>(dAb, sTmp, LDP, m0, n32);
+  }
+  __syncthreads();
+
+  // dk = (A^T dw) beta + (dA k) beta + (diag(beta) dA)^T k ; dbeta += sum((dA k) * k)
+  if (n64 < a.K) {
+    float acc[1][8][4];
+    acc_zero(acc);
+    WarpGemm<1, 8, false, true, T>::run(acc, sDA, LDP, m0, sK, LDX, n64, C);  // dA k
+    const float b_lo = sBeta[m0 + g8], b_hi = sBeta[m0 + g8 + 8];
+#pragma unroll
+    for (int ni = 0; ni < 8; ++ni) {
+      const int col = n64 + ni * 8 + 2 * t4;
+      const int o_lo = (m0 + g8) * LDX + col, o_hi = (m0 + g8 + 8) * LDX + col;
+      const float2 k_lo = ld_pair<T>(sK + o_lo), k_hi = ld_pair<T>(sK + o_hi);
+      const float2 d_lo = ld_pair<T>(sDW + o_lo), d_hi = ld_pair<T>(sDW + o_hi);  // first-pass dk (rounded to T)
+      dbeta_lo += acc[0][ni][0] * k_lo.x + acc[0][ni][1] * k_lo.y;
+      dbeta_hi += acc[0][ni][2] * k_hi.x + acc[0][ni][3] * k_hi.y;
+      acc[0][ni][0] = d_lo.x + acc[0][ni][0] * b_lo;
+      acc[0][ni][1] = d_lo.y + acc[0][ni][1] * b_lo;
+      acc[0][ni][2] = d_hi.x + acc[0][ni][2] * b_hi;
+      acc[0][ni][3] = d_hi.y + acc[0][ni][3] * b_hi;
+    }
+    WarpGemm<1, 8, true, true, T>::run(acc, sTmp, LDP, m0, sK, LDX, n64, C);  // (diag(beta) dA)^T k
+    // each thread overwrites exactly the sDW elements it just read
+    acc_to_smem<1, 8, T>(acc, sDW, LDX, m0, n64);
+  }
+  // dbeta: quad reduction, then the two column halves meet in shared memory
+  dbeta_lo += __shfl_xor_sync(0xffffffffu, dbeta_lo, 1);
+  dbeta_lo += __shfl_xor_sync(0xffffffffu, dbeta_lo, 2);
+  dbeta_hi += __shfl_xor_sync(0xffffffffu, dbeta_hi, 1);
+  dbeta_hi += __shfl_xor_sync(0xffffffffu, dbeta_hi, 2);
+  if (t4 == 0) {
+    atomicAdd(&sDB[m0 + g8], dbeta_lo);
+    atomicAdd(&sDB[m0 + g8 + 8], dbeta_hi);
+  }
+  if (GATED) {
+    // dg = rowsum(dA2 * Gram) - colsum(dA2 * Gram), Gram = diag(beta) k k^T
+    float gram[1][4][4];
+    acc_zero(gram);
+    WarpGemm<1, 4, false, false, T>::run(gram, sK, LDX, m0, sK, LDX, n32, round_up(a.K, 16));
+    const float b_lo = sBeta[m0 + g8], b_hi = sBeta[m0 + g8 + 8];
+    float r_lo = 0.f, r_hi = 0.f;
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni) {
+      const float p0 = dA2[0][ni][0] * gram[0][ni][0] * b_lo, p1 = dA2[0][ni][1] * gram[0][ni][1] * b_lo;
+      const float p2 = dA2[0][ni][2] * gram[0][ni][2] * b_hi, p3 = dA2[0][ni][3] * gram[0][ni][3] * b_hi;
+      r_lo += p0 + p1;
+      r_hi += p2 + p3;
+      float c0 = p0 + p2, c1 = p1 + p3;
+      c0 += __shfl_xor_sync(0xffffffffu, c0, 4);
+      c0 += __shfl_xor_sync(0xffffffffu, c0, 8);
+      c0 += __shfl_xor_sync(0xffffffffu, c0, 16);
+      c1 += __shfl_xor_sync(0xffffffffu, c1, 4);
+      c1 += __shfl_xor_sync(0xffffffffu, c1, 8);
+      c1 += __shfl_xor_sync(0xffffffffu, c1, 16);
+      if (g8 == 0) {
+        atomicAdd(&sDG[n32 + ni * 8 + 2 * t4], -c0);
+        atomicAdd(&sDG[n32 + ni * 8 + 2 * t4 + 1], -c1);
+      }
+    }
+    r_lo += __shfl_xor_sync(0xffffffffu, r_lo, 1);
+    r_lo += __shfl_xor_sync(0xffffffffu, r_lo, 2);
+    r_hi += __shfl_xor_sync(0xffffffffu, r_hi, 1);
+    r_hi += __shfl_xor_sync(0xffffffffu, r_hi, 2);
+    if (t4 == 0) {
+      atomicAdd(&sDG[m0 + g8], r_lo);
+      atomicAdd(&sDG[m0 + g8 + 8], r_hi);
+    }
+  }
+  __syncthreads();
+  tile_store<T>(reinterpret_cast<T *>(a.dk) + offk, ks, sDW, LDX, rows, a.K, tid, 256);
+  if (tid < rows) {
+    reinterpret_cast<float *>(a.dbeta)[tok_off(a, s, hd, t0 + tid, 1)] = sDB[tid];
+    if (GATED) reinterpret_cast<float *>(a.dg)[tok_off(a, s, hd, t0 + tid, 1)] = sDG[tid];
+  }
+}
+
 template <typename T, bool GATED, bool RECOMPUTE> static int launch_wy_fwd(const flab_args *a, cudaStream_t stream) {
   constexpr int LDX = WT + Num<T>::pad, LDP = C + Num<T>::pad, NM = GATED ? 2 : 1;
   if (sizeof(T) == 2 && a->K <= WT && a->V <= WT) {
@@ -579,6 +778,13 @@ template <typename T, bool GATED, bool RECOMPUTE> static int launch_wy_fwd(const
 
 template <typename T, bool GATED> static int launch_wy_bwd(const flab_args *a, cudaStream_t stream) {
   constexpr int LDX = WT + Num<T>::pad, LDP = C + Num<T>::pad;
+  if (sizeof(T) == 2 && a->K <= WT && a->V <= WT) {
+    size_t smem = ((size_t)4 * C * LDX + (size_t)(GATED ? 4 : 3) * C * LDP) * sizeof(T) + 4 * C * sizeof(float);
+    auto kern = wy_bwd16_kernel<T, GATED>;
+    if (int e = set_smem(kern, smem)) return e;
+    kern<<<dim3(a->NT, a->H), 256, smem, stream>>>(*a);
+    return check_launch("wy_bwd");
+  }
   size_t smem = ((size_t)3 * C * LDX + (size_t)(GATED ? 4 : 3) * C * LDP) * sizeof(T) + 3 * C * sizeof(float);
   auto kern = wy_bwd_kernel<T, GATED>;
   if (int e = set_smem(kern, smem)) return e;
