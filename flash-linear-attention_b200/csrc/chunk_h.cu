@@ -52,18 +52,31 @@ __global__ void __launch_bounds__(128) chunk_h_kernel(const flab_args a) {
     const int rows = min(C, s.len - t0);
     tile_load<T>(sX + buf * C * LD, LD, X + (size_t)t0 * xs, xs, rows, C, kw, HB, tid, 128);
     tile_load<T>(sY + buf * C * LD, LD, Y + (size_t)t0 * ys, ys, rows, C, vw, HB, tid, 128);
-    if (GATE == 1 && tid < C) sG[buf * C + tid] = tid < rows ? G[(size_t)(t0 + tid) * gs] : 0.f;
     if (GATE == 2) tile_load<float>(sGK + buf * C * LDG, LDG, GK + (size_t)t0 * xs, xs, rows, C, kw, HB, tid, 128);
     cp_async_commit();
   };
 
+  // scalar gate of token `tid` of chunk `it`, fetched into a register one chunk ahead: the load's latency never
+  // sits between two barriers of the serial chain
+  auto gate_of = [&](int it) -> float {
+    const int t0 = it * C;
+    return (GATE == 1 && tid < C && t0 + tid < s.len) ? G[(size_t)(t0 + tid) * gs] : 0.f;
+  };
   const int first = BWD ? s.nt - 1 : 0, step = BWD ? -1 : 1;
-  if (s.nt > 0) load(first, 0);
+  float g_pf = 0.f;
+  if (s.nt > 0) {
+    load(first, 0);
+    g_pf = gate_of(first);
+  }
   for (int i = 0; i < s.nt; ++i) {
     const int it = first + i * step, cur = i & 1;
+    if (GATE == 1 && tid < C) sG[cur * C + tid] = g_pf;
     cp_async_wait<0>();
     __syncthreads();  // tiles of this chunk have landed; every warp is done with the previous chunk
-    if (i + 1 < s.nt) load(it + step, cur ^ 1);
+    if (i + 1 < s.nt) {
+      load(it + step, cur ^ 1);
+      g_pf = gate_of(it + step);
+    }
     T *x = sX + cur * C * LD, *y = sY + cur * C * LD;
     const int rows = min(C, s.len - it * C);
     const int last = rows - 1;

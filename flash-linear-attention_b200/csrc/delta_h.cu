@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
   T *sSall = sVTall + NSLAB * 2 * NVT * C * LDB;   // [NSLAB][KP][LDB] rounded state
   T *sOpall = sSall + NSLAB * KP * LDB;            // [NSLAB][64][LDB] gate-scaled operand of the state update
   float *sG = reinterpret_cast<float *>(sOpall + NSLAB * C * LDB);  // [2][64] gates; [64] e^{b}; [64] e^{b_L-b}
-  float *sE1 = sG + 2 * C, *sE2 = sE1 + C;
+  float *sE1 = sG + 2 * C + slab * 2 * C, *sE2 = sE1 + C;  // per slab: the slabs only meet at barrier (1)
   T *sVT = sVTall + slab * 2 * NVT * C * LDB, *sS = sSall + slab * KP * LDB, *sOp = sOpall + slab * C * LDB;
 
   const int v0 = (blockIdx.x * NSLAB + slab) * DBV;
@@ -101,7 +101,6 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
 #pragma unroll
     for (int j = 0; j < NVT; ++j)
       tile_load<T>(sVT + (buf * NVT + j) * C * LDB, LDB, vt_src[j] + (size_t)t0 * vs, vs, rows, C, vw, DBV, stid, 256);
-    if (tid < C) sG[buf * C + tid] = (use_g && tid < rows) ? G[(size_t)(t0 + tid) * gs] : 0.f;
     cp_async_commit();
   };
   // tiles read by the state update (fwd: k, bwd: q and w)
@@ -114,18 +113,34 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
     cp_async_commit();
   };
 
+  // gate of token `tid` of chunk `it`; fetched into a register one chunk ahead so that the load's latency is
+  // never between two barriers of the serial chain
+  auto gate_of = [&](int it) -> float {
+    const int t0 = it * C;
+    return (use_g && tid < C && t0 + tid < s.len) ? G[(size_t)(t0 + tid) * gs] : 0.f;
+  };
+  // barrier among the eight warps of one slab (everything between (1) and the next (1) is slab-private,
+  // except the staggered k buffer, which is refilled after (3))
+  auto slab_sync = [&]() {
+    if (NSLAB == 1) __syncthreads();
+    else asm volatile("bar.sync %0, 256;" ::"r"(1 + slab) : "memory");
+  };
   const int first = BWD ? s.nt - 1 : 0, step = BWD ? -1 : 1;
+  float g_pf = 0.f;
   if (s.nt > 0) {
     load_late(first, 0);
     load_early(first, 0);
+    g_pf = gate_of(first);
   }
   for (int i = 0; i < s.nt; ++i) {
     const int it = first + i * step, cur = i & 1;
+    if (tid < C) sG[cur * C + tid] = g_pf;
     cp_async_wait<0>();
     __syncthreads();  // (1) tiles of this chunk have landed; every warp is done with the previous chunk
     if (i + 1 < s.nt) {  // prefetch into the buffers the previous chunk used
       load_late(it + step, cur ^ 1);
       if (!STAG) load_early(it + step, cur ^ 1);
+      g_pf = gate_of(it + step);
     }
     const int t0 = it * C, rows = min(C, s.len - t0), last = rows - 1;
     T *vt = sVT + cur * NVT * C * LDB;
@@ -133,9 +148,9 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
     const float gl = gc[last];
     // (a) rounded state -> shared; per-token gate factors; bwd: do' = do * e^{b} * scale in place
     acc_to_smem<SMI, SNI, T>(acc, sS, LDB, ms, ns);
-    if (tid < C) {
-      sE1[tid] = use_g ? fexp<T>(gc[tid]) : 1.f;
-      sE2[tid] = use_g ? fexp<T>(gl - gc[tid]) : 1.f;
+    if (stid < C) {
+      sE1[stid] = use_g ? fexp<T>(gc[stid]) : 1.f;
+      sE2[stid] = use_g ? fexp<T>(gl - gc[stid]) : 1.f;
     }
     if (BWD) {
       for (int e = stid; e < C * (DBV / 2); e += 256) {
@@ -145,7 +160,7 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
         st_pair<T>(p, Num<T>::f(p[0]) * f, Num<T>::f(p[1]) * f);
       }
     }
-    __syncthreads();  // (2)
+    slab_sync();  // (2)
     // (b) state at the chunk boundary -> global (coalesced, off the critical path)
     {
       const size_t hoff = ((size_t)(s.c0 + it) * a.H + hd) * a.K * a.V + v0;
@@ -174,7 +189,7 @@ __global__ void __launch_bounds__(256 * NSLAB) delta_h_kernel(const flab_args a)
       acc_to_smem<1, 4, T>(p, y, LDB, m0, n0);
       acc_to_smem<1, 4, T>(op, sOp, LDB, m0, n0);
     }
-    __syncthreads();  // (3)
+    if (STAG) __syncthreads(); else slab_sync();  // (3)
     if (STAG && i + 1 < s.nt) load_early(it + step, cur ^ 1);  // every warp has left (c): the k buffer is free
     // (d) v_new / dv2 -> global
     tile_store<T>(Vout + (size_t)t0 * vs, vs, BWD ? vt + C * LDB : vt, LDB, rows, vw, stid, 256);
@@ -207,7 +222,7 @@ template <typename T, int KP, bool BWD, int NSLAB> static int launch_delta_h(con
   constexpr int NKT = BWD ? 3 : 2, NVT = BWD ? 2 : 1;
   constexpr int NKBUF = (BWD && NSLAB == 2) ? 5 : 2 * NKT;
   size_t smem = ((size_t)NKBUF * C * LDK + NSLAB * ((size_t)2 * NVT * C * LDB + (size_t)KP * LDB + (size_t)C * LDB)) * sizeof(T) +
-                4 * C * sizeof(float);
+                (2 + 2 * NSLAB) * C * sizeof(float);
   auto kern = delta_h_kernel<T, KP, BWD, NSLAB>;
   if (int e = set_smem(kern, smem)) return e;
   kern<<<dim3(cdiv(a->V, DBV * NSLAB), a->N * a->H), 256 * NSLAB, smem, stream>>>(*a);
