@@ -34,6 +34,21 @@ __global__ void cumsum_kernel(const flab_args a, const T *__restrict__ x, float 
   const size_t base = tok_off(a, s, h, 0, S) + sc;
   const size_t st = tok_stride(a, S);
   float acc = 0.f;
+  if (LOCAL) {
+    // a chunk is at most 64 tokens: fetch the whole column first (independent loads, all in flight together),
+    // then run the dependent chain over registers
+    const bool rev = (a.flags & FLAB_F_REVERSE) != 0;
+    const int len = t1 - t0;
+    float v[C];
+#pragma unroll
+    for (int j = 0; j < C; ++j) v[j] = j < len ? Num<T>::f(x[base + (size_t)(rev ? t1 - 1 - j : t0 + j) * st]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < C; ++j) {
+      acc += v[j];
+      if (j < len) y[base + (size_t)(rev ? t1 - 1 - j : t0 + j) * st] = acc;
+    }
+    return;
+  }
   if (a.flags & FLAB_F_REVERSE) {
     for (int t = t1 - 1; t >= t0; --t) {
       acc += Num<T>::f(x[base + (size_t)t * st]);
@@ -53,7 +68,7 @@ template <bool LOCAL> static int launch_cumsum(const flab_args *a, int S, void *
   FLAB_REQUIRE(S > 0, FLAB_E_BADARG, "cumsum: S must be positive");
   if (LOCAL) FLAB_REQUIRE(a->NT > 0, FLAB_E_BADARG, "cumsum: NT must be positive");
   long cols = (long)(LOCAL ? a->NT : a->N) * a->H * S;
-  int threads = 128;
+  const int threads = LOCAL ? 64 : 128;
   long blocks = (cols + threads - 1) / threads;
   FLAB_DISPATCH_ALL(a->dtype, T,
                     cumsum_kernel<T, LOCAL><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(

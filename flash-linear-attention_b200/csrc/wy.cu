@@ -509,6 +509,7 @@ __global__ void __launch_bounds__(128) wy_bwd_kernel(const flab_args a) {
       float kv = Num<T>::f(sX[row * LDX + col]);
       if (r >> 1) dbeta_hi += xb * kv; else dbeta_lo += xb * kv;
       acc[mi][ni][r] += Num<T>::f(sD[row * LDX + col]) + xb * sBeta[row];
+      if (a.x && row < rows && col < kw) acc[mi][ni][r] += Num<T>::f(reinterpret_cast<const T *>(a.x)[offk + (size_t)row * ks + k0 + col]);
     }
     // each thread overwrites exactly the sD elements it just read
     acc_to_smem<1, 16, T>(acc, sD, LDX, m0, 0);
@@ -653,6 +654,13 @@ __global__ void __launch_bounds__(256, 2) wy_bwd16_kernel(const flab_args a) {
     FLAB_ACC_FOREACH(1, 4, m0, n32, row, col, mi, ni, r) { dAcc[mi][ni][r] = row > col ? rnd<T>(-dAcc[mi][ni][r]) : 0.f; }
   };
 
+  // optional dk of an earlier stage to accumulate onto: fetched into the v buffer once v is no longer needed
+  const T *dk_in = reinterpret_cast<const T *>(a.x);
+  auto load_dk_in = [&]() {
+    if (dk_in) tile_load<T>(sV, LDX, dk_in + offk, ks, rows, C, a.K, WT, tid, 256);
+    cp_async_commit();
+  };
+
   cp_async_wait<1>();
   __syncthreads();  // Aw, k, dw have landed
   if (!GATED) {
@@ -660,6 +668,7 @@ __global__ void __launch_bounds__(256, 2) wy_bwd16_kernel(const flab_args a) {
     cp_async_wait<0>();
     __syncthreads();  // v, du have landed
     pass(sV, sDU, sAw, a.V, dA);
+    load_dk_in();
     transform(dA, sAw);
   } else {
     pass(sK, sDW, sAw, a.K, dA);
@@ -667,6 +676,7 @@ __global__ void __launch_bounds__(256, 2) wy_bwd16_kernel(const flab_args a) {
     cp_async_wait<0>();
     __syncthreads();  // Au, v, du have landed; every warp is done with the staging buffers
     pass(sV, sDU, sAu, a.V, dA2);
+    load_dk_in();
     transform(dA2, sAu);
     FLAB_ACC_FOREACH(1, 4, m0, n32, row, col, mi, ni, r) {
       const float x2 = dA2[mi][ni][r] * safe_fexp<T>(sG[row] - sG[col]);
@@ -674,7 +684,8 @@ __global__ void __launch_bounds__(256, 2) wy_bwd16_kernel(const flab_args a) {
       dA[mi][ni][r] = rnd<T>(dA[mi][ni][r] + x2);
     }
   }
-  __syncthreads();  // dv is complete in sDU; the staging buffers are idle
+  cp_async_wait<0>();
+  __syncthreads();  // dv is complete in sDU; the staging buffers are idle; dk_in has landed
   tile_store<T>(reinterpret_cast<T *>(a.dv) + offv, vs, sDU, LDX, rows, a.V, tid, 256);
   acc_to_smem<1, 4, T>(dA, sDA, LDP, m0, n32);
   {
@@ -702,6 +713,13 @@ __global__ void __launch_bounds__(256, 2) wy_bwd16_kernel(const flab_args a) {
       acc[0][ni][1] = d_lo.y + acc[0][ni][1] * b_lo;
       acc[0][ni][2] = d_hi.x + acc[0][ni][2] * b_hi;
       acc[0][ni][3] = d_hi.y + acc[0][ni][3] * b_hi;
+      if (dk_in) {
+        const float2 i_lo = ld_pair<T>(sV + o_lo), i_hi = ld_pair<T>(sV + o_hi);
+        acc[0][ni][0] += i_lo.x;
+        acc[0][ni][1] += i_lo.y;
+        acc[0][ni][2] += i_hi.x;
+        acc[0][ni][3] += i_hi.y;
+      }
     }
     WarpGemm<1, 8, true, true, T>::run(acc, sTmp, LDP, m0, sK, LDX, n64, C);  // (diag(beta) dA)^T k
     // each thread overwrites exactly the sDW elements it just read

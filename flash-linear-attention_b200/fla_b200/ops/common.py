@@ -125,14 +125,15 @@ def fwd_recompute_w_u(geo: Geometry, k, v, beta, aw, au=None):
     return w, u
 
 
-def bwd_prepare_wy_repr(geo: Geometry, k, v, beta, aw, dw, du, g=None, au=None):
+def bwd_prepare_wy_repr(geo: Geometry, k, v, beta, aw, dw, du, g=None, au=None, dk_in=None):
     """Backward of the WY transform (fla/ops/delta_rule/wy_fast.py:619,
-    fla/ops/gated_delta_rule/wy_fast.py:565). Returns (dk, dv, dbeta, dg)."""
+    fla/ops/gated_delta_rule/wy_fast.py:565). Returns (dk, dv, dbeta, dg). `dk_in` (optional, same dtype as
+    k) is added to the returned dk inside the kernel, in fp32, before the single rounding."""
     dk, dv = torch.empty_like(k), torch.empty_like(v)
     dbeta = torch.empty(beta.shape, dtype=torch.float32, device=k.device)
     dg = torch.empty(beta.shape, dtype=torch.float32, device=k.device) if g is not None else None
     _lib.call("flab_wy_bwd", k, **geo.kw(), k=k, v=v, beta=beta, g=g, aw=aw, au=au, dw=dw, du=du, dk=dk, dv=dv,
-              dbeta=dbeta, dg=dg)
+              dbeta=dbeta, dg=dg, x=dk_in)
     return dk, dv, dbeta, dg
 
 

@@ -31,8 +31,7 @@ def chunk_delta_rule_bwd(geo, q, k, v, beta, aw, scale, initial_state, do, dht, 
     dh, dh0, dv = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, dht=dht,
                                                    want_dh0=initial_state is not None)
     dq, dk, dw, _ = C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, w=w, dv=dv)
-    dk2, dv, db, _ = C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv)
-    dk.add_(dk2)
+    dk, dv, db, _ = C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv, dk_in=dk)
     return dq, dk, dv, db, dh0
 
 

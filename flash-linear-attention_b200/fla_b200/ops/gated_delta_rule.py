@@ -50,8 +50,7 @@ def chunk_gated_delta_rule_bwd(geo, q, k, v, g, beta, aw, au, scale, initial_sta
     dh, dh0, dv = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g, dht=dht,
                                                    want_dh0=initial_state is not None)
     dq, dk, dw, dg = C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=g, w=w, dv=dv)
-    dk2, dv, db, dg2 = C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv, g=g, au=au)
-    dk.add_(dk2)
+    dk, dv, db, dg2 = C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv, g=g, au=au, dk_in=dk)
     dg.add_(dg2)
     dg = C.chunk_local_cumsum(dg, reverse=True, offsets=geo.offsets_tensor, head_first=geo.head_first)
     return dq, dk, dv, db, dg, dh0

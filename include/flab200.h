@@ -131,7 +131,9 @@ int flab_wy_fwd(const flab_args *a, void *stream);
 int flab_wy_recompute(const flab_args *a, void *stream);
 /* Replaces bwd_prepare_wy_repr (fla/ops/delta_rule/wy_fast.py:619,
  * fla/ops/gated_delta_rule/wy_fast.py:565): reads k, v, beta, g (gated only), aw, au (gated only),
- * dw, du; writes dk, dv, dbeta (fp32) and dg (fp32, gated only). */
+ * dw, du; writes dk, dv, dbeta (fp32) and dg (fp32, gated only). Optional x: a dk of the element type
+ * to accumulate onto (the reference adds the dk of chunk_bwd_dqkwg afterwards, chunk.py:168); the sum
+ * is formed in fp32 and rounded once. */
 int flab_wy_bwd(const flab_args *a, void *stream);
 
 /* ---- state recurrence of the (gated) delta rule ----------------------------------------------
