@@ -241,6 +241,17 @@ template <bool BWD> static int dispatch_delta_h(const flab_args *a, void *stream
   return FLAB_OK;
 }
 
+// tcgen05 / TMA kernel for the shapes it covers (tc_delta_h.cu); 1 = handled, 0 = not applicable
+int tc_delta_fwd_h_try(const flab_args *a, cudaStream_t stream);
+static bool tc_scan_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("FLA_B200_NO_TC");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 }  // namespace flab
 
 extern "C" {
@@ -249,6 +260,10 @@ int flab_delta_fwd_h(const flab_args *a, void *stream) {
   using namespace flab;
   if (int e = check_common(a)) return e;
   FLAB_REQUIRE(a->k && a->w && a->u && a->h && a->v_new, FLAB_E_BADARG, "delta_fwd_h needs k, w, u, h and v_new");
+  if (tc_scan_enabled()) {
+    const int r = tc_delta_fwd_h_try(a, (cudaStream_t)stream);
+    if (r != 0) return r < 0 ? r : FLAB_OK;
+  }
   return dispatch_delta_h<false>(a, stream);
 }
 
