@@ -243,6 +243,7 @@ template <bool BWD> static int dispatch_delta_h(const flab_args *a, void *stream
 
 // tcgen05 / TMA kernel for the shapes it covers (tc_delta_h.cu); 1 = handled, 0 = not applicable
 int tc_delta_fwd_h_try(const flab_args *a, cudaStream_t stream);
+int tc_delta_bwd_dhu_try(const flab_args *a, cudaStream_t stream);
 static bool tc_scan_enabled() {
   static int v = -1;
   if (v < 0) {
@@ -272,6 +273,10 @@ int flab_delta_bwd_dhu(const flab_args *a, void *stream) {
   if (int e = check_common(a)) return e;
   FLAB_REQUIRE(a->q && a->k && a->w && a->d_o && a->dv && a->dh && a->dv2, FLAB_E_BADARG,
                "delta_bwd_dhu needs q, k, w, d_o, dv, dh and dv2");
+  if (tc_scan_enabled()) {
+    const int r = tc_delta_bwd_dhu_try(a, (cudaStream_t)stream);
+    if (r != 0) return r < 0 ? r : FLAB_OK;
+  }
   return dispatch_delta_h<true>(a, stream);
 }
 }

@@ -1,6 +1,12 @@
-// tcgen05 / TMA version of the forward delta-rule state scan (bf16 / fp16, K = 128, V % 64 == 0):
-//   per chunk t:  h[t] = S;  v_new = u - e^{b} (w S);  S <- e^{b_L} S + k^T (e^{b_L - b} v_new)
+// tcgen05 / TMA version of the delta-rule state scans (bf16 / fp16, K = 128, V % 64 == 0):
+//   forward, per chunk t:  h[t] = S;  v_new = u - e^{b} (w S);  S <- e^{b_L} S + k^T (e^{b_L - b} v_new)
 //   (fla/ops/common/chunk_delta_h.py:248-321)
+//   backward, chunks in reverse:  dh[t] = S;  dv2 = dv + e^{b_L - b} (k S);
+//                                 S <- e^{b_L} S + q^T (scale e^{b} do) - w^T (e^{b} dv2)
+//   (fla/ops/common/chunk_delta_h.py:323-423)
+// The two directions share one kernel: "P" below is the dependent product against the rounded state
+// (forward w S, backward k S), "y" the tile it corrects (u -> v_new, dv -> dv2), "op" the gate-scaled
+// operand of the state update.
 // One CTA per (sequence, head, value tile of 128 or 64 columns); the chunks of a sequence form a serial
 // chain, so the kernel is organised around the latency of one step:
 //   warp EW     : TMA producer - streams the w, k, u tiles of the next chunks into a ring of stages
@@ -26,20 +32,24 @@ struct TcDhParams {
   int ab_fmt;   // 1 bf16, 0 fp16
 };
 
-template <int VB /* BV / 64 */, int NS>
+template <int VB /* BV / 64 */, int NS, bool BWD>
 __global__ void __launch_bounds__(64 * (4 * VB + 1), 1)
-tc_delta_fwd_h_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapK,
-                      const __grid_constant__ CUtensorMap mapU, const __grid_constant__ CUtensorMap mapH,
-                      const __grid_constant__ CUtensorMap mapVn, const TcDhParams p) {
+tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant__ CUtensorMap mapA2,
+                  const __grid_constant__ CUtensorMap mapA3, const __grid_constant__ CUtensorMap mapY,
+                  const __grid_constant__ CUtensorMap mapDo, const __grid_constant__ CUtensorMap mapH,
+                  const __grid_constant__ CUtensorMap mapYo, const TcDhParams p) {
+  // tensor maps: A1 = A operand of P (fwd w, bwd k); A2, A3 = transposed A operands of the update (fwd k, -;
+  // bwd q, w); Y = corrected tile (fwd u, bwd dv); Do = do (bwd); H = h / dh (store); Yo = v_new / dv2 (store)
   using namespace tc;
   constexpr int K = 128, BV = 64 * VB, NC = 32;  // NC: state columns per epilogue thread
   constexpr int EW = BV / 8, ET = 32 * EW;         // epilogue warps (4 lane quadrants x BV/32 column groups), threads
-  constexpr uint32_t KT_BYTES = 2 * 8192, U_BYTES = VB * 8192, STAGE_BYTES = 2 * KT_BYTES + U_BYTES;
+  constexpr int NKT = BWD ? 3 : 2, NVT = BWD ? 2 : 1;  // [tokens x K] and [tokens x BV] tiles per chunk
+  constexpr uint32_t KT_BYTES = 2 * 8192, U_BYTES = VB * 8192, STAGE_BYTES = NKT * KT_BYTES + NVT * U_BYTES;
   constexpr uint32_t TM_DS = 0, TM_P = 128;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char *sStage = base;                        // [NS][w | k | u]
+  unsigned char *sStage = base;                        // [NS][A1 | A2 (| A3) | y (| do)]
   unsigned char *sS = sStage + NS * STAGE_BYTES;       // [VB][128 state rows][128 B] rounded state, B operand of w S
   unsigned char *sOp = sS + VB * K * 128;              // [VB][64 tokens][128 B] B operand of k^T op
   unsigned char *sVn = sOp + VB * 8192;                // [VB][64 tokens][128 B] v_new, same layout (source of the tile store)
@@ -85,17 +95,21 @@ tc_delta_fwd_h_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_con
       for (int i = 0; i < nt && !abort_flag; ++i) {
         const int st = i % NS, ph = (i / NS) & 1;
         if (!mbar_wait(&empty[st], ph ^ 1)) { fail(41); break; }
-        const int t0 = s.bos + i * C;
-        unsigned char *wt = sStage + st * STAGE_BYTES, *kt = wt + KT_BYTES, *ut = kt + KT_BYTES;
+        const int t0 = s.bos + (BWD ? nt - 1 - i : i) * C;
+        unsigned char *t1 = sStage + st * STAGE_BYTES, *yt = t1 + NKT * KT_BYTES;
         mbar_expect_tx(&full[st], STAGE_BYTES);
         const int c1 = a.head_first ? t0 : hd, c2 = a.head_first ? hd : t0;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          tma_load_4d(wt + j * 8192, &mapW, &full[st], 64 * j, c1, c2, s.b);
-          tma_load_4d(kt + j * 8192, &mapK, &full[st], 64 * j, c1, c2, s.b);
+          tma_load_4d(t1 + j * 8192, &mapA1, &full[st], 64 * j, c1, c2, s.b);
+          tma_load_4d(t1 + KT_BYTES + j * 8192, &mapA2, &full[st], 64 * j, c1, c2, s.b);
+          if (BWD) tma_load_4d(t1 + 2 * KT_BYTES + j * 8192, &mapA3, &full[st], 64 * j, c1, c2, s.b);
         }
 #pragma unroll
-        for (int j = 0; j < VB; ++j) tma_load_4d(ut + j * 8192, &mapU, &full[st], v0 + 64 * j, c1, c2, s.b);
+        for (int j = 0; j < VB; ++j) {
+          tma_load_4d(yt + j * 8192, &mapY, &full[st], v0 + 64 * j, c1, c2, s.b);
+          if (BWD) tma_load_4d(yt + U_BYTES + j * 8192, &mapDo, &full[st], v0 + 64 * j, c1, c2, s.b);
+        }
       }
     }
   } else if (warp == EW + 1) {
@@ -109,17 +123,26 @@ tc_delta_fwd_h_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_con
         if (!mbar_wait(&full[st], ph)) { fail(42); break; }
         if (!mbar_wait(&s_ready, sp)) { fail(43); break; }
         fence_after_sync();
-        const uint32_t wt = smem_u32(sStage + st * STAGE_BYTES), kt = wt + KT_BYTES;
+        const uint32_t t1 = smem_u32(sStage + st * STAGE_BYTES), t2 = t1 + KT_BYTES, t3 = t2 + KT_BYTES;
         // descriptors differ from step to step only in the 16-byte-granular start address (low bits)
-        const uint64_t dw0 = desc_kmajor(wt, 0, 8192), dk0 = desc_mnmajor(kt, 0, 8192);
+        const uint64_t d1 = desc_kmajor(t1, 0, 8192), d2 = desc_mnmajor(t2, 0, 8192);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma(tmem + TM_P, dw0 + (uint64_t)(((k >> 2) * 8192 + (k & 3) * 32) >> 4), ds0 + (uint64_t)((k * 2048) >> 4), idesc_p, k > 0);
+          umma(tmem + TM_P, d1 + (uint64_t)(((k >> 2) * 8192 + (k & 3) * 32) >> 4), ds0 + (uint64_t)((k * 2048) >> 4), idesc_p, k > 0);
         umma_commit(&p_done);
         if (!mbar_wait(&op_ready, sp)) { fail(44); break; }
         fence_after_sync();
+        if (!BWD) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma(tmem + TM_DS, dk0 + (uint64_t)((k * 2048) >> 4), do0 + (uint64_t)((k * 2048) >> 4), idesc_s, k > 0);
+          for (int k = 0; k < 4; ++k) umma(tmem + TM_DS, d2 + (uint64_t)((k * 2048) >> 4), do0 + (uint64_t)((k * 2048) >> 4), idesc_s, k > 0);
+        } else {
+          // q^T (scale e^{b} do): the do tile was rescaled in place by the epilogue; then w^T (-e^{b} dv2)
+          const uint64_t d3 = desc_mnmajor(t3, 0, 8192), dd = desc_mnmajor(t1 + NKT * KT_BYTES + U_BYTES, 0, 8192);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma(tmem + TM_DS, d2 + (uint64_t)((k * 2048) >> 4), dd + (uint64_t)((k * 2048) >> 4), idesc_s, k > 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma(tmem + TM_DS, d3 + (uint64_t)((k * 2048) >> 4), do0 + (uint64_t)((k * 2048) >> 4), idesc_s, 1);
+        }
         umma_commit(&ds_done);
         umma_commit(&empty[st]);
       }
@@ -134,8 +157,10 @@ tc_delta_fwd_h_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_con
     const int row_lo = 16 * wq + g8, row_hi = row_lo + 8;
     const size_t st_off = ((size_t)n * a.H + hd) * K * a.V + (size_t)srow * a.V + v0 + sc0;
     float S[NC];
-    if (a.h0) {
-      const float4 *src = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(a.h0) + st_off);
+    const float *S0 = reinterpret_cast<const float *>(BWD ? a.dht : a.h0);
+    float *S1 = reinterpret_cast<float *>(BWD ? a.dh0 : a.ht);
+    if (S0) {
+      const float4 *src = reinterpret_cast<const float4 *>(S0 + st_off);
 #pragma unroll
       for (int j = 0; j < NC / 4; ++j) {
         const float4 x = src[j];
@@ -147,10 +172,15 @@ tc_delta_fwd_h_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_con
     }
     const float *G = use_g ? reinterpret_cast<const float *>(a.g) + tok_off(a, s, hd, 0, 1) : nullptr;
     const size_t gs = tok_stride(a, 1);
-    auto gate_of = [&](int i) -> float { return (use_g && tid < C && i * C + tid < s.len) ? G[(size_t)(i * C + tid) * gs] : 0.f; };
+    // i counts processed chunks; the backward scan walks them in reverse
+    auto chunk_at = [&](int i) { return BWD ? nt - 1 - i : i; };
+    auto gate_of = [&](int i) -> float {
+      const int t = chunk_at(i) * C + tid;
+      return (use_g && tid < C && t < s.len) ? G[(size_t)t * gs] : 0.f;
+    };
     float g_pf = nt > 0 ? gate_of(0) : 0.f;
     float d_prev = 1.f;
-    bf16 *vout = reinterpret_cast<bf16 *>(a.v_new);
+    bf16 *vout = reinterpret_cast<bf16 *>(BWD ? a.dv2 : a.v_new);
     const size_t vs = tok_stride(a, a.V);
     bool ok = true;
     for (int i = 0; i <= nt; ++i) {
@@ -197,30 +227,57 @@ tc_delta_fwd_h_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_con
       if (abort_snap[0]) break;
       if (tid == 0) {  // h[t]: one tile store per 64-column box, straight from the operand tile
 #pragma unroll
-        for (int j = 0; j < VB; ++j) tma_store_2d(&mapH, sS + j * (K * 128), v0 + 64 * j, ((s.c0 + i) * a.H + hd) * K);
+        for (int j = 0; j < VB; ++j) tma_store_2d(&mapH, sS + j * (K * 128), v0 + 64 * j, ((s.c0 + chunk_at(i)) * a.H + hd) * K);
         tma_store_commit();
       }
       if (i + 1 < nt) g_pf = gate_of(i + 1);
-      const int rows = min(C, s.len - i * C), last = rows - 1;
+      const int it = chunk_at(i), rows = min(C, s.len - it * C), last = rows - 1;
       const float *gc = sG + sp * C;
       const float gl = gc[last];
+      // row factors: fa multiplies P, fo turns the corrected tile into op
+      //   forward : v_new = u - e^{b} P,         op = e^{b_L-b} v_new
+      //   backward: dv2   = dv + e^{b_L-b} P,    op = -e^{b} dv2,   do' = scale e^{b} do
       float e1_lo = 1.f, e1_hi = 1.f, e2_lo = 1.f, e2_hi = 1.f;
       if (use_g) {
         e1_lo = __expf(gc[row_lo]), e1_hi = __expf(gc[row_hi]);
         e2_lo = __expf(gl - gc[row_lo]), e2_hi = __expf(gl - gc[row_hi]);
         d_prev = __expf(gl);
       }
-      if (row_lo >= rows) e2_lo = 0.f;  // rows past the end of the sequence contribute nothing to the state
-      if (row_hi >= rows) e2_hi = 0.f;
-      // ---- phase B: P = w S  ->  v_new, op
+      const bool in_lo = row_lo < rows, in_hi = row_hi < rows;  // rows past the end of the sequence add nothing to the state
+      const float fa_lo = BWD ? e2_lo : -e1_lo, fa_hi = BWD ? e2_hi : -e1_hi;
+      const float fo_lo = in_lo ? (BWD ? -e1_lo : e2_lo) : 0.f, fo_hi = in_hi ? (BWD ? -e1_hi : e2_hi) : 0.f;
+      // ---- phase B: P -> corrected tile y', op
       const int st = i % NS, ph = (i / NS) & 1;
-      if (!mbar_wait(&full[st], ph)) { fail(46); ok = false; }  // u tile (already complete: the product waited on it)
+      if (!mbar_wait(&full[st], ph)) { fail(46); ok = false; }  // y (and do) tiles (already complete: the product waited on it)
+      unsigned char *yt = sStage + st * STAGE_BYTES + NKT * KT_BYTES;
+      if (BWD) {
+        // do' = scale e^{b} do, in place (runs while the tensor core computes P)
+        unsigned char *dt = yt + U_BYTES;
+        const float s_lo = in_lo ? e1_lo * a.scale : 0.f, s_hi = in_hi ? e1_hi * a.scale : 0.f;
+#pragma unroll
+        for (int ni = 0; ni < NC / 8; ++ni) {
+          const int col = NC * chh + 8 * ni + 2 * t4;
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            const uint32_t off = (uint32_t)(col >> 6) * 8192u + sw128_offset(hf ? row_hi : row_lo, col & 63);
+            const float f = hf ? s_hi : s_lo;
+            if (p.ab_fmt) {
+              __nv_bfloat162 *q2 = reinterpret_cast<__nv_bfloat162 *>(dt + off);
+              const float2 x = __bfloat1622float2(*q2);
+              *q2 = __floats2bfloat162_rn(x.x * f, x.y * f);
+            } else {
+              __half2 *q2 = reinterpret_cast<__half2 *>(dt + off);
+              const float2 x = __half22float2(*q2);
+              *q2 = __floats2half2_rn(x.x * f, x.y * f);
+            }
+          }
+        }
+      }
       if (!mbar_wait(&p_done, sp)) { fail(47); ok = false; }
       fence_after_sync();
       float pr[NC / 8][4];
       tmem_ld_frag<NC / 8>(tmem + lane_base + TM_P + NC * chh, pr);
       tmem_ld_wait();
-      const unsigned char *ut = sStage + st * STAGE_BYTES + 2 * KT_BYTES;
 #pragma unroll
       for (int ni = 0; ni < NC / 8; ++ni) {
         const int col = NC * chh + 8 * ni + 2 * t4;
@@ -230,24 +287,24 @@ tc_delta_fwd_h_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_con
           const uint32_t off = (uint32_t)(col >> 6) * 8192u + sw128_offset(row, col & 63);
           float u0, u1;
           if (p.ab_fmt) {
-            const float2 uu = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(ut + off));
+            const float2 uu = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(yt + off));
             u0 = uu.x, u1 = uu.y;
           } else {
-            const float2 uu = __half22float2(*reinterpret_cast<const __half2 *>(ut + off));
+            const float2 uu = __half22float2(*reinterpret_cast<const __half2 *>(yt + off));
             u0 = uu.x, u1 = uu.y;
           }
-          const float e1 = hf ? e1_hi : e1_lo, e2 = hf ? e2_hi : e2_lo;
-          const float x0 = u0 - e1 * pr[ni][2 * hf], x1 = u1 - e1 * pr[ni][2 * hf + 1];
+          const float fa = hf ? fa_hi : fa_lo, fo = hf ? fo_hi : fo_lo;
+          const float x0 = fmaf(fa, pr[ni][2 * hf], u0), x1 = fmaf(fa, pr[ni][2 * hf + 1], u1);
           if (p.ab_fmt) {
             const __nv_bfloat162 vn = __floats2bfloat162_rn(x0, x1);
             *reinterpret_cast<__nv_bfloat162 *>(sVn + off) = vn;
             const float2 vr = __bfloat1622float2(vn);
-            *reinterpret_cast<__nv_bfloat162 *>(sOp + off) = __floats2bfloat162_rn(vr.x * e2, vr.y * e2);
+            *reinterpret_cast<__nv_bfloat162 *>(sOp + off) = __floats2bfloat162_rn(vr.x * fo, vr.y * fo);
           } else {
             const __half2 vn = __floats2half2_rn(x0, x1);
             *reinterpret_cast<__half2 *>(sVn + off) = vn;
             const float2 vr = __half22float2(vn);
-            *reinterpret_cast<__half2 *>(sOp + off) = __floats2half2_rn(vr.x * e2, vr.y * e2);
+            *reinterpret_cast<__half2 *>(sOp + off) = __floats2half2_rn(vr.x * fo, vr.y * fo);
           }
         }
       }
@@ -263,14 +320,14 @@ tc_delta_fwd_h_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_con
       if (abort_snap[1]) break;
       if (rows == C) {
         if (tid == 0) {
-          const int t0 = s.bos + i * C, c1 = a.head_first ? t0 : hd, c2 = a.head_first ? hd : t0;
+          const int t0 = s.bos + it * C, c1 = a.head_first ? t0 : hd, c2 = a.head_first ? hd : t0;
 #pragma unroll
-          for (int j = 0; j < VB; ++j) tma_store_4d(&mapVn, sVn + j * 8192, v0 + 64 * j, c1, c2, s.b);
+          for (int j = 0; j < VB; ++j) tma_store_4d(&mapYo, sVn + j * 8192, v0 + 64 * j, c1, c2, s.b);
           tma_store_commit();
         }
       } else {
         // ragged last chunk: a tile store would write past the end of the sequence
-        bf16 *dst = vout + tok_off(a, s, hd, i * C, a.V) + v0;
+        bf16 *dst = vout + tok_off(a, s, hd, it * C, a.V) + v0;
         for (int e = tid; e < rows * (BV / 8); e += ET) {
           const int r_ = e / (BV / 8), c_ = (e - r_ * (BV / 8)) * 8;
           *reinterpret_cast<int4 *>(dst + (size_t)r_ * vs + c_) =
@@ -279,8 +336,8 @@ tc_delta_fwd_h_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_con
       }
     }
     if (tid == 0) tma_store_wait_all();
-    if (ok && !abort_flag && a.ht) {
-      float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(a.ht) + st_off);
+    if (ok && !abort_flag && S1) {
+      float4 *dst = reinterpret_cast<float4 *>(S1 + st_off);
 #pragma unroll
       for (int j = 0; j < NC / 4; ++j) dst[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
     }
@@ -290,35 +347,48 @@ tc_delta_fwd_h_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_con
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
-template <int VB, int NS> static int launch_tc_dh(const flab_args *a, cudaStream_t stream) {
+template <int VB, int NS, bool BWD> static int launch_tc_dh(const flab_args *a, cudaStream_t stream) {
   constexpr int BV = 64 * VB;
-  CUtensorMap mW, mK, mU, mH, mVn;
-  if (int e = make_token_map(&mW, a->w, a, a->K)) return e;
-  if (int e = make_token_map(&mK, a->k, a, a->K)) return e;
-  if (int e = make_token_map(&mU, a->u, a, a->V)) return e;
-  if (int e = make_state_map(&mH, a->h, a, 128)) return e;
-  if (int e = make_token_map(&mVn, a->v_new, a, a->V)) return e;
+  CUtensorMap mA1, mA2, mA3, mY, mDo, mH, mYo;
+  if (int e = make_token_map(&mA1, BWD ? a->k : a->w, a, a->K)) return e;
+  if (int e = make_token_map(&mA2, BWD ? a->q : a->k, a, a->K)) return e;
+  if (int e = make_token_map(&mA3, BWD ? a->w : a->k, a, a->K)) return e;
+  if (int e = make_token_map(&mY, BWD ? a->dv : a->u, a, a->V)) return e;
+  if (int e = make_token_map(&mDo, BWD ? a->d_o : a->u, a, a->V)) return e;
+  if (int e = make_state_map(&mH, BWD ? a->dh : a->h, a, 128)) return e;
+  if (int e = make_token_map(&mYo, BWD ? a->dv2 : a->v_new, a, a->V)) return e;
   TcDhParams p;
   p.a = *a;
   p.v_tiles = a->V / BV;
   p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
-  constexpr uint32_t STAGE = 2 * 16384 + VB * 8192;
+  constexpr uint32_t STAGE = (BWD ? 3 : 2) * 16384 + (BWD ? 2 : 1) * VB * 8192;
   const size_t smem = 1024 + NS * (size_t)STAGE + (size_t)VB * 128 * 128 + 2 * (size_t)VB * 8192 + 2 * C * sizeof(float);
-  auto kern = tc_delta_fwd_h_kernel<VB, NS>;
+  auto kern = tc_delta_h_kernel<VB, NS, BWD>;
   if (int e = set_smem(kern, smem)) return e;
-  kern<<<dim3(p.v_tiles, a->N * a->H), 64 * (4 * VB + 1), smem, stream>>>(mW, mK, mU, mH, mVn, p);
-  return check_launch("delta_fwd_h(tc)");
+  kern<<<dim3(p.v_tiles, a->N * a->H), 64 * (4 * VB + 1), smem, stream>>>(mA1, mA2, mA3, mY, mDo, mH, mYo, p);
+  return check_launch(BWD ? "delta_bwd_dhu(tc)" : "delta_fwd_h(tc)");
 }
 
-// Returns 1 if the tcgen05 kernel took the call, 0 if the shape is outside its domain, < 0 on error.
+static bool tc_dh_ok(const flab_args *a, const void *const *ptrs, int n) {
+  if (a->dtype != FLAB_BF16 && a->dtype != FLAB_FP16) return false;
+  if (a->K != 128 || a->V % 64 != 0) return false;
+  for (int i = 0; i < n; ++i)
+    if (ptrs[i] && reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return false;
+  return true;
+}
+
+// Return 1 if the tcgen05 kernel took the call, 0 if the shape is outside its domain, < 0 on error.
 int tc_delta_fwd_h_try(const flab_args *a, cudaStream_t stream) {
-  if (a->dtype != FLAB_BF16 && a->dtype != FLAB_FP16) return 0;
-  if (a->K != 128 || a->V % 64 != 0) return 0;
-  const void *ptrs[5] = {a->k, a->w, a->u, a->h, a->v_new};
-  for (int i = 0; i < 5; ++i)
-    if (reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return 0;
-  if ((a->h0 && reinterpret_cast<uintptr_t>(a->h0) % 16 != 0) || (a->ht && reinterpret_cast<uintptr_t>(a->ht) % 16 != 0)) return 0;
-  const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 3>(a, stream) : launch_tc_dh<1, 4>(a, stream);
+  const void *ptrs[7] = {a->k, a->w, a->u, a->h, a->v_new, a->h0, a->ht};
+  if (!tc_dh_ok(a, ptrs, 7)) return 0;
+  const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 3, false>(a, stream) : launch_tc_dh<1, 4, false>(a, stream);
+  return rc < 0 ? rc : 1;
+}
+
+int tc_delta_bwd_dhu_try(const flab_args *a, cudaStream_t stream) {
+  const void *ptrs[9] = {a->q, a->k, a->w, a->d_o, a->dv, a->dh, a->dv2, a->dht, a->dh0};
+  if (!tc_dh_ok(a, ptrs, 9)) return 0;
+  const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 2, true>(a, stream) : launch_tc_dh<1, 3, true>(a, stream);
   return rc < 0 ? rc : 1;
 }
 
