@@ -260,43 +260,28 @@ __global__ void __launch_bounds__(256, 2) chunk_dqkwg_kernel(const flab_args a) 
     }
     FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
       const bool hi = r >> 1;
-      float xq = dq[mi][ni][r] * (hi ? e_hi : e_lo) * a.scale;
-      float xk = dk[mi][ni][r] * (hi ? f_hi : f_lo);
-      if (use_g) {
-        float qv = Num<T>::f(sQ[row * LDK + col]), kv = Num<T>::f(sK[row * LDK + col]);
-        float d = xq * qv - xk * kv;
-        if (hi) dg_hi += d; else dg_lo += d;
-        dkk += xk * kv;
-      }
+      const float xq = dq[mi][ni][r] * (hi ? e_hi : e_lo) * a.scale;
+      const float xk = dk[mi][ni][r] * (hi ? f_hi : f_lo);
+      if (use_g) dkk += xk * Num<T>::f(sK[row * LDK + col]);
       dq[mi][ni][r] = xq;
       dk[mi][ni][r] = xk;
     }
-    if (use_g) {
-      // ds2 = ds * (q k^T): row sums add to dg, column sums subtract
-      float qk[1][4][4];
-      acc_zero(qk);
-      WarpGemm<1, 4, false, false, T>::run(qk, sQ, LDK, m0, sK, LDK, n0, QB);
-#pragma unroll
-      for (int ni = 0; ni < 4; ++ni) {
-        float p0 = ds[0][ni][0] * qk[0][ni][0], p1 = ds[0][ni][1] * qk[0][ni][1];
-        float p2 = ds[0][ni][2] * qk[0][ni][2], p3 = ds[0][ni][3] * qk[0][ni][3];
-        dg_lo += p0 + p1;
-        dg_hi += p2 + p3;
-        float c0 = p0 + p2, c1 = p1 + p3;
-        c0 += __shfl_xor_sync(0xffffffffu, c0, 4);
-        c0 += __shfl_xor_sync(0xffffffffu, c0, 8);
-        c0 += __shfl_xor_sync(0xffffffffu, c0, 16);
-        c1 += __shfl_xor_sync(0xffffffffu, c1, 4);
-        c1 += __shfl_xor_sync(0xffffffffu, c1, 8);
-        c1 += __shfl_xor_sync(0xffffffffu, c1, 16);
-        if (g8 == 0) {
-          atomicAdd(&sDG[n0 + ni * 8 + 2 * (lane & 3)], -c0);
-          atomicAdd(&sDG[n0 + ni * 8 + 2 * (lane & 3) + 1], -c1);
-        }
-      }
-    }
     WarpGemm<1, 4, false, true, T>::run(dq, sDS, LDP, m0, sK, LDK, n0, C);
     WarpGemm<1, 4, true, true, T>::run(dk, sDS, LDP, m0, sQ, LDK, n0, C);
+    if (use_g) {
+      // dg_i += <q_i, dq_i> - <k_i, dk_i> over the finished rows. This holds the inter-chunk terms and, because
+      // rowsum_i(ds * (q k^T)) = <q_i, (ds k)_i> and colsum_j(ds * (q k^T)) = <k_j, (ds^T q)_j>, the intra-chunk
+      // terms of fla/ops/common/chunk_o.py:520-560 as well, without forming q k^T.
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) {
+        const int col = n0 + ni * 8 + 2 * (lane & 3);
+        const int o_lo = (m0 + g8) * LDK + col, o_hi = (m0 + g8 + 8) * LDK + col;
+        const float2 q_lo = ld_pair<T>(sQ + o_lo), q_hi = ld_pair<T>(sQ + o_hi);
+        const float2 k_lo = ld_pair<T>(sK + o_lo), k_hi = ld_pair<T>(sK + o_hi);
+        dg_lo += dq[0][ni][0] * q_lo.x + dq[0][ni][1] * q_lo.y - dk[0][ni][0] * k_lo.x - dk[0][ni][1] * k_lo.y;
+        dg_hi += dq[0][ni][2] * q_hi.x + dq[0][ni][3] * q_hi.y - dk[0][ni][2] * k_hi.x - dk[0][ni][3] * k_hi.y;
+      }
+    }
     __syncthreads();  // all warps done reading q / k / w
     acc_to_smem<1, 4, T>(dq, sQ, LDK, m0, n0);
     acc_to_smem<1, 4, T>(dk, sK, LDK, m0, n0);
