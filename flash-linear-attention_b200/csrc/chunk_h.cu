@@ -167,6 +167,18 @@ template <typename T, bool BWD> static int launch_chunk_h(const flab_args *a, cu
   return check_launch(BWD ? "chunk_bwd_dh" : "chunk_fwd_h");
 }
 
+// tcgen05 / TMA kernels for the shapes they cover (tc_delta_h.cu); 1 = handled, 0 = not applicable
+int tc_chunk_fwd_h_try(const flab_args *a, cudaStream_t stream);
+int tc_chunk_bwd_dh_try(const flab_args *a, cudaStream_t stream);
+static bool tc_scan_on() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("FLA_B200_NO_TC");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 }  // namespace flab
 
 extern "C" {
@@ -177,6 +189,10 @@ int flab_chunk_fwd_h(const flab_args *a, void *stream) {
   FLAB_REQUIRE(a->k && a->v && a->h, FLAB_E_BADARG, "chunk_fwd_h needs k, v and h");
   FLAB_REQUIRE(!(a->g && a->gk), FLAB_E_UNSUPPORTED, "chunk_fwd_h: g and gk together are not supported");
   FLAB_REQUIRE(!a->gv, FLAB_E_UNSUPPORTED, "chunk_fwd_h: gv is not supported");
+  if (tc_scan_on()) {
+    const int r = tc_chunk_fwd_h_try(a, (cudaStream_t)stream);
+    if (r != 0) return r < 0 ? r : FLAB_OK;
+  }
   FLAB_DISPATCH_ALL(a->dtype, T, return (launch_chunk_h<T, false>(a, (cudaStream_t)stream)));
   return FLAB_OK;
 }
@@ -187,6 +203,10 @@ int flab_chunk_bwd_dh(const flab_args *a, void *stream) {
   FLAB_REQUIRE(a->q && a->d_o && a->dh, FLAB_E_BADARG, "chunk_bwd_dh needs q, d_o and dh");
   FLAB_REQUIRE(!(a->g && a->gk), FLAB_E_UNSUPPORTED, "chunk_bwd_dh: g and gk together are not supported");
   FLAB_REQUIRE(!a->gv, FLAB_E_UNSUPPORTED, "chunk_bwd_dh: gv is not supported");
+  if (tc_scan_on()) {
+    const int r = tc_chunk_bwd_dh_try(a, (cudaStream_t)stream);
+    if (r != 0) return r < 0 ? r : FLAB_OK;
+  }
   FLAB_DISPATCH_ALL(a->dtype, T, return (launch_chunk_h<T, true>(a, (cudaStream_t)stream)));
   return FLAB_OK;
 }

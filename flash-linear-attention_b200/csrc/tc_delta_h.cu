@@ -4,7 +4,10 @@
 //   backward, chunks in reverse:  dh[t] = S;  dv2 = dv + e^{b_L - b} (k S);
 //                                 S <- e^{b_L} S + q^T (scale e^{b} do) - w^T (e^{b} dv2)
 //   (fla/ops/common/chunk_delta_h.py:323-423)
-// The two directions share one kernel: "P" below is the dependent product against the rounded state
+// and of the plain chunk-state scans S <- e^{b_L} S + k^T (e^{b_L-b} v), dS <- e^{b_L} dS + q^T (scale e^{b} do)
+// (fla/ops/common/chunk_h.py:42-122, 125-215; scalar gate or none), which are the same chain without the
+// dependent product.
+// The directions share one kernel: "P" below is the dependent product against the rounded state
 // (forward w S, backward k S), "y" the tile it corrects (u -> v_new, dv -> dv2), "op" the gate-scaled
 // operand of the state update.
 // One CTA per (sequence, head, value tile of 128 or 64 columns); the chunks of a sequence form a serial
@@ -32,18 +35,22 @@ struct TcDhParams {
   int ab_fmt;   // 1 bf16, 0 fp16
 };
 
-template <int VB /* BV / 64 */, int NS, bool BWD>
+enum { DH_FWD = 0, DH_BWD = 1, DH_SIMPLE_FWD = 2, DH_SIMPLE_BWD = 3 };
+
+template <int VB /* BV / 64 */, int NS, int MODE>
 __global__ void __launch_bounds__(64 * (4 * VB + 1), 1)
 tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant__ CUtensorMap mapA2,
                   const __grid_constant__ CUtensorMap mapA3, const __grid_constant__ CUtensorMap mapY,
                   const __grid_constant__ CUtensorMap mapDo, const __grid_constant__ CUtensorMap mapH,
                   const __grid_constant__ CUtensorMap mapYo, const TcDhParams p) {
-  // tensor maps: A1 = A operand of P (fwd w, bwd k); A2, A3 = transposed A operands of the update (fwd k, -;
-  // bwd q, w); Y = corrected tile (fwd u, bwd dv); Do = do (bwd); H = h / dh (store); Yo = v_new / dv2 (store)
+  // tensor maps: A1 = A operand of P (fwd w, bwd k; simple: the transposed A operand of the update, k or q);
+  // A2, A3 = transposed A operands of the update (fwd k, -; bwd q, w); Y = corrected tile (fwd u, bwd dv; simple:
+  // v or do); Do = do (bwd); H = h / dh (store); Yo = v_new / dv2 (store)
   using namespace tc;
   constexpr int K = 128, BV = 64 * VB, NC = 32;  // NC: state columns per epilogue thread
   constexpr int EW = BV / 8, ET = 32 * EW;         // epilogue warps (4 lane quadrants x BV/32 column groups), threads
-  constexpr int NKT = BWD ? 3 : 2, NVT = BWD ? 2 : 1;  // [tokens x K] and [tokens x BV] tiles per chunk
+  constexpr bool BWD = (MODE & 1) != 0, SIMPLE = MODE >= 2;
+  constexpr int NKT = SIMPLE ? 1 : (BWD ? 3 : 2), NVT = (BWD && !SIMPLE) ? 2 : 1;  // [tokens x K] and [tokens x BV] tiles per chunk
   constexpr uint32_t KT_BYTES = 2 * 8192, U_BYTES = VB * 8192, STAGE_BYTES = NKT * KT_BYTES + NVT * U_BYTES;
   constexpr uint32_t TM_DS = 0, TM_P = 128;
 
@@ -102,13 +109,13 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           tma_load_4d(t1 + j * 8192, &mapA1, &full[st], 64 * j, c1, c2, s.b);
-          tma_load_4d(t1 + KT_BYTES + j * 8192, &mapA2, &full[st], 64 * j, c1, c2, s.b);
-          if (BWD) tma_load_4d(t1 + 2 * KT_BYTES + j * 8192, &mapA3, &full[st], 64 * j, c1, c2, s.b);
+          if (NKT > 1) tma_load_4d(t1 + KT_BYTES + j * 8192, &mapA2, &full[st], 64 * j, c1, c2, s.b);
+          if (NKT > 2) tma_load_4d(t1 + 2 * KT_BYTES + j * 8192, &mapA3, &full[st], 64 * j, c1, c2, s.b);
         }
 #pragma unroll
         for (int j = 0; j < VB; ++j) {
           tma_load_4d(yt + j * 8192, &mapY, &full[st], v0 + 64 * j, c1, c2, s.b);
-          if (BWD) tma_load_4d(yt + U_BYTES + j * 8192, &mapDo, &full[st], v0 + 64 * j, c1, c2, s.b);
+          if (NVT > 1) tma_load_4d(yt + U_BYTES + j * 8192, &mapDo, &full[st], v0 + 64 * j, c1, c2, s.b);
         }
       }
     }
@@ -121,18 +128,20 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
       for (int i = 0; i < nt && !abort_flag; ++i) {
         const int st = i % NS, ph = (i / NS) & 1, sp = i & 1;
         if (!mbar_wait(&full[st], ph)) { fail(42); break; }
-        if (!mbar_wait(&s_ready, sp)) { fail(43); break; }
-        fence_after_sync();
-        const uint32_t t1 = smem_u32(sStage + st * STAGE_BYTES), t2 = t1 + KT_BYTES, t3 = t2 + KT_BYTES;
+        const uint32_t t1 = smem_u32(sStage + st * STAGE_BYTES), t2 = SIMPLE ? t1 : t1 + KT_BYTES, t3 = t2 + KT_BYTES;
         // descriptors differ from step to step only in the 16-byte-granular start address (low bits)
         const uint64_t d1 = desc_kmajor(t1, 0, 8192), d2 = desc_mnmajor(t2, 0, 8192);
+        if (!SIMPLE) {
+          if (!mbar_wait(&s_ready, sp)) { fail(43); break; }
+          fence_after_sync();
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma(tmem + TM_P, d1 + (uint64_t)(((k >> 2) * 8192 + (k & 3) * 32) >> 4), ds0 + (uint64_t)((k * 2048) >> 4), idesc_p, k > 0);
-        umma_commit(&p_done);
+          for (int k = 0; k < 8; ++k)
+            umma(tmem + TM_P, d1 + (uint64_t)(((k >> 2) * 8192 + (k & 3) * 32) >> 4), ds0 + (uint64_t)((k * 2048) >> 4), idesc_p, k > 0);
+          umma_commit(&p_done);
+        }
         if (!mbar_wait(&op_ready, sp)) { fail(44); break; }
         fence_after_sync();
-        if (!BWD) {
+        if (!BWD || SIMPLE) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) umma(tmem + TM_DS, d2 + (uint64_t)((k * 2048) >> 4), do0 + (uint64_t)((k * 2048) >> 4), idesc_s, k > 0);
         } else {
@@ -157,7 +166,7 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
     const int row_lo = 16 * wq + g8, row_hi = row_lo + 8;
     const size_t st_off = ((size_t)n * a.H + hd) * K * a.V + (size_t)srow * a.V + v0 + sc0;
     float S[NC];
-    const float *S0 = reinterpret_cast<const float *>(BWD ? a.dht : a.h0);
+    const float *S0 = reinterpret_cast<const float *>(BWD ? a.dht : a.h0);  // same slots in every mode
     float *S1 = reinterpret_cast<float *>(BWD ? a.dh0 : a.ht);
     if (S0) {
       const float4 *src = reinterpret_cast<const float4 *>(S0 + st_off);
@@ -218,7 +227,7 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
       fence_proxy_async();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_ready);
+      if (!SIMPLE && lane == 0) mbar_arrive(&s_ready);
       if (tid == 0) {
         tma_store_wait_read();  // the v_new store of the previous chunk has read its tile
         abort_snap[0] = abort_flag;
@@ -244,13 +253,17 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
         d_prev = __expf(gl);
       }
       const bool in_lo = row_lo < rows, in_hi = row_hi < rows;  // rows past the end of the sequence add nothing to the state
+      //   simple  : op = e^{b_L-b} v (forward), op = scale e^{b} do (backward)
       const float fa_lo = BWD ? e2_lo : -e1_lo, fa_hi = BWD ? e2_hi : -e1_hi;
-      const float fo_lo = in_lo ? (BWD ? -e1_lo : e2_lo) : 0.f, fo_hi = in_hi ? (BWD ? -e1_hi : e2_hi) : 0.f;
+      float fo_lo = BWD ? -e1_lo : e2_lo, fo_hi = BWD ? -e1_hi : e2_hi;
+      if (SIMPLE && BWD) fo_lo = e1_lo * a.scale, fo_hi = e1_hi * a.scale;
+      if (!in_lo) fo_lo = 0.f;
+      if (!in_hi) fo_hi = 0.f;
       // ---- phase B: P -> corrected tile y', op
       const int st = i % NS, ph = (i / NS) & 1;
       if (!mbar_wait(&full[st], ph)) { fail(46); ok = false; }  // y (and do) tiles (already complete: the product waited on it)
       unsigned char *yt = sStage + st * STAGE_BYTES + NKT * KT_BYTES;
-      if (BWD) {
+      if (BWD && !SIMPLE) {
         // do' = scale e^{b} do, in place (runs while the tensor core computes P)
         unsigned char *dt = yt + U_BYTES;
         const float s_lo = in_lo ? e1_lo * a.scale : 0.f, s_hi = in_hi ? e1_hi * a.scale : 0.f;
@@ -273,11 +286,13 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
           }
         }
       }
-      if (!mbar_wait(&p_done, sp)) { fail(47); ok = false; }
-      fence_after_sync();
       float pr[NC / 8][4];
-      tmem_ld_frag<NC / 8>(tmem + lane_base + TM_P + NC * chh, pr);
-      tmem_ld_wait();
+      if (!SIMPLE) {
+        if (!mbar_wait(&p_done, sp)) { fail(47); ok = false; }
+        fence_after_sync();
+        tmem_ld_frag<NC / 8>(tmem + lane_base + TM_P + NC * chh, pr);
+        tmem_ld_wait();
+      }
 #pragma unroll
       for (int ni = 0; ni < NC / 8; ++ni) {
         const int col = NC * chh + 8 * ni + 2 * t4;
@@ -294,6 +309,11 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
             u0 = uu.x, u1 = uu.y;
           }
           const float fa = hf ? fa_hi : fa_lo, fo = hf ? fo_hi : fo_lo;
+          if (SIMPLE) {
+            if (p.ab_fmt) *reinterpret_cast<__nv_bfloat162 *>(sOp + off) = __floats2bfloat162_rn(u0 * fo, u1 * fo);
+            else *reinterpret_cast<__half2 *>(sOp + off) = __floats2half2_rn(u0 * fo, u1 * fo);
+            continue;
+          }
           const float x0 = fmaf(fa, pr[ni][2 * hf], u0), x1 = fmaf(fa, pr[ni][2 * hf + 1], u1);
           if (p.ab_fmt) {
             const __nv_bfloat162 vn = __floats2bfloat162_rn(x0, x1);
@@ -318,6 +338,7 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
       }
       named_barrier(1, ET);  // v_new tile complete
       if (abort_snap[1]) break;
+      if (SIMPLE) continue;  // no corrected tile to store
       if (rows == C) {
         if (tid == 0) {
           const int t0 = s.bos + it * C, c1 = a.head_first ? t0 : hd, c2 = a.head_first ? hd : t0;
@@ -347,26 +368,30 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
-template <int VB, int NS, bool BWD> static int launch_tc_dh(const flab_args *a, cudaStream_t stream) {
+template <int VB, int NS, int MODE> static int launch_tc_dh(const flab_args *a, cudaStream_t stream) {
   constexpr int BV = 64 * VB;
+  constexpr bool BWD = (MODE & 1) != 0, SIMPLE = MODE >= 2;
   CUtensorMap mA1, mA2, mA3, mY, mDo, mH, mYo;
-  if (int e = make_token_map(&mA1, BWD ? a->k : a->w, a, a->K)) return e;
-  if (int e = make_token_map(&mA2, BWD ? a->q : a->k, a, a->K)) return e;
-  if (int e = make_token_map(&mA3, BWD ? a->w : a->k, a, a->K)) return e;
-  if (int e = make_token_map(&mY, BWD ? a->dv : a->u, a, a->V)) return e;
-  if (int e = make_token_map(&mDo, BWD ? a->d_o : a->u, a, a->V)) return e;
+  const void *a1 = SIMPLE ? (BWD ? a->q : a->k) : (BWD ? a->k : a->w);
+  const void *y = SIMPLE ? (BWD ? a->d_o : a->v) : (BWD ? a->dv : a->u);
+  if (int e = make_token_map(&mA1, a1, a, a->K)) return e;
+  if (int e = make_token_map(&mA2, SIMPLE ? a1 : (BWD ? a->q : a->k), a, a->K)) return e;
+  if (int e = make_token_map(&mA3, (BWD && !SIMPLE) ? a->w : a1, a, a->K)) return e;
+  if (int e = make_token_map(&mY, y, a, a->V)) return e;
+  if (int e = make_token_map(&mDo, (BWD && !SIMPLE) ? a->d_o : y, a, a->V)) return e;
   if (int e = make_state_map(&mH, BWD ? a->dh : a->h, a, 128)) return e;
-  if (int e = make_token_map(&mYo, BWD ? a->dv2 : a->v_new, a, a->V)) return e;
+  if (int e = make_token_map(&mYo, SIMPLE ? y : (BWD ? a->dv2 : a->v_new), a, a->V)) return e;
   TcDhParams p;
   p.a = *a;
   p.v_tiles = a->V / BV;
   p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
-  constexpr uint32_t STAGE = (BWD ? 3 : 2) * 16384 + (BWD ? 2 : 1) * VB * 8192;
+  constexpr int NKT = SIMPLE ? 1 : (BWD ? 3 : 2), NVT = (BWD && !SIMPLE) ? 2 : 1;
+  constexpr uint32_t STAGE = NKT * 16384 + NVT * VB * 8192;
   const size_t smem = 1024 + NS * (size_t)STAGE + (size_t)VB * 128 * 128 + 2 * (size_t)VB * 8192 + 2 * C * sizeof(float);
-  auto kern = tc_delta_h_kernel<VB, NS, BWD>;
+  auto kern = tc_delta_h_kernel<VB, NS, MODE>;
   if (int e = set_smem(kern, smem)) return e;
   kern<<<dim3(p.v_tiles, a->N * a->H), 64 * (4 * VB + 1), smem, stream>>>(mA1, mA2, mA3, mY, mDo, mH, mYo, p);
-  return check_launch(BWD ? "delta_bwd_dhu(tc)" : "delta_fwd_h(tc)");
+  return check_launch(SIMPLE ? (BWD ? "chunk_bwd_dh(tc)" : "chunk_fwd_h(tc)") : (BWD ? "delta_bwd_dhu(tc)" : "delta_fwd_h(tc)"));
 }
 
 static bool tc_dh_ok(const flab_args *a, const void *const *ptrs, int n) {
@@ -381,14 +406,31 @@ static bool tc_dh_ok(const flab_args *a, const void *const *ptrs, int n) {
 int tc_delta_fwd_h_try(const flab_args *a, cudaStream_t stream) {
   const void *ptrs[7] = {a->k, a->w, a->u, a->h, a->v_new, a->h0, a->ht};
   if (!tc_dh_ok(a, ptrs, 7)) return 0;
-  const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 3, false>(a, stream) : launch_tc_dh<1, 4, false>(a, stream);
+  const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 3, DH_FWD>(a, stream) : launch_tc_dh<1, 4, DH_FWD>(a, stream);
   return rc < 0 ? rc : 1;
 }
 
 int tc_delta_bwd_dhu_try(const flab_args *a, cudaStream_t stream) {
   const void *ptrs[9] = {a->q, a->k, a->w, a->d_o, a->dv, a->dh, a->dv2, a->dht, a->dh0};
   if (!tc_dh_ok(a, ptrs, 9)) return 0;
-  const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 2, true>(a, stream) : launch_tc_dh<1, 3, true>(a, stream);
+  const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 2, DH_BWD>(a, stream) : launch_tc_dh<1, 3, DH_BWD>(a, stream);
+  return rc < 0 ? rc : 1;
+}
+
+// Plain chunk-state scans (scalar gate or none; the per-channel gate of GLA keeps the mma.sync kernel).
+int tc_chunk_fwd_h_try(const flab_args *a, cudaStream_t stream) {
+  if (a->gk || a->gv) return 0;
+  const void *ptrs[5] = {a->k, a->v, a->h, a->h0, a->ht};
+  if (!tc_dh_ok(a, ptrs, 5)) return 0;
+  const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 4, DH_SIMPLE_FWD>(a, stream) : launch_tc_dh<1, 4, DH_SIMPLE_FWD>(a, stream);
+  return rc < 0 ? rc : 1;
+}
+
+int tc_chunk_bwd_dh_try(const flab_args *a, cudaStream_t stream) {
+  if (a->gk || a->gv) return 0;
+  const void *ptrs[5] = {a->q, a->d_o, a->dh, a->dht, a->dh0};
+  if (!tc_dh_ok(a, ptrs, 5)) return 0;
+  const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 4, DH_SIMPLE_BWD>(a, stream) : launch_tc_dh<1, 4, DH_SIMPLE_BWD>(a, stream);
   return rc < 0 ? rc : 1;
 }
 
