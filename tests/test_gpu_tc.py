@@ -36,3 +36,135 @@ def test_tc_selftest():
         err = ((got - w).norm() / w.norm()).item()
         print(f"D{i + 1}: rel err {err:.2e}")
         assert err < 2e-3, f"product {i + 1} differs: rel err {err:.3e}"
+
+
+# ---------------------------------------------------------------------------------------------
+# tcgen05 state scans against a plain fp32 PyTorch restatement of the same stage
+# (fla/ops/common/chunk_delta_h.py:248-423, fla/ops/common/chunk_h.py:42-215), K = 128 so that the
+# tensor-core kernels take the call; ragged sequences, both layouts, 64 / 128 / 256 value columns.
+# ---------------------------------------------------------------------------------------------
+def _rnd(x, dt):
+    return x.to(dt).float()
+
+
+def _chunks(T):
+    return [(t, min(t + 64, T)) for t in range(0, T, 64)]
+
+
+def _ref_delta_fwd(k, w, u, g, h0, dt):
+    """Per (sequence, head) tensors [T, D] fp32. Returns h [NT,K,V], v_new [T,V], final state."""
+    S = h0.clone()
+    hs, vn = [], torch.zeros_like(u)
+    for lo, hi in _chunks(k.shape[0]):
+        hs.append(_rnd(S, dt))
+        gc = g[lo:hi] if g is not None else torch.zeros(hi - lo, device=k.device)
+        x = _rnd(u[lo:hi] - gc.exp()[:, None] * (w[lo:hi] @ _rnd(S, dt)), dt)
+        vn[lo:hi] = x
+        S = S * gc[-1].exp() + k[lo:hi].T @ _rnd(x * (gc[-1] - gc).exp()[:, None], dt)
+    return torch.stack(hs), vn, S
+
+
+def _ref_delta_bwd(q, k, w, do, dv, g, dht, scale, dt):
+    S = dht.clone()
+    T = q.shape[0]
+    ch = _chunks(T)
+    dhs, dv2 = [None] * len(ch), torch.zeros_like(dv)
+    for i in range(len(ch) - 1, -1, -1):
+        lo, hi = ch[i]
+        dhs[i] = _rnd(S, dt)
+        gc = g[lo:hi] if g is not None else torch.zeros(hi - lo, device=q.device)
+        x = _rnd(dv[lo:hi] + (gc[-1] - gc).exp()[:, None] * (k[lo:hi] @ _rnd(S, dt)), dt)
+        dv2[lo:hi] = x
+        dop = _rnd(do[lo:hi] * (gc.exp() * scale)[:, None], dt)
+        S = S * gc[-1].exp() + q[lo:hi].T @ dop - w[lo:hi].T @ _rnd(x * gc.exp()[:, None], dt)
+    return torch.stack(dhs), dv2, S
+
+
+def _ref_simple(x, y, g, s0, scale, bwd, dt):
+    S = s0.clone()
+    ch = _chunks(x.shape[0])
+    hs = [None] * len(ch)
+    for i in (range(len(ch) - 1, -1, -1) if bwd else range(len(ch))):
+        lo, hi = ch[i]
+        hs[i] = _rnd(S, dt)
+        gc = g[lo:hi] if g is not None else torch.zeros(hi - lo, device=x.device)
+        f = gc.exp() * scale if bwd else (gc[-1] - gc).exp()
+        S = S * gc[-1].exp() + x[lo:hi].T @ _rnd(y[lo:hi] * f[:, None], dt)
+    return torch.stack(hs), S
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)).item()
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("V,head_first,gated,lens", [
+    (128, False, True, [200, 64, 333]),
+    (64, False, False, [130]),
+    (256, False, True, [191]),
+    (128, True, True, None),
+])
+def test_tc_scans_against_torch(dt, V, head_first, gated, lens):
+    from fla_b200.ops import common as C
+    from fla_b200.utils import Geometry
+    torch.manual_seed(3)
+    H, K, scale = 2, 128, 128 ** -0.5
+    if lens is None:
+        B, T, offsets = 2, 150, None
+        seqs = [(b, 0, T) for b in range(B)]
+    else:
+        B, T = 1, sum(lens)
+        offs = [0]
+        for L in lens:
+            offs.append(offs[-1] + L)
+        offsets = torch.tensor(offs, dtype=torch.long, device="cuda")
+        seqs = [(0, offs[i], offs[i + 1]) for i in range(len(lens))]
+    N = len(seqs)
+
+    def tok(D, s=1.0):
+        shape = (B, H, T, D) if head_first else (B, T, H, D)
+        return (torch.randn(shape, device="cuda") * s).to(dt)
+
+    q, k, w = tok(K, 0.3), tok(K, 0.3), tok(K, 0.1)
+    u, do, dv = tok(V), tok(V), tok(V)
+    g = None
+    if gated:
+        graw = -torch.rand((B, H, T) if head_first else (B, T, H), device="cuda") * 0.1
+        g = C.chunk_local_cumsum(graw, offsets=offsets, head_first=head_first)
+    h0 = torch.randn(N, H, K, V, device="cuda") * 0.1
+    dht = torch.randn(N, H, K, V, device="cuda") * 0.1
+    geo = Geometry(k, u, offsets, head_first)
+
+    h, v_new, ht = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=h0, output_final_state=True)
+    dh, dh0, dv2 = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g, dht=dht, want_dh0=True)
+    hs, hts = C.chunk_fwd_h(geo, k, u, g=g, h0=h0, output_final_state=True)
+    dhs, dh0s = C.chunk_bwd_dh(geo, q, do, scale, g=g, dht=dht, want_dh0=True)
+    torch.cuda.synchronize()
+    assert _lib.load().flab_tc_error_state() == 0
+
+    def sl(x, b, hd, lo, hi):
+        return (x[b, hd, lo:hi] if head_first else x[b, lo:hi, hd]).float()
+
+    c0 = 0
+    for n, (b, lo, hi) in enumerate(seqs):
+        nt = (hi - lo + 63) // 64
+        for hd in range(H):
+            gg = sl(g, b, hd, lo, hi) if gated else None
+            args = [sl(x, b, hd, lo, hi) for x in (q, k, w, u, do, dv)]
+            qq, kk, ww, uu, dd, dvv = args
+            rh, rvn, rht = _ref_delta_fwd(kk, ww, uu, gg, h0[n, hd], dt)
+            got_h = h.view(-1, H, K, V)[c0:c0 + nt, hd]
+            assert _rel(got_h, rh) < 1e-2, ("h", n, hd, _rel(got_h, rh))
+            assert _rel(sl(v_new, b, hd, lo, hi), rvn) < 1e-2
+            assert _rel(ht[n, hd], rht) < 1e-2
+            rdh, rdv2, rdh0 = _ref_delta_bwd(qq, kk, ww, dd, dvv, gg, dht[n, hd], scale, dt)
+            assert _rel(dh.view(-1, H, K, V)[c0:c0 + nt, hd], rdh) < 1e-2
+            assert _rel(sl(dv2, b, hd, lo, hi), rdv2) < 1e-2
+            assert _rel(dh0[n, hd], rdh0) < 1e-2
+            rhs, rhts = _ref_simple(kk, uu, gg, h0[n, hd], 1.0, False, dt)
+            assert _rel(hs.view(-1, H, K, V)[c0:c0 + nt, hd], rhs) < 1e-2
+            assert _rel(hts[n, hd], rhts) < 1e-2
+            rdhs, rdh0s = _ref_simple(qq, dd, gg, dht[n, hd], scale, True, dt)
+            assert _rel(dhs.view(-1, H, K, V)[c0:c0 + nt, hd], rdhs) < 1e-2
+            assert _rel(dh0s[n, hd], rdh0s) < 1e-2
+        c0 += nt
