@@ -336,6 +336,7 @@ template <typename T, bool USE_DW> static int launch_dqkwg(const flab_args *a, c
 
 // tcgen05 / TMA kernels for the shapes they cover (tc_chunk_o.cu); 1 = handled, 0 = not applicable
 template <int MODE> int tc_chunk_o_try(const flab_args *a, cudaStream_t stream, const char *name);
+int tc_dqkwg_try(const flab_args *a, cudaStream_t stream);
 static bool tc_enabled() {
   static int v = -1;
   if (v < 0) {
@@ -396,8 +397,12 @@ int flab_chunk_bwd_dqkwg(const flab_args *a, void *stream) {
   FLAB_REQUIRE(!a->g || a->dg, FLAB_E_BADARG, "chunk_bwd_dqkwg: g given but dg is NULL");
   FLAB_REQUIRE(a->V <= 256, FLAB_E_UNSUPPORTED, "chunk_bwd_dqkwg: V = %d > 256", a->V);
   const bool use_dw = a->w != nullptr;
+  if (use_dw) FLAB_REQUIRE(a->dv && a->dw, FLAB_E_BADARG, "chunk_bwd_dqkwg: w given but dv or dw is NULL");
+  if (tc_enabled()) {
+    const int r = tc_dqkwg_try(a, (cudaStream_t)stream);
+    if (r != 0) return r < 0 ? r : FLAB_OK;
+  }
   if (use_dw) {
-    FLAB_REQUIRE(a->dv && a->dw, FLAB_E_BADARG, "chunk_bwd_dqkwg: w given but dv or dw is NULL");
     FLAB_DISPATCH_16(a->dtype, T, return (launch_dqkwg<T, true>(a, (cudaStream_t)stream)));
   } else {
     FLAB_DISPATCH_ALL(a->dtype, T, return (launch_dqkwg<T, false>(a, (cudaStream_t)stream)));

@@ -76,11 +76,13 @@ int make_state_map(CUtensorMap *map, const void *base, const flab_args *a, int b
 int tc_chunk_o_error();
 int recurrent_error();
 int tc_delta_h_error();
+int tc_dqkwg_error();
 
 }  // namespace flab
 
 extern "C" int flab_tc_error_state(void) {
   int e = flab::tc_chunk_o_error();
   if (!e) e = flab::recurrent_error();
-  return e ? e : flab::tc_delta_h_error();
+  if (!e) e = flab::tc_delta_h_error();
+  return e ? e : flab::tc_dqkwg_error();
 }
