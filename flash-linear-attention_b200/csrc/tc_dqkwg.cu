@@ -5,8 +5,9 @@
 //   dg_i = <q_i, dq_i> - <k_i, dk_i> + <w_i, dw_i>;  dg_last += e^{b_L} <h, dh> + <k, dk_inter>
 //   (fla/ops/common/chunk_o.py:444-600)
 // Persistent kernel, one CTA per SM, work item = (chunk, head).  Eighteen warps:
-//   warp 16 : TMA producer - X = {do, v, dv, h, dh} (112 KB) and Y = {q, k, w} (48 KB), one buffer each: X of the
-//             next item streams in while the current item works on Y, and the other way round
+//   warp 16 : TMA producer - X = {do, v, dv, h, dh} (112 KB, one buffer) and Y = {q, k, w} (48 KB, two buffers):
+//             X of the next item streams in while the current item works on Y; the outputs leave from the Y
+//             buffer of the previous item while the next one fills
 //   warp 17 : MMA issuer   - ds = do v^T; then the three products against the states; then the two
 //             intra-chunk products, accumulated onto dq and dk in TMEM
 //   warps 0-15 : epilogue, warp = (TMEM lane quadrant = 16 tokens, 32-column group)
@@ -43,12 +44,12 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char *sDo = base, *sV = sDo + T16, *sH = sV + T16, *sDH = sH + T32, *sDv = sDH + T32;  // X
-  unsigned char *sQ = sDv + (USE_DW ? T16 : 0), *sK = sQ + T16, *sW = sK + T16;                    // Y
-  unsigned char *sDS = sW + (USE_DW ? T16 : 0);                                                    // [64][128 B]
+  unsigned char *sY = sDv + (USE_DW ? T16 : 0);  // [2][q | k | w]
+  unsigned char *sDS = sY + 2 * Y_BYTES;         // [64][128 B]
   float *sG = reinterpret_cast<float *>(sDS + 8192);  // [2][64] gates
   float *sDG = sG + 2 * C;                            // [2][64] dg rows
   float *sRed = sDG + 2 * C;                          // [2][2]  <h, dh>, <k, dk_inter>
-  __shared__ uint64_t fullX, emptyX, fullY, emptyY, ds_done, e1_done, inter_done, e1b_done, all_done, acc_free;
+  __shared__ uint64_t fullX, emptyX, fullY[2], emptyY[2], ds_done, e1_done, dk_done, e1b_done, all_done, acc_free;
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
   __shared__ volatile int abort_snap[2];
@@ -57,12 +58,14 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     mbar_init(&fullX, 1);
-    mbar_init(&emptyX, 1);
-    mbar_init(&fullY, 1);
-    mbar_init(&emptyY, 1);
+    mbar_init(&emptyX, 17);  // the products against the states have completed + every epilogue warp is done with h, dh
+    for (int j = 0; j < 2; ++j) {
+      mbar_init(&fullY[j], 1);
+      mbar_init(&emptyY[j], 1);
+    }
     mbar_init(&ds_done, 1);
     mbar_init(&e1_done, 16);
-    mbar_init(&inter_done, 1);
+    mbar_init(&dk_done, 1);
     mbar_init(&e1b_done, 16);
     mbar_init(&all_done, 1);
     mbar_init(&acc_free, 16);
@@ -110,13 +113,15 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
           tma_load_2d(sH + j * T16, &m.h, &fullX, 64 * j, srow);
           tma_load_2d(sDH + j * T16, &m.dh, &fullX, 64 * j, srow);
         }
-        if (!mbar_wait(&emptyY, ph ^ 1)) { fail(62); break; }
-        mbar_expect_tx(&fullY, Y_BYTES);
+        const int yb = i & 1, yph = (i >> 1) & 1;
+        unsigned char *sQ = sY + yb * Y_BYTES, *sK = sQ + T16, *sW = sK + T16;
+        if (!mbar_wait(&emptyY[yb], yph ^ 1)) { fail(62); break; }
+        mbar_expect_tx(&fullY[yb], Y_BYTES);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          tma_load_4d(sQ + j * 8192, &m.q, &fullY, 64 * j, c1, c2, s.b);
-          tma_load_4d(sK + j * 8192, &m.k, &fullY, 64 * j, c1, c2, s.b);
-          if (USE_DW) tma_load_4d(sW + j * 8192, &m.w, &fullY, 64 * j, c1, c2, s.b);
+          tma_load_4d(sQ + j * 8192, &m.q, &fullY[yb], 64 * j, c1, c2, s.b);
+          tma_load_4d(sK + j * 8192, &m.k, &fullY[yb], 64 * j, c1, c2, s.b);
+          if (USE_DW) tma_load_4d(sW + j * 8192, &m.w, &fullY[yb], 64 * j, c1, c2, s.b);
         }
       }
     }
@@ -131,7 +136,6 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
       const uint64_t d_dv = desc_kmajor(smem_u32(sDv), 0, 8192);
       const uint64_t d_h = desc_kmajor(smem_u32(sH), 0, T16), d_dh = desc_kmajor(smem_u32(sDH), 0, T16);
       const uint64_t d_dsk = desc_kmajor(smem_u32(sDS), 0, 8192), d_dsm = desc_mnmajor(smem_u32(sDS), 0, 8192);
-      const uint64_t d_k = desc_mnmajor(smem_u32(sK), 0, 8192), d_q = desc_mnmajor(smem_u32(sQ), 0, 8192);
       // per-step advance of the start-address field (16-byte units)
       auto kx = [](int k, uint32_t box) -> uint64_t { return (uint64_t)(((k >> 2) * box + (k & 3) * 32) >> 4); };
       auto mx = [](int k) -> uint64_t { return (uint64_t)((k * 2048) >> 4); };
@@ -146,16 +150,18 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
         if (i > 0 && !mbar_wait(&acc_free, ph ^ 1)) { fail(65); break; }
         fence_after_sync();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma(tmem + TM_DQ, d_do + kx(k, 8192), d_h + kx(k, T16), id_st, k > 0);
-#pragma unroll
         for (int k = 0; k < 8; ++k) umma(tmem + TM_DK, d_v + kx(k, 8192), d_dh + kx(k, T16), id_st, k > 0);
+        umma_commit(&dk_done);  // the epilogue takes <k, dk_inter> from it while the other products run
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma(tmem + TM_DQ, d_do + kx(k, 8192), d_h + kx(k, T16), id_st, k > 0);
         if (USE_DW) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma(tmem + TM_DW, d_dv + kx(k, 8192), d_h + kx(k, T16), id_st, k > 0);
         }
-        umma_commit(&inter_done);
         umma_commit(&emptyX);
-        if (!mbar_wait(&fullY, ph)) { fail(66); break; }
+        const int yb = i & 1, yph = (i >> 1) & 1;
+        const uint64_t d_q = desc_mnmajor(smem_u32(sY + yb * Y_BYTES), 0, 8192), d_k = desc_mnmajor(smem_u32(sY + yb * Y_BYTES + T16), 0, 8192);
+        if (!mbar_wait(&fullY[yb], yph)) { fail(66); break; }
         if (use_g && !mbar_wait(&e1b_done, ph)) { fail(67); break; }
         fence_after_sync();
 #pragma unroll
@@ -191,6 +197,7 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
       else *reinterpret_cast<__half2 *>(ptr) = __floats2half2_rn(x, y);
     };
     float g_pf = gate_of(0);
+    bool store_pending = false;  // thread 0: a tile store of the previous item may still be reading its Y buffer
     for (int i = 0; i < n_local; ++i) {
       const int ph = i & 1;
       int c, hd, n, it;
@@ -199,6 +206,8 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
       const Seq s = seq_of(a, n);
       const int t0 = it * C, rows = min(C, s.len - t0), last = rows - 1;
       float *gs = sG + ph * C, *dgs = sDG + ph * C, *red = sRed + ph * 2;
+      const int yb = i & 1, yph = (i >> 1) & 1;
+      unsigned char *sQ = sY + yb * Y_BYTES, *sK = sQ + T16, *sW = sK + T16;
       if (tid < C) {
         gs[tid] = g_pf;
         dgs[tid] = 0.f;
@@ -213,22 +222,6 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
       const float f_lo = use_g ? __expf(fminf(gl - g_lo, 0.f)) : 1.f, f_hi = use_g ? __expf(fminf(gl - g_hi, 0.f)) : 1.f;
       // ---- E1: <h, dh>; ds -> masked / decayed operand; row factors onto do, v, dv
       if (!mbar_wait(&fullX, ph)) fail(68);
-      if (use_g) {
-        float hd_ = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int idx = tid + ET * j;  // 16-byte piece of the [2 boxes][128 rows][8 pieces] tiles
-          const int4 xa = *reinterpret_cast<const int4 *>(sH + idx * 16), xb = *reinterpret_cast<const int4 *>(sDH + idx * 16);
-          const uint32_t *ua = reinterpret_cast<const uint32_t *>(&xa), *ub = reinterpret_cast<const uint32_t *>(&xb);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 fa = ld2(reinterpret_cast<const unsigned char *>(&ua[e])), fb = ld2(reinterpret_cast<const unsigned char *>(&ub[e]));
-            hd_ = fmaf(fa.x, fb.x, fmaf(fa.y, fb.y, hd_));
-          }
-        }
-        hd_ = warp_sum(hd_);
-        if (lane == 0) atomicAdd(&red[0], hd_);
-      }
       if (!mbar_wait(&ds_done, ph)) fail(69);
       fence_after_sync();
       if (cq < 2) {
@@ -280,10 +273,34 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&e1_done);
-      // ---- E1b: <k, dk_inter> from the inter-chunk dk before the intra-chunk product lands on it
-      if (!mbar_wait(&fullY, ph)) fail(70);
+      // <h, dh> while the tensor core works; then this warp is done with the X tiles
       if (use_g) {
-        if (!mbar_wait(&inter_done, ph)) fail(71);
+        float hd_ = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int idx = tid + ET * j;  // 16-byte piece of the [2 boxes][128 rows][8 pieces] tiles
+          const int4 xa = *reinterpret_cast<const int4 *>(sH + idx * 16), xb = *reinterpret_cast<const int4 *>(sDH + idx * 16);
+          const uint32_t *ua = reinterpret_cast<const uint32_t *>(&xa), *ub = reinterpret_cast<const uint32_t *>(&xb);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 fa = ld2(reinterpret_cast<const unsigned char *>(&ua[e])), fb = ld2(reinterpret_cast<const unsigned char *>(&ub[e]));
+            hd_ = fmaf(fa.x, fb.x, fmaf(fa.y, fb.y, hd_));
+          }
+        }
+        hd_ = warp_sum(hd_);
+        if (lane == 0) atomicAdd(&red[0], hd_);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&emptyX);
+      if (tid == 0 && store_pending) {  // the previous item's outputs have left their Y buffer
+        tma_store_wait_read();
+        mbar_arrive(&emptyY[yb ^ 1]);
+        store_pending = false;
+      }
+      // ---- E1b: <k, dk_inter> from the inter-chunk dk before the intra-chunk product lands on it
+      if (!mbar_wait(&fullY[yb], yph)) fail(70);
+      if (use_g) {
+        if (!mbar_wait(&dk_done, ph)) fail(71);
         fence_after_sync();
         float dki[4][4];
         tmem_ld_frag<4>(tmem + lane_base + TM_DK + 32 * cq, dki);
@@ -369,8 +386,7 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
             if (USE_DW) tma_store_4d(&m.dw, sW + j * 8192, 64 * j, c1, c2, s.b);
           }
           tma_store_commit();
-          tma_store_wait_read();
-          mbar_arrive(&emptyY);
+          store_pending = true;  // released during the next item (or at the end)
         }
       } else {
         // ragged last chunk of a sequence: a tile store would write past its end
@@ -384,7 +400,7 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
           if (USE_DW) *reinterpret_cast<int4 *>(reinterpret_cast<bf16 *>(a.dw) + go) = *reinterpret_cast<const int4 *>(sW + so);
         }
         named_barrier(2, ET);
-        if (tid == 0) mbar_arrive(&emptyY);
+        if (tid == 0) mbar_arrive(&emptyY[yb]);
       }
     }
     if (tid == 0) tma_store_wait_all();
@@ -411,7 +427,7 @@ template <bool USE_DW> static int launch_tc_dqkwg(const flab_args *a, cudaStream
   p.a = *a;
   p.n_items = a->NT * a->H;
   p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
-  const size_t smem = 1024 + (size_t)(USE_DW ? 6 : 4) * 16384 + 2 * 32768 + 8192 + (4 * C + 4) * sizeof(float);
+  const size_t smem = 1024 + (size_t)(USE_DW ? 9 : 6) * 16384 + 2 * 32768 + 8192 + (4 * C + 4) * sizeof(float);
   auto kern = tc_dqkwg_kernel<USE_DW>;
   if (int e = set_smem(kern, smem)) return e;
   int dev = 0, sms = 148;
