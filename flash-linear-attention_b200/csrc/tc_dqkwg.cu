@@ -11,6 +11,7 @@
 //   warp 17 : MMA issuer   - ds = do v^T; then the three products against the states; then the two
 //             intra-chunk products, accumulated onto dq and dk in TMEM
 //   warps 0-15 : epilogue, warp = (TMEM lane quadrant = 16 tokens, 32-column group)
+//   warp 18 : output     - tile stores of dq, dk, dw from the Y buffer, then hands the buffer back to the producer
 // The row factors of the inter-chunk terms are applied to the A operands in shared memory (do, v, dv are
 // rescaled in place after ds has been formed from the unscaled tiles), so that inter- and intra-chunk parts
 // add up in one accumulator and TMEM holds ds | dq | dk | dw = 448 columns.  dq, dk, dw are written over the
@@ -34,7 +35,7 @@ struct TcDqMaps {
 };
 
 template <bool USE_DW>
-__global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant__ TcDqMaps m, const TcDqParams p) {
+__global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant__ TcDqMaps m, const TcDqParams p) {
   using namespace tc;
   constexpr uint32_t T16 = 16384, T32 = 32768;
   constexpr uint32_t X_BYTES = (USE_DW ? 3 : 2) * T16 + 2 * T32, Y_BYTES = (USE_DW ? 3 : 2) * T16;
@@ -49,7 +50,7 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
   float *sG = reinterpret_cast<float *>(sDS + 8192);  // [2][64] gates
   float *sDG = sG + 2 * C;                            // [2][64] dg rows
   float *sRed = sDG + 2 * C;                          // [2][2]  <h, dh>, <k, dk_inter>
-  __shared__ uint64_t fullX, emptyX, fullY[2], emptyY[2], ds_done, e1_done, dk_done, e1b_done, all_done, acc_free;
+  __shared__ uint64_t fullX, emptyX, fullY[2], emptyY[2], ds_done, e1_done, dk_done, e1b_done, all_done, acc_free, out_ready;
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
   __shared__ volatile int abort_snap[2];
@@ -69,6 +70,7 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
     mbar_init(&e1b_done, 16);
     mbar_init(&all_done, 1);
     mbar_init(&acc_free, 16);
+    mbar_init(&out_ready, 16);
     abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -171,12 +173,47 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
         umma_commit(&all_done);
       }
     }
+  } else if (warp == 18) {
+    // ------------------------------------------------------------------ output warp
+    if (lane == 0) {
+      for (int i = 0; i < n_local && !abort_flag; ++i) {
+        const int yb = i & 1;
+        int c, hd, n, it;
+        decode(i, c, hd);
+        chunk_of(a, c, n, it);
+        const Seq s = seq_of(a, n);
+        const int t0 = it * C, rows = min(C, s.len - t0);
+        unsigned char *sQ = sY + yb * Y_BYTES, *sK = sQ + T16, *sW = sK + T16;
+        if (!mbar_wait(&out_ready, i & 1)) { fail(73); break; }
+        if (rows == C) {  // (a ragged chunk was written out by the epilogue warps themselves)
+          const int tt = s.bos + t0, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            tma_store_4d(&m.dq, sQ + j * 8192, 64 * j, c1, c2, s.b);
+            tma_store_4d(&m.dk, sK + j * 8192, 64 * j, c1, c2, s.b);
+            if (USE_DW) tma_store_4d(&m.dw, sW + j * 8192, 64 * j, c1, c2, s.b);
+          }
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+        mbar_arrive(&emptyY[yb]);
+      }
+      tma_store_wait_all();
+    }
   } else {
     // ------------------------------------------------------------------ epilogue warps 0-15
     const int wq = warp & 3, cq = warp >> 2, g8 = lane >> 2, t4 = lane & 3;
     const uint32_t lane_base = (uint32_t)(32 * wq) << 16;
     const int row_lo = 16 * wq + g8, row_hi = row_lo + 8;
     const int colb = 32 * cq + 2 * t4;  // this thread's columns: colb + 8 ni (+1)
+    // byte offsets of this thread's 16 element pairs inside a [2 boxes][64 tokens][128 B] tile
+    uint32_t o_lo_[4], o_hi_[4];
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni) {
+      const int col = colb + 8 * ni;
+      o_lo_[ni] = (uint32_t)(col >> 6) * 8192u + sw128_offset(row_lo, col & 63);
+      o_hi_[ni] = (uint32_t)(col >> 6) * 8192u + sw128_offset(row_hi, col & 63);
+    }
     const float *Gbase = reinterpret_cast<const float *>(a.g);
     // gate of token `tid` of local item i (fetched one item ahead)
     auto gate_of = [&](int i) -> float {
@@ -197,7 +234,6 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
       else *reinterpret_cast<__half2 *>(ptr) = __floats2half2_rn(x, y);
     };
     float g_pf = gate_of(0);
-    bool store_pending = false;  // thread 0: a tile store of the previous item may still be reading its Y buffer
     for (int i = 0; i < n_local; ++i) {
       const int ph = i & 1;
       int c, hd, n, it;
@@ -252,7 +288,7 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
           const int col = colb + 8 * ni;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
-            const uint32_t off = (uint32_t)(col >> 6) * 8192u + sw128_offset(hf ? row_hi : row_lo, col & 63);
+            const uint32_t off = hf ? o_hi_[ni] : o_lo_[ni];
             float2 x = ld2(sDo + off);
             const float sd = hf ? sd_hi : sd_lo;
             st2(sDo + off, x.x * sd, x.y * sd);
@@ -292,11 +328,6 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&emptyX);
-      if (tid == 0 && store_pending) {  // the previous item's outputs have left their Y buffer
-        tma_store_wait_read();
-        mbar_arrive(&emptyY[yb ^ 1]);
-        store_pending = false;
-      }
       // ---- E1b: <k, dk_inter> from the inter-chunk dk before the intra-chunk product lands on it
       if (!mbar_wait(&fullY[yb], yph)) fail(70);
       if (use_g) {
@@ -309,8 +340,7 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
 #pragma unroll
         for (int ni = 0; ni < 4; ++ni) {
           const int col = colb + 8 * ni;
-          const uint32_t o_lo = (uint32_t)(col >> 6) * 8192u + sw128_offset(row_lo, col & 63);
-          const uint32_t o_hi = (uint32_t)(col >> 6) * 8192u + sw128_offset(row_hi, col & 63);
+          const uint32_t o_lo = o_lo_[ni], o_hi = o_hi_[ni];
           const float2 k_lo = ld2(sK + o_lo), k_hi = ld2(sK + o_hi);
           if (row_lo < rows) dkk += dki[ni][0] * k_lo.x + dki[ni][1] * k_lo.y;
           if (row_hi < rows) dkk += dki[ni][2] * k_hi.x + dki[ni][3] * k_hi.y;
@@ -336,8 +366,7 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
 #pragma unroll
       for (int ni = 0; ni < 4; ++ni) {
         const int col = colb + 8 * ni;
-        const uint32_t o_lo = (uint32_t)(col >> 6) * 8192u + sw128_offset(row_lo, col & 63);
-        const uint32_t o_hi = (uint32_t)(col >> 6) * 8192u + sw128_offset(row_hi, col & 63);
+        const uint32_t o_lo = o_lo_[ni], o_hi = o_hi_[ni];
         if (use_g) {
           const float2 q_lo = ld2(sQ + o_lo), q_hi = ld2(sQ + o_hi), k_lo = ld2(sK + o_lo), k_hi = ld2(sK + o_hi);
           dg_lo += dq[ni][0] * q_lo.x + dq[ni][1] * q_lo.y - dk[ni][0] * k_lo.x - dk[ni][1] * k_lo.y;
@@ -376,19 +405,7 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
         if (tid == last) x += red[0] * __expf(gl) + red[1];
         reinterpret_cast<float *>(a.dg)[tok_off(a, s, hd, t0 + tid, 1)] = x;
       }
-      if (rows == C) {
-        if (tid == 0) {
-          const int tt = s.bos + t0, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            tma_store_4d(&m.dq, sQ + j * 8192, 64 * j, c1, c2, s.b);
-            tma_store_4d(&m.dk, sK + j * 8192, 64 * j, c1, c2, s.b);
-            if (USE_DW) tma_store_4d(&m.dw, sW + j * 8192, 64 * j, c1, c2, s.b);
-          }
-          tma_store_commit();
-          store_pending = true;  // released during the next item (or at the end)
-        }
-      } else {
+      if (rows < C) {
         // ragged last chunk of a sequence: a tile store would write past its end
         const size_t ks = tok_stride(a, a.K), off0 = tok_off(a, s, hd, t0, a.K);
         for (int e = tid; e < rows * 16; e += ET) {
@@ -399,11 +416,10 @@ __global__ void __launch_bounds__(576, 1) tc_dqkwg_kernel(const __grid_constant_
           *reinterpret_cast<int4 *>(reinterpret_cast<bf16 *>(a.dk) + go) = *reinterpret_cast<const int4 *>(sK + so);
           if (USE_DW) *reinterpret_cast<int4 *>(reinterpret_cast<bf16 *>(a.dw) + go) = *reinterpret_cast<const int4 *>(sW + so);
         }
-        named_barrier(2, ET);
-        if (tid == 0) mbar_arrive(&emptyY[yb]);
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&out_ready);  // this warp is done with the Y buffer
     }
-    if (tid == 0) tma_store_wait_all();
   }
   fence_before_sync();
   __syncthreads();
@@ -434,7 +450,7 @@ template <bool USE_DW> static int launch_tc_dqkwg(const flab_args *a, cudaStream
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = p.n_items < sms ? p.n_items : sms;
-  kern<<<grid, 576, smem, stream>>>(m, p);
+  kern<<<grid, 608, smem, stream>>>(m, p);
   return check_launch("chunk_bwd_dqkwg(tc)");
 }
 
