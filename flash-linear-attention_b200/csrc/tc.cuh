@@ -185,19 +185,31 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, float (&r)[32
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, float (&r)[8]) {
+  uint32_t *u = reinterpret_cast<uint32_t *>(r);
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+               : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7])
+               : "r"(taddr)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Load a [16 x 8*NI] block (NI multiple of 4) into acc[NI][4]; taddr = lane/column of its corner.
 template <int NI> __device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, float (&acc)[NI][4]) {
-  static_assert(NI % 4 == 0, "NI must be a multiple of 4");
+  static_assert(NI % 4 == 0 || NI == 2, "NI must be 2 or a multiple of 4");
+  if constexpr (NI == 2) {
+    float(&blk)[8] = *reinterpret_cast<float(*)[8]>(&acc[0][0]);
+    tmem_ld_16x256b_x2(taddr, blk);
+  } else {
 #pragma unroll
-  for (int j = 0; j < NI / 8; ++j) {
-    float(&blk)[32] = *reinterpret_cast<float(*)[32]>(&acc[8 * j][0]);
-    tmem_ld_16x256b_x8(taddr + 64u * j, blk);
-  }
-  if (NI % 8 != 0) {
-    float(&blk)[16] = *reinterpret_cast<float(*)[16]>(&acc[NI - 4][0]);
-    tmem_ld_16x256b_x4(taddr + 8u * (NI - 4), blk);
+    for (int j = 0; j < NI / 8; ++j) {
+      float(&blk)[32] = *reinterpret_cast<float(*)[32]>(&acc[8 * j][0]);
+      tmem_ld_16x256b_x8(taddr + 64u * j, blk);
+    }
+    if constexpr (NI % 8 != 0) {
+      float(&blk)[16] = *reinterpret_cast<float(*)[16]>(&acc[NI - 4][0]);
+      tmem_ld_16x256b_x4(taddr + 8u * (NI - 4), blk);
+    }
   }
 }
 

@@ -77,6 +77,7 @@ int tc_chunk_o_error();
 int recurrent_error();
 int tc_delta_h_error();
 int tc_dqkwg_error();
+int tc_wy_bwd_error();
 
 }  // namespace flab
 
@@ -84,5 +85,6 @@ extern "C" int flab_tc_error_state(void) {
   int e = flab::tc_chunk_o_error();
   if (!e) e = flab::recurrent_error();
   if (!e) e = flab::tc_delta_h_error();
-  return e ? e : flab::tc_dqkwg_error();
+  if (!e) e = flab::tc_dqkwg_error();
+  return e ? e : flab::tc_wy_bwd_error();
 }

@@ -810,6 +810,17 @@ template <typename T, bool GATED> static int launch_wy_bwd(const flab_args *a, c
   return check_launch("wy_bwd");
 }
 
+// tcgen05 / TMA kernel for the shapes it covers (tc_wy_bwd.cu); 1 = handled, 0 = not applicable
+int tc_wy_bwd_try(const flab_args *a, cudaStream_t stream);
+static bool tc_wy_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("FLA_B200_NO_TC");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 }  // namespace flab
 
 extern "C" {
@@ -844,6 +855,10 @@ int flab_wy_bwd(const flab_args *a, void *stream) {
                "wy_bwd needs k, v, beta, aw, dw, du, dk, dv and dbeta");
   const bool gated = a->g != nullptr;
   FLAB_REQUIRE(!gated || (a->au && a->dg), FLAB_E_BADARG, "wy_bwd: g given but au or dg is NULL");
+  if (tc_wy_enabled()) {
+    const int r = tc_wy_bwd_try(a, (cudaStream_t)stream);
+    if (r != 0) return r < 0 ? r : FLAB_OK;
+  }
   FLAB_DISPATCH_16(a->dtype, T, {
     if (gated) return (launch_wy_bwd<T, true>(a, (cudaStream_t)stream));
     return (launch_wy_bwd<T, false>(a, (cudaStream_t)stream));
