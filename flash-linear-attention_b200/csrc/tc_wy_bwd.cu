@@ -266,8 +266,22 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
     };
     float b_pf, g_pf;
     scalars_of(0, b_pf, g_pf);
-    int n_ragged = 0;
-    for (int i = 0; i < n_local; ++i) {
+    // beta, gate and the zeroed dbeta / dg rows of item i live in slot i & 1; they are published by the barrier at
+    // the end of item i - 1 (item 0: the barrier below)
+    auto publish = [&](int slot) {
+      if (tid < C) {
+        sBeta[slot * C + tid] = b_pf;
+        sG[slot * C + tid] = g_pf;
+        sDB[slot * C + tid] = 0.f;
+        sDG[slot * C + tid] = 0.f;
+      }
+    };
+    publish(0);
+    scalars_of(1, b_pf, g_pf);
+    if (tid == 0) abort_snap[0] = abort_flag;
+    named_barrier(1, ET);
+    bool live = !abort_snap[0];
+    for (int i = 0; i < n_local && live; ++i) {
       const int b = i & 1, ph = (i >> 1) & 1, ip = i & 1;
       Seq s;
       int hd, t0, rows;
@@ -275,16 +289,6 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
       unsigned char *in = sIn + b * IN_BYTES;
       unsigned char *tK = in, *tV = in + T16, *tDW = in + 2 * T16, *tDU = in + 3 * T16, *tDKI = in + 4 * T16;
       float *bs = sBeta + ip * C, *gs = sG + ip * C, *dbs = sDB + ip * C, *dgs = sDG + ip * C;
-      if (tid < C) {
-        bs[tid] = b_pf;
-        gs[tid] = g_pf;
-        dbs[tid] = 0.f;
-        dgs[tid] = 0.f;
-      }
-      if (tid == 0) abort_snap[0] = abort_flag;
-      named_barrier(1, ET);
-      if (abort_snap[0]) break;
-      scalars_of(i + 1, b_pf, g_pf);
       const float b_lo = bs[row_lo], b_hi = bs[row_hi], g_lo = gs[row_lo], g_hi = gs[row_hi];
       if (!mbar_wait(&full[b], ph)) fail(89);
       if (rows < C) {
@@ -297,7 +301,6 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(&zero_done);
-        ++n_ragged;
       }
       // ---- E1: masked dA operands; then dv, first part of dk and dbeta while the tensor core transforms dA
       if (!mbar_wait(&b1_done, ip)) fail(90);
@@ -330,24 +333,6 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&e1_done);
-      float db_lo = 0.f, db_hi = 0.f;
-      float dk1[4][4];
-      {
-        float vb[4][4];
-        tmem_ld_frag<4>(tmem + lane_base + TM_KB + 32 * cq, dk1);
-        tmem_ld_frag<4>(tmem + lane_base + TM_VB + 32 * cq, vb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int ni = 0; ni < 4; ++ni) {
-          const float2 k_lo = ld2(tK + o128_lo[ni]), k_hi = ld2(tK + o128_hi[ni]);
-          const float2 v_lo = ld2(tV + o128_lo[ni]), v_hi = ld2(tV + o128_hi[ni]);
-          db_lo += dk1[ni][0] * k_lo.x + dk1[ni][1] * k_lo.y + vb[ni][0] * v_lo.x + vb[ni][1] * v_lo.y;
-          db_hi += dk1[ni][2] * k_hi.x + dk1[ni][3] * k_hi.y + vb[ni][2] * v_hi.x + vb[ni][3] * v_hi.y;
-          dk1[ni][0] *= b_lo, dk1[ni][1] *= b_lo, dk1[ni][2] *= b_hi, dk1[ni][3] *= b_hi;
-          st2(tDU + o128_lo[ni], vb[ni][0] * b_lo, vb[ni][1] * b_lo);  // dv, over du (the tensor core is done with it)
-          st2(tDU + o128_hi[ni], vb[ni][2] * b_hi, vb[ni][3] * b_hi);
-        }
-      }
       // ---- E2: first product of the transform, rounded, becomes the operand of the second
       if (!mbar_wait(&b2_done, ip)) fail(91);
       fence_after_sync();
@@ -370,6 +355,25 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&e2_done);
+      // dv, the first part of dk and of dbeta, while the tensor core runs the second product of the transform
+      float db_lo = 0.f, db_hi = 0.f;
+      float dk1[4][4];
+      {
+        float vb[4][4];
+        tmem_ld_frag<4>(tmem + lane_base + TM_KB + 32 * cq, dk1);
+        tmem_ld_frag<4>(tmem + lane_base + TM_VB + 32 * cq, vb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni) {
+          const float2 k_lo = ld2(tK + o128_lo[ni]), k_hi = ld2(tK + o128_hi[ni]);
+          const float2 v_lo = ld2(tV + o128_lo[ni]), v_hi = ld2(tV + o128_hi[ni]);
+          db_lo += dk1[ni][0] * k_lo.x + dk1[ni][1] * k_lo.y + vb[ni][0] * v_lo.x + vb[ni][1] * v_lo.y;
+          db_hi += dk1[ni][2] * k_hi.x + dk1[ni][3] * k_hi.y + vb[ni][2] * v_hi.x + vb[ni][3] * v_hi.y;
+          dk1[ni][0] *= b_lo, dk1[ni][1] *= b_lo, dk1[ni][2] *= b_hi, dk1[ni][3] *= b_hi;
+          st2(tDU + o128_lo[ni], vb[ni][0] * b_lo, vb[ni][1] * b_lo);  // dv, over du (the tensor core is done with it)
+          st2(tDU + o128_hi[ni], vb[ni][2] * b_hi, vb[ni][3] * b_hi);
+        }
+      }
       // ---- E3: dA = -strict_lower(.) (+ decayed dA_u), and diag(beta) dA
       if (!mbar_wait(&b3_done, ip)) fail(92);
       fence_after_sync();
@@ -469,9 +473,11 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
         }
       }
       fence_proxy_async();
-      if (tid == 0) abort_snap[1] = abort_flag;
+      publish(ip ^ 1);  // scalars of the next item
+      if (tid == 0) abort_snap[ip] = abort_flag;
       named_barrier(1, ET);  // dk, dv tiles and the dbeta / dg rows are complete
-      if (abort_snap[1]) break;
+      if (abort_snap[ip]) live = false;
+      scalars_of(i + 2, b_pf, g_pf);
       if (tid < rows) {
         const size_t o = tok_off(a, s, hd, t0 + tid, 1);
         reinterpret_cast<float *>(a.dbeta)[o] = dbs[tid];
