@@ -78,6 +78,7 @@ int recurrent_error();
 int tc_delta_h_error();
 int tc_dqkwg_error();
 int tc_wy_bwd_error();
+int tc_wy_fwd_error();
 
 }  // namespace flab
 
@@ -86,5 +87,6 @@ extern "C" int flab_tc_error_state(void) {
   if (!e) e = flab::recurrent_error();
   if (!e) e = flab::tc_delta_h_error();
   if (!e) e = flab::tc_dqkwg_error();
-  return e ? e : flab::tc_wy_bwd_error();
+  if (!e) e = flab::tc_wy_bwd_error();
+  return e ? e : flab::tc_wy_fwd_error();
 }

@@ -8,11 +8,11 @@
 // A is rounded to the element type before it multiplies anything, as in the reference.
 // K and V are walked in tiles of 128 columns, so any head dimension works.
 #include "common.cuh"
+#include "wy_inverse.cuh"
 
 namespace flab {
 
 constexpr int WT = 128;  // column tile of k / v
-constexpr int LDL = C + 1;
 
 // Inverse of the unit lower-triangular M = I - N for `nmat` 64x64 matrices held side by side in
 // shared memory (N = Lo, the negated strict lower part of the Gram matrix).  Result X = M^-1
@@ -200,75 +200,6 @@ __global__ void __launch_bounds__(128) wy_fwd_kernel(const flab_args a) {
       tile_store<T>(dst + d0, st, sX, LDX, rows, dw_, tid, 128);
     }
   }
-}
-
-// In-place variant for 256 threads: X holds NMAT negated strict-lower Gram matrices ([64][LDL] fp32 each, zero
-// on and above the diagonal) and leaves their inverses (unit diagonal included). Same blocked scheme as
-// tri_inverse; every level reads a block into registers or scratch before it is overwritten. Scr is scratch of
-// NMAT * 32 * 33 floats. All 256 threads must call this.
-template <int NMAT> __device__ __forceinline__ void tri_inverse8(float *X, float *Scr, int tid) {
-  const int warp = tid >> 5, lane = tid & 31;
-  // ---- level 0: warps 0..3 -> diagonal block, half-warp -> matrix
-  if (warp < 4) {
-    const int half = lane >> 4, j = lane & 15, mat = half < NMAT ? half : 0;
-    float *n = X + mat * C * LDL + (16 * warp) * (LDL + 1);
-    float nc[16], x[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) nc[i] = n[i * LDL + j];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float acc = nc[i];
-#pragma unroll
-      for (int m = 0; m < i; ++m) acc = fmaf(__shfl_sync(0xffffffffu, nc[i], (lane & 16) + m), x[m], acc);
-      x[i] = (j < i) ? acc : 0.f;
-    }
-    __syncwarp();
-    if (half < NMAT) {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) n[i * LDL + j] = x[i] + (i == j ? 1.f : 0.f);
-    }
-  }
-  __syncthreads();
-  // ---- level 1: X21 = X22 (N21 X11); warp -> (matrix, 32-block, 8-column half of the 16x16 result)
-  {
-    const int mat = (warp >> 1) & 1, blk = warp & 1, n0 = 8 * (warp >> 2);
-    const bool on = mat < NMAT;
-    const int o = 32 * blk;
-    float *Xm = X + (on ? mat : 0) * C * LDL;
-    float *scr = Scr + ((on ? mat : 0) * 2 + blk) * 16 * 17;
-    if (on) {
-      float t1[1][1][4];
-      acc_zero(t1);
-      warp_gemm_f32<1, 1, 16, false, true>(t1, Xm + (o + 16) * LDL + o, LDL, 0, Xm + o * LDL + o, LDL, n0);
-      FLAB_ACC_FOREACH(1, 1, 0, n0, row, col, mi, ni, r) { scr[row * 17 + col] = t1[mi][ni][r]; }
-    }
-    __syncthreads();
-    if (on) {
-      float t2[1][1][4];
-      acc_zero(t2);
-      warp_gemm_f32<1, 1, 16, false, true>(t2, Xm + (o + 16) * LDL + o + 16, LDL, 0, scr, 17, n0);
-      FLAB_ACC_FOREACH(1, 1, 0, n0, row, col, mi, ni, r) { Xm[(o + 16 + row) * LDL + o + col] = t2[mi][ni][r]; }
-    }
-  }
-  __syncthreads();
-  // ---- level 2: X_BA = X_BB (N_BA X_AA); two matrices: warp -> (matrix, 16x16 tile); one: warp -> 16x8 tile
-  {
-    constexpr int NI2 = NMAT == 2 ? 2 : 1;
-    const int mat = NMAT == 2 ? (warp >> 2) : 0, tile = NMAT == 2 ? (warp & 3) : warp;
-    const int m0 = 16 * (tile & 1), n0 = 8 * NI2 * (tile >> 1);
-    float *Xm = X + mat * C * LDL;
-    float *scr = Scr + mat * 32 * 33;
-    float t1[1][NI2][4];
-    acc_zero(t1);
-    warp_gemm_f32<1, NI2, 32, false, true>(t1, Xm + 32 * LDL, LDL, m0, Xm, LDL, n0);
-    FLAB_ACC_FOREACH(1, NI2, m0, n0, row, col, mi, ni, r) { scr[row * 33 + col] = t1[mi][ni][r]; }
-    __syncthreads();
-    float t2[1][NI2][4];
-    acc_zero(t2);
-    warp_gemm_f32<1, NI2, 32, false, true>(t2, Xm + 32 * LDL + 32, LDL, m0, scr, 33, n0);
-    FLAB_ACC_FOREACH(1, NI2, m0, n0, row, col, mi, ni, r) { Xm[(32 + row) * LDL + col] = t2[mi][ni][r]; }
-  }
-  __syncthreads();
 }
 
 // Forward for 16-bit element types with K, V <= 128: eight warps, the whole k and v tiles of the chunk resident
@@ -812,6 +743,7 @@ template <typename T, bool GATED> static int launch_wy_bwd(const flab_args *a, c
 
 // tcgen05 / TMA kernel for the shapes it covers (tc_wy_bwd.cu); 1 = handled, 0 = not applicable
 int tc_wy_bwd_try(const flab_args *a, cudaStream_t stream);
+int tc_wy_fwd_try(const flab_args *a, cudaStream_t stream);
 static bool tc_wy_enabled() {
   static int v = -1;
   if (v < 0) {
@@ -830,6 +762,10 @@ int flab_wy_fwd(const flab_args *a, void *stream) {
   if (int e = check_common(a)) return e;
   FLAB_REQUIRE(a->k && a->v && a->beta && a->aw && a->w && a->u, FLAB_E_BADARG, "wy_fwd needs k, v, beta, aw, w and u");
   FLAB_REQUIRE(!a->g || a->au, FLAB_E_BADARG, "wy_fwd: g given but au is NULL");
+  if (tc_wy_enabled()) {
+    const int r = tc_wy_fwd_try(a, (cudaStream_t)stream);
+    if (r != 0) return r < 0 ? r : FLAB_OK;
+  }
   FLAB_DISPATCH_16(a->dtype, T, {
     if (a->g) return (launch_wy_fwd<T, true, false>(a, (cudaStream_t)stream));
     return (launch_wy_fwd<T, false, false>(a, (cudaStream_t)stream));
