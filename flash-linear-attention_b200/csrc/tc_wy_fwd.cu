@@ -6,7 +6,8 @@
 //   warps 0-7 / 8-15 : two epilogue groups working on even / odd items.  The 64x64 fp32 inverse is SIMT work
 //                      (forward substitution + fp32 block merges, wy_inverse.cuh) with little parallelism, so one
 //                      group inverts while the other group's products, conversions and stores run.
-//   warp 16 : TMA producer - k and v of an item into the item's group buffer
+//   warp 16 : TMA producer - k and v of an item into a ring of three stages shared by the groups, so that the
+//             next item of a group is already resident while the previous one is still being stored
 //   warp 17 : MMA issuer   - k k^T, then (A_w diag(beta)) k and (A_u diag(beta)) v, software-pipelined over
 //                            the two groups; each group owns 256 TMEM columns (the Gram block is re-used by w)
 //   warps 18, 19 : output  - tile stores of A_w, A_u (after the inverse) and of w, u (which the epilogue builds over
@@ -37,13 +38,15 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
   constexpr uint32_t T16 = 16384, T8 = 8192;
   constexpr uint32_t F_BYTES = C * LDL * 4 + 32 * 33 * 4;  // fp32 work matrix + scratch of the inverse
   constexpr uint32_t F_PAD = (F_BYTES + 1023) & ~1023u;
-  constexpr uint32_t G_BYTES = 2 * T16 + 4 * T8 + F_PAD;   // one group's buffers
+  constexpr int NS = 3;                                    // k / v stages
+  constexpr uint32_t S_BYTES = 2 * T16;                    // one stage: k | v (replaced in place by w | u)
+  constexpr uint32_t G_BYTES = 4 * T8 + F_PAD;             // one group's private buffers
   constexpr uint32_t TM_GROUP = 256, TM_W = 0, TM_U = 128;  // per group; the Gram block sits in the first 64 columns of w
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float *sScal = reinterpret_cast<float *>(base + 2 * G_BYTES);  // [2 groups][beta 64 | gate 64]
-  __shared__ uint64_t full[2], empty[2], g1_done[2], e1_done[2], g23_done[2], acc_free[2], out_ready[2];
+  float *sScal = reinterpret_cast<float *>(base + NS * S_BYTES + 2 * G_BYTES);  // [2 groups][beta 64 | gate 64]
+  __shared__ uint64_t full[NS], empty[NS], g1_done[2], e1_done[2], g23_done[2], acc_free[2], out_ready[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
   __shared__ volatile int abort_snap[2][2];
@@ -51,9 +54,11 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
   const flab_args &a = p.a;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < NS; ++j) {
       mbar_init(&full[j], 1);
       mbar_init(&empty[j], 1);
+    }
+    for (int j = 0; j < 2; ++j) {
       mbar_init(&g1_done[j], 1);
       mbar_init(&e1_done[j], 8);
       mbar_init(&g23_done[j], 1);
@@ -83,24 +88,25 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
     t0 = it * C;
     rows = min(C, s.len - t0);
   };
-  // group buffers: k | v | A_w | A_u | A_w diag(beta) | A_u diag(beta) | fp32 work
-  auto gbuf = [&](int g) -> unsigned char * { return base + g * G_BYTES; };
+  // stage: k | v; group buffers: A_w | A_u | A_w diag(beta) | A_u diag(beta) | fp32 work
+  auto sbuf = [&](int st) -> unsigned char * { return base + st * S_BYTES; };
+  auto gbuf = [&](int g) -> unsigned char * { return base + NS * S_BYTES + g * G_BYTES; };
 
   if (warp == 16) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       for (int i = 0; i < n_local && !abort_flag; ++i) {
-        const int g = i & 1, ph = (i >> 1) & 1;
+        const int st = i % NS, sph = (i / NS) & 1;
         Seq s;
         int hd, t0, rows;
         locate(i, s, hd, t0, rows);
         const int tt = s.bos + t0, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
-        if (!mbar_wait(&empty[g], ph ^ 1)) { fail(101); break; }
-        mbar_expect_tx(&full[g], 2 * T16);
+        if (!mbar_wait(&empty[st], sph ^ 1)) { fail(101); break; }
+        mbar_expect_tx(&full[st], S_BYTES);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          tma_load_4d(gbuf(g) + j * 8192, &m.k, &full[g], 64 * j, c1, c2, s.b);
-          tma_load_4d(gbuf(g) + T16 + j * 8192, &m.v, &full[g], 64 * j, c1, c2, s.b);
+          tma_load_4d(sbuf(st) + j * 8192, &m.k, &full[st], 64 * j, c1, c2, s.b);
+          tma_load_4d(sbuf(st) + T16 + j * 8192, &m.v, &full[st], 64 * j, c1, c2, s.b);
         }
       }
     }
@@ -112,11 +118,11 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
       auto kx = [](int k) -> uint64_t { return (uint64_t)(((k >> 2) * 8192 + (k & 3) * 32) >> 4); };
       auto mx = [](int k) -> uint64_t { return (uint64_t)((k * 2048) >> 4); };
       auto gram = [&](int i) -> bool {
-        const int g = i & 1, ph = (i >> 1) & 1;
-        if (!mbar_wait(&full[g], ph)) { fail(102); return false; }
+        const int g = i & 1, ph = (i >> 1) & 1, st = i % NS, sph = (i / NS) & 1;
+        if (!mbar_wait(&full[st], sph)) { fail(102); return false; }
         if (i >= 2 && !mbar_wait(&acc_free[g], ph ^ 1)) { fail(103); return false; }  // w of the group's previous item has been read
         fence_after_sync();
-        const uint64_t dk = desc_kmajor(smem_u32(gbuf(g)), 0, 8192);
+        const uint64_t dk = desc_kmajor(smem_u32(sbuf(st)), 0, 8192);
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma(tmem + g * TM_GROUP + TM_W, dk + kx(k), dk + kx(k), id_g, k > 0);
         umma_commit(&g1_done[g]);
@@ -129,9 +135,9 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
         if (!ok) break;
         if (!mbar_wait(&e1_done[g], ph)) { fail(104); break; }
         fence_after_sync();
-        const uint32_t gb = smem_u32(gbuf(g));
-        const uint64_t dkm = desc_mnmajor(gb, 0, 8192), dvm = desc_mnmajor(gb + T16, 0, 8192);
-        const uint64_t dabw = desc_kmajor(gb + 2 * T16 + 2 * T8, 0, 8192), dabu = desc_kmajor(gb + 2 * T16 + (GATED ? 3 : 2) * T8, 0, 8192);
+        const uint32_t gb = smem_u32(gbuf(g)), sb = smem_u32(sbuf(i % NS));
+        const uint64_t dkm = desc_mnmajor(sb, 0, 8192), dvm = desc_mnmajor(sb + T16, 0, 8192);
+        const uint64_t dabw = desc_kmajor(gb + 2 * T8, 0, 8192), dabu = desc_kmajor(gb + (GATED ? 3 : 2) * T8, 0, 8192);
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma(tmem + g * TM_GROUP + TM_W, dabw + kx(k), dkm + mx(k), id_w, k > 0);
 #pragma unroll
@@ -149,24 +155,24 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
         int hd, t0, rows;
         locate(i, s, hd, t0, rows);
         const int tt = s.bos + t0, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
-        unsigned char *gb = gbuf(g);
+        unsigned char *gb = gbuf(g), *sb = sbuf(i % NS);
         if (!mbar_wait(&e1_done[g], ph)) { fail(105); break; }
         if (rows == C) {  // (a ragged chunk is written out by the epilogue warps themselves)
-          tma_store_4d(&m.aw, gb + 2 * T16, 0, c1, c2, s.b);
-          if (GATED) tma_store_4d(&m.au, gb + 2 * T16 + T8, 0, c1, c2, s.b);
+          tma_store_4d(&m.aw, gb, 0, c1, c2, s.b);
+          if (GATED) tma_store_4d(&m.au, gb + T8, 0, c1, c2, s.b);
           tma_store_commit();
         }
         if (!mbar_wait(&out_ready[g], ph)) { fail(106); break; }
         if (rows == C) {
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            tma_store_4d(&m.w, gb + j * 8192, 64 * j, c1, c2, s.b);
-            tma_store_4d(&m.u, gb + T16 + j * 8192, 64 * j, c1, c2, s.b);
+            tma_store_4d(&m.w, sb + j * 8192, 64 * j, c1, c2, s.b);
+            tma_store_4d(&m.u, sb + T16 + j * 8192, 64 * j, c1, c2, s.b);
           }
           tma_store_commit();
           tma_store_wait_read();
         }
-        mbar_arrive(&empty[g]);
+        mbar_arrive(&empty[i % NS]);
       }
       tma_store_wait_all();
     }
@@ -177,7 +183,7 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
     const uint32_t tm = tmem + g * TM_GROUP + ((uint32_t)(32 * wq) << 16);
     const int row_lo = 16 * wq + g8, row_hi = row_lo + 8;
     unsigned char *gb = gbuf(g);
-    unsigned char *tK = gb, *tV = gb + T16, *sAw = gb + 2 * T16, *sAu = sAw + T8, *sAbw = sAu + T8, *sAbu = sAbw + T8;
+    unsigned char *sAw = gb, *sAu = sAw + T8, *sAbw = sAu + T8, *sAbu = sAbw + T8;
     float *sF = reinterpret_cast<float *>(sAbu + T8), *sScr = sF + C * LDL;
     float *bs = sScal + g * 2 * C, *gs = bs + C;
     auto grp_sync = [&]() { asm volatile("bar.sync %0, 256;" ::"r"(1 + g) : "memory"); };
@@ -232,6 +238,7 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
     scalars_of(g, b_pf, g_pf);
     for (int i = g; i < n_local; i += 2) {
       const int ph = (i >> 1) & 1;
+      unsigned char *tK = sbuf(i % NS), *tV = tK + T16;
       Seq s;
       int hd, t0, rows;
       locate(i, s, hd, t0, rows);
@@ -357,7 +364,7 @@ template <bool GATED> static int launch_tc_wy_fwd(const flab_args *a, cudaStream
   p.n_items = a->NT * a->H;
   p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
   constexpr uint32_t F_PAD = ((C * LDL * 4 + 32 * 33 * 4) + 1023) & ~1023u;
-  const size_t smem = 1024 + 2 * (size_t)(2 * 16384 + 4 * 8192 + F_PAD) + 4 * C * sizeof(float);
+  const size_t smem = 1024 + 3 * (size_t)(2 * 16384) + 2 * (size_t)(4 * 8192 + F_PAD) + 4 * C * sizeof(float);
   auto kern = tc_wy_fwd_kernel<GATED>;
   if (int e = set_smem(kern, smem)) return e;
   int dev = 0, sms = 148;
