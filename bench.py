@@ -394,7 +394,7 @@ def main():
         pk = peaks()
         nbytes = B * H * (2 * K * V * 4 + (2 * K + 2 * V) * 2 + 8)
         ach = nbytes / (ms_k * 1e-3) / 1e9
-        line["roofline"] = {"kernel": "recurrent_fwd_kernel (decode)", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
+        line["roofline"] = {"kernel": "recurrent_stream_kernel (decode)", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
                             "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
                             "ms_per_launch": ms_k}
 

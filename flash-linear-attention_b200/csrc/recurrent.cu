@@ -185,10 +185,11 @@ __global__ void __launch_bounds__(RC_WARPS * 32, (RPW <= 8 ? 2 : 1)) recurrent_f
 
 // ------------------------------------------------------------------------------------------------
 // Streaming variant of the delta-rule recurrence for V == 128, K <= 128 with an initial state (the
-// decode configuration).  Persistent CTAs, one per SM, 8 consumer warps + 1 producer warp:
+// decode configuration).  Persistent CTAs, one per SM, two groups of 8 consumer warps (each group works on
+// alternate items, so that four warps per scheduler hide each other's latencies); no producer warp:
 //  * the 64 KB fp32 state tile of each (sequence, head) arrives through a 3-deep ring of bulk async
-//    copies (one cp.async.bulk per tile, completion on an mbarrier); the producer refills a slot as
-//    soon as the 8 consumer warps have drained it into registers (an "empty" mbarrier, no CTA barrier);
+//    copies (one cp.async.bulk per tile, completion on an mbarrier); a slot is refilled by one thread of the
+//    group that used it, right after the group barrier that follows the drain of the slot into registers;
 //  * a consumer warp owns 16 state rows, a lane 4 columns; the k / q values of the warp's rows sit in
 //    one register per lane (lanes 0-15: k, lanes 16-31: q*scale) and are broadcast with shuffles; they
 //    and v, g, beta are fetched one token ahead, so no global-load latency is exposed;
@@ -205,14 +206,15 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
 }
 
 template <typename T>
-__global__ void __launch_bounds__(288, 1) recurrent_stream_kernel(const flab_args a, int n_items) {
+__global__ void __launch_bounds__(512, 1) recurrent_stream_kernel(const flab_args a, int n_items) {
   using namespace tc;
   constexpr int RPW = 16;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   float *sState = reinterpret_cast<float *>(smem_raw);  // [RS_STAGES][128][128]
-  __shared__ __align__(16) float sRed[2][2][8][RC_V];   // [parity][S^T q | S^T k][warp][column]
-  __shared__ float sKQ[2][8];
-  __shared__ uint64_t full[RS_STAGES], empty[RS_STAGES];
+  __shared__ __align__(16) float sRedAll[2][2][2][8][RC_V];  // [group][parity][S^T q | S^T k][warp][column]
+  __shared__ float sKQAll[2][2][8];
+  __shared__ volatile int fail_snap[2][2];
+  __shared__ uint64_t full[RS_STAGES];
   __shared__ volatile int fail_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K = a.K, V = a.V;  // V == 128
@@ -224,35 +226,25 @@ __global__ void __launch_bounds__(288, 1) recurrent_stream_kernel(const flab_arg
   const T *beta = reinterpret_cast<const T *>(a.beta);
   const bool beta_vec = (a.flags & FLAB_F_BETA_VECTOR) != 0;
   const int n_local = n_items > (int)blockIdx.x ? (n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  auto refill = [&](int i) {  // one thread: tile of local item i -> its slot
+    if (i >= n_local) return;
+    const int st = i % RS_STAGES;
+    mbar_expect_tx(&full[st], tile_bytes);
+    bulk_load(sState + (size_t)st * 128 * RC_V, h0 + (size_t)(blockIdx.x + i * gridDim.x) * K * V, tile_bytes, &full[st]);
+  };
   if (tid == 0) {
-    for (int i = 0; i < RS_STAGES; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 8);
-    }
+    for (int i = 0; i < RS_STAGES; ++i) mbar_init(&full[i], 1);
     fail_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
+    for (int i = 0; i < RS_STAGES; ++i) refill(i);
   }
   __syncthreads();
-  if (warp == 8) {
-    // -------------------------------------------------------------------------------- producer
-    if (lane == 0) {
-      for (int i = 0; i < n_local && !fail_flag; ++i) {
-        const int st = i % RS_STAGES;
-        if (!mbar_wait(&empty[st], ((i / RS_STAGES) & 1) ^ 1)) {
-          atomicCAS(&tu_tc_error, 0, 21);
-          fail_flag = 1;
-          break;
-        }
-        const int item = blockIdx.x + i * gridDim.x;
-        mbar_expect_tx(&full[st], tile_bytes);
-        bulk_load(sState + (size_t)st * 128 * RC_V, h0 + (size_t)item * K * V, tile_bytes, &full[st]);
-      }
-    }
-    return;
-  }
   // ---------------------------------------------------------------------------------- consumers
-  const int c0 = 4 * lane, r0 = warp * RPW;
+  const int grp = warp >> 3, gw = warp & 7;
+  float (*sRed)[2][8][RC_V] = sRedAll[grp];
+  float (*sKQ)[8] = sKQAll[grp];
+  const int c0 = 4 * lane, r0 = gw * RPW;
   float n_kq = 0.f, n_v[4] = {0.f, 0.f, 0.f, 0.f}, n_b[4] = {1.f, 1.f, 1.f, 1.f}, n_eg = 1.f;
   auto fetch = [&](int li, int i_t) {  // vectors of token i_t of local item li -> registers
     if (li >= n_local) return;
@@ -272,19 +264,18 @@ __global__ void __launch_bounds__(288, 1) recurrent_stream_kernel(const flab_arg
       n_b[j] = (beta && beta_vec) ? Num<T>::f(beta[ov + c0 + j]) : bs;
     }
   };
-  fetch(0, 0);
+  fetch(grp, 0);
   int par = 0;
-  for (int i = 0; i < n_local; ++i) {
+  for (int i = grp; i < n_local; i += 2) {
     const int item = blockIdx.x + i * gridDim.x;
     const int n = item / a.H, hd = item % a.H;
     const Seq s = seq_of(a, n);
     const int st = i % RS_STAGES;
-    if (fail_flag) break;
     if (!mbar_wait(&full[st], (i / RS_STAGES) & 1)) {
       atomicCAS(&tu_tc_error, 0, 20);
       fail_flag = 1;
-      break;
     }
+
     float S[RPW][4];
     const float *tile = sState + (size_t)st * 128 * RC_V;
 #pragma unroll
@@ -294,8 +285,12 @@ __global__ void __launch_bounds__(288, 1) recurrent_stream_kernel(const flab_arg
       if (kk < K) x = *reinterpret_cast<const float4 *>(tile + (size_t)kk * RC_V + c0);
       S[r][0] = x.x, S[r][1] = x.y, S[r][2] = x.z, S[r][3] = x.w;
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[st]);  // this warp has drained the slot
+    // every warp of the group has drained the slot: refill it; the group leaves as one if a wait has run out (a
+    // thread of it samples the flag, everybody reads the sample after the barrier)
+    if ((tid & 255) == 0) fail_snap[grp][(i >> 1) & 1] = fail_flag;
+    named_barrier(1 + grp, 256);
+    if (fail_snap[grp][(i >> 1) & 1]) break;
+    if ((tid & 255) == 0) refill(i + RS_STAGES);
 
     for (int i_t = 0; i_t < s.len; ++i_t) {
       const size_t ov = tok_off(a, s, hd, i_t, V);
@@ -303,7 +298,7 @@ __global__ void __launch_bounds__(288, 1) recurrent_stream_kernel(const flab_arg
       float vv[4], bb[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) vv[j] = n_v[j], bb[j] = n_b[j];
-      if (i_t + 1 < s.len) fetch(i, i_t + 1); else fetch(i + 1, 0);
+      if (i_t + 1 < s.len) fetch(i, i_t + 1); else fetch(i + 2, 0);
       float pq[4] = {0.f, 0.f, 0.f, 0.f}, pk[4] = {0.f, 0.f, 0.f, 0.f}, kq_part = 0.f;
 #pragma unroll
       for (int r = 0; r < RPW; ++r) {
@@ -316,10 +311,10 @@ __global__ void __launch_bounds__(288, 1) recurrent_stream_kernel(const flab_arg
           pq[j] = fmaf(S[r][j], qv, pq[j]);
         }
       }
-      *reinterpret_cast<float4 *>(&sRed[par][0][warp][c0]) = make_float4(pq[0], pq[1], pq[2], pq[3]);
-      *reinterpret_cast<float4 *>(&sRed[par][1][warp][c0]) = make_float4(pk[0], pk[1], pk[2], pk[3]);
-      if (lane == 0) sKQ[par][warp] = kq_part;
-      named_barrier(1, 256);
+      *reinterpret_cast<float4 *>(&sRed[par][0][gw][c0]) = make_float4(pq[0], pq[1], pq[2], pq[3]);
+      *reinterpret_cast<float4 *>(&sRed[par][1][gw][c0]) = make_float4(pk[0], pk[1], pk[2], pk[3]);
+      if (lane == 0) sKQ[par][gw] = kq_part;
+      named_barrier(1 + grp, 256);
       float kq = 0.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) pq[j] = pk[j] = 0.f;
@@ -336,7 +331,7 @@ __global__ void __launch_bounds__(288, 1) recurrent_stream_kernel(const flab_arg
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float u_ = vv[j] - pk[j];
-        if (a.u && warp == 0) reinterpret_cast<T *>(a.u)[ov + c0 + j] = Num<T>::t(u_);
+        if (a.u && gw == 0) reinterpret_cast<T *>(a.u)[ov + c0 + j] = Num<T>::t(u_);
         vn[j] = u_ * bb[j];
         pq[j] = fmaf(vn[j], kq, pq[j]);
       }
@@ -346,7 +341,7 @@ __global__ void __launch_bounds__(288, 1) recurrent_stream_kernel(const flab_arg
 #pragma unroll
         for (int j = 0; j < 4; ++j) S[r][j] = fmaf(kv, vn[j], S[r][j]);
       }
-      if (warp == 0) {
+      if (gw == 0) {
         if (sizeof(T) == 2) {
           uint2 pkd;
           if (Num<T>::id == FLAB_BF16) {
@@ -382,7 +377,7 @@ template <typename T> static int launch_recurrent_stream(const flab_args *a, cud
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int n_items = a->N * a->H;
-  kern<<<n_items < sms ? n_items : sms, 288, smem, stream>>>(*a, n_items);
+  kern<<<n_items < sms ? n_items : sms, 512, smem, stream>>>(*a, n_items);
   return check_launch("recurrent_delta_fwd(stream)");
 }
 
