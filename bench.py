@@ -196,13 +196,17 @@ def time_stage(fn, reps=10, warm=3):
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
+    # one event pair per call and the median over calls: a call that makes the caching allocator go to the driver
+    # (a device-wide stall that is not the kernel's) does not leak into the stage's figure
+    evs = []
     for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
         fn()
-    b.record()
+        b.record()
+        evs.append((a, b))
     torch.cuda.synchronize()
-    return a.elapsed_time(b) / reps
+    return statistics.median(x.elapsed_time(y) for x, y in evs)
 
 
 def stage_breakdown(op, i):

@@ -35,21 +35,21 @@ struct TcOParams {
 template <int KB /*K/64*/, int VB /*BV/64*/, int MODE, int NS /*smem stages*/>
 __global__ void __launch_bounds__(576, 1)
 tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_constant__ CUtensorMap mapX2,
-                  const __grid_constant__ CUtensorMap mapY, const __grid_constant__ CUtensorMap mapH, const TcOParams p) {
+                  const __grid_constant__ CUtensorMap mapY, const __grid_constant__ CUtensorMap mapH,
+                  const __grid_constant__ CUtensorMap mapOut, const TcOParams p) {
   using namespace tc;
   constexpr int K = 64 * KB, BV = 64 * VB;
   constexpr bool HAS_H = MODE != TMODE_DV_LOCAL;
   constexpr uint32_t X_BYTES = KB * 8192, Y_BYTES = VB * 8192, H_BYTES = HAS_H ? VB * K * 128 : 0;
   constexpr uint32_t STAGE_BYTES = 2 * X_BYTES + Y_BYTES + H_BYTES;
-  constexpr int LDO = BV + 8;  // padded staging rows for the coalesced store
   constexpr uint32_t TM_STAGE = 256, TM_S = 0, TM_O = 64;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char *sStage = base;                         // [NS][STAGE_BYTES]
   unsigned char *sP = sStage + NS * STAGE_BYTES;         // [2][8192] score tiles (swizzled K-major)
-  bf16 *sOutAll = reinterpret_cast<bf16 *>(sP + 2 * 8192);  // [2][64][LDO]
-  float *sG = reinterpret_cast<float *>(sOutAll + 2 * C * LDO);  // [2][64]
+  unsigned char *sOutAll = sP + 2 * 8192;                   // [2][VB][64][128 B] output tiles (swizzled, source of the tile store)
+  float *sG = reinterpret_cast<float *>(sOutAll + 2 * Y_BYTES);  // [2][64]
   __shared__ uint64_t full[NS], empty[NS], s_done[2], p_ready[2], o_done[2], t_free[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
@@ -161,7 +161,7 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
     const int m0 = wq * 16;
     const uint32_t lane_base = (uint32_t)(32 * wq) << 16;
     constexpr int NIO = 4 * VB;  // accumulator n-tiles of this warp's half of the O columns
-    bf16 *sOut = sOutAll + grp * C * LDO;
+    unsigned char *sOut = sOutAll + grp * Y_BYTES;
     const int row_lo = m0 + g8, row_hi = row_lo + 8;
     for (int i = grp; i < n_local; i += 2) {
       const int st = grp, ph = (i >> 1) & 1;
@@ -241,7 +241,8 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
       tmem_ld_wait();
       fence_before_sync();
       mbar_arrive(&t_free[st]);
-      named_barrier(1 + grp, 256);  // this group's previous store has drained sOut
+      if (etid == 0) tma_store_wait_read();  // this group's previous tile store has read sOut
+      named_barrier(1 + grp, 256);
       const float osc = MODE == TMODE_O ? a.scale : 1.f;
 #pragma unroll
       for (int ni = 0; ni < NIO; ++ni)
@@ -250,13 +251,30 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
           const int row = hf ? row_hi : row_lo, col = (BV / 2) * chh + 8 * ni + 2 * t4;
           const float x0 = (o2[ni][2 * hf] + (HAS_H ? o1[ni][2 * hf] : 0.f)) * osc;
           const float x1 = (o2[ni][2 * hf + 1] + (HAS_H ? o1[ni][2 * hf + 1] : 0.f)) * osc;
-          if (p.ab_fmt) *reinterpret_cast<__nv_bfloat162 *>(sOut + row * LDO + col) = __floats2bfloat162_rn(x0, x1);
-          else *reinterpret_cast<__half2 *>(sOut + row * LDO + col) = __floats2half2_rn(x0, x1);
+          unsigned char *dst = sOut + (col >> 6) * 8192 + sw128_offset(row, col & 63);
+          if (p.ab_fmt) *reinterpret_cast<__nv_bfloat162 *>(dst) = __floats2bfloat162_rn(x0, x1);
+          else *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(x0, x1);
         }
+      fence_proxy_async();
       named_barrier(1 + grp, 256);
-      bf16 *out = reinterpret_cast<bf16 *>(MODE == TMODE_O ? a.o : a.dv) + tok_off(a, s, hd, t0, a.V) + vt * BV;
-      tile_store<bf16>(out, tok_stride(a, a.V), sOut, LDO, rows, BV, etid, 256);
+      if (rows == C) {
+        if (etid == 0) {  // one tile store per 64-column box; ordinary global stores would stall the next fence.proxy.async
+          const int tt = s.bos + t0, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
+#pragma unroll
+          for (int j = 0; j < VB; ++j) tma_store_4d(&mapOut, sOut + j * 8192, vt * BV + 64 * j, c1, c2, s.b);
+          tma_store_commit();
+        }
+      } else {
+        // ragged last chunk of a sequence: a tile store would write past its end
+        bf16 *out = reinterpret_cast<bf16 *>(MODE == TMODE_O ? a.o : a.dv) + tok_off(a, s, hd, t0, a.V) + vt * BV;
+        const size_t vs = tok_stride(a, a.V);
+        for (int e = etid; e < rows * (BV / 8); e += 256) {
+          const int r_ = e / (BV / 8), c_ = (e - r_ * (BV / 8)) * 8;
+          *reinterpret_cast<int4 *>(out + (size_t)r_ * vs + c_) = *reinterpret_cast<const int4 *>(sOut + (c_ >> 6) * 8192 + sw128_offset(r_, c_ & 63));
+        }
+      }
     }
+    if (etid == 0) tma_store_wait_all();
   }
   fence_before_sync();
   __syncthreads();
@@ -265,7 +283,7 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
 
 template <int KB, int VB, int MODE, int NS> static int launch_tc_o(const flab_args *a, cudaStream_t stream, const char *name) {
   constexpr int K = 64 * KB, BV = 64 * VB;
-  CUtensorMap mX1, mX2, mY, mH;
+  CUtensorMap mX1, mX2, mY, mH, mOut;
   const void *x1 = MODE == TMODE_O ? a->q : a->k, *x2 = MODE == TMODE_O ? a->k : a->q;
   const void *y = MODE == TMODE_O ? a->v : a->d_o, *hs = MODE == TMODE_O ? a->h : a->dh;
   if (int e = make_token_map(&mX1, x1, a, a->K)) return e;
@@ -276,20 +294,21 @@ template <int KB, int VB, int MODE, int NS> static int launch_tc_o(const flab_ar
   } else {
     mH = mY;
   }
+  if (int e = make_token_map(&mOut, MODE == TMODE_O ? a->o : a->dv, a, a->V)) return e;
   TcOParams p;
   p.a = *a;
   p.v_tiles = a->V / BV;
   p.n_items = a->NT * a->H * p.v_tiles;
   p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
   constexpr uint32_t STAGE = 2 * KB * 8192 + VB * 8192 + (MODE != TMODE_DV_LOCAL ? VB * K * 128 : 0);
-  const size_t smem = 1024 + NS * (size_t)STAGE + 2 * 8192 + 2 * (size_t)C * (BV + 8) * 2 + 2 * C * sizeof(float);
+  const size_t smem = 1024 + NS * (size_t)STAGE + 2 * 8192 + 2 * (size_t)VB * 8192 + 2 * C * sizeof(float);
   auto kern = tc_chunk_o_kernel<KB, VB, MODE, NS>;
   if (int e = set_smem(kern, smem)) return e;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = p.n_items < sms ? p.n_items : sms;
-  kern<<<grid, 576, smem, stream>>>(mX1, mX2, mY, mH, p);
+  kern<<<grid, 576, smem, stream>>>(mX1, mX2, mY, mH, mOut, p);
   return check_launch(name);
 }
 
@@ -297,8 +316,9 @@ template <int KB, int VB, int MODE, int NS> static int launch_tc_o(const flab_ar
 template <int MODE> int tc_chunk_o_try(const flab_args *a, cudaStream_t stream, const char *name) {
   if (a->dtype != FLAB_BF16 && a->dtype != FLAB_FP16) return 0;
   if ((a->K != 64 && a->K != 128) || a->V % 64 != 0) return 0;
-  const void *ptrs[4] = {a->q, a->k, MODE == TMODE_O ? a->v : a->d_o, MODE == TMODE_O ? a->h : (MODE == TMODE_DV ? a->dh : a->q)};
-  for (int i = 0; i < 4; ++i)
+  const void *ptrs[5] = {a->q, a->k, MODE == TMODE_O ? a->v : a->d_o, MODE == TMODE_O ? a->h : (MODE == TMODE_DV ? a->dh : a->q),
+                         MODE == TMODE_O ? a->o : a->dv};
+  for (int i = 0; i < 5; ++i)
     if (reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return 0;
   // shared-memory stages: as many as fit next to the two score tiles and the two staging buffers
   constexpr bool L = MODE == TMODE_DV_LOCAL;
