@@ -234,6 +234,7 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       else *reinterpret_cast<__half2 *>(ptr) = __floats2half2_rn(x, y);
     };
     float g_pf = gate_of(0);
+    float pend_val = 0.f, *pend_ptr = nullptr;  // dg of the previous item, not yet written
     for (int i = 0; i < n_local; ++i) {
       const int ph = i & 1;
       int c, hd, n, it;
@@ -309,6 +310,10 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&e1_done);
+      if (pend_ptr) {
+        *pend_ptr = pend_val;
+        pend_ptr = nullptr;
+      }
       // <h, dh> while the tensor core works; then this warp is done with the X tiles
       if (use_g) {
         float hd_ = 0.f;
@@ -401,9 +406,11 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       named_barrier(1, ET);  // output tiles and dg rows complete
       if (abort_snap[1]) break;
       if (use_g && tid < rows) {
-        float x = dgs[tid];
-        if (tid == last) x += red[0] * __expf(gl) + red[1];
-        reinterpret_cast<float *>(a.dg)[tok_off(a, s, hd, t0 + tid, 1)] = x;
+        // held back until after the next fence.proxy.async: that fence waits for the thread's outstanding global
+        // stores, and it sits on the critical chain of the next item
+        pend_val = dgs[tid];
+        if (tid == last) pend_val += red[0] * __expf(gl) + red[1];
+        pend_ptr = reinterpret_cast<float *>(a.dg) + tok_off(a, s, hd, t0 + tid, 1);
       }
       if (rows < C) {
         // ragged last chunk of a sequence: a tile store would write past its end
@@ -420,6 +427,7 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&out_ready);  // this warp is done with the Y buffer
     }
+    if (pend_ptr) *pend_ptr = pend_val;
   }
   fence_before_sync();
   __syncthreads();

@@ -281,6 +281,14 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
     if (tid == 0) abort_snap[0] = abort_flag;
     named_barrier(1, ET);
     bool live = !abort_snap[0];
+    long long pend_off = -1;  // dbeta / dg of the previous item, not yet written
+    float pend_db = 0.f, pend_dg = 0.f;
+    auto flush_pending = [&]() {
+      if (pend_off < 0) return;
+      reinterpret_cast<float *>(a.dbeta)[pend_off] = pend_db;
+      if (GATED) reinterpret_cast<float *>(a.dg)[pend_off] = pend_dg;
+      pend_off = -1;
+    };
     for (int i = 0; i < n_local && live; ++i) {
       const int b = i & 1, ph = (i >> 1) & 1, ip = i & 1;
       Seq s;
@@ -333,6 +341,7 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&e1_done);
+      flush_pending();
       // ---- E2: first product of the transform, rounded, becomes the operand of the second
       if (!mbar_wait(&b2_done, ip)) fail(91);
       fence_after_sync();
@@ -479,9 +488,11 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
       if (abort_snap[ip]) live = false;
       scalars_of(i + 2, b_pf, g_pf);
       if (tid < rows) {
-        const size_t o = tok_off(a, s, hd, t0 + tid, 1);
-        reinterpret_cast<float *>(a.dbeta)[o] = dbs[tid];
-        if (GATED) reinterpret_cast<float *>(a.dg)[o] = dgs[tid];
+        // held back until after the next fence.proxy.async (it waits for the thread's outstanding global stores
+        // and sits on the critical chain of the next item)
+        pend_off = (long long)tok_off(a, s, hd, t0 + tid, 1);
+        pend_db = dbs[tid];
+        if (GATED) pend_dg = dgs[tid];
       }
       if (rows < C) {
         // ragged last chunk of a sequence: a tile store would write past its end
@@ -497,6 +508,7 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&out_ready);  // this warp is done with the item's tiles
     }
+    flush_pending();
   }
   fence_before_sync();
   __syncthreads();
