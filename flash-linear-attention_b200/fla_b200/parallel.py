@@ -9,6 +9,9 @@
   obtains (M, b) of its slab from ONE extra state scan whose value dimension is widened by K identity
   columns, the boundary states are then passed rank to rank (point-to-point send/recv, [H,K,V] fp32 = 1 MiB
   at H=16, K=V=128), and a local correction pass recomputes the slab with its true initial state.
+  Backward uses the same structure with the transposed transition: the gradient of a slab's initial state is
+  dS_in = M^T dS_out + c, where c is what the slab's own outputs contribute (a reverse scan with dS_out = 0);
+  the chain runs from the last rank to the first, then every rank runs its full backward with the true dS_out.
   The reference has no such mode; its unused two-level scan (fla/ops/common/chunk_h_split.py:164-260) only
   covers diagonal decay.
 """
@@ -111,7 +114,7 @@ def _fwd_slab(q, k, v, g, beta, scale, S_in_of):
     # correction pass with the true initial state
     h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g_cum, h0=S_in.unsqueeze(0), output_final_state=False)
     o = C.chunk_fwd_o(geo, q, k, v_new, h, g=g_cum, scale=scale)
-    return o, S_out, (g_cum, aw, au, w, h, v_new, geo)
+    return o, S_out, (g_cum, aw, au, w, h, v_new, geo, M, S_in)
 
 
 def sp_chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, group=None):
@@ -132,3 +135,54 @@ def sp_chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=No
     if output_final_state:
         ht = broadcast_from(S_out.clone(), world - 1, group).unsqueeze(0)
     return o, ht
+
+
+class SPChunkGatedDeltaRuleFunction(torch.autograd.Function):
+    """chunk_gated_delta_rule on one T-slab per rank, differentiable. Collective calls happen inside forward and
+    backward, so every rank of `group` must run both, in the same order."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, group):
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
+        beta_k = beta.to(k.dtype)
+        S0 = None if initial_state is None else initial_state.float()[0]
+        o, S_out, saved = _fwd_slab(q, k, v, g.float(), beta_k, scale, lambda M, b: handoff_states(M, b, S0, group))
+        g_cum, aw, au, w, h, v_new, geo, M, S_in = saved
+        ht = broadcast_from(S_out.clone(), world - 1, group).unsqueeze(0) if output_final_state else None
+        ctx.save_for_backward(q, k, v, g_cum, beta_k, aw, au, w, h, v_new, M, S_in)
+        ctx.geo, ctx.scale, ctx.group, ctx.g_dtype, ctx.beta_dtype = geo, scale, group, g.dtype, beta.dtype
+        ctx.has_h0 = initial_state is not None
+        return o, ht
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        from .ops import common as C
+        from .ops.gated_delta_rule import chunk_gated_delta_rule_bwd
+        q, k, v, g_cum, beta, aw, au, w, h, v_new, M, S_in = ctx.saved_tensors
+        geo, scale, group = ctx.geo, ctx.scale, ctx.group
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        do = do.contiguous()
+        # what this slab's outputs alone contribute to the gradient of its initial state (dS_out = 0)
+        dv = C.chunk_bwd_dv_local(geo, q, k, g_cum, do, scale)
+        _, c, _ = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g_cum, dht=None, want_dh0=True)
+        # the gradient of the whole-sequence final state enters at the last rank
+        ext = None if dht is None or rank != world - 1 else dht.float()[0]
+        dS_out, dS_in = handoff_states(M.transpose(1, 2).contiguous(), c[0], ext, group, reverse=True)
+        dq, dk, dv, db, dg, _ = chunk_gated_delta_rule_bwd(geo, q, k, v, g_cum, beta, aw, au, scale, S_in.unsqueeze(0), do,
+                                                          dS_out.unsqueeze(0), saved=(w, h, v_new))
+        dh0 = dS_in.unsqueeze(0) if (ctx.has_h0 and rank == 0) else None
+        if ctx.has_h0 and rank != 0:
+            dh0 = torch.zeros_like(dS_in).unsqueeze(0)
+        return dq, dk, dv, dg.to(ctx.g_dtype), db.to(ctx.beta_dtype), None, dh0, None, None
+
+
+def sp_chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, group=None):
+    """Differentiable chunk_gated_delta_rule for ONE sequence split along T over the ranks of `group` (same slab
+    rules as `sp_chunk_gated_delta_rule_fwd`). `initial_state` and its gradient live on rank 0; a gradient of the
+    returned final state is taken from the LAST rank only (the state is that rank's, broadcast to the others)."""
+    assert q.shape[0] == 1, "sequence parallel mode takes one sequence (B = 1) per call"
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    assert rank == world - 1 or q.shape[1] % 64 == 0, "slabs before the last one must be multiples of 64 tokens"
+    scale = k.shape[-1] ** -0.5 if scale is None else scale
+    return SPChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, group)
