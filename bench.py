@@ -44,6 +44,12 @@ SIDE_METRICS = {
     "decode": "fused_recurrent_gated_delta_rule decode tokens/s (256 sequences, H=16 D=128)",
 }
 
+# DRAM bytes per token-head of each stage's kernel, from the ncu capture summarised in
+# profiles/gdn_kernels_ncu_full_T2048.md (dram__bytes_read.sum + dram__bytes_write.sum at T=2048, 262 144
+# token-heads; the traffic of these kernels is proportional to the number of tokens)
+NCU_BYTES_PER_TOKENHEAD = {"wy_fwd": 1074, "delta_fwd_h": 1415, "chunk_fwd_o": 1499, "dv_local": 941,
+                           "delta_bwd_dhu": 1953, "dqkwg": 3240, "wy_bwd": 1966}
+
 WORKLOADS = {
     # name: (op, B, T, H, K, V)
     "gdn": ("gated_delta", 8, 4096, 16, 128, 128),
@@ -399,7 +405,8 @@ def main():
         nbytes = B * H * (2 * K * V * 4 + (2 * K + 2 * V) * 2 + 8)
         ach = nbytes / (ms_k * 1e-3) / 1e9
         line["roofline"] = {"kernel": "recurrent_stream_kernel (decode)", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
-                            "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                            "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": 485e6,
+                            "traffic_source": "ncu, same workload (profiles/decode_stream_kernel_ncu_full.md)", "peak_source": pk["source"],
                             "ms_per_launch": ms_k}
 
     # ---- end to end: host buffers in, every result back to the host, inside the timed region
@@ -451,7 +458,9 @@ def main():
             else:
                 ach, peak, unit, bound = s["flops"] / (s["ms"] * 1e-3) / 1e12, pk["bf16_tflops"], "TFLOP/s", "tensor"
             line["roofline"] = {"kernel": top, "bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
-                                "traffic": None, "peak_source": pk["source"], "ms_per_launch": s["ms"],
+                                "traffic": (NCU_BYTES_PER_TOKENHEAD[top] * B * T * H if op == "gated_delta" and top in NCU_BYTES_PER_TOKENHEAD else None),
+                                "traffic_source": "ncu at T=2048 scaled by tokens (profiles/gdn_kernels_ncu_full_T2048.md)",
+                                "peak_source": pk["source"], "ms_per_launch": s["ms"],
                                 "tensor_frac": s["flops"] / (s["ms"] * 1e-3) / 1e12 / pk["bf16_tflops"]}
             line["stages_ms"] = {k_: round(v_["ms"] * v_["launches_per_step"], 4) for k_, v_ in stages.items()}
         line["cpu_baseline"], _ = cpu_sample(op, B, T, H, K, V, dtype)
