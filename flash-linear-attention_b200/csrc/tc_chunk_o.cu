@@ -316,6 +316,7 @@ template <int KB, int VB, int MODE, int NS> static int launch_tc_o(const flab_ar
 template <int MODE> int tc_chunk_o_try(const flab_args *a, cudaStream_t stream, const char *name) {
   if (a->dtype != FLAB_BF16 && a->dtype != FLAB_FP16) return 0;
   if ((a->K != 64 && a->K != 128) || a->V % 64 != 0) return 0;
+  if ((unsigned long long)a->NT * a->H * a->K >= (1ull << 31)) return 0;  // tile coordinates of the state tensor are 32-bit
   const void *ptrs[5] = {a->q, a->k, MODE == TMODE_O ? a->v : a->d_o, MODE == TMODE_O ? a->h : (MODE == TMODE_DV ? a->dh : a->q),
                          MODE == TMODE_O ? a->o : a->dv};
   for (int i = 0; i < 5; ++i)

@@ -397,6 +397,7 @@ template <int VB, int NS, int MODE> static int launch_tc_dh(const flab_args *a, 
 static bool tc_dh_ok(const flab_args *a, const void *const *ptrs, int n) {
   if (a->dtype != FLAB_BF16 && a->dtype != FLAB_FP16) return false;
   if (a->K != 128 || a->V % 64 != 0) return false;
+  if ((unsigned long long)a->NT * a->H * a->K >= (1ull << 31)) return false;  // tile coordinates of the state tensor are 32-bit
   for (int i = 0; i < n; ++i)
     if (ptrs[i] && reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return false;
   return true;

@@ -466,6 +466,7 @@ template <bool USE_DW> static int launch_tc_dqkwg(const flab_args *a, cudaStream
 int tc_dqkwg_try(const flab_args *a, cudaStream_t stream) {
   if (a->dtype != FLAB_BF16 && a->dtype != FLAB_FP16) return 0;
   if (a->K != 128 || a->V != 128) return 0;
+  if ((unsigned long long)a->NT * a->H * a->K >= (1ull << 31)) return 0;  // tile coordinates of the state tensor are 32-bit
   const void *ptrs[11] = {a->q, a->k, a->w, a->v, a->d_o, a->dv, a->h, a->dh, a->dq, a->dk, a->dw};
   for (int i = 0; i < 11; ++i)
     if (ptrs[i] && reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return 0;

@@ -480,3 +480,27 @@ def test_fused_forward_entry_equals_staged_forward():
         o2, h2 = o_.chunk_gated_delta_rule(q, i["k"], i["v"], i["g"], i["beta"], initial_state=i["h0"],
                                            output_final_state=True, offsets=off, head_first=False)
         assert torch.equal(o1, o2) and torch.equal(h1, h2)
+
+
+def test_one_long_sequence_tail_matches_recurrent():
+    """B=1, T=2^18, H=16: 64-bit offsets and 32-bit tile coordinates hold; the last 2048 tokens of the chunked
+    forward agree with the token-recurrent kernel started from the chunked state at T-2048."""
+    import torch.nn.functional as F
+    from fla_b200.ops import chunk_gated_delta_rule, fused_recurrent_gated_delta_rule
+    T, H, K, V, tail = 1 << 18, 16, 128, 128, 2048
+    g0 = torch.Generator(device="cuda").manual_seed(5)
+    q = F.normalize(torch.randn(1, T, H, K, device="cuda", generator=g0), dim=-1).bfloat16()
+    k = F.normalize(torch.randn(1, T, H, K, device="cuda", generator=g0), dim=-1).bfloat16()
+    v = torch.randn(1, T, H, V, device="cuda", generator=g0).bfloat16()
+    g = F.logsigmoid(torch.randn(1, T, H, device="cuda", generator=g0)) * 0.1
+    beta = torch.rand(1, T, H, device="cuda", generator=g0).sigmoid().bfloat16()
+    with torch.no_grad():
+        o, ht = chunk_gated_delta_rule(q, k, v, g, beta, output_final_state=True, head_first=False)
+        cut = T - tail
+        _, h_cut = chunk_gated_delta_rule(q[:, :cut], k[:, :cut], v[:, :cut], g[:, :cut], beta[:, :cut],
+                                          output_final_state=True, head_first=False)
+        o_t, ht_t = fused_recurrent_gated_delta_rule(q[:, cut:], k[:, cut:], v[:, cut:], g[:, cut:], beta[:, cut:],
+                                                     initial_state=h_cut, output_final_state=True, head_first=False)
+    assert torch.isfinite(o).all()
+    assert_close("o tail", o_t, o[:, cut:], 5e-3)
+    assert_close("ht", ht_t, ht, 5e-3)
