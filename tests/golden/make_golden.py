@@ -1,7 +1,7 @@
 """Generate tests/golden/ref_vectors.npz from the reference's own naive PyTorch functions.
 
-Run in a container that has the reference checkout (default /root/reference; override with
-FLA_REFERENCE):   python tests/golden/make_golden.py
+Run where a checkout of the reference is available, with FLA_REFERENCE set to its path:
+    FLA_REFERENCE=<path to flash-linear-attention> python tests/golden/make_golden.py
 The reference package is imported through a stub parent module so that its top-level __init__
 (which registers HF model configs) does not run.  Everything is CPU fp32, seeded.
 """
@@ -14,7 +14,9 @@ import numpy as np
 import torch
 import torch.nn.functional as F
 
-REF = os.environ.get("FLA_REFERENCE", "/root/reference")
+REF = os.environ.get("FLA_REFERENCE")
+if not REF or not os.path.isdir(os.path.join(REF, "fla")):
+    sys.exit("set FLA_REFERENCE to the path of a flash-linear-attention checkout")
 stub = types.ModuleType("fla")
 stub.__path__ = [os.path.join(REF, "fla")]
 sys.modules["fla"] = stub
