@@ -140,6 +140,7 @@ def _sgla_ref(i, scale=None, offsets=None, head_first=False, **kw):
 @pytest.mark.parametrize("B,T,H,K,V,dtype,head_first", [
     (2, 130, 3, 64, 64, torch.bfloat16, False),
     (2, 256, 2, 128, 128, torch.bfloat16, False),
+    (2, 150, 2, 128, 128, torch.float16, True),    # tcgen05 kernels: head-first, fp16, ragged last chunk
     (1, 300, 2, 100, 60, torch.bfloat16, False),
     (2, 63, 2, 32, 64, torch.float16, True),
     (2, 200, 2, 64, 128, torch.float32, False),
@@ -262,6 +263,8 @@ DELTA_TOL = {"dq": 8e-3, "dk": 8e-3, "dv": 8e-3, "dh0": 8e-3, "dbeta": 2e-2, "dg
 @pytest.mark.parametrize("B,T,H,K,V,dtype,head_first", [
     (2, 130, 2, 64, 64, torch.bfloat16, False),
     (2, 256, 2, 128, 128, torch.bfloat16, False),
+    (2, 150, 2, 128, 128, torch.float16, True),    # tcgen05 kernels: head-first, fp16, ragged last chunk
+    (1, 333, 3, 128, 128, torch.bfloat16, False),
     (1, 300, 2, 100, 60, torch.bfloat16, False),
     (2, 63, 2, 32, 64, torch.float16, True),
     (1, 7, 2, 64, 64, torch.bfloat16, False),
@@ -274,6 +277,9 @@ def test_chunk_delta_rule(B, T, H, K, V, dtype, head_first):
 @pytest.mark.parametrize("B,T,H,K,V,dtype,head_first,gate_div", [
     (2, 130, 2, 64, 64, torch.bfloat16, False, 1.0),
     (2, 256, 2, 128, 128, torch.bfloat16, False, 1.0),
+    (2, 150, 2, 128, 128, torch.float16, True, 1.0),    # tcgen05 kernels: head-first, fp16, ragged last chunk
+    (1, 333, 3, 128, 128, torch.bfloat16, False, 10.0),
+    (1, 40, 2, 128, 128, torch.bfloat16, False, 1.0),   # a single ragged chunk
     (1, 300, 2, 100, 60, torch.bfloat16, False, 1.0),
     (2, 63, 2, 32, 64, torch.float16, True, 1.0),
     (2, 200, 2, 64, 64, torch.bfloat16, False, 10.0),
