@@ -3,9 +3,11 @@
 //   fwd_o     : o = (q*scale*e^{b}) h + tril(A) v                                (fla/ops/gla/chunk.py:320-393)
 //   bwd_dav   : dA = tril(do v^T) * scale;  dv = tril(A)^T do + (k e^{b_L-b}) dh (fla/ops/gla/chunk.py:583-710)
 //   bwd_dqkg  : dq, dk (intra + inter) and dg with the in-chunk reverse cumsum   (fla/ops/gla/chunk.py:409-567, 726-837)
-// The gate couples every (i, j, k) triple, so the intra-chunk terms cannot be factored into one
-// GEMM with row/column scaling; they are evaluated directly in fp32 (exponents are always <= 0, so
-// nothing overflows and no re-basing is needed).  The state products use the tile GEMM.
+// The gate couples every (i, j, channel) triple, so the intra-chunk terms are not one GEMM with row / column
+// scaling.  They are evaluated in fp32 with the gate factors split at a reference row per block of 16 rows,
+// e^{b_i - b_j} = e^{b_i - b_r} e^{b_r - b_j}: the exponentials are taken once per element and the (i, j) pairs
+// become plain FMAs; a block whose decay over its 16 tokens would overflow the split takes the direct form.
+// The state products use the tile GEMM.
 #include "common.cuh"
 
 namespace flab {
@@ -20,6 +22,8 @@ __global__ void __launch_bounds__(256) gla_fwd_intra_kernel(const flab_args a) {
   constexpr int LD = GT + 1;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float *sQ = reinterpret_cast<float *>(smem_raw), *sK = sQ + C * LD, *sB = sK + C * LD;
+  float *sKs = sB + C * LD;   // [64][LD] k rows re-based to the reference row of the current row block
+  float *sQs = sKs + C * LD;  // [16][LD] q rows of the current row block, re-based likewise
   const int tid = threadIdx.x;
   int n, it;
   chunk_of(a, blockIdx.x, n, it);
@@ -29,10 +33,18 @@ __global__ void __launch_bounds__(256) gla_fwd_intra_kernel(const flab_args a) {
   const size_t ks = tok_stride(a, a.K), offk = tok_off(a, s, hd, t0, a.K);
   const T *q = reinterpret_cast<const T *>(a.q) + offk, *k = reinterpret_cast<const T *>(a.k) + offk;
   const float *b = reinterpret_cast<const float *>(a.gk) + offk;
-  // thread owns pairs p = tid, tid + 256, ... of the 64 x 64 grid (row-major); 16 pairs each
-  float acc[16];
+  // The triple (i, j, channel) only couples through e^{b_i - b_j}.  For a block of 16 rows with first row r,
+  // e^{b_i - b_j} = e^{b_i - b_r} e^{b_r - b_j}: both factors are applied once per element (not once per pair) and
+  // the pairs are plain fp32 FMAs.  For j before the block the second exponent is <= 0.  Inside the block it is
+  // positive but bounded by the decay over 16 tokens; when that exceeds e^60 in some channel (never with gates from
+  // a log-sigmoid) the pairs of that block are evaluated directly instead.
+  // thread = (row il of the block, column group jj): pairs (16 I + il, jj + 16 m) for m <= I
+  const int il = tid >> 4, jj = tid & 15;
+  float acc[4][4];
 #pragma unroll
-  for (int p = 0; p < 16; ++p) acc[p] = 0.f;
+  for (int I = 0; I < 4; ++I)
+#pragma unroll
+    for (int m = 0; m < 4; ++m) acc[I][m] = 0.f;
   for (int k0 = 0; k0 < a.K; k0 += GT) {
     const int kw = min(GT, a.K - k0);
     __syncthreads();
@@ -45,21 +57,56 @@ __global__ void __launch_bounds__(256) gla_fwd_intra_kernel(const flab_args a) {
     }
     __syncthreads();
 #pragma unroll
-    for (int p = 0; p < 16; ++p) {
-      const int e = tid + p * 256, i = e >> 6, j = e & 63;
-      if (i >= j && i < rows) {
-        float x = 0.f;
-        for (int c = 0; c < kw; ++c) x = fmaf(sQ[i * LD + c] * sK[j * LD + c], expf(sB[i * LD + c] - sB[j * LD + c]), x);
-        acc[p] += x;
+    for (int I = 0; I < 4; ++I) {
+      const int r0 = 16 * I, rend = min(r0 + 16, rows);
+      if (r0 >= rows) break;  // uniform
+      // decay across the block, worst channel (b is non-increasing along the tokens)
+      float span = 0.f;
+      if (tid < GT) span = sB[r0 * LD + tid] - sB[(rend - 1) * LD + tid];
+      const bool direct = __syncthreads_or(span > 60.f);
+      const int jend = direct ? r0 : rend;  // rows of k that get re-based
+      for (int e = tid; e < jend * GT; e += 256) {
+        const int r = e / GT, c = e - r * GT;
+        sKs[r * LD + c] = sK[r * LD + c] * expf(sB[r0 * LD + c] - sB[r * LD + c]);
       }
+      for (int e = tid; e < 16 * GT; e += 256) {
+        const int r = e / GT, c = e - r * GT;
+        sQs[r * LD + c] = (r0 + r < rows) ? sQ[(r0 + r) * LD + c] * expf(sB[(r0 + r) * LD + c] - sB[r0 * LD + c]) : 0.f;
+      }
+      __syncthreads();
+      const int i = r0 + il;
+      if (i < rows) {
+        const float *qs = sQs + il * LD;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          if (m > I) break;
+          const int j = jj + 16 * m;
+          if (j > i) continue;
+          float x = 0.f;
+          if (m < I || !direct) {
+            const float *kk = sKs + j * LD;
+#pragma unroll 8
+            for (int c = 0; c < GT; ++c) x = fmaf(qs[c], kk[c], x);
+          } else {
+            for (int c = 0; c < kw; ++c) x = fmaf(sQ[i * LD + c] * sK[j * LD + c], expf(sB[i * LD + c] - sB[j * LD + c]), x);
+          }
+          acc[I][m] += x;
+        }
+      }
+      __syncthreads();
     }
   }
   float *A = reinterpret_cast<float *>(a.a) + tok_off(a, s, hd, t0, C);
   const size_t as_ = tok_stride(a, C);
 #pragma unroll
-  for (int p = 0; p < 16; ++p) {
-    const int e = tid + p * 256, i = e >> 6, j = e & 63;
-    if (i < rows) A[(size_t)i * as_ + j] = (i >= j) ? acc[p] * a.scale : 0.f;
+  for (int I = 0; I < 4; ++I) {
+    const int i = 16 * I + il;
+    if (i >= rows) continue;
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int j = jj + 16 * m;
+      A[(size_t)i * as_ + j] = (m <= I && j <= i) ? acc[I][m] * a.scale : 0.f;
+    }
   }
 }
 
@@ -202,8 +249,8 @@ __global__ void __launch_bounds__(128) gla_bwd_dav_kernel(const flab_args a) {
 
 // ------------------------------------------------------------------------------------------------
 // dq, dk, dg.  grid (NT, H, K/64); 256 threads.  Phase 1: inter-chunk products on the tile GEMM
-// (do h^T, v dh^T), results parked in fp32 shared memory.  Phase 2: intra-chunk terms evaluated
-// directly; thread = (token row, 4-way interleaved channel slice).
+// (do h^T, v dh^T), results parked in fp32 shared memory.  Phase 2: intra-chunk terms, block of 16 rows by
+// block of 16 rows, with the gate factors hoisted out of the (i, j) pair loops.
 // ------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
@@ -221,10 +268,11 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
   T *sH = sVV + C * LDV;                   // [64 channels][LDV]
   T *sDH = sH + GT * LDV;                  // [64 channels][LDV]
   // phase 2 view
-  float *sQ = reinterpret_cast<float *>(region);  // [64][LD]
-  float *sK = sQ + C * LD;
+  float *sK = reinterpret_cast<float *>(region);  // [64][LD]
   float *sB = sK + C * LD;
-  float *sDA = sB + C * LD;  // [64][LD]
+  float *sDA = sB + C * LD;   // [64][LD]
+  float *sKF = sDA + C * LD;  // [64][LD] k re-based to the reference row of the current row block
+  float *sQs = sKF + C * LD;  // [16][LD] q of the current row block, re-based likewise
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int n, it;
@@ -277,10 +325,12 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
   {
     const T *q = reinterpret_cast<const T *>(a.q) + offk, *k = reinterpret_cast<const T *>(a.k) + offk;
     const float *dA = reinterpret_cast<const float *>(a.da) + tok_off(a, s, hd, t0, C);
-    for (int e = tid; e < C * GT; e += 256) {
-      int r = e / GT, c = e - r * GT;
-      bool ok = r < rows && c < kw;
-      sQ[r * LD + c] = ok ? Num<T>::f(q[(size_t)r * ks + c]) : 0.f;
+    float qreg[C * GT / 256];  // q of element e = tid + 256 p (row e / 64, channel e % 64): row block I owns p = 4 I .. 4 I + 3
+#pragma unroll
+    for (int p = 0; p < C * GT / 256; ++p) {
+      const int e = tid + 256 * p, r = e / GT, c = e - r * GT;
+      const bool ok = r < rows && c < kw;
+      qreg[p] = ok ? Num<T>::f(q[(size_t)r * ks + c]) : 0.f;
       sK[r * LD + c] = ok ? Num<T>::f(k[(size_t)r * ks + c]) : 0.f;
       sB[r * LD + c] = ok ? b[(size_t)r * ks + c] : 0.f;
       sDA[r * LD + c] = (r < rows && c <= r) ? dA[(size_t)r * as_ + c] : 0.f;  // c indexes the 64 columns of dA here
@@ -292,52 +342,97 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
       for (int j = 0; j < rows; ++j) x = fmaf(sDK[j * LD + tid], sK[j * LD + tid], x);
       sGK[tid] += x;
     }
-    __syncthreads();
-    const int i = tid >> 2, sl = tid & 3;
-    float aq[GT / 4], ak[GT / 4], bi[GT / 4];
+    // Intra-chunk terms, one block of 16 rows i at a time (first row r): e^{b_i - b_j} = e^{b_i - b_r} e^{b_r - b_j},
+    // each factor applied once per element, the (i, j) pairs are plain FMAs.  For j before the block the second
+    // exponent is <= 0; inside the block it is bounded by the decay over 16 tokens, and when that exceeds e^60 in
+    // some channel the in-block pairs are evaluated directly instead.
 #pragma unroll
-    for (int m = 0; m < GT / 4; ++m) {
-      aq[m] = 0.f;
-      ak[m] = 0.f;
-      bi[m] = sB[i * LD + sl + 4 * m];
-    }
-    if (i < rows) {
-      for (int j = 0; j <= i; ++j) {
-        const float d = sDA[i * LD + j];
+    for (int I = 0; I < 4; ++I) {
+      const int r0 = 16 * I, rend = min(r0 + 16, rows);
+      if (r0 >= rows) break;  // uniform
+      float span = 0.f;
+      if (tid < GT) span = sB[r0 * LD + tid] - sB[(rend - 1) * LD + tid];
+      const bool direct = __syncthreads_or(span > 60.f);
+      const int jend = direct ? r0 : rend;
+      for (int e = tid; e < jend * GT; e += 256) {
+        const int r = e / GT, c = e - r * GT;
+        sKF[r * LD + c] = sK[r * LD + c] * expf(sB[r0 * LD + c] - sB[r * LD + c]);
+      }
 #pragma unroll
-        for (int m = 0; m < GT / 4; ++m) {
-          const int c = sl + 4 * m;
-          aq[m] = fmaf(d * sK[j * LD + c], expf(bi[m] - sB[j * LD + c]), aq[m]);
+      for (int pp = 0; pp < 4; ++pp) {
+        const int e = tid + 256 * pp, r = e / GT, c = e - r * GT;  // row r of the block
+        sQs[r * LD + c] = qreg[4 * I + pp] * expf(sB[(r0 + r) * LD + c] - sB[r0 * LD + c]);
+      }
+      __syncthreads();
+      {  // dq of the block's rows: thread = (row il, channels cg + 16 m)
+        const int il = tid >> 4, cg = tid & 15, i = r0 + il;
+        if (i < rows) {
+          float t[4] = {0.f, 0.f, 0.f, 0.f};
+          const int jn = min(jend, i + 1);
+          for (int j = 0; j < jn; ++j) {
+            const float d = sDA[i * LD + j];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) t[m] = fmaf(d, sKF[j * LD + cg + 16 * m], t[m]);
+          }
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const int c = cg + 16 * m;
+            const float bi = sB[i * LD + c];
+            float val = t[m] * expf(bi - sB[r0 * LD + c]);
+            if (direct)
+              for (int j = r0; j <= i; ++j) val = fmaf(sDA[i * LD + j] * sK[j * LD + c], expf(bi - sB[j * LD + c]), val);
+            sDQ[i * LD + c] += val;
+          }
         }
       }
-      for (int i2 = i; i2 < rows; ++i2) {
-        const float d = sDA[i2 * LD + i];
+      {  // dk contributions of the block to every row j it reaches: thread = (row j, channels sl + 4 m)
+        const int j = tid >> 2, sl = tid & 3;
+        if (j < jend) {
+          float T_[GT / 4];
 #pragma unroll
-        for (int m = 0; m < GT / 4; ++m) {
-          const int c = sl + 4 * m;
-          ak[m] = fmaf(d * sQ[i2 * LD + c], expf(sB[i2 * LD + c] - bi[m]), ak[m]);
+          for (int m = 0; m < GT / 4; ++m) T_[m] = 0.f;
+          for (int i2 = max(j, r0); i2 < rend; ++i2) {
+            const float d = sDA[i2 * LD + j];
+            const float *qs = sQs + (i2 - r0) * LD + sl;
+#pragma unroll
+            for (int m = 0; m < GT / 4; ++m) T_[m] = fmaf(d, qs[4 * m], T_[m]);
+          }
+#pragma unroll
+          for (int m = 0; m < GT / 4; ++m) {
+            const int c = sl + 4 * m;
+            sDK[j * LD + c] += T_[m] * expf(sB[r0 * LD + c] - sB[j * LD + c]);
+          }
+        } else if (direct && j < rend) {
+          for (int m = 0; m < GT / 4; ++m) {
+            const int c = sl + 4 * m;
+            if (c >= kw) continue;
+            float x = 0.f;
+            for (int i2 = j; i2 < rend; ++i2)
+              x = fmaf(sDA[i2 * LD + j] * Num<T>::f(q[(size_t)i2 * ks + c]), expf(sB[i2 * LD + c] - sB[j * LD + c]), x);
+            sDK[j * LD + c] += x;
+          }
         }
       }
+      __syncthreads();
     }
-#pragma unroll
-    for (int m = 0; m < GT / 4; ++m) {
-      const int c = sl + 4 * m;
-      sDQ[i * LD + c] += aq[m];
-      sDK[i * LD + c] += ak[m];
-    }
-    __syncthreads();
     // outputs; dg = reverse in-chunk cumsum of (q dq - k dk) + per-channel chunk term
     T *dq = reinterpret_cast<T *>(a.dq) + offk, *dk = reinterpret_cast<T *>(a.dk) + offk;
-    for (int e = tid; e < rows * kw; e += 256) {
-      int r = e / kw, c = e - r * kw;
-      dq[(size_t)r * ks + c] = Num<T>::t(sDQ[r * LD + c]);
-      dk[(size_t)r * ks + c] = Num<T>::t(sDK[r * LD + c]);
+#pragma unroll
+    for (int p = 0; p < C * GT / 256; ++p) {
+      const int e = tid + 256 * p, r = e / GT, c = e - r * GT;
+      const float dqv = sDQ[r * LD + c], dkv = sDK[r * LD + c];
+      if (r < rows && c < kw) {
+        dq[(size_t)r * ks + c] = Num<T>::t(dqv);
+        dk[(size_t)r * ks + c] = Num<T>::t(dkv);
+      }
+      sDQ[r * LD + c] = qreg[p] * dqv - sK[r * LD + c] * dkv;  // the integrand of dg
     }
+    __syncthreads();
     if (tid < kw) {
       float *dg = reinterpret_cast<float *>(a.dgk) + offk;
       float run = sGK[tid];
       for (int r = rows - 1; r >= 0; --r) {
-        run += sQ[r * LD + tid] * sDQ[r * LD + tid] - sK[r * LD + tid] * sDK[r * LD + tid];
+        run += sDQ[r * LD + tid];
         dg[(size_t)r * ks + tid] = run;
       }
     }
@@ -352,7 +447,7 @@ template <typename T, int BV> static size_t gla_o_smem(const flab_args *a, bool 
 }
 
 template <typename T> static int launch_gla_fwd_intra(const flab_args *a, cudaStream_t stream) {
-  size_t smem = (size_t)3 * C * (GT + 1) * sizeof(float);
+  size_t smem = ((size_t)4 * C + 16) * (GT + 1) * sizeof(float);
   auto kern = gla_fwd_intra_kernel<T>;
   if (int e = set_smem(kern, smem)) return e;
   kern<<<dim3(a->NT, a->H), 256, smem, stream>>>(*a);
@@ -392,7 +487,7 @@ template <typename T> static int launch_gla_bwd_dav(const flab_args *a, cudaStre
 template <typename T> static int launch_gla_bwd_dqkg(const flab_args *a, cudaStream_t stream) {
   const int VP = round_up(a->V, 16), LDV = VP + Num<T>::pad;
   size_t p1 = ((size_t)2 * C * LDV + (size_t)2 * GT * LDV) * sizeof(T);
-  size_t p2 = (size_t)4 * C * (GT + 1) * sizeof(float);
+  size_t p2 = ((size_t)4 * C + 16) * (GT + 1) * sizeof(float);
   size_t smem = ((size_t)2 * C * (GT + 1) + GT) * sizeof(float) + (p1 > p2 ? p1 : p2);
   auto kern = gla_bwd_dqkg_kernel<T>;
   if (int e = set_smem(kern, smem)) return e;
