@@ -67,11 +67,11 @@ __global__ void __launch_bounds__(256) gla_fwd_intra_kernel(const flab_args a) {
       const int jend = direct ? r0 : rend;  // rows of k that get re-based
       for (int e = tid; e < jend * GT; e += 256) {
         const int r = e / GT, c = e - r * GT;
-        sKs[r * LD + c] = sK[r * LD + c] * expf(sB[r0 * LD + c] - sB[r * LD + c]);
+        sKs[r * LD + c] = sK[r * LD + c] * fexp<T>(sB[r0 * LD + c] - sB[r * LD + c]);
       }
       for (int e = tid; e < 16 * GT; e += 256) {
         const int r = e / GT, c = e - r * GT;
-        sQs[r * LD + c] = (r0 + r < rows) ? sQ[(r0 + r) * LD + c] * expf(sB[(r0 + r) * LD + c] - sB[r0 * LD + c]) : 0.f;
+        sQs[r * LD + c] = (r0 + r < rows) ? sQ[(r0 + r) * LD + c] * fexp<T>(sB[(r0 + r) * LD + c] - sB[r0 * LD + c]) : 0.f;
       }
       __syncthreads();
       const int i = r0 + il;
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) gla_fwd_intra_kernel(const flab_args a) {
 #pragma unroll 8
             for (int c = 0; c < GT; ++c) x = fmaf(qs[c], kk[c], x);
           } else {
-            for (int c = 0; c < kw; ++c) x = fmaf(sQ[i * LD + c] * sK[j * LD + c], expf(sB[i * LD + c] - sB[j * LD + c]), x);
+            for (int c = 0; c < kw; ++c) x = fmaf(sQ[i * LD + c] * sK[j * LD + c], fexp<T>(sB[i * LD + c] - sB[j * LD + c]), x);
           }
           acc[I][m] += x;
         }
@@ -356,12 +356,12 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
       const int jend = direct ? r0 : rend;
       for (int e = tid; e < jend * GT; e += 256) {
         const int r = e / GT, c = e - r * GT;
-        sKF[r * LD + c] = sK[r * LD + c] * expf(sB[r0 * LD + c] - sB[r * LD + c]);
+        sKF[r * LD + c] = sK[r * LD + c] * fexp<T>(sB[r0 * LD + c] - sB[r * LD + c]);
       }
 #pragma unroll
       for (int pp = 0; pp < 4; ++pp) {
         const int e = tid + 256 * pp, r = e / GT, c = e - r * GT;  // row r of the block
-        sQs[r * LD + c] = qreg[4 * I + pp] * expf(sB[(r0 + r) * LD + c] - sB[r0 * LD + c]);
+        sQs[r * LD + c] = qreg[4 * I + pp] * fexp<T>(sB[(r0 + r) * LD + c] - sB[r0 * LD + c]);
       }
       __syncthreads();
       {  // dq of the block's rows: thread = (row il, channels cg + 16 m)
@@ -378,9 +378,9 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
           for (int m = 0; m < 4; ++m) {
             const int c = cg + 16 * m;
             const float bi = sB[i * LD + c];
-            float val = t[m] * expf(bi - sB[r0 * LD + c]);
+            float val = t[m] * fexp<T>(bi - sB[r0 * LD + c]);
             if (direct)
-              for (int j = r0; j <= i; ++j) val = fmaf(sDA[i * LD + j] * sK[j * LD + c], expf(bi - sB[j * LD + c]), val);
+              for (int j = r0; j <= i; ++j) val = fmaf(sDA[i * LD + j] * sK[j * LD + c], fexp<T>(bi - sB[j * LD + c]), val);
             sDQ[i * LD + c] += val;
           }
         }
@@ -400,7 +400,7 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
 #pragma unroll
           for (int m = 0; m < GT / 4; ++m) {
             const int c = sl + 4 * m;
-            sDK[j * LD + c] += T_[m] * expf(sB[r0 * LD + c] - sB[j * LD + c]);
+            sDK[j * LD + c] += T_[m] * fexp<T>(sB[r0 * LD + c] - sB[j * LD + c]);
           }
         } else if (direct && j < rend) {
           for (int m = 0; m < GT / 4; ++m) {
@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
             if (c >= kw) continue;
             float x = 0.f;
             for (int i2 = j; i2 < rend; ++i2)
-              x = fmaf(sDA[i2 * LD + j] * Num<T>::f(q[(size_t)i2 * ks + c]), expf(sB[i2 * LD + c] - sB[j * LD + c]), x);
+              x = fmaf(sDA[i2 * LD + j] * Num<T>::f(q[(size_t)i2 * ks + c]), fexp<T>(sB[i2 * LD + c] - sB[j * LD + c]), x);
             sDK[j * LD + c] += x;
           }
         }
