@@ -5,9 +5,10 @@
 //   dg_i = <q_i, dq_i> - <k_i, dk_i> + <w_i, dw_i>;  dg_last += e^{b_L} <h, dh> + <k, dk_inter>
 //   (fla/ops/common/chunk_o.py:444-600)
 // Persistent kernel, one CTA per SM, work item = (chunk, head).  Eighteen warps:
-//   warp 16 : TMA producer - X = {do, v, dv, h, dh} (112 KB, one buffer) and Y = {q, k, w} (48 KB, two buffers):
-//             X of the next item streams in while the current item works on Y; the outputs leave from the Y
-//             buffer of the previous item while the next one fills
+//   warp 16 : TMA producer - X1 = {do, v, dv} (48 KB, two buffers), X2 = {h, dh} (64 KB, one buffer) and
+//             Y = {q, k, w} (48 KB, one buffer).  The item starts on X1 (ds, row factors), so X1 of the next item
+//             is fetched a whole item ahead; X2 is refilled as soon as the products against the states are done,
+//             Y as soon as the outputs (built over q, k, w) have been read by the tile store
 //   warp 17 : MMA issuer   - ds = do v^T; then the three products against the states; then the two
 //             intra-chunk products, accumulated onto dq and dk in TMEM
 //   warps 0-15 : epilogue, warp = (TMEM lane quadrant = 16 tokens, 32-column group)
@@ -38,19 +39,20 @@ template <bool USE_DW>
 __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant__ TcDqMaps m, const TcDqParams p) {
   using namespace tc;
   constexpr uint32_t T16 = 16384, T32 = 32768;
-  constexpr uint32_t X_BYTES = (USE_DW ? 3 : 2) * T16 + 2 * T32, Y_BYTES = (USE_DW ? 3 : 2) * T16;
+  constexpr uint32_t X1_BYTES = (USE_DW ? 3 : 2) * T16, X2_BYTES = 2 * T32, Y_BYTES = (USE_DW ? 3 : 2) * T16;
   constexpr uint32_t TM_DS = 0, TM_DQ = 64, TM_DK = 192, TM_DW = 320;
   constexpr int ET = 512;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char *sDo = base, *sV = sDo + T16, *sH = sV + T16, *sDH = sH + T32, *sDv = sDH + T32;  // X
-  unsigned char *sY = sDv + (USE_DW ? T16 : 0);  // [2][q | k | w]
-  unsigned char *sDS = sY + 2 * Y_BYTES;         // [64][128 B]
+  unsigned char *sX1 = base;                       // [2][do | v | dv]
+  unsigned char *sH = sX1 + 2 * X1_BYTES, *sDH = sH + T32;  // X2
+  unsigned char *sY = sDH + T32;                   // [q | k | w]
+  unsigned char *sDS = sY + Y_BYTES;               // [64][128 B]
   float *sG = reinterpret_cast<float *>(sDS + 8192);  // [2][64] gates
   float *sDG = sG + 2 * C;                            // [2][64] dg rows
   float *sRed = sDG + 2 * C;                          // [2][2]  <h, dh>, <k, dk_inter>
-  __shared__ uint64_t fullX, emptyX, fullY[2], emptyY[2], ds_done, e1_done, dk_done, e1b_done, all_done, acc_free, out_ready;
+  __shared__ uint64_t fullX1[2], emptyX1[2], fullX2, emptyX2, fullY, emptyY, ds_done, e1_done, dk_done, e1b_done, all_done, acc_free, out_ready;
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
   __shared__ volatile int abort_snap[2];
@@ -58,12 +60,14 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
   const flab_args &a = p.a;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    mbar_init(&fullX, 1);
-    mbar_init(&emptyX, 17);  // the products against the states have completed + every epilogue warp is done with h, dh
     for (int j = 0; j < 2; ++j) {
-      mbar_init(&fullY[j], 1);
-      mbar_init(&emptyY[j], 1);
+      mbar_init(&fullX1[j], 1);
+      mbar_init(&emptyX1[j], 1);
     }
+    mbar_init(&fullX2, 1);
+    mbar_init(&emptyX2, 17);  // the products against the states have completed + every epilogue warp is done with h, dh
+    mbar_init(&fullY, 1);
+    mbar_init(&emptyY, 1);
     mbar_init(&ds_done, 1);
     mbar_init(&e1_done, 16);
     mbar_init(&dk_done, 1);
@@ -105,25 +109,31 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
         const int t0 = s.bos + it * C;
         const int c1 = a.head_first ? t0 : hd, c2 = a.head_first ? hd : t0;
         const int srow = ((s.c0 + it) * a.H + hd) * 128;
-        if (!mbar_wait(&emptyX, ph ^ 1)) { fail(61); break; }
-        mbar_expect_tx(&fullX, X_BYTES);
+        const int xb = i & 1, xph = (i >> 1) & 1;
+        unsigned char *sDo = sX1 + xb * X1_BYTES, *sV = sDo + T16, *sDv = sV + T16;
+        if (!mbar_wait(&emptyX1[xb], xph ^ 1)) { fail(61); break; }
+        mbar_expect_tx(&fullX1[xb], X1_BYTES);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          tma_load_4d(sDo + j * 8192, &m.d_o, &fullX, 64 * j, c1, c2, s.b);
-          tma_load_4d(sV + j * 8192, &m.v, &fullX, 64 * j, c1, c2, s.b);
-          if (USE_DW) tma_load_4d(sDv + j * 8192, &m.dv, &fullX, 64 * j, c1, c2, s.b);
-          tma_load_2d(sH + j * T16, &m.h, &fullX, 64 * j, srow);
-          tma_load_2d(sDH + j * T16, &m.dh, &fullX, 64 * j, srow);
+          tma_load_4d(sDo + j * 8192, &m.d_o, &fullX1[xb], 64 * j, c1, c2, s.b);
+          tma_load_4d(sV + j * 8192, &m.v, &fullX1[xb], 64 * j, c1, c2, s.b);
+          if (USE_DW) tma_load_4d(sDv + j * 8192, &m.dv, &fullX1[xb], 64 * j, c1, c2, s.b);
         }
-        const int yb = i & 1, yph = (i >> 1) & 1;
-        unsigned char *sQ = sY + yb * Y_BYTES, *sK = sQ + T16, *sW = sK + T16;
-        if (!mbar_wait(&emptyY[yb], yph ^ 1)) { fail(62); break; }
-        mbar_expect_tx(&fullY[yb], Y_BYTES);
+        if (!mbar_wait(&emptyX2, ph ^ 1)) { fail(74); break; }
+        mbar_expect_tx(&fullX2, X2_BYTES);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          tma_load_4d(sQ + j * 8192, &m.q, &fullY[yb], 64 * j, c1, c2, s.b);
-          tma_load_4d(sK + j * 8192, &m.k, &fullY[yb], 64 * j, c1, c2, s.b);
-          if (USE_DW) tma_load_4d(sW + j * 8192, &m.w, &fullY[yb], 64 * j, c1, c2, s.b);
+          tma_load_2d(sH + j * T16, &m.h, &fullX2, 64 * j, srow);
+          tma_load_2d(sDH + j * T16, &m.dh, &fullX2, 64 * j, srow);
+        }
+        unsigned char *sQ = sY, *sK = sQ + T16, *sW = sK + T16;
+        if (!mbar_wait(&emptyY, ph ^ 1)) { fail(62); break; }
+        mbar_expect_tx(&fullY, Y_BYTES);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          tma_load_4d(sQ + j * 8192, &m.q, &fullY, 64 * j, c1, c2, s.b);
+          tma_load_4d(sK + j * 8192, &m.k, &fullY, 64 * j, c1, c2, s.b);
+          if (USE_DW) tma_load_4d(sW + j * 8192, &m.w, &fullY, 64 * j, c1, c2, s.b);
         }
       }
     }
@@ -134,8 +144,6 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       const uint32_t id_st = instr_desc(64, 128, p.ab_fmt, 0, 0);   // x state^T   : A, B K-major
       const uint32_t id_dq = instr_desc(64, 128, p.ab_fmt, 0, 1);   // ds k        : A K-major, B MN-major
       const uint32_t id_dk = instr_desc(64, 128, p.ab_fmt, 1, 1);   // ds^T q      : A, B MN-major
-      const uint64_t d_do = desc_kmajor(smem_u32(sDo), 0, 8192), d_v = desc_kmajor(smem_u32(sV), 0, 8192);
-      const uint64_t d_dv = desc_kmajor(smem_u32(sDv), 0, 8192);
       const uint64_t d_h = desc_kmajor(smem_u32(sH), 0, T16), d_dh = desc_kmajor(smem_u32(sDH), 0, T16);
       const uint64_t d_dsk = desc_kmajor(smem_u32(sDS), 0, 8192), d_dsm = desc_mnmajor(smem_u32(sDS), 0, 8192);
       // per-step advance of the start-address field (16-byte units)
@@ -143,13 +151,17 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       auto mx = [](int k) -> uint64_t { return (uint64_t)((k * 2048) >> 4); };
       for (int i = 0; i < n_local && !abort_flag; ++i) {
         const int ph = i & 1;
-        if (!mbar_wait(&fullX, ph)) { fail(63); break; }
+        const int xb = i & 1, xph = (i >> 1) & 1;
+        const uint32_t x1 = smem_u32(sX1 + xb * X1_BYTES);
+        const uint64_t d_do = desc_kmajor(x1, 0, 8192), d_v = desc_kmajor(x1 + T16, 0, 8192), d_dv = desc_kmajor(x1 + 2 * T16, 0, 8192);
+        if (!mbar_wait(&fullX1[xb], xph)) { fail(63); break; }
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma(tmem + TM_DS, d_do + kx(k, 8192), d_v + kx(k, 8192), id_ds, k > 0);
         umma_commit(&ds_done);
         if (!mbar_wait(&e1_done, ph)) { fail(64); break; }
         if (i > 0 && !mbar_wait(&acc_free, ph ^ 1)) { fail(65); break; }
+        if (!mbar_wait(&fullX2, ph)) { fail(75); break; }
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma(tmem + TM_DK, d_v + kx(k, 8192), d_dh + kx(k, T16), id_st, k > 0);
@@ -160,10 +172,10 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma(tmem + TM_DW, d_dv + kx(k, 8192), d_h + kx(k, T16), id_st, k > 0);
         }
-        umma_commit(&emptyX);
-        const int yb = i & 1, yph = (i >> 1) & 1;
-        const uint64_t d_q = desc_mnmajor(smem_u32(sY + yb * Y_BYTES), 0, 8192), d_k = desc_mnmajor(smem_u32(sY + yb * Y_BYTES + T16), 0, 8192);
-        if (!mbar_wait(&fullY[yb], yph)) { fail(66); break; }
+        umma_commit(&emptyX1[xb]);
+        umma_commit(&emptyX2);
+        const uint64_t d_q = desc_mnmajor(smem_u32(sY), 0, 8192), d_k = desc_mnmajor(smem_u32(sY + T16), 0, 8192);
+        if (!mbar_wait(&fullY, ph)) { fail(66); break; }
         if (use_g && !mbar_wait(&e1b_done, ph)) { fail(67); break; }
         fence_after_sync();
 #pragma unroll
@@ -177,13 +189,12 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
     // ------------------------------------------------------------------ output warp
     if (lane == 0) {
       for (int i = 0; i < n_local && !abort_flag; ++i) {
-        const int yb = i & 1;
         int c, hd, n, it;
         decode(i, c, hd);
         chunk_of(a, c, n, it);
         const Seq s = seq_of(a, n);
         const int t0 = it * C, rows = min(C, s.len - t0);
-        unsigned char *sQ = sY + yb * Y_BYTES, *sK = sQ + T16, *sW = sK + T16;
+        unsigned char *sQ = sY, *sK = sQ + T16, *sW = sK + T16;
         if (!mbar_wait(&out_ready, i & 1)) { fail(73); break; }
         if (rows == C) {  // (a ragged chunk was written out by the epilogue warps themselves)
           const int tt = s.bos + t0, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
@@ -196,7 +207,7 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
           tma_store_commit();
           tma_store_wait_read();
         }
-        mbar_arrive(&emptyY[yb]);
+        mbar_arrive(&emptyY);
       }
       tma_store_wait_all();
     }
@@ -243,8 +254,9 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       const Seq s = seq_of(a, n);
       const int t0 = it * C, rows = min(C, s.len - t0), last = rows - 1;
       float *gs = sG + ph * C, *dgs = sDG + ph * C, *red = sRed + ph * 2;
-      const int yb = i & 1, yph = (i >> 1) & 1;
-      unsigned char *sQ = sY + yb * Y_BYTES, *sK = sQ + T16, *sW = sK + T16;
+      const int xb = i & 1, xph = (i >> 1) & 1;
+      unsigned char *sDo = sX1 + xb * X1_BYTES, *sV = sDo + T16, *sDv = sV + T16;
+      unsigned char *sQ = sY, *sK = sQ + T16, *sW = sK + T16;
       if (tid < C) {
         gs[tid] = g_pf;
         dgs[tid] = 0.f;
@@ -258,7 +270,7 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       const float e_lo = use_g ? __expf(g_lo) : 1.f, e_hi = use_g ? __expf(g_hi) : 1.f;
       const float f_lo = use_g ? __expf(fminf(gl - g_lo, 0.f)) : 1.f, f_hi = use_g ? __expf(fminf(gl - g_hi, 0.f)) : 1.f;
       // ---- E1: <h, dh>; ds -> masked / decayed operand; row factors onto do, v, dv
-      if (!mbar_wait(&fullX, ph)) fail(68);
+      if (!mbar_wait(&fullX1[xb], xph)) fail(68);
       if (!mbar_wait(&ds_done, ph)) fail(69);
       fence_after_sync();
       if (cq < 2) {
@@ -314,8 +326,9 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
         *pend_ptr = pend_val;
         pend_ptr = nullptr;
       }
-      // <h, dh> while the tensor core works; then this warp is done with the X tiles
+      // <h, dh> while the tensor core works; then this warp is done with the state tiles
       if (use_g) {
+        if (!mbar_wait(&fullX2, ph)) fail(76);
         float hd_ = 0.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -332,9 +345,9 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
         if (lane == 0) atomicAdd(&red[0], hd_);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&emptyX);
+      if (lane == 0) mbar_arrive(&emptyX2);
       // ---- E1b: <k, dk_inter> from the inter-chunk dk before the intra-chunk product lands on it
-      if (!mbar_wait(&fullY[yb], yph)) fail(70);
+      if (!mbar_wait(&fullY, ph)) fail(70);
       if (use_g) {
         if (!mbar_wait(&dk_done, ph)) fail(71);
         fence_after_sync();
