@@ -303,6 +303,51 @@ template <int MI, int NI, bool A_T, bool B_KN> struct WarpGemm<MI, NI, A_T, B_KN
   }
 };
 
+// Tile product on fp32 shared-memory operands through the TF32 tensor-core path (m16n8k8): operands are expected
+// to be rounded to TF32 already (to_tf32 when the tile is written), accumulation is fp32. Used where the operands of
+// a 16-bit op have to carry more than 8 mantissa bits (differences of nearly cancelling sums downstream).
+// Same conventions as WarpGemm: A_T / B_KN select the storage order, acc is the m16n8 fragment.
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+template <int MI, int NI, bool A_T, bool B_KN>
+__device__ __forceinline__ void warp_gemm_tf32(float (&acc)[MI][NI][4], const float *A, int lda, int m0, const float *B, int ldb,
+                                               int n0, int kdim) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  for (int k0 = 0; k0 < kdim; k0 += 8) {
+    uint32_t af[MI][4];
+#pragma unroll
+    for (int mi = 0; mi < MI; ++mi) {
+      const int m = m0 + 16 * mi + g, k = k0 + t4;
+      af[mi][0] = __float_as_uint(A_T ? A[k * lda + m] : A[m * lda + k]);
+      af[mi][1] = __float_as_uint(A_T ? A[k * lda + m + 8] : A[(m + 8) * lda + k]);
+      af[mi][2] = __float_as_uint(A_T ? A[(k + 4) * lda + m] : A[m * lda + k + 4]);
+      af[mi][3] = __float_as_uint(A_T ? A[(k + 4) * lda + m + 8] : A[(m + 8) * lda + k + 4]);
+    }
+#pragma unroll
+    for (int ni = 0; ni < NI; ++ni) {
+      const int n = n0 + 8 * ni + g, k = k0 + t4;
+      const uint32_t b0 = __float_as_uint(B_KN ? B[k * ldb + n] : B[n * ldb + k]);
+      const uint32_t b1 = __float_as_uint(B_KN ? B[(k + 4) * ldb + n] : B[n * ldb + k + 4]);
+#pragma unroll
+      for (int mi = 0; mi < MI; ++mi)
+        asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(acc[mi][ni][0]), "+f"(acc[mi][ni][1]), "+f"(acc[mi][ni][2]), "+f"(acc[mi][ni][3])
+                     : "r"(af[mi][0]), "r"(af[mi][1]), "r"(af[mi][2]), "r"(af[mi][3]), "r"(b0), "r"(b1));
+    }
+  }
+}
+// fp32 operand tiles: true fp32 FMAs when the op's element type is fp32, the TF32 path for 16-bit element types
+template <int MI, int NI, bool A_T, bool B_KN, typename T>
+__device__ __forceinline__ void gemm_f32tile(float (&acc)[MI][NI][4], const float *A, int lda, int m0, const float *B, int ldb, int n0,
+                                             int kdim) {
+  if constexpr (sizeof(T) == 4) WarpGemm<MI, NI, A_T, B_KN, float>::run(acc, A, lda, m0, B, ldb, n0, kdim);
+  else warp_gemm_tf32<MI, NI, A_T, B_KN>(acc, A, lda, m0, B, ldb, n0, kdim);
+}
+template <typename T> __device__ __forceinline__ float tile_round(float x) { return sizeof(T) == 4 ? x : to_tf32(x); }
+
 // fp32 tile product with the contraction length known at compile time (fully unrolled, so the
 // shared-memory operand loads of later steps overlap the FMAs of earlier ones)
 template <int MI, int NI, int KD, bool A_T, bool B_KN>

@@ -248,20 +248,26 @@ __global__ void __launch_bounds__(128) gla_bwd_dav_kernel(const flab_args a) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// dq, dk, dg.  grid (NT, H, K/64); 256 threads.  Phase 1: inter-chunk products on the tile GEMM
-// (do h^T, v dh^T), results parked in fp32 shared memory.  Phase 2: intra-chunk terms, block of 16 rows by
-// block of 16 rows, with the gate factors hoisted out of the (i, j) pair loops.
+// dq, dk, dg.  grid (NT, H, K/64); 256 threads = 8 warps, warp (rb, ch) owns rows 16 rb .. and channels 32 ch .. of
+// the chunk's [64][64] dq and dk tiles in mma fragments, from the first product to the last.
+// Phase 1: inter-chunk products (do h^T, v dh^T).  Phase 2: intra-chunk terms as tile products on fp32 operand
+// tiles (TF32 tensor-core path for 16-bit element types, plain FMAs for fp32), with the per-channel gates split
+// per block of 16 rows: e^{b_i - b_j} = e^{b_i - b_r} e^{b_r - b_j}, r the block's first row.
+//   dq_i  = e^{b_i - b_r} sum_j dA_ij (k_j e^{b_r - b_j})          one product per row block I against KF_I
+//   dk_j  = sum_I e^{b_rI - b_j} sum_{i in I} dA_ij (q_i e^{b_i - b_rI})
+// For j before the block the exponent b_r - b_j is <= 0; inside the block it is bounded by the decay over 16
+// tokens, and a block where that exceeds e^60 in some channel evaluates its in-block pairs directly.
 // ------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int VP = round_up(a.V, 16);
   const int LDV = VP + Num<T>::pad;
-  constexpr int LD = GT + 1;
-  float *sDQ = reinterpret_cast<float *>(smem_raw);  // [64][LD] inter dq -> total dq
-  float *sDK = sDQ + C * LD;                         // [64][LD]
-  float *sGK = sDK + C * LD;                         // [64] per-channel chunk term of dg
-  unsigned char *region = reinterpret_cast<unsigned char *>(sGK + GT);
+  constexpr int LD = GT + 1;   // column-walk tiles
+  constexpr int LDF = GT + 4;  // mma operand tiles (fragment loads conflict-free)
+  float *sGK = reinterpret_cast<float *>(smem_raw);  // [64] per-channel chunk term of dg
+  int *sDirect = reinterpret_cast<int *>(sGK + GT);  // [4] row block evaluates its in-block pairs directly
+  unsigned char *region = reinterpret_cast<unsigned char *>(sDirect + 4);
   // phase 1 view
   T *sDO = reinterpret_cast<T *>(region);  // [64][LDV]
   T *sVV = sDO + C * LDV;                  // [64][LDV]
@@ -269,12 +275,14 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
   T *sDH = sH + GT * LDV;                  // [64 channels][LDV]
   // phase 2 view
   float *sK = reinterpret_cast<float *>(region);  // [64][LD]
-  float *sB = sK + C * LD;
-  float *sDA = sB + C * LD;   // [64][LD]
-  float *sKF = sDA + C * LD;  // [64][LD] k re-based to the reference row of the current row block
-  float *sQs = sKF + C * LD;  // [16][LD] q of the current row block, re-based likewise
+  float *sB = sK + C * LD;                        // [64][LD]
+  float *tDA = sB + C * LD;                       // [64][LDF] tril(dA)
+  float *tQs = tDA + C * LDF;                     // [64][LDF] q re-based to the first row of its row block
+  float *tKF = tQs + C * LDF;                     // [16+32+48+64][LDF] k re-based to the first row of block I, stacked
+  float *sOQ = tKF;                               // [64][LD] total dq (after the products)
+  float *sOK = sOQ + C * LD;                      // [64][LD] total dk
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5;
   int n, it;
   chunk_of(a, blockIdx.x, n, it);
   const int hd = blockIdx.y, k0 = blockIdx.z * GT;
@@ -283,6 +291,8 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
   const size_t ks = tok_stride(a, a.K), vs = tok_stride(a, a.V), as_ = tok_stride(a, C);
   const size_t offk = tok_off(a, s, hd, t0, a.K) + k0, offv = tok_off(a, s, hd, t0, a.V);
   const float *b = reinterpret_cast<const float *>(a.gk) + offk;
+  const int rb = warp & 3, ch = warp >> 2, m0 = rb * 16, n0 = ch * 32;
+  float dq[1][4][4], dk[1][4][4];
 
   // ---- phase 1
   {
@@ -292,32 +302,22 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
     tile_load<T>(sH, LDV, reinterpret_cast<const T *>(a.h) + hoff, (size_t)a.V, kw, GT, a.V, VP, tid, 256);
     tile_load<T>(sDH, LDV, reinterpret_cast<const T *>(a.dh) + hoff, (size_t)a.V, kw, GT, a.V, VP, tid, 256);
     cp_async_commit();
+    if (tid < 4) sDirect[tid] = 0;
     cp_async_wait<0>();
     __syncthreads();
-    const int rb = warp & 3, ch = warp >> 2, m0 = rb * 16, n0 = ch * 32;
-    float dq[1][4][4], dk[1][4][4];
     acc_zero(dq);
     acc_zero(dk);
     WarpGemm<1, 4, false, false, T>::run(dq, sDO, LDV, m0, sH, LDV, n0, VP);
     WarpGemm<1, 4, false, false, T>::run(dk, sVV, LDV, m0, sDH, LDV, n0, VP);
-    FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
-      float e1 = 0.f, e2 = 0.f;
-      if (row < rows && col < kw) {
-        float bi = b[(size_t)row * ks + col];
-        e1 = expf(bi) * a.scale;
-        e2 = expf(b[(size_t)last * ks + col] - bi);
-      }
-      sDQ[row * LD + col] = dq[mi][ni][r] * e1;
-      sDK[row * LD + col] = dk[mi][ni][r] * e2;
-    }
-    // per-channel sum_v h * dh
-    if (tid < GT) {
+    // per-channel sum_v h * dh: four threads per channel
+    {
+      const int c = tid >> 2, sl = tid & 3;
       float x = 0.f;
-      if (tid < kw) {
-        for (int c = 0; c < a.V; ++c) x = fmaf(Num<T>::f(sH[tid * LDV + c]), Num<T>::f(sDH[tid * LDV + c]), x);
-        x *= expf(b[(size_t)last * ks + tid]);
-      }
-      sGK[tid] = x;
+      if (c < kw)
+        for (int v = sl; v < a.V; v += 4) x = fmaf(Num<T>::f(sH[c * LDV + v]), Num<T>::f(sDH[c * LDV + v]), x);
+      x += __shfl_xor_sync(0xffffffffu, x, 1);
+      x += __shfl_xor_sync(0xffffffffu, x, 2);
+      if (sl == 0) sGK[c] = c < kw ? x * expf(b[(size_t)last * ks + c]) : 0.f;
     }
   }
   __syncthreads();
@@ -333,111 +333,122 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
       qreg[p] = ok ? Num<T>::f(q[(size_t)r * ks + c]) : 0.f;
       sK[r * LD + c] = ok ? Num<T>::f(k[(size_t)r * ks + c]) : 0.f;
       sB[r * LD + c] = ok ? b[(size_t)r * ks + c] : 0.f;
-      sDA[r * LD + c] = (r < rows && c <= r) ? dA[(size_t)r * as_ + c] : 0.f;  // c indexes the 64 columns of dA here
+      tDA[r * LDF + c] = (r < rows && c <= r) ? tile_round<T>(dA[(size_t)r * as_ + c]) : 0.f;  // c = column of dA here
     }
     __syncthreads();
-    // sum_j dk_inter * k per channel (before the intra terms are added)
     if (tid < GT) {
-      float x = 0.f;
-      for (int j = 0; j < rows; ++j) x = fmaf(sDK[j * LD + tid], sK[j * LD + tid], x);
-      sGK[tid] += x;
+#pragma unroll
+      for (int I = 0; I < 4; ++I) {
+        const int r0 = 16 * I, rend = min(r0 + 16, rows);
+        if (r0 < rows && sB[r0 * LD + tid] - sB[(rend - 1) * LD + tid] > 60.f) sDirect[I] = 1;
+      }
     }
-    // Intra-chunk terms, one block of 16 rows i at a time (first row r): e^{b_i - b_j} = e^{b_i - b_r} e^{b_r - b_j},
-    // each factor applied once per element, the (i, j) pairs are plain FMAs.  For j before the block the second
-    // exponent is <= 0; inside the block it is bounded by the decay over 16 tokens, and when that exceeds e^60 in
-    // some channel the in-block pairs are evaluated directly instead.
-#pragma unroll
-    for (int I = 0; I < 4; ++I) {
-      const int r0 = 16 * I, rend = min(r0 + 16, rows);
-      if (r0 >= rows) break;  // uniform
-      float span = 0.f;
-      if (tid < GT) span = sB[r0 * LD + tid] - sB[(rend - 1) * LD + tid];
-      const bool direct = __syncthreads_or(span > 60.f);
-      const int jend = direct ? r0 : rend;
-      for (int e = tid; e < jend * GT; e += 256) {
-        const int r = e / GT, c = e - r * GT;
-        sKF[r * LD + c] = sK[r * LD + c] * fexp<T>(sB[r0 * LD + c] - sB[r * LD + c]);
+    {  // gates of the inter-chunk terms; sum_j dk_inter k per channel (before the intra terms are added)
+      float part[4][2];
+      FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
+        const float bi = sB[row * LD + col];
+        const bool ok = row < rows && col < kw;
+        dq[mi][ni][r] *= ok ? expf(bi) * a.scale : 0.f;
+        dk[mi][ni][r] *= ok ? expf(sB[last * LD + col] - bi) : 0.f;
+        const float x = dk[mi][ni][r] * sK[row * LD + col];
+        if (r < 2) part[ni][r] = x;
+        else part[ni][r - 2] += x;
       }
+      const int lane = tid & 31;
 #pragma unroll
-      for (int pp = 0; pp < 4; ++pp) {
-        const int e = tid + 256 * pp, r = e / GT, c = e - r * GT;  // row r of the block
-        sQs[r * LD + c] = qreg[4 * I + pp] * fexp<T>(sB[(r0 + r) * LD + c] - sB[r0 * LD + c]);
-      }
-      __syncthreads();
-      {  // dq of the block's rows: thread = (row il, channels cg + 16 m)
-        const int il = tid >> 4, cg = tid & 15, i = r0 + il;
-        if (i < rows) {
-          float t[4] = {0.f, 0.f, 0.f, 0.f};
-          const int jn = min(jend, i + 1);
-          for (int j = 0; j < jn; ++j) {
-            const float d = sDA[i * LD + j];
+      for (int ni = 0; ni < 4; ++ni)
 #pragma unroll
-            for (int m = 0; m < 4; ++m) t[m] = fmaf(d, sKF[j * LD + cg + 16 * m], t[m]);
-          }
-#pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            const int c = cg + 16 * m;
-            const float bi = sB[i * LD + c];
-            float val = t[m] * fexp<T>(bi - sB[r0 * LD + c]);
-            if (direct)
-              for (int j = r0; j <= i; ++j) val = fmaf(sDA[i * LD + j] * sK[j * LD + c], fexp<T>(bi - sB[j * LD + c]), val);
-            sDQ[i * LD + c] += val;
-          }
+        for (int h2 = 0; h2 < 2; ++h2) {
+          float x = part[ni][h2];
+          x += __shfl_xor_sync(0xffffffffu, x, 4);
+          x += __shfl_xor_sync(0xffffffffu, x, 8);
+          x += __shfl_xor_sync(0xffffffffu, x, 16);
+          if (lane < 4) atomicAdd(&sGK[n0 + 8 * ni + 2 * lane + h2], x);
         }
-      }
-      {  // dk contributions of the block to every row j it reaches: thread = (row j, channels sl + 4 m)
-        const int j = tid >> 2, sl = tid & 3;
-        if (j < jend) {
-          float T_[GT / 4];
-#pragma unroll
-          for (int m = 0; m < GT / 4; ++m) T_[m] = 0.f;
-          for (int i2 = max(j, r0); i2 < rend; ++i2) {
-            const float d = sDA[i2 * LD + j];
-            const float *qs = sQs + (i2 - r0) * LD + sl;
-#pragma unroll
-            for (int m = 0; m < GT / 4; ++m) T_[m] = fmaf(d, qs[4 * m], T_[m]);
-          }
-#pragma unroll
-          for (int m = 0; m < GT / 4; ++m) {
-            const int c = sl + 4 * m;
-            sDK[j * LD + c] += T_[m] * fexp<T>(sB[r0 * LD + c] - sB[j * LD + c]);
-          }
-        } else if (direct && j < rend) {
-          for (int m = 0; m < GT / 4; ++m) {
-            const int c = sl + 4 * m;
-            if (c >= kw) continue;
-            float x = 0.f;
-            for (int i2 = j; i2 < rend; ++i2)
-              x = fmaf(sDA[i2 * LD + j] * Num<T>::f(q[(size_t)i2 * ks + c]), fexp<T>(sB[i2 * LD + c] - sB[j * LD + c]), x);
-            sDK[j * LD + c] += x;
-          }
-        }
-      }
-      __syncthreads();
     }
-    // outputs; dg = reverse in-chunk cumsum of (q dq - k dk) + per-channel chunk term
-    T *dq = reinterpret_cast<T *>(a.dq) + offk, *dk = reinterpret_cast<T *>(a.dk) + offk;
+    __syncthreads();
+    // operand tiles
 #pragma unroll
     for (int p = 0; p < C * GT / 256; ++p) {
       const int e = tid + 256 * p, r = e / GT, c = e - r * GT;
-      const float dqv = sDQ[r * LD + c], dkv = sDK[r * LD + c];
-      if (r < rows && c < kw) {
-        dq[(size_t)r * ks + c] = Num<T>::t(dqv);
-        dk[(size_t)r * ks + c] = Num<T>::t(dkv);
+      tQs[r * LDF + c] = tile_round<T>(qreg[p] * fexp<T>(sB[r * LD + c] - sB[(r & ~15) * LD + c]));
+    }
+#pragma unroll
+    for (int I = 0; I < 4; ++I) {
+      const int r0 = 16 * I;
+      if (r0 >= rows) break;  // uniform
+      const int jend = sDirect[I] ? r0 : min(r0 + 16, rows);
+      float *dst = tKF + 8 * I * (I + 1) * LDF;
+      for (int e = tid; e < (r0 + 16) * GT; e += 256) {
+        const int r = e / GT, c = e - r * GT;
+        dst[r * LDF + c] = r < jend ? tile_round<T>(sK[r * LD + c] * fexp<T>(sB[r0 * LD + c] - sB[r * LD + c])) : 0.f;
       }
-      sDQ[r * LD + c] = qreg[p] * dqv - sK[r * LD + c] * dkv;  // the integrand of dg
+    }
+    __syncthreads();
+    // dq of row block rb
+    if (m0 < rows) {
+      const bool direct = sDirect[rb] != 0;
+      float acc[1][4][4];
+      acc_zero(acc);
+      gemm_f32tile<1, 4, false, true, T>(acc, tDA, LDF, m0, tKF + 8 * rb * (rb + 1) * LDF, LDF, n0, m0 + 16);
+      FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
+        const float bi = sB[row * LD + col];
+        float val = acc[mi][ni][r] * fexp<T>(bi - sB[m0 * LD + col]);
+        if (direct && row < rows)
+          for (int j = m0; j <= row; ++j) val = fmaf(tDA[row * LDF + j] * sK[j * LD + col], fexp<T>(bi - sB[j * LD + col]), val);
+        dq[mi][ni][r] += val;
+      }
+    }
+    // dk of rows 16 rb ..: contributions of every row block I >= rb
+    for (int I = rb; I < 4; ++I) {
+      const int r0 = 16 * I, rend = min(r0 + 16, rows);
+      if (r0 >= rows) break;
+      if (I == rb && sDirect[I]) {
+        FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
+          if (row < rend && col < kw) {
+            float x = 0.f;
+            for (int i2 = row; i2 < rend; ++i2)
+              x = fmaf(tDA[i2 * LDF + row] * Num<T>::f(q[(size_t)i2 * ks + col]), fexp<T>(sB[i2 * LD + col] - sB[row * LD + col]), x);
+            dk[mi][ni][r] += x;
+          }
+        }
+        continue;
+      }
+      float acc[1][4][4];
+      acc_zero(acc);
+      gemm_f32tile<1, 4, true, true, T>(acc, tDA + r0 * LDF, LDF, m0, tQs + r0 * LDF, LDF, n0, 16);
+      FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
+        dk[mi][ni][r] = fmaf(acc[mi][ni][r], fexp<T>(sB[r0 * LD + col] - sB[row * LD + col]), dk[mi][ni][r]);
+      }
+    }
+    __syncthreads();
+    FLAB_ACC_FOREACH(1, 4, m0, n0, row, col, mi, ni, r) {
+      sOQ[row * LD + col] = dq[mi][ni][r];
+      sOK[row * LD + col] = dk[mi][ni][r];
+    }
+    __syncthreads();
+    // outputs; dg = reverse in-chunk cumsum of (q dq - k dk) + per-channel chunk term
+    T *dqo = reinterpret_cast<T *>(a.dq) + offk, *dko = reinterpret_cast<T *>(a.dk) + offk;
+#pragma unroll
+    for (int p = 0; p < C * GT / 256; ++p) {
+      const int e = tid + 256 * p, r = e / GT, c = e - r * GT;
+      const float dqv = sOQ[r * LD + c], dkv = sOK[r * LD + c];
+      if (r < rows && c < kw) {
+        dqo[(size_t)r * ks + c] = Num<T>::t(dqv);
+        dko[(size_t)r * ks + c] = Num<T>::t(dkv);
+      }
+      sOQ[r * LD + c] = qreg[p] * dqv - sK[r * LD + c] * dkv;  // the integrand of dg
     }
     __syncthreads();
     if (tid < kw) {
       float *dg = reinterpret_cast<float *>(a.dgk) + offk;
       float run = sGK[tid];
       for (int r = rows - 1; r >= 0; --r) {
-        run += sDQ[r * LD + tid];
+        run += sOQ[r * LD + tid];
         dg[(size_t)r * ks + tid] = run;
       }
     }
   }
-  (void)lane;
 }
 
 template <typename T, int BV> static size_t gla_o_smem(const flab_args *a, bool dav) {
@@ -487,8 +498,8 @@ template <typename T> static int launch_gla_bwd_dav(const flab_args *a, cudaStre
 template <typename T> static int launch_gla_bwd_dqkg(const flab_args *a, cudaStream_t stream) {
   const int VP = round_up(a->V, 16), LDV = VP + Num<T>::pad;
   size_t p1 = ((size_t)2 * C * LDV + (size_t)2 * GT * LDV) * sizeof(T);
-  size_t p2 = ((size_t)4 * C + 16) * (GT + 1) * sizeof(float);
-  size_t smem = ((size_t)2 * C * (GT + 1) + GT) * sizeof(float) + (p1 > p2 ? p1 : p2);
+  size_t p2 = ((size_t)2 * C * (GT + 1) + (size_t)(2 * C + 160) * (GT + 4)) * sizeof(float);
+  size_t smem = (GT + 4) * sizeof(float) + (p1 > p2 ? p1 : p2);
   auto kern = gla_bwd_dqkg_kernel<T>;
   if (int e = set_smem(kern, smem)) return e;
   kern<<<dim3(a->NT, a->H, cdiv(a->K, GT)), 256, smem, stream>>>(*a);
