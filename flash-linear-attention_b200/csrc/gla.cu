@@ -16,15 +16,22 @@ constexpr int GT = 64;  // key-channel tile of the intra / dqkg kernels
 
 // ------------------------------------------------------------------------------------------------
 // A = intra-chunk scores (fp32). grid (NT, H); 256 threads; K walked in tiles of 64 channels.
+// The triple (i, j, channel) only couples through e^{b_i - b_j}.  For a block of 16 rows with first row r,
+// e^{b_i - b_j} = e^{b_i - b_r} e^{b_r - b_j}: both factors are applied once per element, which leaves one tile
+// product per 16 x 16 block of A (TF32 tensor-core path for 16-bit element types, plain FMAs for fp32).  For j
+// before the block the second exponent is <= 0.  Inside the block it is positive but bounded by the decay over 16
+// tokens; when that exceeds e^60 in some channel (never with gates from a log-sigmoid) the diagonal block is
+// evaluated directly instead.
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) gla_fwd_intra_kernel(const flab_args a) {
-  constexpr int LD = GT + 1;
+__global__ void __launch_bounds__(256, 2) gla_fwd_intra_kernel(const flab_args a) {
+  constexpr int LD = GT + 1, LDF = GT + 4;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float *sQ = reinterpret_cast<float *>(smem_raw), *sK = sQ + C * LD, *sB = sK + C * LD;
-  float *sKs = sB + C * LD;   // [64][LD] k rows re-based to the reference row of the current row block
-  float *sQs = sKs + C * LD;  // [16][LD] q rows of the current row block, re-based likewise
-  const int tid = threadIdx.x;
+  float *sK = reinterpret_cast<float *>(smem_raw), *sB = sK + C * LD;
+  float *tQs = sB + C * LD;    // [64][LDF] q re-based to the first row of its row block
+  float *tKF = tQs + C * LDF;  // [16+32+48+64][LDF] k re-based to the first row of block I, stacked
+  __shared__ int sDirect[4];
+  const int tid = threadIdx.x, warp = tid >> 5;
   int n, it;
   chunk_of(a, blockIdx.x, n, it);
   const int hd = blockIdx.y;
@@ -33,80 +40,92 @@ __global__ void __launch_bounds__(256) gla_fwd_intra_kernel(const flab_args a) {
   const size_t ks = tok_stride(a, a.K), offk = tok_off(a, s, hd, t0, a.K);
   const T *q = reinterpret_cast<const T *>(a.q) + offk, *k = reinterpret_cast<const T *>(a.k) + offk;
   const float *b = reinterpret_cast<const float *>(a.gk) + offk;
-  // The triple (i, j, channel) only couples through e^{b_i - b_j}.  For a block of 16 rows with first row r,
-  // e^{b_i - b_j} = e^{b_i - b_r} e^{b_r - b_j}: both factors are applied once per element (not once per pair) and
-  // the pairs are plain fp32 FMAs.  For j before the block the second exponent is <= 0.  Inside the block it is
-  // positive but bounded by the decay over 16 tokens; when that exceeds e^60 in some channel (never with gates from
-  // a log-sigmoid) the pairs of that block are evaluated directly instead.
-  // thread = (row il of the block, column group jj): pairs (16 I + il, jj + 16 m) for m <= I
-  const int il = tid >> 4, jj = tid & 15;
-  float acc[4][4];
+  // the ten 16 x 16 blocks (I, m <= I) on and below the diagonal: warp w owns block w, warps 0 and 1 also 8 and 9
+  const int nblk = warp < 2 ? 2 : 1;
+  int bI[2], bM[2];
 #pragma unroll
-  for (int I = 0; I < 4; ++I)
-#pragma unroll
-    for (int m = 0; m < 4; ++m) acc[I][m] = 0.f;
+  for (int x = 0; x < 2; ++x) {
+    const int id = warp + 8 * x;
+    const int I = id < 1 ? 0 : id < 3 ? 1 : id < 6 ? 2 : 3;
+    bI[x] = I;
+    bM[x] = id - I * (I + 1) / 2;
+  }
+  float acc[2][1][2][4];
+  acc_zero(acc[0]);
+  acc_zero(acc[1]);
   for (int k0 = 0; k0 < a.K; k0 += GT) {
     const int kw = min(GT, a.K - k0);
     __syncthreads();
-    for (int e = tid; e < C * GT; e += 256) {
-      int r = e / GT, c = e - r * GT;
-      bool ok = r < rows && c < kw;
-      sQ[r * LD + c] = ok ? Num<T>::f(q[(size_t)r * ks + k0 + c]) : 0.f;
+    if (tid < 4) sDirect[tid] = 0;
+    float qreg[C * GT / 256];
+#pragma unroll
+    for (int p = 0; p < C * GT / 256; ++p) {
+      const int e = tid + 256 * p, r = e / GT, c = e - r * GT;
+      const bool ok = r < rows && c < kw;
+      qreg[p] = ok ? Num<T>::f(q[(size_t)r * ks + k0 + c]) : 0.f;
       sK[r * LD + c] = ok ? Num<T>::f(k[(size_t)r * ks + k0 + c]) : 0.f;
       sB[r * LD + c] = ok ? b[(size_t)r * ks + k0 + c] : 0.f;
     }
     __syncthreads();
+    if (tid < GT) {
+#pragma unroll
+      for (int I = 0; I < 4; ++I) {
+        const int r0 = 16 * I, rend = min(r0 + 16, rows);
+        if (r0 < rows && sB[r0 * LD + tid] - sB[(rend - 1) * LD + tid] > 60.f) sDirect[I] = 1;
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < C * GT / 256; ++p) {
+      const int e = tid + 256 * p, r = e / GT, c = e - r * GT;
+      tQs[r * LDF + c] = tile_round<T>(qreg[p] * fexp<T>(sB[r * LD + c] - sB[(r & ~15) * LD + c]));
+    }
+    __syncthreads();
 #pragma unroll
     for (int I = 0; I < 4; ++I) {
-      const int r0 = 16 * I, rend = min(r0 + 16, rows);
+      const int r0 = 16 * I;
       if (r0 >= rows) break;  // uniform
-      // decay across the block, worst channel (b is non-increasing along the tokens)
-      float span = 0.f;
-      if (tid < GT) span = sB[r0 * LD + tid] - sB[(rend - 1) * LD + tid];
-      const bool direct = __syncthreads_or(span > 60.f);
-      const int jend = direct ? r0 : rend;  // rows of k that get re-based
-      for (int e = tid; e < jend * GT; e += 256) {
+      const int jend = sDirect[I] ? r0 : min(r0 + 16, rows);
+      float *dst = tKF + 8 * I * (I + 1) * LDF;
+      for (int e = tid; e < (r0 + 16) * GT; e += 256) {
         const int r = e / GT, c = e - r * GT;
-        sKs[r * LD + c] = sK[r * LD + c] * fexp<T>(sB[r0 * LD + c] - sB[r * LD + c]);
+        dst[r * LDF + c] = r < jend ? tile_round<T>(sK[r * LD + c] * fexp<T>(sB[r0 * LD + c] - sB[r * LD + c])) : 0.f;
       }
-      for (int e = tid; e < 16 * GT; e += 256) {
-        const int r = e / GT, c = e - r * GT;
-        sQs[r * LD + c] = (r0 + r < rows) ? sQ[(r0 + r) * LD + c] * fexp<T>(sB[(r0 + r) * LD + c] - sB[r0 * LD + c]) : 0.f;
-      }
-      __syncthreads();
-      const int i = r0 + il;
-      if (i < rows) {
-        const float *qs = sQs + il * LD;
+    }
+    __syncthreads();
 #pragma unroll
-        for (int m = 0; m < 4; ++m) {
-          if (m > I) break;
-          const int j = jj + 16 * m;
-          if (j > i) continue;
-          float x = 0.f;
-          if (m < I || !direct) {
-            const float *kk = sKs + j * LD;
-#pragma unroll 8
-            for (int c = 0; c < GT; ++c) x = fmaf(qs[c], kk[c], x);
-          } else {
-            for (int c = 0; c < kw; ++c) x = fmaf(sQ[i * LD + c] * sK[j * LD + c], fexp<T>(sB[i * LD + c] - sB[j * LD + c]), x);
+    for (int x = 0; x < 2; ++x) {
+      if (x >= nblk) break;
+      const int I = bI[x], m = bM[x], r0 = 16 * I;
+      if (r0 >= rows) continue;
+      gemm_f32tile<1, 2, false, false, T>(acc[x], tQs, LDF, r0, tKF + 8 * I * (I + 1) * LDF, LDF, 16 * m, GT);
+      if (m == I && sDirect[I]) {
+        FLAB_ACC_FOREACH(1, 2, r0, 16 * m, row, col, mi, ni, r) {
+          if (row < rows && col <= row) {
+            float v = 0.f;
+            for (int c = 0; c < kw; ++c)
+              v = fmaf(Num<T>::f(q[(size_t)row * ks + k0 + c]) * sK[col * LD + c], fexp<T>(sB[row * LD + c] - sB[col * LD + c]), v);
+            acc[x][mi][ni][r] += v;
           }
-          acc[I][m] += x;
         }
       }
-      __syncthreads();
     }
   }
   float *A = reinterpret_cast<float *>(a.a) + tok_off(a, s, hd, t0, C);
   const size_t as_ = tok_stride(a, C);
 #pragma unroll
-  for (int I = 0; I < 4; ++I) {
-    const int i = 16 * I + il;
-    if (i >= rows) continue;
-#pragma unroll
-    for (int m = 0; m < 4; ++m) {
-      const int j = jj + 16 * m;
-      A[(size_t)i * as_ + j] = (m <= I && j <= i) ? acc[I][m] * a.scale : 0.f;
+  for (int x = 0; x < 2; ++x) {
+    if (x >= nblk) break;
+    const int I = bI[x], m = bM[x];
+    FLAB_ACC_FOREACH(1, 2, 16 * I, 16 * m, row, col, mi, ni, r) {
+      if (row < rows) A[(size_t)row * as_ + col] = col <= row ? acc[x][mi][ni][r] * a.scale : 0.f;
     }
+  }
+  // the six blocks above the diagonal are zero
+  for (int e = tid; e < 6 * 256; e += 256) {
+    const int id = e >> 8, w = e & 255, I = id < 3 ? 0 : id < 5 ? 1 : 2;
+    const int m = I + 1 + (id - (I == 0 ? 0 : I == 1 ? 3 : 5));
+    const int row = 16 * I + (w >> 4), col = 16 * m + (w & 15);
+    if (row < rows) A[(size_t)row * as_ + col] = 0.f;
   }
 }
 
@@ -458,7 +477,7 @@ template <typename T, int BV> static size_t gla_o_smem(const flab_args *a, bool 
 }
 
 template <typename T> static int launch_gla_fwd_intra(const flab_args *a, cudaStream_t stream) {
-  size_t smem = ((size_t)4 * C + 16) * (GT + 1) * sizeof(float);
+  size_t smem = ((size_t)2 * C * (GT + 1) + (size_t)(C + 160) * (GT + 4)) * sizeof(float);
   auto kern = gla_fwd_intra_kernel<T>;
   if (int e = set_smem(kern, smem)) return e;
   kern<<<dim3(a->NT, a->H), 256, smem, stream>>>(*a);
