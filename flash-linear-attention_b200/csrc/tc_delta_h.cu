@@ -35,7 +35,7 @@ struct TcDhParams {
   int ab_fmt;   // 1 bf16, 0 fp16
 };
 
-enum { DH_FWD = 0, DH_BWD = 1, DH_SIMPLE_FWD = 2, DH_SIMPLE_BWD = 3 };
+enum { DH_FWD = 0, DH_BWD = 1, DH_SIMPLE_FWD = 2, DH_SIMPLE_BWD = 3, DH_GK_FWD = 4, DH_GK_BWD = 5 };
 
 template <int VB /* BV / 64 */, int NS, int MODE>
 __global__ void __launch_bounds__(64 * (4 * VB + 1), 1)
@@ -49,7 +49,7 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
   using namespace tc;
   constexpr int K = 128, BV = 64 * VB, NC = 32;  // NC: state columns per epilogue thread
   constexpr int EW = BV / 8, ET = 32 * EW;         // epilogue warps (4 lane quadrants x BV/32 column groups), threads
-  constexpr bool BWD = (MODE & 1) != 0, SIMPLE = MODE >= 2;
+  constexpr bool BWD = (MODE & 1) != 0, SIMPLE = MODE >= 2, GK = MODE >= 4;  // GK: simple scan with a gate per key channel
   constexpr int NKT = SIMPLE ? 1 : (BWD ? 3 : 2), NVT = (BWD && !SIMPLE) ? 2 : 1;  // [tokens x K] and [tokens x BV] tiles per chunk
   constexpr uint32_t KT_BYTES = 2 * 8192, U_BYTES = VB * 8192, STAGE_BYTES = NKT * KT_BYTES + NVT * U_BYTES;
   constexpr uint32_t TM_DS = 0, TM_P = 128;
@@ -60,7 +60,7 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
   unsigned char *sS = sStage + NS * STAGE_BYTES;       // [VB][128 state rows][128 B] rounded state, B operand of w S
   unsigned char *sOp = sS + VB * K * 128;              // [VB][64 tokens][128 B] B operand of k^T op
   unsigned char *sVn = sOp + VB * 8192;                // [VB][64 tokens][128 B] v_new, same layout (source of the tile store)
-  float *sG = reinterpret_cast<float *>(sVn + VB * 8192);  // [2][64] gates
+  float *sG = reinterpret_cast<float *>(sVn + VB * 8192);  // [2][64] gates ([2][128]: the last row's gates per channel, GK)
   __shared__ uint64_t full[NS], empty[NS], s_ready, p_done, op_ready, ds_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
@@ -141,7 +141,12 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
         }
         if (!mbar_wait(&op_ready, sp)) { fail(44); break; }
         fence_after_sync();
-        if (!BWD || SIMPLE) {
+        if (GK) {
+          // (k e^{b_L-b})^T v or (scale q e^{b})^T do: the key tile was rescaled in place, the value tile is used as loaded
+          const uint64_t dy = desc_mnmajor(t1 + NKT * KT_BYTES, 0, 8192);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma(tmem + TM_DS, d2 + (uint64_t)((k * 2048) >> 4), dy + (uint64_t)((k * 2048) >> 4), idesc_s, k > 0);
+        } else if (!BWD || SIMPLE) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) umma(tmem + TM_DS, d2 + (uint64_t)((k * 2048) >> 4), do0 + (uint64_t)((k * 2048) >> 4), idesc_s, k > 0);
         } else {
@@ -187,7 +192,26 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
       const int t = chunk_at(i) * C + tid;
       return (use_g && tid < C && t < s.len) ? G[(size_t)t * gs] : 0.f;
     };
-    float g_pf = nt > 0 ? gate_of(0) : 0.f;
+    // GK: gates [tokens][K] fp32; the last row of the chunk (decay of the state rows) goes through shared memory,
+    // the factors of this thread's 16 key-tile elements are fetched a chunk ahead into registers
+    const float *GKp = GK ? reinterpret_cast<const float *>(a.gk) + tok_off(a, s, hd, 0, K) : nullptr;
+    const size_t gks = tok_stride(a, K);
+    auto gk_last_of = [&](int i) -> float {
+      const int it_ = chunk_at(i), t = it_ * C + min(C, s.len - it_ * C) - 1;
+      return tid < K ? GKp[(size_t)t * gks + tid] : 0.f;
+    };
+    float2 gk_pf[2][NC / 8];
+    auto gk_load = [&](int i) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int t = chunk_at(i) * C + (hf ? row_hi : row_lo);
+#pragma unroll
+        for (int ni = 0; ni < NC / 8; ++ni)
+          gk_pf[hf][ni] = t < s.len ? *reinterpret_cast<const float2 *>(GKp + (size_t)t * gks + NC * chh + 8 * ni + 2 * t4) : make_float2(0.f, 0.f);
+      }
+    };
+    float g_pf = nt > 0 ? (GK ? gk_last_of(0) : gate_of(0)) : 0.f;
+    if (GK && nt > 0) gk_load(0);
     float d_prev = 1.f;
     bf16 *vout = reinterpret_cast<bf16 *>(BWD ? a.dv2 : a.v_new);
     const size_t vs = tok_stride(a, a.V);
@@ -223,7 +247,9 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
           *reinterpret_cast<int4 *>(sS + (col >> 6) * (K * 128) + srow * 128 + ((((col & 63) >> 3) ^ (srow & 7)) << 4)) = x;
         }
       }
-      if (tid < C) sG[sp * C + tid] = g_pf;
+      if (GK) {
+        if (tid < K) sG[sp * K + tid] = g_pf;
+      } else if (tid < C) sG[sp * C + tid] = g_pf;
       fence_proxy_async();
       fence_before_sync();
       __syncwarp();
@@ -239,15 +265,16 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
         for (int j = 0; j < VB; ++j) tma_store_2d(&mapH, sS + j * (K * 128), v0 + 64 * j, ((s.c0 + chunk_at(i)) * a.H + hd) * K);
         tma_store_commit();
       }
-      if (i + 1 < nt) g_pf = gate_of(i + 1);
+      if (i + 1 < nt) g_pf = GK ? gk_last_of(i + 1) : gate_of(i + 1);
       const int it = chunk_at(i), rows = min(C, s.len - it * C), last = rows - 1;
-      const float *gc = sG + sp * C;
-      const float gl = gc[last];
+      const float *gc = sG + sp * (GK ? K : C);
+      const float gl = GK ? 0.f : gc[last];
       // row factors: fa multiplies P, fo turns the corrected tile into op
       //   forward : v_new = u - e^{b} P,         op = e^{b_L-b} v_new
       //   backward: dv2   = dv + e^{b_L-b} P,    op = -e^{b} dv2,   do' = scale e^{b} do
       float e1_lo = 1.f, e1_hi = 1.f, e2_lo = 1.f, e2_hi = 1.f;
-      if (use_g) {
+      if (GK) d_prev = __expf(gc[srow]);
+      if (use_g && !GK) {
         e1_lo = __expf(gc[row_lo]), e1_hi = __expf(gc[row_hi]);
         e2_lo = __expf(gl - gc[row_lo]), e2_hi = __expf(gl - gc[row_hi]);
         d_prev = __expf(gl);
@@ -286,6 +313,34 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
           }
         }
       }
+      if (GK) {
+        // key tile rescaled in place: k e^{b_L-b} (forward), scale q e^{b} (backward); rows past the end are zeroed
+        unsigned char *kt = sStage + st * STAGE_BYTES;
+#pragma unroll
+        for (int ni = 0; ni < NC / 8; ++ni) {
+          const int col = NC * chh + 8 * ni + 2 * t4;
+          const float gl0 = gc[col], gl1 = gc[col + 1];
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            const uint32_t off = (uint32_t)(col >> 6) * 8192u + sw128_offset(hf ? row_hi : row_lo, col & 63);
+            const float2 bb = gk_pf[hf][ni];
+            float f0, f1;
+            if (BWD) f0 = a.scale * __expf(bb.x), f1 = a.scale * __expf(bb.y);
+            else f0 = __expf(gl0 - bb.x), f1 = __expf(gl1 - bb.y);
+            if (!(hf ? in_hi : in_lo)) f0 = f1 = 0.f;
+            if (p.ab_fmt) {
+              __nv_bfloat162 *q2 = reinterpret_cast<__nv_bfloat162 *>(kt + off);
+              const float2 x = __bfloat1622float2(*q2);
+              *q2 = __floats2bfloat162_rn(x.x * f0, x.y * f1);
+            } else {
+              __half2 *q2 = reinterpret_cast<__half2 *>(kt + off);
+              const float2 x = __half22float2(*q2);
+              *q2 = __floats2half2_rn(x.x * f0, x.y * f1);
+            }
+          }
+        }
+        if (i + 1 < nt) gk_load(i + 1);
+      }
       float pr[NC / 8][4];
       if (!SIMPLE) {
         if (!mbar_wait(&p_done, sp)) { fail(47); ok = false; }
@@ -294,7 +349,7 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
         tmem_ld_wait();
       }
 #pragma unroll
-      for (int ni = 0; ni < NC / 8; ++ni) {
+      for (int ni = 0; ni < (GK ? 0 : NC / 8); ++ni) {
         const int col = NC * chh + 8 * ni + 2 * t4;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
@@ -370,7 +425,7 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
 
 template <int VB, int NS, int MODE> static int launch_tc_dh(const flab_args *a, cudaStream_t stream) {
   constexpr int BV = 64 * VB;
-  constexpr bool BWD = (MODE & 1) != 0, SIMPLE = MODE >= 2;
+  constexpr bool BWD = (MODE & 1) != 0, SIMPLE = MODE >= 2, GK = MODE >= 4;
   CUtensorMap mA1, mA2, mA3, mY, mDo, mH, mYo;
   const void *a1 = SIMPLE ? (BWD ? a->q : a->k) : (BWD ? a->k : a->w);
   const void *y = SIMPLE ? (BWD ? a->d_o : a->v) : (BWD ? a->dv : a->u);
@@ -387,7 +442,7 @@ template <int VB, int NS, int MODE> static int launch_tc_dh(const flab_args *a, 
   p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
   constexpr int NKT = SIMPLE ? 1 : (BWD ? 3 : 2), NVT = (BWD && !SIMPLE) ? 2 : 1;
   constexpr uint32_t STAGE = NKT * 16384 + NVT * VB * 8192;
-  const size_t smem = 1024 + NS * (size_t)STAGE + (size_t)VB * 128 * 128 + 2 * (size_t)VB * 8192 + 2 * C * sizeof(float);
+  const size_t smem = 1024 + NS * (size_t)STAGE + (size_t)VB * 128 * 128 + 2 * (size_t)VB * 8192 + 2 * (GK ? 128 : C) * sizeof(float);
   auto kern = tc_delta_h_kernel<VB, NS, MODE>;
   if (int e = set_smem(kern, smem)) return e;
   kern<<<dim3(p.v_tiles, a->N * a->H), 64 * (4 * VB + 1), smem, stream>>>(mA1, mA2, mA3, mY, mDo, mH, mYo, p);
@@ -418,19 +473,29 @@ int tc_delta_bwd_dhu_try(const flab_args *a, cudaStream_t stream) {
   return rc < 0 ? rc : 1;
 }
 
-// Plain chunk-state scans (scalar gate or none; the per-channel gate of GLA keeps the mma.sync kernel).
+// Plain chunk-state scans: no gate, a scalar gate per (token, head), or a gate per key channel (GLA).
 int tc_chunk_fwd_h_try(const flab_args *a, cudaStream_t stream) {
-  if (a->gk || a->gv) return 0;
-  const void *ptrs[5] = {a->k, a->v, a->h, a->h0, a->ht};
-  if (!tc_dh_ok(a, ptrs, 5)) return 0;
+  if (a->gv || (a->gk && a->g)) return 0;
+  const void *ptrs[6] = {a->k, a->v, a->h, a->h0, a->ht, a->gk};
+  if (!tc_dh_ok(a, ptrs, 6)) return 0;
+  if (a->gk) {
+    if (a->V % 128 != 0) return 0;  // the 16 epilogue warps of the 128-column tile cover the [64][128] key tile
+    const int rc = launch_tc_dh<2, 4, DH_GK_FWD>(a, stream);
+    return rc < 0 ? rc : 1;
+  }
   const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 4, DH_SIMPLE_FWD>(a, stream) : launch_tc_dh<1, 4, DH_SIMPLE_FWD>(a, stream);
   return rc < 0 ? rc : 1;
 }
 
 int tc_chunk_bwd_dh_try(const flab_args *a, cudaStream_t stream) {
-  if (a->gk || a->gv) return 0;
-  const void *ptrs[5] = {a->q, a->d_o, a->dh, a->dht, a->dh0};
-  if (!tc_dh_ok(a, ptrs, 5)) return 0;
+  if (a->gv || (a->gk && a->g)) return 0;
+  const void *ptrs[6] = {a->q, a->d_o, a->dh, a->dht, a->dh0, a->gk};
+  if (!tc_dh_ok(a, ptrs, 6)) return 0;
+  if (a->gk) {
+    if (a->V % 128 != 0) return 0;
+    const int rc = launch_tc_dh<2, 4, DH_GK_BWD>(a, stream);
+    return rc < 0 ? rc : 1;
+  }
   const int rc = (a->V % 128 == 0) ? launch_tc_dh<2, 4, DH_SIMPLE_BWD>(a, stream) : launch_tc_dh<1, 4, DH_SIMPLE_BWD>(a, stream);
   return rc < 0 ? rc : 1;
 }

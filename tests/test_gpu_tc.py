@@ -168,3 +168,72 @@ def test_tc_scans_against_torch(dt, V, head_first, gated, lens):
             assert _rel(dhs.view(-1, H, K, V)[c0:c0 + nt, hd], rdhs) < 1e-2
             assert _rel(dh0s[n, hd], rdh0s) < 1e-2
         c0 += nt
+
+
+def _ref_gk(x, y, gk, s0, scale, bwd, dt):
+    """Chunk-state scan with a gate per key channel: x = k (forward) or q (backward), gk [T, K] chunk-local cumsum."""
+    S = s0.clone()
+    ch = _chunks(x.shape[0])
+    hs = [None] * len(ch)
+    for i in (range(len(ch) - 1, -1, -1) if bwd else range(len(ch))):
+        lo, hi = ch[i]
+        hs[i] = _rnd(S, dt)
+        gc = gk[lo:hi]
+        f = gc.exp() * scale if bwd else (gc[-1:] - gc).exp()
+        S = S * gc[-1].exp()[:, None] + _rnd(x[lo:hi] * f, dt).T @ y[lo:hi]
+    return torch.stack(hs), S
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("V,head_first,lens", [
+    (128, False, [200, 64, 333]),
+    (256, False, [191]),
+    (128, True, None),
+])
+def test_tc_channel_gate_scans_against_torch(dt, V, head_first, lens):
+    from fla_b200.ops import common as C
+    from fla_b200.utils import Geometry
+    torch.manual_seed(5)
+    H, K, scale = 2, 128, 128 ** -0.5
+    if lens is None:
+        B, T, offsets = 2, 150, None
+        seqs = [(b, 0, T) for b in range(B)]
+    else:
+        B, T = 1, sum(lens)
+        offs = [0]
+        for L in lens:
+            offs.append(offs[-1] + L)
+        offsets = torch.tensor(offs, dtype=torch.long, device="cuda")
+        seqs = [(0, offs[i], offs[i + 1]) for i in range(len(lens))]
+    N = len(seqs)
+
+    def tok(D, s=1.0):
+        shape = (B, H, T, D) if head_first else (B, T, H, D)
+        return (torch.randn(shape, device="cuda") * s).to(dt)
+
+    q, k, v, do = tok(K, 0.3), tok(K, 0.3), tok(V), tok(V)
+    graw = -torch.rand((B, H, T, K) if head_first else (B, T, H, K), device="cuda") * 0.2
+    gk = C.chunk_local_cumsum(graw, offsets=offsets, head_first=head_first)
+    h0 = torch.randn(N, H, K, V, device="cuda") * 0.1
+    dht = torch.randn(N, H, K, V, device="cuda") * 0.1
+    geo = Geometry(k, v, offsets, head_first)
+    hs, hts = C.chunk_fwd_h(geo, k, v, gk=gk, h0=h0, output_final_state=True)
+    dhs, dh0s = C.chunk_bwd_dh(geo, q, do, scale, gk=gk, dht=dht, want_dh0=True)
+    torch.cuda.synchronize()
+    assert _lib.load().flab_tc_error_state() == 0
+
+    def sl(x, b, hd, lo, hi):
+        return (x[b, hd, lo:hi] if head_first else x[b, lo:hi, hd]).float()
+
+    c0 = 0
+    for n, (b, lo, hi) in enumerate(seqs):
+        nt = (hi - lo + 63) // 64
+        for hd in range(H):
+            qq, kk, vv, dd, gg = (sl(x, b, hd, lo, hi) for x in (q, k, v, do, gk))
+            rhs, rhts = _ref_gk(kk, vv, gg, h0[n, hd], 1.0, False, dt)
+            assert _rel(hs.view(-1, H, K, V)[c0:c0 + nt, hd], rhs) < 1e-2
+            assert _rel(hts[n, hd], rhts) < 1e-2
+            rdhs, rdh0s = _ref_gk(qq, dd, gg, dht[n, hd], scale, True, dt)
+            assert _rel(dhs.view(-1, H, K, V)[c0:c0 + nt, hd], rdhs) < 1e-2
+            assert _rel(dh0s[n, hd], rdh0s) < 1e-2
+        c0 += nt
