@@ -299,6 +299,15 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
   float *tQs = tDA + C * LDF;                     // [64][LDF] q re-based to the first row of its row block
   float *tKF = tQs + C * LDF;                     // [16+32+48+64][LDF] k re-based to the first row of block I, stacked
   float *sOQ = tKF;                               // [64][LD] total dq (after the products)
+  // staging of the phase-2 inputs, fetched while phase 1 runs: behind the phase-1 tiles, inside what becomes tKF
+  const size_t p1_bytes = ((size_t)2 * C * LDV + (size_t)2 * GT * LDV) * sizeof(T);
+  const size_t p2_bytes = ((size_t)2 * C * LD + (size_t)(2 * C + 160) * LDF) * sizeof(float);
+  constexpr size_t STG_BYTES = (size_t)2 * C * GT * sizeof(T) + (size_t)(C * GT + 10 * 256) * sizeof(float);
+  const size_t stg_off = p1_bytes + STG_BYTES > p2_bytes ? p1_bytes : p2_bytes - STG_BYTES;
+  float *stB = reinterpret_cast<float *>(region + ((stg_off + 15) & ~(size_t)15));  // [64][64] gates
+  float *stDA = stB + C * GT;                     // [10][16][16] blocks (I, m <= I) of dA
+  T *stQ = reinterpret_cast<T *>(stDA + 10 * 256);  // [64][64]
+  T *stK = stQ + C * GT;                          // [64][64]
   float *sOK = sOQ + C * LD;                      // [64][LD] total dk
 
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -321,8 +330,22 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
     tile_load<T>(sH, LDV, reinterpret_cast<const T *>(a.h) + hoff, (size_t)a.V, kw, GT, a.V, VP, tid, 256);
     tile_load<T>(sDH, LDV, reinterpret_cast<const T *>(a.dh) + hoff, (size_t)a.V, kw, GT, a.V, VP, tid, 256);
     cp_async_commit();
+    {
+      const float *dA = reinterpret_cast<const float *>(a.da) + tok_off(a, s, hd, t0, C);
+      tile_load<T>(stQ, GT, reinterpret_cast<const T *>(a.q) + offk, ks, rows, C, kw, GT, tid, 256);
+      tile_load<T>(stK, GT, reinterpret_cast<const T *>(a.k) + offk, ks, rows, C, kw, GT, tid, 256);
+      tile_load<float>(stB, GT, b, ks, rows, C, kw, GT, tid, 256);
+      {  // one 16 x 16 block of dA per group of 64 threads and pass
+        const int grp = tid >> 6, w = tid & 63;
+        for (int id = grp; id < 10; id += 4) {
+          const int I = id < 1 ? 0 : id < 3 ? 1 : id < 6 ? 2 : 3, m = id - I * (I + 1) / 2;
+          tile_load<float>(stDA + id * 256, 16, dA + (size_t)(16 * I) * as_ + 16 * m, as_, max(0, min(16, rows - 16 * I)), 16, 16, 16, w, 64);
+        }
+      }
+      cp_async_commit();
+    }
     if (tid < 4) sDirect[tid] = 0;
-    cp_async_wait<0>();
+    cp_async_wait<1>();
     __syncthreads();
     acc_zero(dq);
     acc_zero(dk);
@@ -339,20 +362,21 @@ __global__ void __launch_bounds__(256) gla_bwd_dqkg_kernel(const flab_args a) {
       if (sl == 0) sGK[c] = c < kw ? x * expf(b[(size_t)last * ks + c]) : 0.f;
     }
   }
+  cp_async_wait<0>();
   __syncthreads();
   // ---- phase 2
   {
-    const T *q = reinterpret_cast<const T *>(a.q) + offk, *k = reinterpret_cast<const T *>(a.k) + offk;
-    const float *dA = reinterpret_cast<const float *>(a.da) + tok_off(a, s, hd, t0, C);
+    const T *q = reinterpret_cast<const T *>(a.q) + offk;
     float qreg[C * GT / 256];  // q of element e = tid + 256 p (row e / 64, channel e % 64): row block I owns p = 4 I .. 4 I + 3
 #pragma unroll
     for (int p = 0; p < C * GT / 256; ++p) {
       const int e = tid + 256 * p, r = e / GT, c = e - r * GT;
       const bool ok = r < rows && c < kw;
-      qreg[p] = ok ? Num<T>::f(q[(size_t)r * ks + c]) : 0.f;
-      sK[r * LD + c] = ok ? Num<T>::f(k[(size_t)r * ks + c]) : 0.f;
-      sB[r * LD + c] = ok ? b[(size_t)r * ks + c] : 0.f;
-      tDA[r * LDF + c] = (r < rows && c <= r) ? tile_round<T>(dA[(size_t)r * as_ + c]) : 0.f;  // c = column of dA here
+      qreg[p] = ok ? Num<T>::f(stQ[e]) : 0.f;
+      sK[r * LD + c] = ok ? Num<T>::f(stK[e]) : 0.f;
+      sB[r * LD + c] = ok ? stB[e] : 0.f;
+      const int I = r >> 4, m = c >> 4;  // c = column of dA here
+      tDA[r * LDF + c] = (r < rows && c <= r) ? tile_round<T>(stDA[(I * (I + 1) / 2 + m) * 256 + (r & 15) * 16 + (c & 15)]) : 0.f;
     }
     __syncthreads();
     if (tid < GT) {
@@ -518,7 +542,9 @@ template <typename T> static int launch_gla_bwd_dqkg(const flab_args *a, cudaStr
   const int VP = round_up(a->V, 16), LDV = VP + Num<T>::pad;
   size_t p1 = ((size_t)2 * C * LDV + (size_t)2 * GT * LDV) * sizeof(T);
   size_t p2 = ((size_t)2 * C * (GT + 1) + (size_t)(2 * C + 160) * (GT + 4)) * sizeof(float);
-  size_t smem = (GT + 4) * sizeof(float) + (p1 > p2 ? p1 : p2);
+  size_t stg = (size_t)2 * C * GT * sizeof(T) + (size_t)(C * GT + 10 * 256) * sizeof(float);  // phase-2 inputs staged during phase 1
+  size_t stg_off = p1 + stg > p2 ? p1 : p2 - stg;
+  size_t smem = (GT + 4) * sizeof(float) + ((stg_off + 15) & ~(size_t)15) + stg;
   auto kern = gla_bwd_dqkg_kernel<T>;
   if (int e = set_smem(kern, smem)) return e;
   kern<<<dim3(a->NT, a->H, cdiv(a->K, GT)), 256, smem, stream>>>(*a);
