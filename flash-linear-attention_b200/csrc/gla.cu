@@ -129,6 +129,88 @@ __global__ void __launch_bounds__(256, 2) gla_fwd_intra_kernel(const flab_args a
   }
 }
 
+// Gate factors of a [rows][K] operand tile, eight channels per thread and pass.  GateRows::fetch issues the global
+// loads of the gate rows (registers) so that they overlap the tile copies in flight; apply() rescales the tile in
+// shared memory once it has landed.  MODE 0: x <- round(x * scale) * e^{b_r};  MODE 1: x <- x * e^{b_last - b_r}.
+// Covers K in {8, 16, 32, 64, 128} with 16-byte aligned gate rows; usable() is false otherwise (scalar loop).
+template <typename T, int MODE> struct GateRows {
+  float4 bv[8][2], bl[2];
+  int cpr, c;
+  static __device__ __forceinline__ bool usable(const flab_args &a, const float *b, size_t ks) {
+    const int cpr = a.K >> 3;
+    return a.K % 8 == 0 && a.K <= 128 && cpr > 0 && 128 % cpr == 0 && ((uintptr_t)b) % 16 == 0 && (ks * sizeof(float)) % 16 == 0;
+  }
+  __device__ __forceinline__ void fetch(const flab_args &a, const float *b, size_t ks, int rows, int tid) {
+    cpr = a.K >> 3;
+    c = (tid % cpr) * 8;  // 128 % cpr == 0: the channel group of a thread is the same in every pass
+    const int rstep = 128 / cpr, r0 = tid / cpr;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int r = r0 + u * rstep;
+      if (r < rows) {
+        bv[u][0] = *reinterpret_cast<const float4 *>(b + (size_t)r * ks + c);
+        bv[u][1] = *reinterpret_cast<const float4 *>(b + (size_t)r * ks + c + 4);
+      } else {
+        bv[u][0] = bv[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    if (MODE == 1) {
+      bl[0] = *reinterpret_cast<const float4 *>(b + (size_t)(rows - 1) * ks + c);
+      bl[1] = *reinterpret_cast<const float4 *>(b + (size_t)(rows - 1) * ks + c + 4);
+    } else {
+      bl[0] = bl[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  __device__ __forceinline__ void apply(T *x, int ld, int rows, float scale, int tid) const {
+    const int rstep = 128 / cpr, r0 = tid / cpr;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int r = r0 + u * rstep;
+      if (r >= rows) continue;
+      T *px = x + r * ld + c;
+      const float g[8] = {bv[u][0].x, bv[u][0].y, bv[u][0].z, bv[u][0].w, bv[u][1].x, bv[u][1].y, bv[u][1].z, bv[u][1].w};
+      const float l[8] = {bl[0].x, bl[0].y, bl[0].z, bl[0].w, bl[1].x, bl[1].y, bl[1].z, bl[1].w};
+      T v[8];
+      if constexpr (sizeof(T) == 2) *reinterpret_cast<int4 *>(v) = *reinterpret_cast<const int4 *>(px);
+      else {
+        *reinterpret_cast<int4 *>(v) = *reinterpret_cast<const int4 *>(px);
+        *reinterpret_cast<int4 *>(v + 4) = *reinterpret_cast<const int4 *>(px + 4);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xf = Num<T>::f(v[j]);
+        v[j] = Num<T>::t(MODE == 0 ? rnd<T>(xf * scale) * expf(g[j]) : xf * expf(l[j] - g[j]));
+      }
+      if constexpr (sizeof(T) == 2) *reinterpret_cast<int4 *>(px) = *reinterpret_cast<const int4 *>(v);
+      else {
+        *reinterpret_cast<int4 *>(px) = *reinterpret_cast<const int4 *>(v);
+        *reinterpret_cast<int4 *>(px + 4) = *reinterpret_cast<const int4 *>(v + 4);
+      }
+    }
+  }
+};
+
+// tril(A) (fp32 [64][64] in global memory) -> operand tile of type T, four columns per thread and pass
+template <typename T> __device__ __forceinline__ void load_tril_A(T *sA, int ldp, const float *A, size_t as_, int rows, int tid) {
+  if (((uintptr_t)A) % 16 == 0 && (as_ * sizeof(float)) % 16 == 0) {
+#pragma unroll
+    for (int u = 0; u < C * C / 4 / 128; ++u) {
+      const int e = tid + 128 * u, i = e >> 4, j = (e & 15) * 4;
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < rows && j <= i) x = *reinterpret_cast<const float4 *>(A + (size_t)i * as_ + j);
+      sA[i * ldp + j] = Num<T>::t(x.x);
+      sA[i * ldp + j + 1] = Num<T>::t(j + 1 <= i ? x.y : 0.f);
+      sA[i * ldp + j + 2] = Num<T>::t(j + 2 <= i ? x.z : 0.f);
+      sA[i * ldp + j + 3] = Num<T>::t(j + 3 <= i ? x.w : 0.f);
+    }
+  } else {
+    for (int e = tid; e < C * C; e += 128) {
+      int i = e >> 6, j = e & 63;
+      sA[i * ldp + j] = Num<T>::t((i < rows && i >= j) ? A[(size_t)i * as_ + j] : 0.f);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // o = (q*scale*e^{b}) h + tril(A) v.  grid (NT, H, V/BV); 4 warps x 16 token rows.
 // ------------------------------------------------------------------------------------------------
@@ -156,17 +238,16 @@ __global__ void __launch_bounds__(128) gla_fwd_o_kernel(const flab_args a) {
   tile_load<T>(sH, LDV, reinterpret_cast<const T *>(a.h) + ((size_t)(s.c0 + it) * a.H + hd) * a.K * a.V + v0, (size_t)a.V,
                a.K, KP, vw, BV, tid, 128);
   cp_async_commit();
-  {
-    const float *A = reinterpret_cast<const float *>(a.a) + tok_off(a, s, hd, t0, C);
-    for (int e = tid; e < C * C; e += 128) {
-      int i = e >> 6, j = e & 63;
-      sA[i * LDP + j] = Num<T>::t((i < rows && i >= j) ? A[(size_t)i * as_ + j] : 0.f);
-    }
-  }
+  const float *b = reinterpret_cast<const float *>(a.gk) + offk;
+  GateRows<T, 0> gates;
+  const bool gvec = GateRows<T, 0>::usable(a, b, ks);
+  if (gvec) gates.fetch(a, b, ks, rows, tid);
+  load_tril_A<T>(sA, LDP, reinterpret_cast<const float *>(a.a) + tok_off(a, s, hd, t0, C), as_, rows, tid);
   cp_async_wait<0>();
   __syncthreads();
-  {
-    const float *b = reinterpret_cast<const float *>(a.gk) + offk;
+  if (gvec) {
+    gates.apply(sQ, LDK, rows, a.scale, tid);
+  } else {
     for (int e = tid; e < rows * a.K; e += 128) {
       int r = e / a.K, c = e - r * a.K;
       float x = rnd<T>(Num<T>::f(sQ[r * LDK + c]) * a.scale) * expf(b[(size_t)r * ks + c]);
@@ -237,17 +318,16 @@ __global__ void __launch_bounds__(128) gla_bwd_dav_kernel(const flab_args a) {
   tile_load<T>(sDH, LDV, reinterpret_cast<const T *>(a.dh) + ((size_t)(s.c0 + it) * a.H + hd) * a.K * a.V + v0, (size_t)a.V,
                a.K, KP, vw, BV, tid, 128);
   cp_async_commit();
-  {
-    const float *A = reinterpret_cast<const float *>(a.a) + tok_off(a, s, hd, t0, C);
-    for (int e = tid; e < C * C; e += 128) {
-      int i = e >> 6, j = e & 63;
-      sA[i * LDP + j] = Num<T>::t((i < rows && i >= j) ? A[(size_t)i * as_ + j] : 0.f);
-    }
-  }
+  const float *b = reinterpret_cast<const float *>(a.gk) + offk;
+  GateRows<T, 1> gates;
+  const bool gvec = GateRows<T, 1>::usable(a, b, ks);
+  if (gvec) gates.fetch(a, b, ks, rows, tid);
+  load_tril_A<T>(sA, LDP, reinterpret_cast<const float *>(a.a) + tok_off(a, s, hd, t0, C), as_, rows, tid);
   cp_async_wait<0>();
   __syncthreads();
-  {
-    const float *b = reinterpret_cast<const float *>(a.gk) + offk;
+  if (gvec) {
+    gates.apply(sKG, LDK, rows, 1.f, tid);
+  } else {
     for (int e = tid; e < rows * a.K; e += 128) {
       int r = e / a.K, c = e - r * a.K;
       float x = Num<T>::f(sKG[r * LDK + c]) * expf(b[(size_t)last * ks + c] - b[(size_t)r * ks + c]);
