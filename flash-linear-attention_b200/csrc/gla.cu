@@ -25,12 +25,14 @@ constexpr int GT = 64;  // key-channel tile of the intra / dqkg kernels
 // ------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256, 2) gla_fwd_intra_kernel(const flab_args a) {
-  constexpr int LD = GT + 1, LDF = GT + 4;
+  constexpr int LDF = GT + 4;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float *sK = reinterpret_cast<float *>(smem_raw), *sB = sK + C * LD;
-  float *tQs = sB + C * LD;    // [64][LDF] q re-based to the first row of its row block
-  float *tKF = tQs + C * LDF;  // [16+32+48+64][LDF] k re-based to the first row of block I, stacked
-  __shared__ int sDirect[4];
+  float *stB = reinterpret_cast<float *>(smem_raw);  // [64][64] gates of the channel tile, as copied
+  float *tQs = stB + C * GT;                          // [64][LDF] q re-based to the first row of its row block
+  float *tKF = tQs + C * LDF;                         // [16+32+48+64][LDF] k re-based to the first row of block I, stacked
+  T *stQ = reinterpret_cast<T *>(tKF + 160 * LDF);    // [64][64] q, k of the channel tile, as copied
+  T *stK = stQ + C * GT;
+  __shared__ int sDirect[2][4];
   const int tid = threadIdx.x, warp = tid >> 5;
   int n, it;
   chunk_of(a, blockIdx.x, n, it);
@@ -53,57 +55,60 @@ __global__ void __launch_bounds__(256, 2) gla_fwd_intra_kernel(const flab_args a
   float acc[2][1][2][4];
   acc_zero(acc[0]);
   acc_zero(acc[1]);
-  for (int k0 = 0; k0 < a.K; k0 += GT) {
+  // the channel tile's inputs are copied asynchronously; the copy of the next tile runs under the products of this one
+  auto stage = [&](int k0) {
     const int kw = min(GT, a.K - k0);
-    __syncthreads();
-    if (tid < 4) sDirect[tid] = 0;
-    float qreg[C * GT / 256];
-#pragma unroll
-    for (int p = 0; p < C * GT / 256; ++p) {
-      const int e = tid + 256 * p, r = e / GT, c = e - r * GT;
-      const bool ok = r < rows && c < kw;
-      qreg[p] = ok ? Num<T>::f(q[(size_t)r * ks + k0 + c]) : 0.f;
-      sK[r * LD + c] = ok ? Num<T>::f(k[(size_t)r * ks + k0 + c]) : 0.f;
-      sB[r * LD + c] = ok ? b[(size_t)r * ks + k0 + c] : 0.f;
-    }
-    __syncthreads();
+    tile_load<T>(stQ, GT, q + k0, ks, rows, C, kw, GT, tid, 256);
+    tile_load<T>(stK, GT, k + k0, ks, rows, C, kw, GT, tid, 256);
+    tile_load<float>(stB, GT, b + k0, ks, rows, C, kw, GT, tid, 256);
+    cp_async_commit();
+  };
+  stage(0);
+  for (int k0 = 0, tile = 0; k0 < a.K; k0 += GT, ++tile) {
+    const int kw = min(GT, a.K - k0);
+    int *direct = sDirect[tile & 1];
+    if (tid < 4) direct[tid] = 0;
+    cp_async_wait<0>();
+    __syncthreads();  // tile landed; the products of the previous tile are done with tQs / tKF
     if (tid < GT) {
 #pragma unroll
       for (int I = 0; I < 4; ++I) {
         const int r0 = 16 * I, rend = min(r0 + 16, rows);
-        if (r0 < rows && sB[r0 * LD + tid] - sB[(rend - 1) * LD + tid] > 60.f) sDirect[I] = 1;
+        if (r0 < rows && stB[r0 * GT + tid] - stB[(rend - 1) * GT + tid] > 60.f) direct[I] = 1;
       }
     }
 #pragma unroll
     for (int p = 0; p < C * GT / 256; ++p) {
       const int e = tid + 256 * p, r = e / GT, c = e - r * GT;
-      tQs[r * LDF + c] = tile_round<T>(qreg[p] * fexp<T>(sB[r * LD + c] - sB[(r & ~15) * LD + c]));
+      tQs[r * LDF + c] = tile_round<T>(Num<T>::f(stQ[e]) * fexp<T>(stB[e] - stB[(r & ~15) * GT + c]));
     }
     __syncthreads();
 #pragma unroll
     for (int I = 0; I < 4; ++I) {
       const int r0 = 16 * I;
       if (r0 >= rows) break;  // uniform
-      const int jend = sDirect[I] ? r0 : min(r0 + 16, rows);
+      const int jend = direct[I] ? r0 : min(r0 + 16, rows);
       float *dst = tKF + 8 * I * (I + 1) * LDF;
       for (int e = tid; e < (r0 + 16) * GT; e += 256) {
         const int r = e / GT, c = e - r * GT;
-        dst[r * LDF + c] = r < jend ? tile_round<T>(sK[r * LD + c] * fexp<T>(sB[r0 * LD + c] - sB[r * LD + c])) : 0.f;
+        dst[r * LDF + c] = r < jend ? tile_round<T>(Num<T>::f(stK[e]) * fexp<T>(stB[r0 * GT + c] - stB[e])) : 0.f;
       }
     }
-    __syncthreads();
+    __syncthreads();  // operand tiles complete, the copied tile is free
+    if (k0 + GT < a.K) stage(k0 + GT);
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
       if (x >= nblk) break;
       const int I = bI[x], m = bM[x], r0 = 16 * I;
       if (r0 >= rows) continue;
       gemm_f32tile<1, 2, false, false, T>(acc[x], tQs, LDF, r0, tKF + 8 * I * (I + 1) * LDF, LDF, 16 * m, GT);
-      if (m == I && sDirect[I]) {
+      if (m == I && direct[I]) {
         FLAB_ACC_FOREACH(1, 2, r0, 16 * m, row, col, mi, ni, r) {
           if (row < rows && col <= row) {
+            const T *qi = q + (size_t)row * ks + k0, *kj = k + (size_t)col * ks + k0;
+            const float *bi = b + (size_t)row * ks + k0, *bj = b + (size_t)col * ks + k0;
             float v = 0.f;
-            for (int c = 0; c < kw; ++c)
-              v = fmaf(Num<T>::f(q[(size_t)row * ks + k0 + c]) * sK[col * LD + c], fexp<T>(sB[row * LD + c] - sB[col * LD + c]), v);
+            for (int c = 0; c < kw; ++c) v = fmaf(Num<T>::f(qi[c]) * Num<T>::f(kj[c]), fexp<T>(bi[c] - bj[c]), v);
             acc[x][mi][ni][r] += v;
           }
         }
@@ -581,7 +586,7 @@ template <typename T, int BV> static size_t gla_o_smem(const flab_args *a, bool 
 }
 
 template <typename T> static int launch_gla_fwd_intra(const flab_args *a, cudaStream_t stream) {
-  size_t smem = ((size_t)2 * C * (GT + 1) + (size_t)(C + 160) * (GT + 4)) * sizeof(float);
+  size_t smem = ((size_t)C * GT + (size_t)(C + 160) * (GT + 4)) * sizeof(float) + (size_t)2 * C * GT * sizeof(T);
   auto kern = gla_fwd_intra_kernel<T>;
   if (int e = set_smem(kern, smem)) return e;
   kern<<<dim3(a->NT, a->H), 256, smem, stream>>>(*a);
