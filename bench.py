@@ -408,6 +408,13 @@ def main():
                             "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": 485e6,
                             "traffic_source": "ncu, same workload (profiles/decode_stream_kernel_ncu_full.md)", "peak_source": pk["source"],
                             "ms_per_launch": ms_k}
+        # the same step replayed from a CUDA graph (fla_b200.decode): fixed buffers, state updated in place
+        from fla_b200.decode import GatedDeltaRuleDecoder
+        dec = GatedDeltaRuleDecoder(B, H, K, V, dtype=dtype, initial_state=h0)
+        for n_ in ("q", "k", "v", "g", "beta"):
+            getattr(dec, n_).copy_(i[n_].view_as(getattr(dec, n_)))
+        ms_g = time_stage(dec.replay, reps=50, warm=5)
+        line["graph_replay"] = {"ms_per_step": ms_g, "value": B / (ms_g * 1e-3), "unit": UNIT}
 
     # ---- end to end: host buffers in, every result back to the host, inside the timed region
     if not args.no_extras:

@@ -510,3 +510,31 @@ def test_one_long_sequence_tail_matches_recurrent():
     assert torch.isfinite(o).all()
     assert_close("o tail", o_t, o[:, cut:], 5e-3)
     assert_close("ht", ht_t, ht, 5e-3)
+
+
+@pytest.mark.gpu
+def test_decoder_graph_replay_matches_functional_api():
+    """The CUDA-graph decode loop (state updated in place) gives bit-identical o and state to calling
+    fused_recurrent_gated_delta_rule once per token."""
+    from fla_b200.decode import GatedDeltaRuleDecoder
+    from fla_b200.ops import fused_recurrent_gated_delta_rule
+    torch.manual_seed(11)
+    B, H, K, V, steps = 5, 3, 128, 128, 6
+    dt = torch.bfloat16
+    h0 = torch.randn(B, H, K, V, device="cuda") * 0.1
+    dec = GatedDeltaRuleDecoder(B, H, K, V, dtype=dt, initial_state=h0)
+    eager = GatedDeltaRuleDecoder(B, H, K, V, dtype=dt, initial_state=h0, use_graph=False)
+    S = h0.clone()
+    for t in range(steps):
+        q = torch.randn(B, 1, H, K, device="cuda").to(dt)
+        k = torch.nn.functional.normalize(torch.randn(B, 1, H, K, device="cuda"), dim=-1).to(dt)
+        v = torch.randn(B, 1, H, V, device="cuda").to(dt)
+        g = torch.nn.functional.logsigmoid(torch.randn(B, 1, H, device="cuda"))
+        beta = torch.rand(B, 1, H, device="cuda").to(dt)
+        o_ref, S = fused_recurrent_gated_delta_rule(q, k, v, g, beta, initial_state=S, output_final_state=True, head_first=False)
+        o = dec.step(q, k, v, g, beta)
+        o2 = eager.step(q, k, v, g, beta)
+        assert torch.equal(o, o_ref) and torch.equal(o2, o_ref), t
+    assert torch.equal(dec.state, S) and torch.equal(eager.state, S)
+    from fla_b200 import _lib
+    assert _lib.load().flab_tc_error_state() == 0
