@@ -260,23 +260,29 @@ extern "C" {
 int flab_delta_fwd_h(const flab_args *a, void *stream) {
   using namespace flab;
   if (int e = check_common(a)) return e;
-  FLAB_REQUIRE(a->k && a->w && a->u && a->h && a->v_new, FLAB_E_BADARG, "delta_fwd_h needs k, w, u, h and v_new");
+  const bool state_only = (a->flags & FLAB_F_STATE_ONLY) != 0;
+  FLAB_REQUIRE(a->k && a->w && a->u && (state_only || (a->h && a->v_new)), FLAB_E_BADARG, "delta_fwd_h needs k, w, u, h and v_new");
+  FLAB_REQUIRE(!state_only || a->ht, FLAB_E_BADARG, "delta_fwd_h: a state-only scan needs ht");
   if (tc_scan_enabled()) {
     const int r = tc_delta_fwd_h_try(a, (cudaStream_t)stream);
     if (r != 0) return r < 0 ? r : FLAB_OK;
   }
+  FLAB_REQUIRE(!state_only, FLAB_E_UNSUPPORTED, "delta_fwd_h: state-only scans cover bf16 / fp16 with K = 128 and V a multiple of 64");
   return dispatch_delta_h<false>(a, stream);
 }
 
 int flab_delta_bwd_dhu(const flab_args *a, void *stream) {
   using namespace flab;
   if (int e = check_common(a)) return e;
-  FLAB_REQUIRE(a->q && a->k && a->w && a->d_o && a->dv && a->dh && a->dv2, FLAB_E_BADARG,
+  const bool state_only = (a->flags & FLAB_F_STATE_ONLY) != 0;
+  FLAB_REQUIRE(a->q && a->k && a->w && a->d_o && a->dv && (state_only || (a->dh && a->dv2)), FLAB_E_BADARG,
                "delta_bwd_dhu needs q, k, w, d_o, dv, dh and dv2");
+  FLAB_REQUIRE(!state_only || a->dh0, FLAB_E_BADARG, "delta_bwd_dhu: a state-only scan needs dh0");
   if (tc_scan_enabled()) {
     const int r = tc_delta_bwd_dhu_try(a, (cudaStream_t)stream);
     if (r != 0) return r < 0 ? r : FLAB_OK;
   }
+  FLAB_REQUIRE(!state_only, FLAB_E_UNSUPPORTED, "delta_bwd_dhu: state-only scans cover bf16 / fp16 with K = 128 and V a multiple of 64");
   return dispatch_delta_h<true>(a, stream);
 }
 }

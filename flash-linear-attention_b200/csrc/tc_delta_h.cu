@@ -33,6 +33,7 @@ struct TcDhParams {
   flab_args a;
   int v_tiles;  // V / BV
   int ab_fmt;   // 1 bf16, 0 fp16
+  int state_only;  // delta modes: h / v_new (dh / dv2) are not stored, only the final state
 };
 
 enum { DH_FWD = 0, DH_BWD = 1, DH_SIMPLE_FWD = 2, DH_SIMPLE_BWD = 3, DH_GK_FWD = 4, DH_GK_BWD = 5 };
@@ -260,7 +261,7 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
       }
       named_barrier(1, ET);  // gates visible; the previous chunk's v_new store has drained its staging tile
       if (abort_snap[0]) break;
-      if (tid == 0) {  // h[t]: one tile store per 64-column box, straight from the operand tile
+      if (tid == 0 && !p.state_only) {  // h[t]: one tile store per 64-column box, straight from the operand tile
 #pragma unroll
         for (int j = 0; j < VB; ++j) tma_store_2d(&mapH, sS + j * (K * 128), v0 + 64 * j, ((s.c0 + chunk_at(i)) * a.H + hd) * K);
         tma_store_commit();
@@ -393,7 +394,7 @@ tc_delta_h_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_consta
       }
       named_barrier(1, ET);  // v_new tile complete
       if (abort_snap[1]) break;
-      if (SIMPLE) continue;  // no corrected tile to store
+      if (SIMPLE || p.state_only) continue;  // no corrected tile to store
       if (rows == C) {
         if (tid == 0) {
           const int t0 = s.bos + it * C, c1 = a.head_first ? t0 : hd, c2 = a.head_first ? hd : t0;
@@ -434,12 +435,15 @@ template <int VB, int NS, int MODE> static int launch_tc_dh(const flab_args *a, 
   if (int e = make_token_map(&mA3, (BWD && !SIMPLE) ? a->w : a1, a, a->K)) return e;
   if (int e = make_token_map(&mY, y, a, a->V)) return e;
   if (int e = make_token_map(&mDo, (BWD && !SIMPLE) ? a->d_o : y, a, a->V)) return e;
-  if (int e = make_state_map(&mH, BWD ? a->dh : a->h, a, 128)) return e;
-  if (int e = make_token_map(&mYo, SIMPLE ? y : (BWD ? a->dv2 : a->v_new), a, a->V)) return e;
+  // a state-only scan stores neither: the maps are still encoded (over a tensor of the right element type) and never used
+  const bool state_only = !SIMPLE && (a->flags & FLAB_F_STATE_ONLY) != 0;
+  if (int e = make_state_map(&mH, state_only ? a->k : (BWD ? a->dh : a->h), a, 128)) return e;
+  if (int e = make_token_map(&mYo, (SIMPLE || state_only) ? y : (BWD ? a->dv2 : a->v_new), a, a->V)) return e;
   TcDhParams p;
   p.a = *a;
   p.v_tiles = a->V / BV;
   p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
+  p.state_only = state_only ? 1 : 0;
   constexpr int NKT = SIMPLE ? 1 : (BWD ? 3 : 2), NVT = (BWD && !SIMPLE) ? 2 : 1;
   constexpr uint32_t STAGE = NKT * 16384 + NVT * VB * 8192;
   const size_t smem = 1024 + NS * (size_t)STAGE + (size_t)VB * 128 * 128 + 2 * (size_t)VB * 8192 + 2 * (GK ? 128 : C) * sizeof(float);

@@ -21,6 +21,7 @@ _DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 F_REVERSE = 1 << 0
 F_BETA_VECTOR = 1 << 1
 F_INPLACE_STATE = 1 << 2
+F_STATE_ONLY = 1 << 4
 
 _PTR_FIELDS = [
     "q", "k", "v", "g", "gk", "gv", "beta", "w", "u", "aw", "au", "h", "h0", "ht", "v_new", "o",

@@ -154,4 +154,119 @@ def chunk_gated_delta_rule_bwd_dhu(geo: Geometry, q, k, w, do, dv, scale, g=None
     return dh, dh0, dv2
 
 
-__all__ = [n for n in dir() if n.startswith(("chunk_", "fwd_", "bwd_"))] + ["prepare_varlen", "Geometry"]
+# ---------------------------------------------------------------------------------------------
+# Delta-rule scans of a FEW LONG sequences, split into slabs along T on one GPU
+# ---------------------------------------------------------------------------------------------
+# The scan is a serial chain per (sequence, head, 128 value columns); with one 2^20-token sequence and 16 heads that is
+# 16 CTAs on 148 SMs.  The chain is affine in the state, S_out = M S_in + b per slab, so the sequence is cut into S
+# slabs that are scanned as S independent sequences, twice: a first pass from the initial state [0 | I] over the
+# value columns [u | 0] yields every slab's (b, M) at once, the slabs' true initial states follow from S - 1 small
+# matrix products, and the second pass starts every slab from its true state.  The backward scan is the transposed
+# chain (dS_in = M^T dS_out + c): its first pass runs from zero to get c, M is kept from the forward.  This is the
+# single-GPU form of the hand-off in fla_b200.parallel (there a slab per rank, here a slab per group of SMs).
+SLAB_MIN_CHUNKS = 256        # chunks per sequence below which the split is not tried
+SLAB_MIN_CHUNKS_PER_SLAB = 64
+_SLAB_VARLEN = {}
+
+
+class SlabPlan:
+    """How the sequences of one call are cut: `S` slabs per sequence, `lengths` of all B * S slabs in order."""
+
+    def __init__(self, B, T, S, chunks_per_slab, device):
+        self.B, self.T, self.S = B, T, S
+        L = chunks_per_slab * CHUNK
+        per_seq = [min(L, T - i * L) for i in range(S)]
+        key = (B, T, S, str(device))
+        if key not in _SLAB_VARLEN:
+            if len(_SLAB_VARLEN) > 16:
+                _SLAB_VARLEN.clear()
+            from ..utils import varlen_from_lengths
+            _SLAB_VARLEN[key] = varlen_from_lengths(per_seq * B, device)
+        self.varlen = _SLAB_VARLEN[key]
+
+    def geometry(self, k, v):
+        """Packed geometry of the slabs over `[B, T, H, D]` tensors viewed as `[1, B * T, H, D]`."""
+        return Geometry.packed(k.view(1, -1, *k.shape[2:]), v.view(1, -1, *v.shape[2:]), self.varlen)
+
+
+def slab_plan(geo: Geometry, k: torch.Tensor) -> Optional[SlabPlan]:
+    """A plan when the call is a few long fixed-length sequences in the domain of the tensor-core scan, else None."""
+    import os
+    if os.environ.get("FLA_B200_NO_SLABS") or os.environ.get("FLA_B200_NO_TC"):
+        return None
+    if geo.varlen is not None or geo.head_first or k.dtype not in (torch.bfloat16, torch.float16):
+        return None
+    if geo.K != 128 or geo.V % 128 != 0:
+        return None
+    nts = -(-geo.T // CHUNK)
+    chains = geo.B * geo.H * (geo.V // 128)
+    sms = torch.cuda.get_device_properties(k.device).multi_processor_count
+    S = min(sms // chains, nts // SLAB_MIN_CHUNKS_PER_SLAB, 16)
+    if nts < SLAB_MIN_CHUNKS or S < 2:
+        return None
+    per = -(-nts // S)
+    return SlabPlan(geo.B, geo.T, -(-nts // per), per, k.device)
+
+
+def slab_delta_fwd_h(plan: SlabPlan, geo: Geometry, k, w, u, g=None, h0=None, output_final_state=False):
+    """`chunk_gated_delta_rule_fwd_h` over slabs. Returns (h, v_new, ht, M) with M `[B, S, H, K, K]` fp32, the slabs'
+    state transitions (kept for the backward scan)."""
+    from .._lib import F_STATE_ONLY
+    B, S, H, K, V = plan.B, plan.S, geo.H, geo.K, geo.V
+    dev = k.device
+    gv = None if g is None else g.view(1, -1, H)
+    # pass 1: [b | M] of every slab
+    u_ext = torch.cat([u, torch.zeros_like(k)], dim=-1)
+    h0_ext = torch.zeros(B * S, H, K, V + K, dtype=torch.float32, device=dev)
+    h0_ext[..., V:] = torch.eye(K, dtype=torch.float32, device=dev)
+    ht_ext = torch.empty_like(h0_ext)
+    ge = plan.geometry(k, u_ext)
+    _lib.call("flab_delta_fwd_h", k, **ge.kw(), flags=F_STATE_ONLY, k=k, w=w, u=u_ext, g=gv, h0=h0_ext, ht=ht_ext)
+    del u_ext, h0_ext
+    ht_ext = ht_ext.view(B, S, H, K, V + K)
+    b_, M = ht_ext[..., :V], ht_ext[..., V:].contiguous()
+    # true initial state of every slab
+    S_in = torch.empty(B, S, H, K, V, dtype=torch.float32, device=dev)
+    cur = torch.zeros(B, H, K, V, dtype=torch.float32, device=dev) if h0 is None else h0.float()
+    for s_ in range(S):
+        S_in[:, s_] = cur
+        if s_ + 1 < S:
+            cur = torch.matmul(M[:, s_], cur) + b_[:, s_]
+    # pass 2
+    gs = plan.geometry(k, u)
+    h = torch.empty(geo.NT, H, K, V, dtype=k.dtype, device=dev)
+    v_new = torch.empty_like(u)
+    ht_s = torch.empty(B * S, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
+    _lib.call("flab_delta_fwd_h", k, **gs.kw(), k=k, w=w, u=u, g=gv, h0=S_in.view(B * S, H, K, V), h=h, v_new=v_new, ht=ht_s)
+    ht = ht_s.view(B, S, H, K, V)[:, -1].contiguous() if output_final_state else None
+    return h, v_new, ht, M
+
+
+def slab_delta_bwd_dhu(plan: SlabPlan, geo: Geometry, M, q, k, w, do, dv, scale, g=None, dht=None, want_dh0=False):
+    """`chunk_gated_delta_rule_bwd_dhu` over slabs, with the transitions M of the forward. Returns (dh, dh0, dv2)."""
+    from .._lib import F_STATE_ONLY
+    B, S, H, K, V = plan.B, plan.S, geo.H, geo.K, geo.V
+    dev = q.device
+    gv = None if g is None else g.view(1, -1, H)
+    gs = plan.geometry(k, dv)
+    # pass 1: c of every slab (the state gradient a slab hands to its predecessor when it receives zero)
+    c_ = torch.empty(B * S, H, K, V, dtype=torch.float32, device=dev)
+    _lib.call("flab_delta_bwd_dhu", q, **gs.kw(), scale=scale, flags=F_STATE_ONLY, q=q, k=k, w=w, g=gv, d_o=do, dv=dv, dh0=c_)
+    c_ = c_.view(B, S, H, K, V)
+    D_out = torch.empty(B, S, H, K, V, dtype=torch.float32, device=dev)
+    cur = torch.zeros(B, H, K, V, dtype=torch.float32, device=dev) if dht is None else dht.float()
+    for s_ in range(S - 1, -1, -1):
+        D_out[:, s_] = cur
+        if s_ > 0:
+            cur = torch.matmul(M[:, s_].transpose(-1, -2), cur) + c_[:, s_]
+    # pass 2
+    dh = torch.empty(geo.NT, H, K, V, dtype=q.dtype, device=dev)
+    dv2 = torch.empty_like(dv)
+    dh0_s = torch.empty(B * S, H, K, V, dtype=torch.float32, device=dev) if want_dh0 else None
+    _lib.call("flab_delta_bwd_dhu", q, **gs.kw(), scale=scale, q=q, k=k, w=w, g=gv, dht=D_out.view(B * S, H, K, V), d_o=do, dv=dv,
+              dh=dh, dh0=dh0_s, dv2=dv2)
+    dh0 = dh0_s.view(B, S, H, K, V)[:, 0].contiguous() if want_dh0 else None
+    return dh, dh0, dv2
+
+
+__all__ = [n for n in dir() if n.startswith(("chunk_", "fwd_", "bwd_", "slab_"))] + ["prepare_varlen", "Geometry"]

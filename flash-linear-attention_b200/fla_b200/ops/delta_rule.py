@@ -14,22 +14,33 @@ from .simple_gla import check_varlen_args
 
 def chunk_delta_rule_fwd(geo, q, k, v, beta, scale, initial_state, output_final_state):
     aw, _, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta)
-    h, v_new, ht = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, h0=initial_state, output_final_state=output_final_state)
+    plan, M = C.slab_plan(geo, k), None
+    if plan is not None:  # a few long sequences: the scan runs over slabs of T side by side
+        h, v_new, ht, M = C.slab_delta_fwd_h(plan, geo, k, w, u, h0=initial_state, output_final_state=output_final_state)
+    else:
+        h, v_new, ht = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, h0=initial_state, output_final_state=output_final_state)
     o = C.chunk_fwd_o(geo, q, k, v_new, h, scale=scale)
-    return o, aw, ht, (w, h, v_new)
+    return o, aw, ht, (w, h, v_new, M)
 
 
 def chunk_delta_rule_bwd(geo, q, k, v, beta, aw, scale, initial_state, do, dht, saved=None):
-    """Same stage order as fla/ops/delta_rule/chunk.py:70-163. `saved` = (w, h, v_new) kept from
-    forward; None recomputes them like the reference."""
+    """Same stage order as fla/ops/delta_rule/chunk.py:70-163. `saved` = (w, h, v_new, M) kept from
+    forward (M: slab transitions of a split scan, else None); None recomputes them like the reference."""
+    plan = C.slab_plan(geo, k)
     if saved is not None:
-        w, h, v_new = saved
+        w, h, v_new, M = saved
     else:
         w, u = C.fwd_recompute_w_u(geo, k, v, beta, aw)
-        h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, h0=initial_state, output_final_state=False)
+        if plan is not None:
+            h, v_new, _, M = C.slab_delta_fwd_h(plan, geo, k, w, u, h0=initial_state, output_final_state=False)
+        else:
+            h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, h0=initial_state, output_final_state=False)
     dv = C.chunk_bwd_dv_local(geo, q, k, None, do, scale)
-    dh, dh0, dv = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, dht=dht,
-                                                   want_dh0=initial_state is not None)
+    if plan is not None:
+        dh, dh0, dv = C.slab_delta_bwd_dhu(plan, geo, M, q, k, w, do, dv, scale, dht=dht, want_dh0=initial_state is not None)
+    else:
+        dh, dh0, dv = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, dht=dht,
+                                                       want_dh0=initial_state is not None)
     dq, dk, dw, _ = C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, w=w, dv=dv)
     dk, dv, db, _ = C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv, dk_in=dk)
     return dq, dk, dv, db, dh0

@@ -17,10 +17,14 @@ def chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta, scale, initial_state, outp
     """Stage order of fla/ops/gated_delta_rule/chunk.py:20-73."""
     g = C.chunk_local_cumsum(g, offsets=geo.offsets_tensor, head_first=geo.head_first)
     aw, au, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta, g=g)
-    h, v_new, ht = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=initial_state,
-                                                  output_final_state=output_final_state)
+    plan, M = C.slab_plan(geo, k), None
+    if plan is not None:  # a few long sequences: the scan runs over slabs of T side by side
+        h, v_new, ht, M = C.slab_delta_fwd_h(plan, geo, k, w, u, g=g, h0=initial_state, output_final_state=output_final_state)
+    else:
+        h, v_new, ht = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=initial_state,
+                                                      output_final_state=output_final_state)
     o = C.chunk_fwd_o(geo, q, k, v_new, h, g=g, scale=scale)
-    return g, o, aw, au, ht, (w, h, v_new)
+    return g, o, aw, au, ht, (w, h, v_new, M)
 
 
 def chunk_gated_delta_rule_fwd_fused(geo, q, k, v, g, beta, scale, initial_state, output_final_state):
@@ -40,15 +44,22 @@ def chunk_gated_delta_rule_fwd_fused(geo, q, k, v, g, beta, scale, initial_state
 
 def chunk_gated_delta_rule_bwd(geo, q, k, v, g, beta, aw, au, scale, initial_state, do, dht, saved=None):
     """Stage order of fla/ops/gated_delta_rule/chunk.py:76-177; `g` is the chunk-local cumsum.
-    `saved` = (w, h, v_new) kept from forward; None recomputes them like the reference."""
+    `saved` = (w, h, v_new, M) kept from forward (M: slab transitions of a split scan, else None); None recomputes them like the reference."""
+    plan = C.slab_plan(geo, k)
     if saved is not None:
-        w, h, v_new = saved
+        w, h, v_new, M = saved
     else:
         w, u = C.fwd_recompute_w_u(geo, k, v, beta, aw, au)
-        h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=initial_state, output_final_state=False)
+        if plan is not None:
+            h, v_new, _, M = C.slab_delta_fwd_h(plan, geo, k, w, u, g=g, h0=initial_state, output_final_state=False)
+        else:
+            h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=initial_state, output_final_state=False)
     dv = C.chunk_bwd_dv_local(geo, q, k, g, do, scale)
-    dh, dh0, dv = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g, dht=dht,
-                                                   want_dh0=initial_state is not None)
+    if plan is not None:
+        dh, dh0, dv = C.slab_delta_bwd_dhu(plan, geo, M, q, k, w, do, dv, scale, g=g, dht=dht, want_dh0=initial_state is not None)
+    else:
+        dh, dh0, dv = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g, dht=dht,
+                                                       want_dh0=initial_state is not None)
     dq, dk, dw, dg = C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=g, w=w, dv=dv)
     dk, dv, db, dg2 = C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv, g=g, au=au, dk_in=dk)
     dg.add_(dg2)
@@ -110,6 +121,10 @@ def chunk_gated_delta_rule(
     if not needs_grad and not torch.is_autocast_enabled():
         q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
         geo = Geometry(k, v, offsets, head_first)
+        if C.slab_plan(geo, k) is not None:  # a few long sequences: staged forward, scan split into slabs of T
+            _, o, _, _, ht, _ = chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta.to(k.dtype), scale, initial_state,
+                                                           output_final_state)
+            return o.to(q.dtype), ht
         return chunk_gated_delta_rule_fwd_fused(geo, q, k, v, g, beta.to(k.dtype), scale, initial_state,
                                                 output_final_state)
     return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, offsets,

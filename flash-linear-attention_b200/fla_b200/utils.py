@@ -84,6 +84,18 @@ def prepare_varlen(offsets: Optional[torch.Tensor], device) -> Optional[Varlen]:
     return out
 
 
+def varlen_from_lengths(lengths, device) -> Varlen:
+    """The same tables as `prepare_varlen`, from sequence lengths already known on the host (no device read)."""
+    host = [0]
+    for L in lengths:
+        host.append(host[-1] + int(L))
+    indices, chunk_offsets = chunk_tables(lengths)
+    cu = torch.tensor(host, dtype=torch.int32, device=device)
+    idx = torch.tensor(indices if indices else [(0, 0)], dtype=torch.int32, device=device).reshape(-1, 2)
+    co = torch.tensor(chunk_offsets, dtype=torch.int32, device=device)
+    return Varlen(cu, idx, co, len(lengths), len(indices), list(lengths))
+
+
 def resolve_offsets(offsets, cu_seqlens):
     """`cu_seqlens=` is accepted as an alias of the reference's `offsets=` keyword."""
     if offsets is not None and cu_seqlens is not None:
@@ -107,6 +119,18 @@ class Geometry:
             self.N, self.NT = self.varlen.N, self.varlen.NT
         else:
             self.N, self.NT = self.B, self.B * (-(-self.T // CHUNK))
+
+    @classmethod
+    def packed(cls, k: torch.Tensor, v: Optional[torch.Tensor], varlen: Varlen) -> "Geometry":
+        """Geometry of sequences packed seq-first into B = 1 (`k` is `[1, T, H, K]`), from ready-made tables."""
+        geo = cls.__new__(cls)
+        geo.B, geo.T, geo.H, geo.K = k.shape
+        geo.V = v.shape[-1] if v is not None else 0
+        geo.head_first = False
+        geo.offsets_tensor = varlen.cu_seqlens
+        geo.varlen = varlen
+        geo.N, geo.NT = varlen.N, varlen.NT
+        return geo
 
     def kw(self):
         return dict(B=self.B, T=self.T, H=self.H, K=self.K, V=self.V, N=self.N, NT=self.NT,

@@ -48,7 +48,8 @@ enum {
   FLAB_F_REVERSE = 1 << 0,       /* cumsum / recurrence run from the last token to the first */
   FLAB_F_BETA_VECTOR = 1 << 1,   /* fused_recurrent_delta_rule: beta is [.., V] not scalar    */
   FLAB_F_INPLACE_STATE = 1 << 2, /* decode: ht may alias h0                                   */
-  FLAB_F_UPPER = 1 << 3          /* reserved                                                  */
+  FLAB_F_UPPER = 1 << 3,         /* reserved                                                  */
+  FLAB_F_STATE_ONLY = 1 << 4     /* delta scans: only the final state is wanted (h, v_new / dh, dv2 may be NULL) */
 };
 
 typedef struct flab_args {
@@ -138,10 +139,13 @@ int flab_wy_bwd(const flab_args *a, void *stream);
 
 /* ---- state recurrence of the (gated) delta rule ----------------------------------------------
  * Replaces chunk_gated_delta_rule_fwd_h (fla/ops/common/chunk_delta_h.py:248): reads k, w, u,
- * g (optional), h0 (optional); writes h, v_new, ht (optional). */
+ * g (optional), h0 (optional); writes h, v_new, ht (optional). With FLAB_F_STATE_ONLY only ht is
+ * written (h and v_new may be NULL): the first pass of a scan split into slabs along T, which needs
+ * each slab's transition only. bf16 / fp16, K = 128, V a multiple of 64; FLAB_E_UNSUPPORTED otherwise. */
 int flab_delta_fwd_h(const flab_args *a, void *stream);
 /* Replaces chunk_gated_delta_rule_bwd_dhu (fla/ops/common/chunk_delta_h.py:323): reads q, k, w,
- * g (optional), dht (optional), d_o, dv; writes dh, dv2, dh0 (optional). */
+ * g (optional), dht (optional), d_o, dv; writes dh, dv2, dh0 (optional). FLAB_F_STATE_ONLY: only
+ * dh0 is written (dh and dv2 may be NULL), same domain as above. */
 int flab_delta_bwd_dhu(const flab_args *a, void *stream);
 
 /* ---- GLA (per-channel gates) -----------------------------------------------------------------

@@ -538,3 +538,36 @@ def test_decoder_graph_replay_matches_functional_api():
     assert torch.equal(dec.state, S) and torch.equal(eager.state, S)
     from fla_b200 import _lib
     assert _lib.load().flab_tc_error_state() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("family,B,T,gate_div", [
+    ("gated", 1, 1100, 30.0),   # weak decay: the slabs' transitions M matter; ragged last slab and chunk
+    ("gated", 2, 1024, 1.0),
+    ("delta", 1, 1024, None),
+])
+def test_scan_split_into_slabs_matches_oracle(monkeypatch, family, B, T, gate_div):
+    """The slab-split scans (forced at a small T) against the oracle, forward and every gradient, at the same bars
+    as the one-chain scans; and the split really ran (transitions M saved)."""
+    from fla_b200.ops import common as C
+    monkeypatch.setattr(C, "SLAB_MIN_CHUNKS", 8)
+    monkeypatch.setattr(C, "SLAB_MIN_CHUNKS_PER_SLAB", 3)
+    H, K, V = 2, 128, 128
+    if family == "gated":
+        d = build(B, T, H, K, V, torch.bfloat16, seed=T, gate="scalar", beta=True, h0=True, norm=True, gate_div=gate_div)
+        names, gpu, ref = ["q", "k", "v", "g", "beta", "h0"], _gdelta_gpu, _gdelta_ref
+    else:
+        d = build(B, T, H, K, V, torch.bfloat16, seed=T, beta=True, h0=True, norm=True)
+        names, gpu, ref = ["q", "k", "v", "beta", "h0"], _delta_gpu, _delta_ref
+    from fla_b200.utils import Geometry
+    kk = d["k"].to(DEV)
+    plan = C.slab_plan(Geometry(kk, d["v"].to(DEV), None, False), kk)
+    assert plan is not None and plan.S >= 4
+    run_both(gpu, ref, d, names, head_first=False, tol_over=DELTA_TOL)
+    # forward only (no autograd): the same split
+    with torch.no_grad():
+        i = {n: x.to(DEV) for n, x in d.items()}
+        o, ht = gpu(i, head_first=False)
+        o_r, ht_r = ref({n: (x.float() if x.is_floating_point() else x) for n, x in d.items()})
+    assert_close("o (no grad)", o_r, o, 5e-3)
+    assert_close("ht (no grad)", ht_r, ht, 5e-3)
