@@ -4,10 +4,13 @@
 //   bwd_dav   : dA = tril(do v^T) * scale;  dv = tril(A)^T do + (k e^{b_L-b}) dh (fla/ops/gla/chunk.py:583-710)
 //   bwd_dqkg  : dq, dk (intra + inter) and dg with the in-chunk reverse cumsum   (fla/ops/gla/chunk.py:409-567, 726-837)
 // The gate couples every (i, j, channel) triple, so the intra-chunk terms are not one GEMM with row / column
-// scaling.  They are evaluated in fp32 with the gate factors split at a reference row per block of 16 rows,
-// e^{b_i - b_j} = e^{b_i - b_r} e^{b_r - b_j}: the exponentials are taken once per element and the (i, j) pairs
-// become plain FMAs; a block whose decay over its 16 tokens would overflow the split takes the direct form.
-// The state products use the tile GEMM.
+// scaling.  The gate factors are split at the first row r of each block of 16 rows,
+// e^{b_i - b_j} = e^{b_i - b_r} e^{b_r - b_j}: the exponentials are taken once per element and each 16-row block
+// becomes one tile product on fp32 operand tiles (TF32 tensor-core path for 16-bit element types - bf16 operands
+// are too coarse for dg, a difference of nearly cancelling sums - and plain FMAs for fp32); a block whose decay
+// over its 16 tokens would overflow the split takes the direct form.  The state products use the tile GEMM.
+// No global load sits between two barriers: inputs of a later phase are copied asynchronously (cp.async) while
+// the earlier phase computes, gate rows are fetched into registers before the wait on the tile copies.
 #include "common.cuh"
 
 namespace flab {

@@ -433,7 +433,10 @@ template <int VB, int NS, int MODE> static int launch_tc_dh(const flab_args *a, 
   if (int e = make_token_map(&mA1, a1, a, a->K)) return e;
   if (int e = make_token_map(&mA2, SIMPLE ? a1 : (BWD ? a->q : a->k), a, a->K)) return e;
   if (int e = make_token_map(&mA3, (BWD && !SIMPLE) ? a->w : a1, a, a->K)) return e;
-  if (int e = make_token_map(&mY, y, a, a->V)) return e;
+  // state-only forward scan: u may be narrower than the state (S = its columns); the tile loads past its last
+  // column are filled with zeros by the copy engine
+  const int ycols = (!SIMPLE && !BWD && (a->flags & FLAB_F_STATE_ONLY) && a->S > 0) ? a->S : a->V;
+  if (int e = make_token_map(&mY, y, a, ycols)) return e;
   if (int e = make_token_map(&mDo, (BWD && !SIMPLE) ? a->d_o : y, a, a->V)) return e;
   // a state-only scan stores neither: the maps are still encoded (over a tensor of the right element type) and never used
   const bool state_only = !SIMPLE && (a->flags & FLAB_F_STATE_ONLY) != 0;

@@ -216,13 +216,13 @@ def slab_delta_fwd_h(plan: SlabPlan, geo: Geometry, k, w, u, g=None, h0=None, ou
     dev = k.device
     gv = None if g is None else g.view(1, -1, H)
     # pass 1: [b | M] of every slab
-    u_ext = torch.cat([u, torch.zeros_like(k)], dim=-1)
     h0_ext = torch.zeros(B * S, H, K, V + K, dtype=torch.float32, device=dev)
     h0_ext[..., V:] = torch.eye(K, dtype=torch.float32, device=dev)
     ht_ext = torch.empty_like(h0_ext)
-    ge = plan.geometry(k, u_ext)
-    _lib.call("flab_delta_fwd_h", k, **ge.kw(), flags=F_STATE_ONLY, k=k, w=w, u=u_ext, g=gv, h0=h0_ext, ht=ht_ext)
-    del u_ext, h0_ext
+    ge = plan.geometry(k, u)
+    ge.V = V + K  # the state is V + K columns wide; u supplies the first V (S = V), the rest read as zero
+    _lib.call("flab_delta_fwd_h", k, **ge.kw(), flags=F_STATE_ONLY, S=V, k=k, w=w, u=u, g=gv, h0=h0_ext, ht=ht_ext)
+    del h0_ext
     ht_ext = ht_ext.view(B, S, H, K, V + K)
     b_, M = ht_ext[..., :V], ht_ext[..., V:].contiguous()
     # true initial state of every slab

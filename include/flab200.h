@@ -141,7 +141,9 @@ int flab_wy_bwd(const flab_args *a, void *stream);
  * Replaces chunk_gated_delta_rule_fwd_h (fla/ops/common/chunk_delta_h.py:248): reads k, w, u,
  * g (optional), h0 (optional); writes h, v_new, ht (optional). With FLAB_F_STATE_ONLY only ht is
  * written (h and v_new may be NULL): the first pass of a scan split into slabs along T, which needs
- * each slab's transition only. bf16 / fp16, K = 128, V a multiple of 64; FLAB_E_UNSUPPORTED otherwise. */
+ * each slab's transition only. bf16 / fp16, K = 128, V a multiple of 64; FLAB_E_UNSUPPORTED otherwise.
+ * In that mode S > 0 gives the number of value columns u really has (S < V, a multiple of 64): the state
+ * columns past S see u = 0, which is how the transition matrix is obtained next to the offset. */
 int flab_delta_fwd_h(const flab_args *a, void *stream);
 /* Replaces chunk_gated_delta_rule_bwd_dhu (fla/ops/common/chunk_delta_h.py:323): reads q, k, w,
  * g (optional), dht (optional), d_o, dv; writes dh, dv2, dh0 (optional). FLAB_F_STATE_ONLY: only
