@@ -26,10 +26,11 @@ def chunk_delta_rule_fwd(geo, q, k, v, beta, scale, initial_state, output_final_
 def chunk_delta_rule_bwd(geo, q, k, v, beta, aw, scale, initial_state, do, dht, saved=None):
     """Same stage order as fla/ops/delta_rule/chunk.py:70-163. `saved` = (w, h, v_new, M) kept from
     forward (M: slab transitions of a split scan, else None); None recomputes them like the reference."""
-    plan = C.slab_plan(geo, k)
     if saved is not None:
         w, h, v_new, M = saved
+        plan = C.slab_plan(geo, k) if M is not None else None  # split the reverse scan iff the forward one was
     else:
+        plan = C.slab_plan(geo, k)
         w, u = C.fwd_recompute_w_u(geo, k, v, beta, aw)
         if plan is not None:
             h, v_new, _, M = C.slab_delta_fwd_h(plan, geo, k, w, u, h0=initial_state, output_final_state=False)

@@ -45,10 +45,11 @@ def chunk_gated_delta_rule_fwd_fused(geo, q, k, v, g, beta, scale, initial_state
 def chunk_gated_delta_rule_bwd(geo, q, k, v, g, beta, aw, au, scale, initial_state, do, dht, saved=None):
     """Stage order of fla/ops/gated_delta_rule/chunk.py:76-177; `g` is the chunk-local cumsum.
     `saved` = (w, h, v_new, M) kept from forward (M: slab transitions of a split scan, else None); None recomputes them like the reference."""
-    plan = C.slab_plan(geo, k)
     if saved is not None:
         w, h, v_new, M = saved
+        plan = C.slab_plan(geo, k) if M is not None else None  # split the reverse scan iff the forward one was
     else:
+        plan = C.slab_plan(geo, k)
         w, u = C.fwd_recompute_w_u(geo, k, v, beta, aw, au)
         if plan is not None:
             h, v_new, _, M = C.slab_delta_fwd_h(plan, geo, k, w, u, g=g, h0=initial_state, output_final_state=False)

@@ -105,10 +105,19 @@ def _fwd_slab(q, k, v, g, beta, scale, S_in_of):
     g_cum = C.chunk_local_cumsum(g, head_first=False)
     aw, au, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta, g=g_cum)
     # one widened scan: value columns [u | 0], initial state [0 | I]  ->  final state [b | M]
-    u_ext = torch.cat([u, torch.zeros_like(k)], dim=-1)
-    h0_ext = torch.cat([torch.zeros(1, H, K, V, device=k.device), torch.eye(K, device=k.device).expand(1, H, K, K)], dim=-1)
-    geo_ext = Geometry(k, u_ext, None, False)
-    _, _, ht_ext = C.chunk_gated_delta_rule_fwd_h(geo_ext, k, w, u_ext, g=g_cum, h0=h0_ext.contiguous(), output_final_state=True)
+    h0_ext = torch.cat([torch.zeros(1, H, K, V, device=k.device), torch.eye(K, device=k.device).expand(1, H, K, K)], dim=-1).contiguous()
+    import os
+    if k.dtype in (torch.bfloat16, torch.float16) and K == 128 and V % 64 == 0 and not os.environ.get("FLA_B200_NO_TC"):
+        # state-only scan: nothing but the final state is stored, u itself is read (columns past V are zero-filled)
+        from . import _lib
+        geo_ext = Geometry(k, u, None, False)
+        geo_ext.V = V + K
+        ht_ext = torch.empty_like(h0_ext)
+        _lib.call("flab_delta_fwd_h", k, **geo_ext.kw(), flags=_lib.F_STATE_ONLY, S=V, k=k, w=w, u=u, g=g_cum, h0=h0_ext, ht=ht_ext)
+    else:
+        u_ext = torch.cat([u, torch.zeros_like(k)], dim=-1)
+        geo_ext = Geometry(k, u_ext, None, False)
+        _, _, ht_ext = C.chunk_gated_delta_rule_fwd_h(geo_ext, k, w, u_ext, g=g_cum, h0=h0_ext, output_final_state=True)
     b, M = ht_ext[0, :, :, :V].contiguous(), ht_ext[0, :, :, V:].contiguous()
     S_in, S_out = S_in_of(M, b)
     # correction pass with the true initial state
@@ -165,12 +174,18 @@ class SPChunkGatedDeltaRuleFunction(torch.autograd.Function):
         do = do.contiguous()
         # what this slab's outputs alone contribute to the gradient of its initial state (dS_out = 0)
         dv = C.chunk_bwd_dv_local(geo, q, k, g_cum, do, scale)
-        _, c, _ = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g_cum, dht=None, want_dh0=True)
+        import os
+        if k.dtype in (torch.bfloat16, torch.float16) and geo.K == 128 and geo.V % 64 == 0 and not os.environ.get("FLA_B200_NO_TC"):
+            from . import _lib  # state-only scan: only the gradient handed to the predecessor is stored
+            c = torch.empty(1, geo.H, geo.K, geo.V, dtype=torch.float32, device=k.device)
+            _lib.call("flab_delta_bwd_dhu", q, **geo.kw(), scale=scale, flags=_lib.F_STATE_ONLY, q=q, k=k, w=w, g=g_cum, d_o=do, dv=dv, dh0=c)
+        else:
+            _, c, _ = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g_cum, dht=None, want_dh0=True)
         # the gradient of the whole-sequence final state enters at the last rank
         ext = None if dht is None or rank != world - 1 else dht.float()[0]
         dS_out, dS_in = handoff_states(M.transpose(1, 2).contiguous(), c[0], ext, group, reverse=True)
         dq, dk, dv, db, dg, _ = chunk_gated_delta_rule_bwd(geo, q, k, v, g_cum, beta, aw, au, scale, S_in.unsqueeze(0), do,
-                                                          dS_out.unsqueeze(0), saved=(w, h, v_new))
+                                                          dS_out.unsqueeze(0), saved=(w, h, v_new, None))
         dh0 = dS_in.unsqueeze(0) if (ctx.has_h0 and rank == 0) else None
         if ctx.has_h0 and rank != 0:
             dh0 = torch.zeros_like(dS_in).unsqueeze(0)
