@@ -42,6 +42,7 @@ SIDE_METRICS = {
     "gla_fp32": "chunk_gla fwd+bwd tokens/s (fp32 B=2 T=512 H=4 D=64)",
     "varlen": "chunk_gated_delta_rule fwd+bwd tokens/s (64 packed sequences, H=32 D=128 bf16)",
     "decode": "fused_recurrent_gated_delta_rule decode tokens/s (256 sequences, H=16 D=128)",
+    "long": "chunk_gated_delta_rule fwd+bwd tokens/s (ONE sequence of 262144 tokens, H=16 D=128 bf16)",
 }
 
 # DRAM bytes per token-head of each stage's kernel, from the ncu capture summarised in
@@ -60,6 +61,9 @@ WORKLOADS = {
     "varlen": ("gated_delta_varlen", 1, 0, 32, 128, 128),
     # one decode step of 256 sequences: fused_recurrent_gated_delta_rule, T = 1, fp32 state carried
     "decode": ("decode", 256, 1, 16, 128, 128),
+    # one long sequence (a quarter of the 2^20-token configuration, so that the host-side input generation stays short):
+    # 16 (sequence, head) chains only, the scans run split into slabs of T
+    "long": ("gated_delta", 1, 262144, 16, 128, 128),
 }
 
 
@@ -307,7 +311,7 @@ def main():
     if op == "gated_delta_varlen":
         T = int(varlen_lengths().sum())
     dtype = torch.float32 if args.workload == "gla_fp32" else torch.bfloat16
-    if op in ("gated_delta_varlen", "decode"):
+    if op in ("gated_delta_varlen", "decode") or args.workload == "long":
         args.no_extras = True  # side workloads: device-resident timing (and the decode roofline) only
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
