@@ -40,6 +40,7 @@ SIDE_METRICS = {
     "delta": "chunk_delta_rule fwd+bwd tokens/s (H=16 D=128 T=4K bf16)",
     "retention": "chunk_simple_gla / retention fwd+bwd tokens/s (H=16 D=128 T=4K bf16)",
     "gla_fp32": "chunk_gla fwd+bwd tokens/s (fp32 B=2 T=512 H=4 D=64)",
+    "gla": "chunk_gla fwd+bwd tokens/s (H=16 D=128 T=4K bf16)",
     "varlen": "chunk_gated_delta_rule fwd+bwd tokens/s (64 packed sequences, H=32 D=128 bf16)",
     "decode": "fused_recurrent_gated_delta_rule decode tokens/s (256 sequences, H=16 D=128)",
     "long": "chunk_gated_delta_rule fwd+bwd tokens/s (ONE sequence of 262144 tokens, H=16 D=128 bf16)",
@@ -57,6 +58,7 @@ WORKLOADS = {
     "delta": ("delta", 8, 4096, 16, 128, 128),
     "retention": ("simple_gla", 8, 4096, 16, 128, 128),
     "gla_fp32": ("gla", 2, 512, 4, 64, 64),
+    "gla": ("gla", 8, 4096, 16, 128, 128),  # not a listed configuration: the GLA kernels at the shape of the others
     # 64 sequences of 256..8192 tokens (seeded), packed into one row with cu_seqlens, H=32
     "varlen": ("gated_delta_varlen", 1, 0, 32, 128, 128),
     # one decode step of 256 sequences: fused_recurrent_gated_delta_rule, T = 1, fp32 state carried
