@@ -176,7 +176,7 @@ class SlabPlan:
         self.B, self.T, self.S = B, T, S
         L = chunks_per_slab * CHUNK
         per_seq = [min(L, T - i * L) for i in range(S)]
-        key = (B, T, S, str(device))
+        key = (B, T, S, chunks_per_slab, str(device))
         if key not in _SLAB_VARLEN:
             if len(_SLAB_VARLEN) > 16:
                 _SLAB_VARLEN.clear()
