@@ -44,6 +44,7 @@ SIDE_METRICS = {
     "varlen": "chunk_gated_delta_rule fwd+bwd tokens/s (64 packed sequences, H=32 D=128 bf16)",
     "decode": "fused_recurrent_gated_delta_rule decode tokens/s (256 sequences, H=16 D=128)",
     "long": "chunk_gated_delta_rule fwd+bwd tokens/s (ONE sequence of 262144 tokens, H=16 D=128 bf16)",
+    "l2norm": "l2_norm fwd+bwd tokens/s (q and k of B=8 T=4096 H=16 D=128 bf16)",
 }
 
 # DRAM bytes per token-head of each stage's kernel, from the ncu capture summarised in
@@ -66,6 +67,8 @@ WORKLOADS = {
     # one long sequence (a quarter of the 2^20-token configuration, so that the host-side input generation stays short):
     # 16 (sequence, head) chains only, the scans run split into slabs of T
     "long": ("gated_delta", 1, 262144, 16, 128, 128),
+    # the step before the op in the reference's layers: l2_norm of q and of k, forward and backward (4 launches)
+    "l2norm": ("l2norm", 8, 4096, 16, 128, 128),
 }
 
 
@@ -116,7 +119,7 @@ def make_inputs(op, B, T, H, K, V, seed, dtype):
     return d
 
 
-GRAD_NAMES = {"gated_delta_varlen": ["q", "k", "v", "g", "beta", "h0"], "decode": [],
+GRAD_NAMES = {"gated_delta_varlen": ["q", "k", "v", "g", "beta", "h0"], "decode": [], "l2norm": ["q", "k"],
               "gated_delta": ["q", "k", "v", "g", "beta", "h0"], "delta": ["q", "k", "v", "beta", "h0"],
               "simple_gla": ["q", "k", "v", "g"], "gla": ["q", "k", "v", "g", "h0"]}
 
@@ -150,6 +153,12 @@ def call_op(op, i, mod):
 
 
 def fwd_bwd(op, i, mod="ours"):
+    if op == "l2norm":
+        from fla_b200.modules import l2_norm
+        i["q"].grad = i["k"].grad = None
+        yq, yk = l2_norm(i["q"]), l2_norm(i["k"])
+        torch.autograd.backward([yq, yk], [i["do"], i["do"]])
+        return yq, yk
     if op == "decode":  # forward only; the new state replaces the old one
         o, ht = call_op(op, i, mod)
         i["h0"] = ht
@@ -313,7 +322,7 @@ def main():
     if op == "gated_delta_varlen":
         T = int(varlen_lengths().sum())
     dtype = torch.float32 if args.workload == "gla_fp32" else torch.bfloat16
-    if op in ("gated_delta_varlen", "decode") or args.workload == "long":
+    if op in ("gated_delta_varlen", "decode", "l2norm") or args.workload == "long":
         args.no_extras = True  # side workloads: device-resident timing (and the decode roofline) only
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
@@ -399,6 +408,14 @@ def main():
             "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic", "config": config,
             "clocks": clk.summary(), "gpu_launches": launches}
 
+    if op == "l2norm" and rank == 0:
+        # pure streaming: forward reads x and writes y, backward reads x and dy and writes dx, for q and for k
+        pk = peaks()
+        nbytes = 10 * B * T * H * K * 2
+        ach = nbytes / (ms_step * 1e-3) / 1e9
+        line["roofline"] = {"kernel": "l2norm_fwd_vec_kernel x2 + l2norm_bwd_vec_kernel x2 (whole step)", "bound": "hbm", "achieved": ach,
+                            "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                            "ms_per_launch": ms_step / 4}
     if op == "decode" and rank == 0:
         # the decode kernel alone (the public-API step above also pays Python / launch overhead per call)
         from fla_b200.ops.recurrent import recurrent_delta_fwd

@@ -28,3 +28,18 @@ def install_as_fla_ops():
     for name, mod in (("gla", gla), ("simple_gla", simple_gla), ("retention", retention),
                       ("delta_rule", delta_rule), ("gated_delta_rule", gated_delta_rule)):
         sys.modules[f"fla.ops.{name}"] = mod
+
+
+def install_as_fla_modules():
+    """Alias `fla.modules.l2norm` (and `fla.modules.l2_norm`) to this package's CUDA implementation."""
+    from . import modules
+    from .modules import l2norm
+    root = sys.modules.get("fla")
+    if root is None:
+        root = types.ModuleType("fla")
+        root.__path__ = []
+        sys.modules["fla"] = root
+    sys.modules["fla.modules"] = modules
+    sys.modules["fla.modules.l2norm"] = l2norm
+    root.modules = modules
+

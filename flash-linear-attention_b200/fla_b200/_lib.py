@@ -75,6 +75,12 @@ def load() -> ctypes.CDLL:
     lib.flab_gated_delta_rule_fwd_workspace.restype = ctypes.c_size_t
     lib.flab_gated_delta_rule_fwd_workspace.argtypes = [ctypes.POINTER(FlabArgs)]
     lib.flab_tc_error_state.restype = ctypes.c_int
+    lib.flab_l2norm_fwd.restype = ctypes.c_int
+    lib.flab_l2norm_fwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                    ctypes.c_float, ctypes.c_void_p]
+    lib.flab_l2norm_bwd.restype = ctypes.c_int
+    lib.flab_l2norm_bwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
+                                    ctypes.c_float, ctypes.c_void_p]
     _lib = lib
     return lib
 

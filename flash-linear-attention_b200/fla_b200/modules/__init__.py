@@ -1,0 +1,5 @@
+# -*- coding: utf-8 -*-
+"""Steps right before / after the chunk ops in the reference's layers (fla/modules)."""
+from .l2norm import L2NormFunction, l2_norm, l2norm_bwd, l2norm_fwd
+
+__all__ = ["L2NormFunction", "l2_norm", "l2norm_fwd", "l2norm_bwd"]

@@ -101,6 +101,14 @@ int flab_chunk_local_cumsum_vector(const flab_args *a, void *stream);
 int flab_chunk_global_cumsum_scalar(const flab_args *a, void *stream);
 int flab_chunk_global_cumsum_vector(const flab_args *a, void *stream);
 
+/* ---- row-wise L2 normalisation (the step before the chunk ops in the reference's layers) ------
+ * Replaces l2norm_fwd / l2norm_bwd (fla/modules/l2norm.py:89, :131): x is [rows, n] contiguous,
+ *   y = x / sqrt(sum_n x^2 + eps);  dx = dy r - sum_n(dy x) r / (sum_n x^2 + eps) x,  r = 1 / sqrt(sum_n x^2 + eps).
+ * Element types are FLAB_BF16 / FLAB_FP16 / FLAB_FP32; the forward output may be fp32 for 16-bit input or
+ * 16-bit for fp32 input (the reference's output_dtype). Arithmetic is fp32. rows == 0 is a no-op. */
+int flab_l2norm_fwd(const void *x, void *y, long long rows, int n, int in_dtype, int out_dtype, float eps, void *stream);
+int flab_l2norm_bwd(const void *x, const void *dy, void *dx, long long rows, int n, int dtype, float eps, void *stream);
+
 /* ---- inter-chunk state recurrence for diagonal decay ---------------------------------------
  * Replaces chunk_fwd_h (fla/ops/common/chunk_h.py:282): reads k, v, g or gk (either may be NULL),
  * h0 (optional); writes h (state at the start of every chunk) and ht (optional). */

@@ -6,9 +6,12 @@ used as a fallback compute path.
 
 Parity pin: every function here is checked in tests/test_oracle_golden.py against vectors produced
 by the reference's own naive PyTorch functions (tests/golden/make_golden.py, run against the
-reference checkout) - see each function's docstring for the reference file:line it restates.
+reference checkout) - see each function's docstring for the reference file:line it restates.  The L2-norm
+functions are pinned against outputs of the reference's Triton kernels run through Triton's CPU interpreter
+(tests/golden/make_golden_l2norm.py).
 """
 
 from .indexing import chunk_indices_ref, chunk_offsets_ref  # noqa: F401
+from .l2norm import l2_norm, l2_norm_bwd  # noqa: F401
 from .naive import (cumsum_global, cumsum_local, delta_rule, gated_delta_rule, gla, retention_log_decay,  # noqa: F401
                     simple_gla)

@@ -2,6 +2,8 @@
 against the CPU oracle on identical seeded inputs, the committed golden vectors of the reference,
 and size-independent properties.  Error metric and shape sweeps follow the reference's tests
 (tests/ops/test_{gla,simple_gla,retention,delta,gated_delta,cumsum}.py)."""
+import os
+
 import pytest
 import torch
 import torch.nn.functional as F
@@ -571,3 +573,47 @@ def test_scan_split_into_slabs_matches_oracle(monkeypatch, family, B, T, gate_di
         o_r, ht_r = ref({n: (x.float() if x.is_floating_point() else x) for n, x in d.items()})
     assert_close("o (no grad)", o_r, o, 5e-3)
     assert_close("ht (no grad)", ht_r, ht, 5e-3)
+
+
+# ------------------------------------------------------------------------------------------------
+# the step before the chunk ops: row-wise L2 normalisation (fla/modules/l2norm.py)
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape,dtype,out_dtype", [
+    ((2, 300, 4, 128), torch.bfloat16, None),
+    ((2, 300, 4, 128), torch.float16, torch.float32),
+    ((3, 77, 2, 64), torch.bfloat16, None),
+    ((1, 50, 3, 256), torch.float32, None),
+    ((1, 50, 3, 256), torch.float32, torch.bfloat16),
+    ((5, 100), torch.float32, None),          # row length that takes the column-loop kernel
+    ((4, 9, 72), torch.bfloat16, None),
+    ((1, 1, 1, 8), torch.float16, None),
+    ((0, 128), torch.bfloat16, None),         # empty input
+])
+def test_l2_norm_matches_oracle(shape, dtype, out_dtype):
+    from fla_b200.modules import l2_norm
+    g0 = torch.Generator().manual_seed(sum(shape) + 1)
+    x = (torch.randn(*shape, generator=g0) * 2).to(dtype)
+    dy = torch.randn(*shape, generator=g0).to(out_dtype or dtype)
+    xg = x.to(DEV).requires_grad_(True)
+    y = l2_norm(xg, 1e-6, out_dtype)
+    assert y.shape == x.shape and y.dtype == (out_dtype or dtype)
+    if x.numel() == 0:
+        return
+    tol = 1e-6 if (dtype == torch.float32 and out_dtype in (None, torch.float32)) else 5e-3
+    assert_close("y", oracle.l2_norm(x, 1e-6, out_dtype), y, tol)
+    y.backward(dy.to(DEV))
+    assert_close("dx", oracle.l2_norm_bwd(x, dy.to(dtype), 1e-6), xg.grad, 1e-6 if dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.gpu
+def test_l2_norm_reference_kernel_vectors():
+    """The CUDA kernels on the inputs of tests/golden/l2norm_vectors.npz (outputs of the reference's own kernels)."""
+    import numpy as np
+    from fla_b200.modules.l2norm import l2norm_bwd, l2norm_fwd
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "l2norm_vectors.npz"))
+    for case in ("f32_128", "f32_100", "f16_64", "f32_tiny"):
+        x, dy, y, dx = (torch.from_numpy(z[f"{case}.{n}"]) for n in ("x", "dy", "y", "dx"))
+        tol = 1e-6 if x.dtype == torch.float32 else 1e-3
+        assert_close(f"{case} y", y, l2norm_fwd(x.to(DEV), 1e-6), tol)
+        assert_close(f"{case} dx", dx, l2norm_bwd(x.to(DEV), dy.to(DEV), 1e-6), tol)

@@ -96,3 +96,28 @@ def test_oracle_varlen_equals_per_sequence_runs():
                                          output_final_state=True, head_first=False)
         torch.testing.assert_close(o[:, a:b], on)
         torch.testing.assert_close(ht[n:n + 1], hn)
+
+
+L2_CASES = ["f32_128", "f32_100", "f16_64", "f32_tiny"]
+
+
+def _l2_golden():
+    import os
+    import numpy as np
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "l2norm_vectors.npz"))
+
+
+def test_l2norm_matches_reference_kernels():
+    """oracle.l2_norm / l2_norm_bwd against outputs of the reference's Triton kernels (CPU interpreter), and the
+    backward formula against autograd of the forward in fp64."""
+    z = _l2_golden()
+    for case in L2_CASES:
+        x, dy, y, dx = (torch.from_numpy(z[f"{case}.{n}"]) for n in ("x", "dy", "y", "dx"))
+        tol = 1e-6 if x.dtype == torch.float32 else 1e-3
+        assert_close(f"{case} y", y, oracle.l2_norm(x, 1e-6), tol)
+        assert_close(f"{case} dx", dx, oracle.l2_norm_bwd(x, dy, 1e-6), tol)
+    x = torch.randn(7, 96, dtype=torch.float64, requires_grad=True)
+    dy = torch.randn(7, 96, dtype=torch.float64)
+    y = x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
+    gx, = torch.autograd.grad((y * dy).sum(), x)
+    assert_close("dx vs autograd", gx.float(), oracle.l2_norm_bwd(x.detach().float(), dy.float(), 1e-6), 1e-5)
