@@ -409,13 +409,19 @@ def main():
             "clocks": clk.summary(), "gpu_launches": launches}
 
     if op == "l2norm" and rank == 0:
-        # pure streaming: forward reads x and writes y, backward reads x and dy and writes dx, for q and for k
+        # pure streaming: forward reads x and writes y, backward reads x and dy and writes dx. The step above also pays
+        # the autograd and launch overhead of four small calls, so the kernels are timed on their own as well.
+        from fla_b200.modules.l2norm import l2norm_bwd, l2norm_fwd
         pk = peaks()
-        nbytes = 10 * B * T * H * K * 2
-        ach = nbytes / (ms_step * 1e-3) / 1e9
-        line["roofline"] = {"kernel": "l2norm_fwd_vec_kernel x2 + l2norm_bwd_vec_kernel x2 (whole step)", "bound": "hbm", "achieved": ach,
-                            "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
-                            "ms_per_launch": ms_step / 4}
+        xq, dyq = i["q"].detach(), i["do"]
+        ms_f = time_stage(lambda: l2norm_fwd(xq), reps=30, warm=5)
+        ms_b = time_stage(lambda: l2norm_bwd(xq, dyq), reps=30, warm=5)
+        tensor_bytes = B * T * H * K * 2
+        ach_f, ach_b = 2 * tensor_bytes / (ms_f * 1e-3) / 1e9, 3 * tensor_bytes / (ms_b * 1e-3) / 1e9
+        line["roofline"] = {"kernel": "l2norm_bwd_vec_kernel", "bound": "hbm", "achieved": ach_b, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                            "frac": ach_b / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"], "ms_per_launch": ms_b}
+        line["kernels"] = {"l2norm_fwd_vec_kernel": {"ms": ms_f, "GB/s": ach_f, "frac": ach_f / pk["hbm_gbs"]},
+                           "l2norm_bwd_vec_kernel": {"ms": ms_b, "GB/s": ach_b, "frac": ach_b / pk["hbm_gbs"]}}
     if op == "decode" and rank == 0:
         # the decode kernel alone (the public-API step above also pays Python / launch overhead per call)
         from fla_b200.ops.recurrent import recurrent_delta_fwd

@@ -10,7 +10,7 @@
 
 namespace flab {
 
-template <typename T> struct Vec16 {
+template <typename T> struct __align__(16) Vec16 {
   static constexpr int N = 16 / sizeof(T);
   T v[N];
 };
@@ -183,8 +183,8 @@ extern "C" {
 
 int flab_l2norm_fwd(const void *x, void *y, long long rows, int n, int in_dtype, int out_dtype, float eps, void *stream) {
   using namespace flab;
-  FLAB_REQUIRE(x && y && rows >= 0 && n > 0, FLAB_E_BADARG, "l2norm_fwd needs x, y, rows >= 0 and n > 0");
   if (rows == 0) return FLAB_OK;
+  FLAB_REQUIRE(x && y && rows > 0 && n > 0, FLAB_E_BADARG, "l2norm_fwd needs x, y, rows >= 0 and n > 0");
   cudaStream_t st = (cudaStream_t)stream;
   const int key = in_dtype * 3 + out_dtype;
   switch (key) {
@@ -203,8 +203,8 @@ int flab_l2norm_fwd(const void *x, void *y, long long rows, int n, int in_dtype,
 
 int flab_l2norm_bwd(const void *x, const void *dy, void *dx, long long rows, int n, int dtype, float eps, void *stream) {
   using namespace flab;
-  FLAB_REQUIRE(x && dy && dx && rows >= 0 && n > 0, FLAB_E_BADARG, "l2norm_bwd needs x, dy, dx, rows >= 0 and n > 0");
   if (rows == 0) return FLAB_OK;
+  FLAB_REQUIRE(x && dy && dx && rows > 0 && n > 0, FLAB_E_BADARG, "l2norm_bwd needs x, dy, dx, rows >= 0 and n > 0");
   cudaStream_t st = (cudaStream_t)stream;
   switch (dtype) {
     case FLAB_BF16: return launch_l2norm_bwd<bf16>(x, dy, dx, rows, n, eps, st);
