@@ -617,3 +617,52 @@ def test_l2_norm_reference_kernel_vectors():
         tol = 1e-6 if x.dtype == torch.float32 else 1e-3
         assert_close(f"{case} y", y, l2norm_fwd(x.to(DEV), 1e-6), tol)
         assert_close(f"{case} dx", dx, l2norm_bwd(x.to(DEV), dy.to(DEV), 1e-6), tol)
+
+
+# ------------------------------------------------------------------------------------------------
+# against outputs of the reference's own CHUNKED Triton kernels (tests/golden/triton_vectors.npz, produced by
+# tests/golden/make_golden_triton.py under Triton's CPU interpreter): rel-L2 <= 5e-3 for 16-bit inputs, <= 1e-5 fp32
+# ------------------------------------------------------------------------------------------------
+def _triton_case(case, names):
+    import numpy as np
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "triton_vectors.npz"))
+    x = {n: torch.from_numpy(z[f"{case}.{n}"]).to(DEV) for n in names}
+    ref = {n[len(case) + 1:]: torch.from_numpy(z[n]) for n in z.files if n.startswith(case + ".")}
+    return x, ref
+
+
+def _compare_with_triton(case, call, names, grad_names, tol, grad_tol=None):
+    x, ref = _triton_case(case, names)
+    for n in grad_names:
+        x[n].requires_grad_(True)
+    o, ht = call(x, ref)
+    assert_close(f"{case} o", ref["o"].float(), o, tol)
+    assert_close(f"{case} ht", ref["ht"].float(), ht, tol)
+    if grad_names:
+        torch.autograd.backward([o, ht], [ref["do"].to(DEV), ref["dht"].to(DEV)])
+        for n in grad_names:
+            assert_close(f"{case} d{n}", ref[f"d{n}"].float(), x[n].grad, (grad_tol or {}).get(n, tol))
+
+
+@pytest.mark.gpu
+def test_against_reference_chunk_kernel_outputs():
+    o_ = ops()
+    gd = ["q", "k", "v", "g", "beta", "h0"]
+    _compare_with_triton("gdn_128", lambda x, r: o_.chunk_gated_delta_rule(
+        x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x["h0"], output_final_state=True, head_first=False), gd, gd, 5e-3)
+    _compare_with_triton("gdn_varlen", lambda x, r: o_.chunk_gated_delta_rule(
+        x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x["h0"], output_final_state=True,
+        cu_seqlens=r["offsets"].to(DEV), head_first=False), gd, gd, 5e-3)
+    _compare_with_triton("delta_128", lambda x, r: o_.chunk_delta_rule(
+        x["q"], x["k"], x["v"], x["beta"], initial_state=x["h0"], output_final_state=True, head_first=False),
+        ["q", "k", "v", "beta", "h0"], [], 5e-3)
+    sg = ["q", "k", "v", "g", "h0"]
+    _compare_with_triton("simple_gla", lambda x, r: o_.chunk_simple_gla(
+        x["q"], x["k"], x["v"], x["g"], initial_state=x["h0"], output_final_state=True, head_first=False), sg, sg, 5e-3)
+    _compare_with_triton("gla_f32", lambda x, r: o_.chunk_gla(
+        x["q"], x["k"], x["v"], x["g"], initial_state=x["h0"], output_final_state=True, head_first=False), sg, sg, 1e-5)
+    rt = ["q", "k", "v", "h0"]
+    _compare_with_triton("retention", lambda x, r: o_.chunk_retention(
+        x["q"], x["k"], x["v"], initial_state=x["h0"], output_final_state=True, head_first=False), rt, rt, 5e-3)
+    _compare_with_triton("decode", lambda x, r: o_.fused_recurrent_gated_delta_rule(
+        x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x["h0"], output_final_state=True, head_first=False), gd, [], 5e-3)

@@ -121,3 +121,54 @@ def test_l2norm_matches_reference_kernels():
     y = x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
     gx, = torch.autograd.grad((y * dy).sum(), x)
     assert_close("dx vs autograd", gx.float(), oracle.l2_norm_bwd(x.detach().float(), dy.float(), 1e-6), 1e-5)
+
+
+# ------------------------------------------------------------------------------------------------
+# the oracle against outputs of the reference's CHUNKED Triton kernels (tests/golden/make_golden_triton.py: the
+# kernels run unmodified under Triton's CPU interpreter).  16-bit cases are fp16.
+# ------------------------------------------------------------------------------------------------
+def _triton_golden():
+    import os
+    import numpy as np
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "triton_vectors.npz"))
+
+
+# measured: 2e-4 .. 5e-4 on the fp16 cases (the kernels round operands to fp16, the oracle does not), 3e-7 on fp32
+TRITON_TOL = {True: 2e-3, False: 2e-6}  # 16-bit case / fp32 case
+
+
+def _check_against_triton(case, call, names, grad_names):
+    z = _triton_golden()
+    xs = {n: torch.from_numpy(z[f"{case}.{n}"]).float().requires_grad_(n in grad_names) for n in names}
+    o, ht = call(xs, z)
+    tol = TRITON_TOL[z[f"{case}.q"].dtype != "float32"]
+    assert_close(f"{case} o", torch.from_numpy(z[f"{case}.o"]).float(), o, tol)
+    assert_close(f"{case} ht", torch.from_numpy(z[f"{case}.ht"]).float(), ht, tol)
+    if grad_names:
+        do, dht = torch.from_numpy(z[f"{case}.do"]).float(), torch.from_numpy(z[f"{case}.dht"]).float()
+        gr = torch.autograd.grad((o * do).sum() + (ht * dht).sum(), [xs[n] for n in grad_names])
+        for n, gx in zip(grad_names, gr):
+            assert_close(f"{case} d{n}", torch.from_numpy(z[f"{case}.d{n}"]).float(), gx, tol)
+
+
+def test_oracle_matches_reference_chunk_kernels():
+    gd = ["q", "k", "v", "g", "beta", "h0"]
+    _check_against_triton("gdn_128", lambda x, z: oracle.gated_delta_rule(
+        x["q"], x["k"], x["v"], x["beta"], g=x["g"], initial_state=x["h0"], output_final_state=True, head_first=False), gd, gd)
+    _check_against_triton("gdn_varlen", lambda x, z: oracle.gated_delta_rule(
+        x["q"], x["k"], x["v"], x["beta"], g=x["g"], initial_state=x["h0"], output_final_state=True,
+        offsets=torch.from_numpy(z["gdn_varlen.offsets"]), head_first=False), gd, gd)
+    _check_against_triton("delta_128", lambda x, z: oracle.delta_rule(
+        x["q"], x["k"], x["v"], x["beta"], initial_state=x["h0"], output_final_state=True, head_first=False),
+        ["q", "k", "v", "beta", "h0"], [])
+    sg = ["q", "k", "v", "g", "h0"]
+    _check_against_triton("simple_gla", lambda x, z: oracle.simple_gla(
+        x["q"], x["k"], x["v"], x["g"], initial_state=x["h0"], output_final_state=True, head_first=False), sg, sg)
+    _check_against_triton("gla_f32", lambda x, z: oracle.gla(
+        x["q"], x["k"], x["v"], gk=x["g"], initial_state=x["h0"], output_final_state=True, head_first=False), sg, sg)
+    rt = ["q", "k", "v", "h0"]
+    _check_against_triton("retention", lambda x, z: oracle.simple_gla(
+        x["q"], x["k"], x["v"], oracle.retention_log_decay(x["q"].shape[2])[None, None, :].expand(x["q"].shape[:3]),
+        initial_state=x["h0"], output_final_state=True, head_first=False), rt, rt)
+    _check_against_triton("decode", lambda x, z: oracle.gated_delta_rule(
+        x["q"], x["k"], x["v"], x["beta"], g=x["g"], initial_state=x["h0"], output_final_state=True, head_first=False), gd, [])
