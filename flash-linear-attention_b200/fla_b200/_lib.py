@@ -78,6 +78,13 @@ def load() -> ctypes.CDLL:
     lib.flab_l2norm_fwd.restype = ctypes.c_int
     lib.flab_l2norm_fwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                     ctypes.c_float, ctypes.c_void_p]
+    vp, ll, ci, cf = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+    lib.flab_rms_norm_swish_gate_partials.restype = ci
+    lib.flab_rms_norm_swish_gate_partials.argtypes = [ll, ci, ci]
+    lib.flab_rms_norm_swish_gate_fwd.restype = ci
+    lib.flab_rms_norm_swish_gate_fwd.argtypes = [vp, vp, vp, vp, vp, ll, ci, ci, cf, vp]
+    lib.flab_rms_norm_swish_gate_bwd.restype = ci
+    lib.flab_rms_norm_swish_gate_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ll, ci, ci, vp]
     lib.flab_l2norm_bwd.restype = ctypes.c_int
     lib.flab_l2norm_bwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
                                     ctypes.c_float, ctypes.c_void_p]

@@ -109,6 +109,19 @@ int flab_chunk_global_cumsum_vector(const flab_args *a, void *stream);
 int flab_l2norm_fwd(const void *x, void *y, long long rows, int n, int in_dtype, int out_dtype, float eps, void *stream);
 int flab_l2norm_bwd(const void *x, const void *dy, void *dx, long long rows, int n, int dtype, float eps, void *stream);
 
+/* ---- RMS norm with weight times a swish gate (the step after the chunk ops in the reference's layers) ----
+ * Replaces layer_norm_fwd / layer_norm_bwd of fla/modules/fused_norm_gate.py (:103, :301) for the case the
+ * delta-rule layers use: IS_RMS_NORM, weight, no bias, no residual (FusedRMSNormSwishGate, :728).
+ *   y = (x rstd w) * (g sigmoid(g)),  rstd = 1 / sqrt(mean_n x^2 + eps)   (rstd [rows] fp32 is written for backward)
+ *   backward writes dx, dgate (element type) and one partial row of dw (fp32 [partials, n]) per thread block;
+ *   the caller sums the partial rows. flab_rms_norm_swish_gate_partials gives their number for (rows, n, dtype).
+ * x, gate, y, dy, dx, dgate: [rows, n] contiguous of element type dtype; weight: fp32 [n]. */
+int flab_rms_norm_swish_gate_partials(long long rows, int n, int dtype);
+int flab_rms_norm_swish_gate_fwd(const void *x, const void *gate, const float *weight, void *y, float *rstd, long long rows, int n, int dtype,
+                                 float eps, void *stream);
+int flab_rms_norm_swish_gate_bwd(const void *x, const void *gate, const float *weight, const void *dy, const float *rstd, void *dx, void *dgate,
+                                 float *dw_partial, long long rows, int n, int dtype, void *stream);
+
 /* ---- inter-chunk state recurrence for diagonal decay ---------------------------------------
  * Replaces chunk_fwd_h (fla/ops/common/chunk_h.py:282): reads k, v, g or gk (either may be NULL),
  * h0 (optional); writes h (state at the start of every chunk) and ht (optional). */

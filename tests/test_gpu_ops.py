@@ -667,3 +667,57 @@ def test_against_reference_chunk_kernel_outputs():
         x["q"], x["k"], x["v"], initial_state=x["h0"], output_final_state=True, head_first=False), rt, rt, 5e-3)
     _compare_with_triton("decode", lambda x, r: o_.fused_recurrent_gated_delta_rule(
         x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x["h0"], output_final_state=True, head_first=False), gd, [], 5e-3)
+
+
+# ------------------------------------------------------------------------------------------------
+# the step after the chunk ops: RMS norm with weight times swish gate (fla/modules/fused_norm_gate.py)
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape,dtype", [
+    ((2, 300, 4, 128), torch.bfloat16),
+    ((2, 130, 3, 128), torch.float16),
+    ((3, 77, 2, 64), torch.bfloat16),
+    ((1, 50, 3, 128), torch.float32),
+    ((5, 100), torch.float32),              # row length that takes the column-loop kernel
+    ((4, 9, 72), torch.bfloat16),
+    ((1, 1, 1, 8), torch.float16),
+    ((1, 7000, 16, 128), torch.bfloat16),   # more rows than one wave of blocks: several row passes per warp
+])
+def test_rms_norm_swish_gate_matches_oracle(shape, dtype):
+    from fla_b200.modules import FusedRMSNormSwishGate
+    g0 = torch.Generator().manual_seed(sum(shape) + 3)
+    x = torch.randn(*shape, generator=g0).to(dtype)
+    gate = torch.randn(*shape, generator=g0).to(dtype)
+    dy = torch.randn(*shape, generator=g0).to(dtype)
+    w = 1 + 0.1 * torch.randn(shape[-1], generator=g0)
+    mod = FusedRMSNormSwishGate(shape[-1], eps=1e-5).to(DEV)
+    with torch.no_grad():
+        mod.weight.copy_(w)
+    xg, gg = x.to(DEV).requires_grad_(True), gate.to(DEV).requires_grad_(True)
+    y = mod(xg, gg)
+    assert y.shape == x.shape and y.dtype == dtype
+    tol = 1e-6 if dtype == torch.float32 else 5e-3
+    assert_close("y", oracle.rms_norm_swish_gate(x, gate, w, 1e-5), y, tol)
+    y.backward(dy.to(DEV))
+    rx, rg, rw = oracle.rms_norm_swish_gate_bwd(x, gate, w, dy, 1e-5)
+    assert_close("dx", rx, xg.grad, tol)
+    assert_close("dgate", rg, gg.grad, tol)
+    assert_close("dw", rw, mod.weight.grad, 1e-5 if dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.gpu
+def test_rms_norm_swish_gate_reference_kernel_vectors():
+    """The CUDA kernels on the inputs of tests/golden/norm_gate_vectors.npz (outputs of the reference's own kernels)."""
+    import numpy as np
+    from fla_b200.modules import rms_norm_swish_gate_fn
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "norm_gate_vectors.npz"))
+    for case in ("f32_128", "f16_128", "f32_100", "f16_64"):
+        x, gate, w, dy, y, dx, dgate, dw = (torch.from_numpy(z[f"{case}.{n}"]).to(DEV) for n in ("x", "gate", "w", "dy", "y", "dx", "dgate", "dw"))
+        tol = 1e-6 if x.dtype == torch.float32 else 1e-3
+        x.requires_grad_(True), gate.requires_grad_(True), w.requires_grad_(True)
+        out = rms_norm_swish_gate_fn(x, gate, w, eps=1e-5)
+        assert_close(f"{case} y", y, out, tol)
+        out.backward(dy)
+        assert_close(f"{case} dx", dx, x.grad, tol)
+        assert_close(f"{case} dgate", dgate, gate.grad, tol)
+        assert_close(f"{case} dw", dw, w.grad, 1e-5 if x.dtype == torch.float32 else 1e-3)

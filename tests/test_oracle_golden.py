@@ -172,3 +172,29 @@ def test_oracle_matches_reference_chunk_kernels():
         initial_state=x["h0"], output_final_state=True, head_first=False), rt, rt)
     _check_against_triton("decode", lambda x, z: oracle.gated_delta_rule(
         x["q"], x["k"], x["v"], x["beta"], g=x["g"], initial_state=x["h0"], output_final_state=True, head_first=False), gd, [])
+
+
+def test_norm_gate_matches_reference_kernels():
+    """oracle.rms_norm_swish_gate(_bwd) against outputs of the reference's norm-gate kernels (CPU interpreter)."""
+    import os
+    import numpy as np
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "norm_gate_vectors.npz"))
+    for case in ("f32_128", "f16_128", "f32_100", "f16_64"):
+        x, gate, w, dy, y, dx, dgate, dw = (torch.from_numpy(z[f"{case}.{n}"]) for n in ("x", "gate", "w", "dy", "y", "dx", "dgate", "dw"))
+        tol = 1e-6 if x.dtype == torch.float32 else 1e-3
+        assert_close(f"{case} y", y, oracle.rms_norm_swish_gate(x, gate, w, 1e-5), tol)
+        gx, gg, gw = oracle.rms_norm_swish_gate_bwd(x, gate, w, dy, 1e-5)
+        assert_close(f"{case} dx", dx, gx, tol)
+        assert_close(f"{case} dgate", dgate, gg, tol)
+        assert_close(f"{case} dw", dw, gw, 1e-5)
+    # the backward formulas against autograd of the forward, fp64
+    x = torch.randn(6, 80, dtype=torch.float64, requires_grad=True)
+    gate = torch.randn(6, 80, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(80, dtype=torch.float64, requires_grad=True)
+    dy = torch.randn(6, 80, dtype=torch.float64)
+    y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * w * gate * torch.sigmoid(gate)
+    ax, ag, aw = torch.autograd.grad((y * dy).sum(), (x, gate, w))
+    gx, gg, gw = oracle.rms_norm_swish_gate_bwd(x.detach().float(), gate.detach().float(), w.detach().float(), dy.float(), 1e-5)
+    assert_close("dx vs autograd", ax.float(), gx, 1e-5)
+    assert_close("dgate vs autograd", ag.float(), gg, 1e-5)
+    assert_close("dw vs autograd", aw.float(), gw, 1e-5)
