@@ -45,6 +45,7 @@ SIDE_METRICS = {
     "decode": "fused_recurrent_gated_delta_rule decode tokens/s (256 sequences, H=16 D=128)",
     "long": "chunk_gated_delta_rule fwd+bwd tokens/s (ONE sequence of 262144 tokens, H=16 D=128 bf16)",
     "l2norm": "l2_norm fwd+bwd tokens/s (q and k of B=8 T=4096 H=16 D=128 bf16)",
+    "norm_gate": "FusedRMSNormSwishGate fwd+bwd tokens/s (o and gate of B=8 T=4096 H=16 D=128 bf16)",
 }
 
 # DRAM bytes per token-head of each stage's kernel, from the ncu capture summarised in
@@ -69,6 +70,8 @@ WORKLOADS = {
     "long": ("gated_delta", 1, 262144, 16, 128, 128),
     # the step before the op in the reference's layers: l2_norm of q and of k, forward and backward (4 launches)
     "l2norm": ("l2norm", 8, 4096, 16, 128, 128),
+    # the step after the op: RMS norm with weight times swish gate on the op's output, forward and backward (2 launches)
+    "norm_gate": ("norm_gate", 8, 4096, 16, 128, 128),
 }
 
 
@@ -119,7 +122,7 @@ def make_inputs(op, B, T, H, K, V, seed, dtype):
     return d
 
 
-GRAD_NAMES = {"gated_delta_varlen": ["q", "k", "v", "g", "beta", "h0"], "decode": [], "l2norm": ["q", "k"],
+GRAD_NAMES = {"gated_delta_varlen": ["q", "k", "v", "g", "beta", "h0"], "decode": [], "l2norm": ["q", "k"], "norm_gate": ["q", "k"],
               "gated_delta": ["q", "k", "v", "g", "beta", "h0"], "delta": ["q", "k", "v", "beta", "h0"],
               "simple_gla": ["q", "k", "v", "g"], "gla": ["q", "k", "v", "g", "h0"]}
 
@@ -159,6 +162,12 @@ def fwd_bwd(op, i, mod="ours"):
         yq, yk = l2_norm(i["q"]), l2_norm(i["k"])
         torch.autograd.backward([yq, yk], [i["do"], i["do"]])
         return yq, yk
+    if op == "norm_gate":  # x = "q", gate = "k" (same shape as the op's output at K = V)
+        from fla_b200.modules import rms_norm_swish_gate_fn
+        i["q"].grad = i["k"].grad = i["w"].grad = None
+        y = rms_norm_swish_gate_fn(i["q"], i["k"], i["w"], eps=1e-5)
+        torch.autograd.backward([y], [i["do"]])
+        return y, None
     if op == "decode":  # forward only; the new state replaces the old one
         o, ht = call_op(op, i, mod)
         i["h0"] = ht
@@ -322,7 +331,7 @@ def main():
     if op == "gated_delta_varlen":
         T = int(varlen_lengths().sum())
     dtype = torch.float32 if args.workload == "gla_fp32" else torch.bfloat16
-    if op in ("gated_delta_varlen", "decode", "l2norm") or args.workload == "long":
+    if op in ("gated_delta_varlen", "decode", "l2norm", "norm_gate") or args.workload == "long":
         args.no_extras = True  # side workloads: device-resident timing (and the decode roofline) only
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
@@ -355,6 +364,8 @@ def main():
     i = {n: x.to(dev) for n, x in host.items()}
     for n in GRAD_NAMES[op]:
         i[n].requires_grad_(True)
+    if op == "norm_gate":
+        i["w"] = torch.ones(K, device=dev, requires_grad=True)
 
     def barrier():
         if world > 1:
@@ -422,6 +433,14 @@ def main():
                             "frac": ach_b / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"], "ms_per_launch": ms_b}
         line["kernels"] = {"l2norm_fwd_vec_kernel": {"ms": ms_f, "GB/s": ach_f, "frac": ach_f / pk["hbm_gbs"]},
                            "l2norm_bwd_vec_kernel": {"ms": ms_b, "GB/s": ach_b, "frac": ach_b / pk["hbm_gbs"]}}
+    if op == "norm_gate" and rank == 0:
+        # pure streaming: forward reads x, gate and writes y; backward reads x, gate, dy and writes dx, dgate
+        pk = peaks()
+        tensor_bytes = B * T * H * K * 2
+        ach = 8 * tensor_bytes / (ms_step * 1e-3) / 1e9
+        line["roofline"] = {"kernel": "norm_gate_fwd_vec_kernel + norm_gate_bwd_vec_kernel (whole step through autograd)", "bound": "hbm",
+                            "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None,
+                            "peak_source": pk["source"], "ms_per_launch": ms_step / 2}
     if op == "decode" and rank == 0:
         # the decode kernel alone (the public-API step above also pays Python / launch overhead per call)
         from fla_b200.ops.recurrent import recurrent_delta_fwd

@@ -31,7 +31,7 @@ def install_as_fla_ops():
 
 
 def install_as_fla_modules():
-    """Alias `fla.modules.l2norm` (and `fla.modules.l2_norm`) to this package's CUDA implementation."""
+    """Alias `fla.modules.l2norm` and `fla.modules.fused_norm_gate` to this package's CUDA implementation."""
     from . import modules
     from .modules import l2norm
     root = sys.modules.get("fla")
@@ -41,5 +41,7 @@ def install_as_fla_modules():
         sys.modules["fla"] = root
     sys.modules["fla.modules"] = modules
     sys.modules["fla.modules.l2norm"] = l2norm
+    from .modules import fused_norm_gate
+    sys.modules["fla.modules.fused_norm_gate"] = fused_norm_gate
     root.modules = modules
 
