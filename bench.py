@@ -434,13 +434,20 @@ def main():
         line["kernels"] = {"l2norm_fwd_vec_kernel": {"ms": ms_f, "GB/s": ach_f, "frac": ach_f / pk["hbm_gbs"]},
                            "l2norm_bwd_vec_kernel": {"ms": ms_b, "GB/s": ach_b, "frac": ach_b / pk["hbm_gbs"]}}
     if op == "norm_gate" and rank == 0:
-        # pure streaming: forward reads x, gate and writes y; backward reads x, gate, dy and writes dx, dgate
+        # pure streaming: forward reads x, gate and writes y (3 tensors); backward reads x, gate, dy and writes dx, dgate (5).
+        # The step above also pays autograd, two casts and the sum of the dw partials; the forward kernel is timed alone too.
+        from fla_b200.modules import rms_norm_swish_gate_fn
         pk = peaks()
         tensor_bytes = B * T * H * K * 2
-        ach = 8 * tensor_bytes / (ms_step * 1e-3) / 1e9
-        line["roofline"] = {"kernel": "norm_gate_fwd_vec_kernel + norm_gate_bwd_vec_kernel (whole step through autograd)", "bound": "hbm",
-                            "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None,
-                            "peak_source": pk["source"], "ms_per_launch": ms_step / 2}
+        with torch.no_grad():
+            ms_f = time_stage(lambda: rms_norm_swish_gate_fn(i["q"], i["k"], i["w"], eps=1e-5), reps=30, warm=5)
+        ms_b = max(ms_step - ms_f, 1e-6)
+        ach_f, ach_b = 3 * tensor_bytes / (ms_f * 1e-3) / 1e9, 5 * tensor_bytes / (ms_b * 1e-3) / 1e9
+        line["roofline"] = {"kernel": "norm_gate_bwd_vec_kernel (step minus forward: includes the dw partial sum)", "bound": "hbm",
+                            "achieved": ach_b, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach_b / pk["hbm_gbs"], "traffic": None,
+                            "peak_source": pk["source"], "ms_per_launch": ms_b}
+        line["kernels"] = {"norm_gate_fwd_vec_kernel": {"ms": ms_f, "GB/s": ach_f, "frac": ach_f / pk["hbm_gbs"]},
+                           "backward (step - forward)": {"ms": ms_b, "GB/s": ach_b, "frac": ach_b / pk["hbm_gbs"]}}
     if op == "decode" and rank == 0:
         # the decode kernel alone (the public-API step above also pays Python / launch overhead per call)
         from fla_b200.ops.recurrent import recurrent_delta_fwd
