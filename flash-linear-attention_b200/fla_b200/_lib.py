@@ -85,6 +85,12 @@ def load() -> ctypes.CDLL:
     lib.flab_rms_norm_swish_gate_fwd.argtypes = [vp, vp, vp, vp, vp, ll, ci, ci, cf, vp]
     lib.flab_rms_norm_swish_gate_bwd.restype = ci
     lib.flab_rms_norm_swish_gate_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ll, ci, ci, vp]
+    lib.flab_short_conv_fwd.restype = ci
+    lib.flab_short_conv_fwd.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]
+    lib.flab_short_conv_bwd.restype = ci
+    lib.flab_short_conv_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]
+    lib.flab_short_conv_update.restype = ci
+    lib.flab_short_conv_update.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]
     lib.flab_l2norm_bwd.restype = ctypes.c_int
     lib.flab_l2norm_bwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
                                     ctypes.c_float, ctypes.c_void_p]

@@ -122,6 +122,20 @@ int flab_rms_norm_swish_gate_fwd(const void *x, const void *gate, const float *w
 int flab_rms_norm_swish_gate_bwd(const void *x, const void *gate, const float *weight, const void *dy, const float *rstd, void *dx, void *dgate,
                                  float *dw_partial, long long rows, int n, int dtype, void *stream);
 
+/* ---- causal depthwise short convolution (q, k, v of the reference's layers pass through it first) ----
+ * Replaces the convolution of ShortConvolution.forward / .step (fla/modules/convolution.py:142-216):
+ *   y[b,t,d] = act(bias[d] + sum_{w<W} weight[d,w] x[b, t-(W-1)+w, d]),  x = 0 before the sequence, act = SiLU or none.
+ * x, y, dy, dx: [B, T, D] contiguous of element type dtype (D a multiple of 16 bytes of elements, 16-byte aligned);
+ * weight fp32 [D, W] (W = 2, 3 or 4), bias fp32 [D] or NULL. Backward adds into dweight (fp32 [D, W]) and dbias
+ * (fp32 [D], with a bias) with atomics: the caller zeroes them. The update entry is the one-token decode step:
+ * cache [B, D, W] (element type dtype) is shifted by one in place, x [B, D] appended, y [B, D] written (W <= 8). */
+int flab_short_conv_fwd(const void *x, const float *weight, const float *bias, void *y, int B, int T, int D, int W, int silu, int dtype,
+                        void *stream);
+int flab_short_conv_bwd(const void *x, const float *weight, const float *bias, const void *dy, void *dx, float *dweight, float *dbias, int B, int T,
+                        int D, int W, int silu, int dtype, void *stream);
+int flab_short_conv_update(const void *x, void *cache, const float *weight, const float *bias, void *y, int B, int D, int W, int silu, int dtype,
+                           void *stream);
+
 /* ---- inter-chunk state recurrence for diagonal decay ---------------------------------------
  * Replaces chunk_fwd_h (fla/ops/common/chunk_h.py:282): reads k, v, g or gk (either may be NULL),
  * h0 (optional); writes h (state at the start of every chunk) and ht (optional). */

@@ -15,6 +15,7 @@ tests/golden/triton_vectors.npz; the oracle agrees with them to 2e-4 .. 5e-4 on 
 
 from .indexing import chunk_indices_ref, chunk_offsets_ref  # noqa: F401
 from .l2norm import l2_norm, l2_norm_bwd  # noqa: F401
+from .short_conv import short_conv, short_conv_step  # noqa: F401
 from .norm_gate import rms_norm_swish_gate, rms_norm_swish_gate_bwd  # noqa: F401
 from .naive import (cumsum_global, cumsum_local, delta_rule, gated_delta_rule, gla, retention_log_decay,  # noqa: F401
                     simple_gla)

@@ -721,3 +721,83 @@ def test_rms_norm_swish_gate_reference_kernel_vectors():
         assert_close(f"{case} dx", dx, x.grad, tol)
         assert_close(f"{case} dgate", dgate, gate.grad, tol)
         assert_close(f"{case} dw", dw, w.grad, 1e-5 if x.dtype == torch.float32 else 1e-3)
+
+
+# ------------------------------------------------------------------------------------------------
+# the convolution in front of q, k, v (fla/modules/convolution.py ShortConvolution)
+# ------------------------------------------------------------------------------------------------
+def _short_conv_module(D, W, bias, act, weight, bias_t, dtype):
+    from fla_b200.modules import ShortConvolution
+    conv = ShortConvolution(D, W, bias=bias, activation=act).to(DEV)
+    with torch.no_grad():
+        conv.weight.copy_(weight.reshape(D, 1, W))
+        if bias:
+            conv.bias.copy_(bias_t)
+    return conv
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,T,D,W,bias,act,dtype", [
+    (2, 300, 256, 4, False, "silu", torch.bfloat16),
+    (2, 100, 2048, 4, False, "silu", torch.bfloat16),   # the layer's width (16 heads x 128)
+    (1, 33, 64, 3, True, None, torch.float16),
+    (3, 2, 32, 4, True, "silu", torch.float32),         # shorter than the filter
+    (1, 65, 40, 2, True, "silu", torch.float32),
+])
+def test_short_conv_matches_oracle(B, T, D, W, bias, act, dtype):
+    g0 = torch.Generator().manual_seed(B * T + D + W)
+    x = torch.randn(B, T, D, generator=g0).to(dtype)
+    dy = torch.randn(B, T, D, generator=g0).to(dtype)
+    w = torch.randn(D, W, generator=g0) * 0.5
+    bt = torch.randn(D, generator=g0) * 0.1 if bias else None
+    conv = _short_conv_module(D, W, bias, act, w, bt, dtype)
+    xg = x.to(DEV).requires_grad_(True)
+    y, cache = conv(xg, output_final_state=True)
+    xr, wr = x.float().requires_grad_(True), w.clone().requires_grad_(True)
+    br = None if bt is None else bt.clone().requires_grad_(True)
+    y_ref, cache_ref = oracle.short_conv(xr, wr, br, act is not None)
+    tol = 1e-6 if dtype == torch.float32 else 5e-3
+    assert_close("y", y_ref, y, tol)
+    assert torch.equal(cache.cpu().float(), cache_ref)
+    y.backward(dy.to(DEV))
+    gr = torch.autograd.grad((y_ref * dy.float()).sum(), [xr, wr] + ([br] if br is not None else []))
+    assert_close("dx", gr[0], xg.grad, tol)
+    assert_close("dweight", gr[1], conv.weight.grad.reshape(D, W), 1e-5 if dtype == torch.float32 else 5e-3)
+    if bias:
+        assert_close("dbias", gr[2], conv.bias.grad, 1e-5 if dtype == torch.float32 else 5e-3)
+    # decode steps from the cache
+    c_ref = cache_ref.to(dtype)
+    for t in range(3):
+        xs = torch.randn(B, 1, D, generator=g0).to(dtype)
+        with torch.no_grad():
+            yt, cache = conv(xs.to(DEV), cache=cache)
+        yt_ref, c_ref = oracle.short_conv_step(xs, c_ref, w, bt, act is not None)
+        assert_close(f"step {t}", yt_ref, yt, tol)
+        assert torch.equal(cache.cpu(), c_ref)
+
+
+@pytest.mark.gpu
+def test_short_conv_reference_module_vectors():
+    """The CUDA kernels on the inputs of tests/golden/short_conv_vectors.npz (outputs of the reference's module)."""
+    import numpy as np
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "short_conv_vectors.npz"))
+    for case in ("w4_silu", "w3_bias", "w2_silu_bias"):
+        g = {k[len(case) + 1:]: torch.from_numpy(z[k]) for k in z.files if k.startswith(case + ".")}
+        silu, bias = bool(g["silu"].item()), g.get("bias")
+        B, T, D = g["x"].shape
+        W = g["weight"].shape[-1]
+        conv = _short_conv_module(D, W, bias is not None, "silu" if silu else None, g["weight"], bias, torch.float32)
+        x = g["x"].to(DEV).requires_grad_(True)
+        y, cache = conv(x, output_final_state=True)
+        assert_close(f"{case} y", g["y"], y, 1e-6)
+        assert torch.equal(cache.cpu(), g["cache"])
+        y.backward(g["dy"].to(DEV))
+        assert_close(f"{case} dx", g["dx"], x.grad, 1e-6)
+        assert_close(f"{case} dweight", g["dweight"], conv.weight.grad, 1e-5)
+        if bias is not None:
+            assert_close(f"{case} dbias", g["dbias"], conv.bias.grad, 1e-5)
+        with torch.no_grad():
+            for t in range(3):
+                yt, cache = conv(g["step_x"][:, t:t + 1].to(DEV), cache=cache)
+                assert_close(f"{case} step {t}", g["step_y"][:, t:t + 1], yt, 1e-6)
+        assert torch.equal(cache.cpu(), g["step_cache"])

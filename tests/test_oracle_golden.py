@@ -198,3 +198,36 @@ def test_norm_gate_matches_reference_kernels():
     assert_close("dx vs autograd", ax.float(), gx, 1e-5)
     assert_close("dgate vs autograd", ag.float(), gg, 1e-5)
     assert_close("dw vs autograd", aw.float(), gw, 1e-5)
+
+
+SC_CASES = ["w4_silu", "w3_bias", "w2_silu_bias"]
+
+
+def _sc_golden():
+    import os
+    import numpy as np
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "short_conv_vectors.npz"))
+
+
+def test_short_conv_matches_reference_module():
+    """oracle.short_conv / short_conv_step against the reference's ShortConvolution run on CPU."""
+    z = _sc_golden()
+    for case in SC_CASES:
+        g = {k[len(case) + 1:]: torch.from_numpy(z[k]) for k in z.files if k.startswith(case + ".")}
+        silu, bias = bool(g["silu"].item()), g.get("bias")
+        x, w = g["x"].clone().requires_grad_(True), g["weight"].clone().requires_grad_(True)
+        b = None if bias is None else bias.clone().requires_grad_(True)
+        y, cache = oracle.short_conv(x, w, b, silu)
+        assert_close(f"{case} y", g["y"], y, 1e-6)
+        assert torch.equal(cache, g["cache"])
+        gr = torch.autograd.grad((y * g["dy"]).sum(), [x, w] + ([b] if b is not None else []))
+        assert_close(f"{case} dx", g["dx"], gr[0], 1e-6)
+        assert_close(f"{case} dweight", g["dweight"], gr[1], 1e-5)
+        if b is not None:
+            assert_close(f"{case} dbias", g["dbias"], gr[2], 1e-5)
+        c = cache
+        with torch.no_grad():
+            for t in range(3):
+                yt, c = oracle.short_conv_step(g["step_x"][:, t:t + 1], c, w, b, silu)
+                assert_close(f"{case} step {t}", g["step_y"][:, t:t + 1], yt, 1e-6)
+        assert torch.equal(c, g["step_cache"])
