@@ -46,6 +46,7 @@ SIDE_METRICS = {
     "long": "chunk_gated_delta_rule fwd+bwd tokens/s (ONE sequence of 262144 tokens, H=16 D=128 bf16)",
     "l2norm": "l2_norm fwd+bwd tokens/s (q and k of B=8 T=4096 H=16 D=128 bf16)",
     "norm_gate": "FusedRMSNormSwishGate fwd+bwd tokens/s (o and gate of B=8 T=4096 H=16 D=128 bf16)",
+    "short_conv": "ShortConvolution fwd+bwd tokens/s (B=8 T=4096 D=2048 W=4 silu bf16)",
 }
 
 # DRAM bytes per token-head of each stage's kernel, from the ncu capture summarised in
@@ -72,6 +73,8 @@ WORKLOADS = {
     "l2norm": ("l2norm", 8, 4096, 16, 128, 128),
     # the step after the op: RMS norm with weight times swish gate on the op's output, forward and backward (2 launches)
     "norm_gate": ("norm_gate", 8, 4096, 16, 128, 128),
+    # the convolution in front of q (or k, v): [B, T, H * D] channels-last, filter of 4, SiLU, forward and backward
+    "short_conv": ("short_conv", 8, 4096, 16, 128, 128),
 }
 
 
@@ -122,7 +125,7 @@ def make_inputs(op, B, T, H, K, V, seed, dtype):
     return d
 
 
-GRAD_NAMES = {"gated_delta_varlen": ["q", "k", "v", "g", "beta", "h0"], "decode": [], "l2norm": ["q", "k"], "norm_gate": ["q", "k"],
+GRAD_NAMES = {"gated_delta_varlen": ["q", "k", "v", "g", "beta", "h0"], "decode": [], "l2norm": ["q", "k"], "norm_gate": ["q", "k"], "short_conv": ["q"],
               "gated_delta": ["q", "k", "v", "g", "beta", "h0"], "delta": ["q", "k", "v", "beta", "h0"],
               "simple_gla": ["q", "k", "v", "g"], "gla": ["q", "k", "v", "g", "h0"]}
 
@@ -162,6 +165,12 @@ def fwd_bwd(op, i, mod="ours"):
         yq, yk = l2_norm(i["q"]), l2_norm(i["k"])
         torch.autograd.backward([yq, yk], [i["do"], i["do"]])
         return yq, yk
+    if op == "short_conv":
+        i["q"].grad = None
+        i["conv"].weight.grad = None
+        y, _ = i["conv"](i["q"].view(i["q"].shape[0], i["q"].shape[1], -1))
+        torch.autograd.backward([y], [i["do"].view(y.shape)])
+        return y, None
     if op == "norm_gate":  # x = "q", gate = "k" (same shape as the op's output at K = V)
         from fla_b200.modules import rms_norm_swish_gate_fn
         i["q"].grad = i["k"].grad = i["w"].grad = None
@@ -331,7 +340,7 @@ def main():
     if op == "gated_delta_varlen":
         T = int(varlen_lengths().sum())
     dtype = torch.float32 if args.workload == "gla_fp32" else torch.bfloat16
-    if op in ("gated_delta_varlen", "decode", "l2norm", "norm_gate") or args.workload == "long":
+    if op in ("gated_delta_varlen", "decode", "l2norm", "norm_gate", "short_conv") or args.workload == "long":
         args.no_extras = True  # side workloads: device-resident timing (and the decode roofline) only
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
@@ -366,6 +375,9 @@ def main():
         i[n].requires_grad_(True)
     if op == "norm_gate":
         i["w"] = torch.ones(K, device=dev, requires_grad=True)
+    if op == "short_conv":
+        from fla_b200.modules import ShortConvolution
+        i["conv"] = ShortConvolution(H * K, 4, activation="silu").to(dev)
 
     def barrier():
         if world > 1:
@@ -374,7 +386,7 @@ def main():
 
     # L2 hygiene: a step whose tensors exceed the 126 MB L2 evicts its own inputs; a small one gets an explicit
     # flush (a 256 MB write) between timed iterations, outside the events that are summed.
-    in_bytes = sum(x.numel() * x.element_size() for x in i.values())
+    in_bytes = sum(x.numel() * x.element_size() for x in i.values() if isinstance(x, torch.Tensor))
     flush = None
     if in_bytes < 256 * 2 ** 20:
         flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device=dev)
@@ -433,21 +445,37 @@ def main():
                             "frac": ach_b / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"], "ms_per_launch": ms_b}
         line["kernels"] = {"l2norm_fwd_vec_kernel": {"ms": ms_f, "GB/s": ach_f, "frac": ach_f / pk["hbm_gbs"]},
                            "l2norm_bwd_vec_kernel": {"ms": ms_b, "GB/s": ach_b, "frac": ach_b / pk["hbm_gbs"]}}
-    if op == "norm_gate" and rank == 0:
-        # pure streaming: forward reads x, gate and writes y (3 tensors); backward reads x, gate, dy and writes dx, dgate (5).
-        # The step above also pays autograd, two casts and the sum of the dw partials; the forward kernel is timed alone too.
-        from fla_b200.modules import rms_norm_swish_gate_fn
+    if op in ("short_conv", "norm_gate") and rank == 0:
+        # streaming kernels of 0.05 - 0.2 ms: through the modules the Python side of a call costs as much as the kernel, so the
+        # kernels are also timed through the C entry points on preallocated buffers (pointers taken once)
         pk = peaks()
-        tensor_bytes = B * T * H * K * 2
-        with torch.no_grad():
-            ms_f = time_stage(lambda: rms_norm_swish_gate_fn(i["q"], i["k"], i["w"], eps=1e-5), reps=30, warm=5)
-        ms_b = max(ms_step - ms_f, 1e-6)
-        ach_f, ach_b = 3 * tensor_bytes / (ms_f * 1e-3) / 1e9, 5 * tensor_bytes / (ms_b * 1e-3) / 1e9
-        line["roofline"] = {"kernel": "norm_gate_bwd_vec_kernel (step minus forward: includes the dw partial sum)", "bound": "hbm",
-                            "achieved": ach_b, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach_b / pk["hbm_gbs"], "traffic": None,
-                            "peak_source": pk["source"], "ms_per_launch": ms_b}
-        line["kernels"] = {"norm_gate_fwd_vec_kernel": {"ms": ms_f, "GB/s": ach_f, "frac": ach_f / pk["hbm_gbs"]},
-                           "backward (step - forward)": {"ms": ms_b, "GB/s": ach_b, "frac": ach_b / pk["hbm_gbs"]}}
+        lib = _lib.load()
+        st = torch.cuda.current_stream().cuda_stream
+        tb = B * T * H * K * 2  # bytes of one [B, T, H * K] bf16 tensor
+        x, dyv = i["q"].detach(), i["do"]
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        if op == "short_conv":
+            w32 = i["conv"].weight.detach().float().reshape(H * K, 4).contiguous()
+            dw = torch.zeros_like(w32)
+            P = [t_.data_ptr() for t_ in (x, w32, y, dyv, dx, dw)]
+            ms_f = time_stage(lambda: lib.flab_short_conv_fwd(P[0], P[1], None, P[2], B, T, H * K, 4, 1, 0, st), reps=30, warm=5)
+            ms_b = time_stage(lambda: lib.flab_short_conv_bwd(P[0], P[1], None, P[3], P[4], P[5], None, B, T, H * K, 4, 1, 0, st), reps=30, warm=5)
+            nf, nb, names = 2, 3, ("short_conv_fwd_kernel", "short_conv_bwd_kernel")
+        else:
+            g, w32 = i["k"].detach(), i["w"].detach()
+            rows = B * T * H
+            rstd, dg = torch.empty(rows, device=dev), torch.empty_like(x)
+            parts = lib.flab_rms_norm_swish_gate_partials(rows, K, 0)
+            dwp = torch.empty(parts, K, device=dev)
+            P = [t_.data_ptr() for t_ in (x, g, w32, y, rstd, dyv, dx, dg, dwp)]
+            ms_f = time_stage(lambda: lib.flab_rms_norm_swish_gate_fwd(P[0], P[1], P[2], P[3], P[4], rows, K, 0, 1e-5, st), reps=30, warm=5)
+            ms_b = time_stage(lambda: lib.flab_rms_norm_swish_gate_bwd(P[0], P[1], P[2], P[5], P[4], P[6], P[7], P[8], rows, K, 0, st), reps=30, warm=5)
+            nf, nb, names = 3, 5, ("norm_gate_fwd_vec_kernel", "norm_gate_bwd_vec_kernel")
+        ach_f, ach_b = nf * tb / (ms_f * 1e-3) / 1e9, nb * tb / (ms_b * 1e-3) / 1e9
+        line["roofline"] = {"kernel": names[1], "bound": "hbm", "achieved": ach_b, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                            "frac": ach_b / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"], "ms_per_launch": ms_b}
+        line["kernels"] = {names[0]: {"ms": ms_f, "GB/s": ach_f, "frac": ach_f / pk["hbm_gbs"]},
+                           names[1]: {"ms": ms_b, "GB/s": ach_b, "frac": ach_b / pk["hbm_gbs"]}}
     if op == "decode" and rank == 0:
         # the decode kernel alone (the public-API step above also pays Python / launch overhead per call)
         from fla_b200.ops.recurrent import recurrent_delta_fwd

@@ -16,12 +16,15 @@ template <typename T> struct __align__(16) V16 {
   T v[N];
 };
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+// hardware reciprocal for 16-bit element types (its 2^-22 is far below their rounding), IEEE division for fp32
+template <typename T> __device__ __forceinline__ float sigmoidf_(float x) {
+  return sizeof(T) == 2 ? __fdividef(1.f, 1.f + __expf(-x)) : 1.f / (1.f + __expf(-x));
+}
 
 template <typename T, int LPR>
 __global__ void __launch_bounds__(256) norm_gate_fwd_vec_kernel(const T *__restrict__ x, const T *__restrict__ g, const float *__restrict__ w,
                                                                 T *__restrict__ y, float *__restrict__ rstd_out, long long rows, float eps) {
-  constexpr int EV = 16 / sizeof(T), RPW = 32 / LPR, N = EV * LPR, UNROLL = 2;
+  constexpr int EV = 16 / sizeof(T), RPW = 32 / LPR, N = EV * LPR, UNROLL = 4;
   const int lane = threadIdx.x & 31, sub = lane / LPR, li = lane % LPR;
   const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * (blockDim.x >> 5);
   float wv[EV];
@@ -54,7 +57,7 @@ __global__ void __launch_bounds__(256) norm_gate_fwd_vec_kernel(const T *__restr
 #pragma unroll
         for (int j = 0; j < EV; ++j) {
           const float gg = Num<T>::f(gi[u].v[j]);
-          out.v[j] = Num<T>::t(f[j] * rstd * wv[j] * gg * sigmoidf_(gg));
+          out.v[j] = Num<T>::t(f[j] * rstd * wv[j] * gg * sigmoidf_<T>(gg));
         }
         *reinterpret_cast<V16<T> *>(y + r * N + li * EV) = out;
         if (li == 0) rstd_out[r] = rstd;
@@ -64,7 +67,7 @@ __global__ void __launch_bounds__(256) norm_gate_fwd_vec_kernel(const T *__restr
 }
 
 template <typename T, int LPR>
-__global__ void __launch_bounds__(256) norm_gate_bwd_vec_kernel(const T *__restrict__ x, const T *__restrict__ g, const float *__restrict__ w,
+__global__ void __launch_bounds__(256, 2) norm_gate_bwd_vec_kernel(const T *__restrict__ x, const T *__restrict__ g, const float *__restrict__ w,
                                                                 const T *__restrict__ dy, const float *__restrict__ rstd_in, T *__restrict__ dx,
                                                                 T *__restrict__ dg, float *__restrict__ dw_partial, long long rows) {
   constexpr int EV = 16 / sizeof(T), RPW = 32 / LPR, N = EV * LPR;
@@ -74,39 +77,49 @@ __global__ void __launch_bounds__(256) norm_gate_bwd_vec_kernel(const T *__restr
   float wv[EV], dwacc[EV];
 #pragma unroll
   for (int j = 0; j < EV; ++j) wv[j] = w[li * EV + j], dwacc[j] = 0.f;
-  for (long long r0 = warp * RPW; r0 < rows; r0 += nwarps * RPW) {
-    const long long r = r0 + sub;
-    const bool on = r < rows;
-    V16<T> xi, gi, yi;
-    float rstd = 0.f;
-    if (on) {
-      xi = *reinterpret_cast<const V16<T> *>(x + r * N + li * EV);
-      gi = *reinterpret_cast<const V16<T> *>(g + r * N + li * EV);
-      yi = *reinterpret_cast<const V16<T> *>(dy + r * N + li * EV);
-      rstd = rstd_in[r];
-    }
-    float xhat[EV], wdy[EV], c1 = 0.f;
-    V16<T> og;
+  constexpr int UNROLL = 2;  // row groups whose loads are in flight together
+  for (long long r0 = warp * RPW * UNROLL; r0 < rows; r0 += nwarps * RPW * UNROLL) {
+    V16<T> xv[UNROLL], gv[UNROLL], yv[UNROLL];
+    float rs[UNROLL];
 #pragma unroll
-    for (int j = 0; j < EV; ++j) {
-      const float xf = on ? Num<T>::f(xi.v[j]) : 0.f, gf = on ? Num<T>::f(gi.v[j]) : 0.f, d = on ? Num<T>::f(yi.v[j]) : 0.f;
-      const float s = sigmoidf_(gf);
-      xhat[j] = xf * rstd;
-      og.v[j] = Num<T>::t(d * (xhat[j] * wv[j]) * (s + gf * s * (1.f - s)));
-      const float d2 = d * gf * s;
-      dwacc[j] = fmaf(d2, xhat[j], dwacc[j]);
-      wdy[j] = d2 * wv[j];
-      c1 = fmaf(xhat[j], wdy[j], c1);
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long r = r0 + u * RPW + sub;
+      rs[u] = 0.f;
+      if (r < rows) {
+        xv[u] = *reinterpret_cast<const V16<T> *>(x + r * N + li * EV);
+        gv[u] = *reinterpret_cast<const V16<T> *>(g + r * N + li * EV);
+        yv[u] = *reinterpret_cast<const V16<T> *>(dy + r * N + li * EV);
+        rs[u] = rstd_in[r];
+      }
     }
 #pragma unroll
-    for (int o = LPR / 2; o > 0; o >>= 1) c1 += __shfl_xor_sync(0xffffffffu, c1, o);
-    c1 *= 1.f / N;
-    if (on) {
-      V16<T> ox;
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long r = r0 + u * RPW + sub;
+      const bool on = r < rows;
+      const float rstd = rs[u];
+      float xhat[EV], wdy[EV], c1 = 0.f;
+      V16<T> og;
 #pragma unroll
-      for (int j = 0; j < EV; ++j) ox.v[j] = Num<T>::t((wdy[j] - xhat[j] * c1) * rstd);
-      *reinterpret_cast<V16<T> *>(dx + r * N + li * EV) = ox;
-      *reinterpret_cast<V16<T> *>(dg + r * N + li * EV) = og;
+      for (int j = 0; j < EV; ++j) {
+        const float xf = on ? Num<T>::f(xv[u].v[j]) : 0.f, gf = on ? Num<T>::f(gv[u].v[j]) : 0.f, d = on ? Num<T>::f(yv[u].v[j]) : 0.f;
+        const float s = sigmoidf_<T>(gf);
+        xhat[j] = xf * rstd;
+        og.v[j] = Num<T>::t(d * (xhat[j] * wv[j]) * (s + gf * s * (1.f - s)));
+        const float d2 = d * gf * s;
+        dwacc[j] = fmaf(d2, xhat[j], dwacc[j]);
+        wdy[j] = d2 * wv[j];
+        c1 = fmaf(xhat[j], wdy[j], c1);
+      }
+#pragma unroll
+      for (int o = LPR / 2; o > 0; o >>= 1) c1 += __shfl_xor_sync(0xffffffffu, c1, o);
+      c1 *= 1.f / N;
+      if (on) {
+        V16<T> ox;
+#pragma unroll
+        for (int j = 0; j < EV; ++j) ox.v[j] = Num<T>::t((wdy[j] - xhat[j] * c1) * rstd);
+        *reinterpret_cast<V16<T> *>(dx + r * N + li * EV) = ox;
+        *reinterpret_cast<V16<T> *>(dg + r * N + li * EV) = og;
+      }
     }
   }
   // dw: lanes with the same columns inside the warp, then the eight warps
@@ -150,19 +163,19 @@ __global__ void __launch_bounds__(256) norm_gate_row_kernel(const T *__restrict_
       if (lane == 0) rstd_io[r] = rstd;
       for (int c = lane; c < n; c += 32) {
         const float gg = Num<T>::f(gr[c]);
-        out[r * n + c] = Num<T>::t(Num<T>::f(xr[c]) * rstd * w[c] * gg * sigmoidf_(gg));
+        out[r * n + c] = Num<T>::t(Num<T>::f(xr[c]) * rstd * w[c] * gg * sigmoidf_<T>(gg));
       }
     } else {
       const T *dr = dy + r * n;
       const float rstd = rstd_io[r];
       float c1 = 0.f;
       for (int c = lane; c < n; c += 32) {
-        const float gf = Num<T>::f(gr[c]), s = sigmoidf_(gf);
+        const float gf = Num<T>::f(gr[c]), s = sigmoidf_<T>(gf);
         c1 = fmaf(Num<T>::f(xr[c]) * rstd, Num<T>::f(dr[c]) * gf * s * w[c], c1);
       }
       c1 = warp_sum(c1) / n;
       for (int c = lane; c < n; c += 32) {
-        const float xf = Num<T>::f(xr[c]), gf = Num<T>::f(gr[c]), d = Num<T>::f(dr[c]), s = sigmoidf_(gf);
+        const float xf = Num<T>::f(xr[c]), gf = Num<T>::f(gr[c]), d = Num<T>::f(dr[c]), s = sigmoidf_<T>(gf);
         const float xh = xf * rstd, d2 = d * gf * s, wd = d2 * w[c];
         dg[r * n + c] = Num<T>::t(d * (xh * w[c]) * (s + gf * s * (1.f - s)));
         out[r * n + c] = Num<T>::t((wd - xh * c1) * rstd);

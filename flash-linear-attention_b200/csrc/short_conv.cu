@@ -2,7 +2,7 @@
 // and v before the chunk op (fla/modules/convolution.py:79-216; fla/layers/gated_deltanet.py:205-228):
 //   pre[b,t,d] = bias[d] + sum_{w<W} weight[d,w] x[b, t-(W-1)+w, d]   (x = 0 before the sequence),  y = silu(pre) or pre
 //   decode step (:189-216): the cache [B, D, W] is shifted by one, x appended, y = act(bias + sum_w cache[., ., w] weight[., w])
-// Layout [B, T, D] with the channels contiguous: a thread owns 16 bytes of channels and walks TT tokens with the last
+// Layout [B, T, D] with the channels contiguous: a thread owns four channels and walks TT tokens with the last
 // W-1 inputs in registers, so x is read once (plus a halo of W-1 tokens per tile) and y written once.
 // Backward: pre is recomputed, dpre = dy * act'(pre);  dx[t] = sum_w weight[d,w] dpre[t+(W-1)-w];
 // dweight[d,w] = sum_{b,t} dpre[t] x[t-(W-1)+w], dbias[d] = sum dpre: per-thread partial sums over the tile, then fp32
@@ -12,22 +12,28 @@
 namespace flab {
 
 constexpr int SC_TT = 32;    // tokens per thread
-constexpr int SC_WMAX = 8;   // longest supported filter
+constexpr int SC_WMAX = 8;   // longest supported filter (decode step)
+constexpr int SC_UN = 4;     // tokens whose loads are in flight together
 
-template <typename T> struct __align__(16) CV {
-  static constexpr int N = 16 / sizeof(T);
+// four channels per thread (8 bytes of a 16-bit type, 16 bytes of fp32): twice that costs the backward kernel its occupancy
+template <typename T> struct __align__(4 * sizeof(T)) CV {
+  static constexpr int N = 4;
   T v[N];
 };
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
-__device__ __forceinline__ float silu_grad_f(float x) {
-  const float s = 1.f / (1.f + __expf(-x));
+// sigmoid: hardware reciprocal for 16-bit element types (its 2^-22 is far below their rounding), IEEE division for fp32
+template <typename T> __device__ __forceinline__ float sigm(float x) {
+  return sizeof(T) == 2 ? __fdividef(1.f, 1.f + __expf(-x)) : 1.f / (1.f + __expf(-x));
+}
+template <typename T> __device__ __forceinline__ float silu_f(float x) { return x * sigm<T>(x); }
+template <typename T> __device__ __forceinline__ float silu_grad_f(float x) {
+  const float s = sigm<T>(x);
   return s * (1.f + x * (1.f - s));
 }
 
 // grid (ceil(T / TT), B, ceil(D / (EV * 256)))
 template <typename T, int W, bool ACT>
-__global__ void __launch_bounds__(256) short_conv_fwd_kernel(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+__global__ void __launch_bounds__(256, 3) short_conv_fwd_kernel(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                                                              T *__restrict__ y, int Tlen, int D) {
   constexpr int EV = CV<T>::N;
   const int c0 = (blockIdx.z * 256 + threadIdx.x) * EV;
@@ -51,28 +57,37 @@ __global__ void __launch_bounds__(256) short_conv_fwd_kernel(const T *__restrict
     for (int j = 0; j < EV; ++j) win[k + 1][j] = t >= 0 ? Num<T>::f(v.v[j]) : 0.f;
   }
   const int tend = min(t0 + SC_TT, Tlen);
-  for (int t = t0; t < tend; ++t) {
-    const CV<T> v = *reinterpret_cast<const CV<T> *>(xb + (size_t)t * D);
+  constexpr int UNF = 2 * SC_UN;
+  for (int tg = t0; tg < tend; tg += UNF) {
+    CV<T> vin[UNF];  // the group's loads are issued before any of them is used
 #pragma unroll
-    for (int k = 0; k < W - 1; ++k)
+    for (int u = 0; u < UNF; ++u)
+      if (tg + u < tend) vin[u] = *reinterpret_cast<const CV<T> *>(xb + (size_t)(tg + u) * D);
 #pragma unroll
-      for (int j = 0; j < EV; ++j) win[k][j] = win[k + 1][j];
-    CV<T> out;
+    for (int u = 0; u < UNF; ++u) {
+      const int t = tg + u;
+      if (t >= tend) break;
 #pragma unroll
-    for (int j = 0; j < EV; ++j) {
-      win[W - 1][j] = Num<T>::f(v.v[j]);
-      float pre = bv[j];
+      for (int k = 0; k < W - 1; ++k)
 #pragma unroll
-      for (int k = 0; k < W; ++k) pre = fmaf(wv[j][k], win[k][j], pre);
-      out.v[j] = Num<T>::t(ACT ? silu_f(pre) : pre);
+        for (int j = 0; j < EV; ++j) win[k][j] = win[k + 1][j];
+      CV<T> out;
+#pragma unroll
+      for (int j = 0; j < EV; ++j) {
+        win[W - 1][j] = Num<T>::f(vin[u].v[j]);
+        float pre = bv[j];
+#pragma unroll
+        for (int k = 0; k < W; ++k) pre = fmaf(wv[j][k], win[k][j], pre);
+        out.v[j] = Num<T>::t(ACT ? silu_f<T>(pre) : pre);
+      }
+      *reinterpret_cast<CV<T> *>(yb + (size_t)t * D) = out;
     }
-    *reinterpret_cast<CV<T> *>(yb + (size_t)t * D) = out;
   }
 }
 
 // Same grid.  The thread recomputes pre over [t0, t0 + TT + W - 1) (the right halo feeds dx of its last tokens).
 template <typename T, int W, bool ACT>
-__global__ void __launch_bounds__(256) short_conv_bwd_kernel(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+__global__ void __launch_bounds__(256, 2) short_conv_bwd_kernel(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                                                              const T *__restrict__ dy, T *__restrict__ dx, float *__restrict__ dw,
                                                              float *__restrict__ db, int Tlen, int D) {
   constexpr int EV = CV<T>::N;
@@ -100,46 +115,53 @@ __global__ void __launch_bounds__(256) short_conv_bwd_kernel(const T *__restrict
   const int tend = min(t0 + SC_TT, Tlen);
   // step s handles token t = t0 + s: computes dpre[t]; once W-1 further tokens are in, dx[t - (W-1)] is complete:
   // dx[u] = sum_w weight[w] dpre[u + (W-1) - w]  ->  with dp[k] = dpre[t - (W-1) + k]:  dx[t-(W-1)] = sum_w weight[w] dp[W-1-w]
-  for (int t = t0; t < tend + (W - 1); ++t) {
-    const bool in_seq = t < Tlen;
-    CV<T> v, g;
-    if (in_seq) {
-      v = *reinterpret_cast<const CV<T> *>(xb + (size_t)t * D);
-      g = *reinterpret_cast<const CV<T> *>(gb + (size_t)t * D);
-    }
+  for (int tg = t0; tg < tend + (W - 1); tg += SC_UN) {
+    CV<T> vin[SC_UN], gin[SC_UN];
 #pragma unroll
-    for (int k = 0; k < W - 1; ++k)
-#pragma unroll
-      for (int j = 0; j < EV; ++j) xin[k][j] = xin[k + 1][j], dp[k][j] = dp[k + 1][j];
-    const bool own = t < tend;  // tokens of the right halo belong to the next tile for dweight / dbias
-#pragma unroll
-    for (int j = 0; j < EV; ++j) {
-      xin[W - 1][j] = in_seq ? Num<T>::f(v.v[j]) : 0.f;
-      float d = 0.f;
-      if (in_seq) {
-        float pre = bv[j];
-#pragma unroll
-        for (int k = 0; k < W; ++k) pre = fmaf(wv[j][k], xin[k][j], pre);
-        d = Num<T>::f(g.v[j]) * (ACT ? silu_grad_f(pre) : 1.f);
+    for (int u = 0; u < SC_UN; ++u)
+      if (tg + u < Tlen && tg + u < tend + (W - 1)) {
+        vin[u] = *reinterpret_cast<const CV<T> *>(xb + (size_t)(tg + u) * D);
+        gin[u] = *reinterpret_cast<const CV<T> *>(gb + (size_t)(tg + u) * D);
       }
-      dp[W - 1][j] = d;
-      if (own) {
-        dbacc[j] += d;
 #pragma unroll
-        for (int k = 0; k < W; ++k) dwacc[j][k] = fmaf(d, xin[k][j], dwacc[j][k]);
-      }
-    }
-    const int u = t - (W - 1);
-    if (u >= t0 && u < tend) {
-      CV<T> out;
+    for (int u = 0; u < SC_UN; ++u) {
+      const int t = tg + u;
+      if (t >= tend + (W - 1)) break;
+      const bool in_seq = t < Tlen;
+#pragma unroll
+      for (int k = 0; k < W - 1; ++k)
+#pragma unroll
+        for (int j = 0; j < EV; ++j) xin[k][j] = xin[k + 1][j], dp[k][j] = dp[k + 1][j];
+      const bool own = t < tend;  // tokens of the right halo belong to the next tile for dweight / dbias
 #pragma unroll
       for (int j = 0; j < EV; ++j) {
-        float a = 0.f;
+        xin[W - 1][j] = in_seq ? Num<T>::f(vin[u].v[j]) : 0.f;
+        float d = 0.f;
+        if (in_seq) {
+          float pre = bv[j];
 #pragma unroll
-        for (int k = 0; k < W; ++k) a = fmaf(wv[j][k], dp[W - 1 - k][j], a);
-        out.v[j] = Num<T>::t(a);
+          for (int k = 0; k < W; ++k) pre = fmaf(wv[j][k], xin[k][j], pre);
+          d = Num<T>::f(gin[u].v[j]) * (ACT ? silu_grad_f<T>(pre) : 1.f);
+        }
+        dp[W - 1][j] = d;
+        if (own) {
+          dbacc[j] += d;
+#pragma unroll
+          for (int k = 0; k < W; ++k) dwacc[j][k] = fmaf(d, xin[k][j], dwacc[j][k]);
+        }
       }
-      *reinterpret_cast<CV<T> *>(ob + (size_t)u * D) = out;
+      const int uo = t - (W - 1);
+      if (uo >= t0 && uo < tend) {
+        CV<T> out;
+#pragma unroll
+        for (int j = 0; j < EV; ++j) {
+          float a = 0.f;
+#pragma unroll
+          for (int k = 0; k < W; ++k) a = fmaf(wv[j][k], dp[W - 1 - k][j], a);
+          out.v[j] = Num<T>::t(a);
+        }
+        *reinterpret_cast<CV<T> *>(ob + (size_t)uo * D) = out;
+      }
     }
   }
 #pragma unroll
@@ -167,7 +189,7 @@ __global__ void __launch_bounds__(256) short_conv_update_kernel(const T *__restr
   const T xv = x[idx];
   c[W - 1] = xv;
   pre = fmaf(Num<T>::f(xv), w[(size_t)d * W + W - 1], pre);
-  y[idx] = Num<T>::t(ACT ? silu_f(pre) : pre);
+  y[idx] = Num<T>::t(ACT ? silu_f<T>(pre) : pre);
 }
 
 template <typename T, int W>
@@ -201,7 +223,8 @@ static int dispatch_short_conv(bool bwd, bool act, const void *x, const float *w
 }
 
 static int short_conv_check(const void *const *ptrs, int n, int D, int dtype) {
-  const int ev = dtype == FLAB_FP32 ? 4 : 8;
+  const int ev = 4;
+  (void)dtype;
   FLAB_REQUIRE(D % ev == 0, FLAB_E_UNSUPPORTED, "short_conv: the channel count (%d) must be a multiple of %d", D, ev);
   for (int i = 0; i < n; ++i)
     FLAB_REQUIRE(!ptrs[i] || reinterpret_cast<uintptr_t>(ptrs[i]) % 16 == 0, FLAB_E_UNSUPPORTED, "short_conv: tensors must be 16-byte aligned");

@@ -43,5 +43,7 @@ def install_as_fla_modules():
     sys.modules["fla.modules.l2norm"] = l2norm
     from .modules import fused_norm_gate
     sys.modules["fla.modules.fused_norm_gate"] = fused_norm_gate
+    from .modules import convolution
+    sys.modules["fla.modules.convolution"] = convolution
     root.modules = modules
 

@@ -125,7 +125,7 @@ int flab_rms_norm_swish_gate_bwd(const void *x, const void *gate, const float *w
 /* ---- causal depthwise short convolution (q, k, v of the reference's layers pass through it first) ----
  * Replaces the convolution of ShortConvolution.forward / .step (fla/modules/convolution.py:142-216):
  *   y[b,t,d] = act(bias[d] + sum_{w<W} weight[d,w] x[b, t-(W-1)+w, d]),  x = 0 before the sequence, act = SiLU or none.
- * x, y, dy, dx: [B, T, D] contiguous of element type dtype (D a multiple of 16 bytes of elements, 16-byte aligned);
+ * x, y, dy, dx: [B, T, D] contiguous of element type dtype (D a multiple of 4, 16-byte aligned);
  * weight fp32 [D, W] (W = 2, 3 or 4), bias fp32 [D] or NULL. Backward adds into dweight (fp32 [D, W]) and dbias
  * (fp32 [D], with a bias) with atomics: the caller zeroes them. The update entry is the one-token decode step:
  * cache [B, D, W] (element type dtype) is shifted by one in place, x [B, D] appended, y [B, D] written (W <= 8). */
