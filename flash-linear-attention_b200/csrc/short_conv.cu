@@ -85,7 +85,8 @@ __global__ void __launch_bounds__(256, 3) short_conv_fwd_kernel(const T *__restr
   }
 }
 
-// Same grid.  The thread recomputes pre over [t0, t0 + TT + W - 1) (the right halo feeds dx of its last tokens).
+// grid (token-tile walkers, B, channel groups).  The thread recomputes pre over [t0, t0 + TT + W - 1) (the right halo
+// feeds dx of its last tokens).
 template <typename T, int W, bool ACT>
 __global__ void __launch_bounds__(256, 2) short_conv_bwd_kernel(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                                                              const T *__restrict__ dy, T *__restrict__ dx, float *__restrict__ dw,
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(256, 2) short_conv_bwd_kernel(const T *__restr
   constexpr int EV = CV<T>::N;
   const int c0 = (blockIdx.z * 256 + threadIdx.x) * EV;
   if (c0 >= D) return;
-  const int t0 = blockIdx.x * SC_TT, b = blockIdx.y;
+  const int b = blockIdx.y;
   const T *xb = x + (size_t)b * Tlen * D + c0, *gb = dy + (size_t)b * Tlen * D + c0;
   T *ob = dx + (size_t)b * Tlen * D + c0;
   float wv[EV][W], bv[EV], xin[W][EV], dp[W][EV], dwacc[EV][W], dbacc[EV];
@@ -102,8 +103,15 @@ __global__ void __launch_bounds__(256, 2) short_conv_bwd_kernel(const T *__restr
     bv[j] = bias ? bias[c0 + j] : 0.f;
     dbacc[j] = 0.f;
 #pragma unroll
-    for (int k = 0; k < W; ++k) wv[j][k] = w[(size_t)(c0 + j) * W + k], dwacc[j][k] = 0.f, dp[k][j] = 0.f;
+    for (int k = 0; k < W; ++k) wv[j][k] = w[(size_t)(c0 + j) * W + k], dwacc[j][k] = 0.f;
   }
+  // a block walks several token tiles (stride gridDim.x) and keeps its dweight / dbias sums in registers across them:
+  // one round of atomics per thread instead of one per tile
+  for (int t0 = blockIdx.x * SC_TT; t0 < Tlen; t0 += gridDim.x * SC_TT) {
+#pragma unroll
+  for (int j = 0; j < EV; ++j)
+#pragma unroll
+    for (int k = 0; k < W; ++k) dp[k][j] = 0.f;
 #pragma unroll
   for (int k = 0; k < W - 1; ++k) {
     const int t = t0 - (W - 1) + k;
@@ -164,6 +172,7 @@ __global__ void __launch_bounds__(256, 2) short_conv_bwd_kernel(const T *__restr
       }
     }
   }
+  }
 #pragma unroll
   for (int j = 0; j < EV; ++j) {
     if (db) atomicAdd(db + c0 + j, dbacc[j]);
@@ -197,6 +206,14 @@ static int launch_short_conv(bool bwd, bool act, const void *x, const float *w, 
                              int B, int Tlen, int D, cudaStream_t st) {
   constexpr int EV = CV<T>::N;
   dim3 grid(cdiv(Tlen, SC_TT), B, cdiv(D, EV * 256));
+  if (bwd) {  // about two waves of blocks (two resident blocks per SM), each walking several token tiles
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int per_x = (int)(B * grid.z);
+    const int gx = (4 * sms + per_x - 1) / per_x;
+    if ((int)grid.x > gx) grid.x = gx < 1 ? 1 : gx;
+  }
   const T *xi = reinterpret_cast<const T *>(x), *gi = reinterpret_cast<const T *>(dy);
   T *o = reinterpret_cast<T *>(out);
   if (!bwd) {
