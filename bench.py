@@ -442,7 +442,9 @@ def main():
         tensor_bytes = B * T * H * K * 2
         ach_f, ach_b = 2 * tensor_bytes / (ms_f * 1e-3) / 1e9, 3 * tensor_bytes / (ms_b * 1e-3) / 1e9
         line["roofline"] = {"kernel": "l2norm_bwd_vec_kernel", "bound": "hbm", "achieved": ach_b, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                            "frac": ach_b / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"], "ms_per_launch": ms_b}
+                            "frac": ach_b / pk["hbm_gbs"], "traffic": 371e6 if (B, T, H, K) == (8, 4096, 16, 128) else None,
+                            "traffic_source": "ncu, same workload (profiles/streaming_modules_ncu_dram.md)", "peak_source": pk["source"],
+                            "ms_per_launch": ms_b}
         line["kernels"] = {"l2norm_fwd_vec_kernel": {"ms": ms_f, "GB/s": ach_f, "frac": ach_f / pk["hbm_gbs"]},
                            "l2norm_bwd_vec_kernel": {"ms": ms_b, "GB/s": ach_b, "frac": ach_b / pk["hbm_gbs"]}}
     if op in ("short_conv", "norm_gate") and rank == 0:
@@ -472,8 +474,11 @@ def main():
             ms_b = time_stage(lambda: lib.flab_rms_norm_swish_gate_bwd(P[0], P[1], P[2], P[5], P[4], P[6], P[7], P[8], rows, K, 0, st), reps=30, warm=5)
             nf, nb, names = 3, 5, ("norm_gate_fwd_vec_kernel", "norm_gate_bwd_vec_kernel")
         ach_f, ach_b = nf * tb / (ms_f * 1e-3) / 1e9, nb * tb / (ms_b * 1e-3) / 1e9
+        # DRAM read + write per launch of the backward kernel at this shape (profiles/streaming_modules_ncu_dram.md)
+        traffic = {"short_conv": 379e6, "norm_gate": 635e6}[op] if (B, T, H, K) == (8, 4096, 16, 128) else None
         line["roofline"] = {"kernel": names[1], "bound": "hbm", "achieved": ach_b, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                            "frac": ach_b / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"], "ms_per_launch": ms_b}
+                            "frac": ach_b / pk["hbm_gbs"], "traffic": traffic, "traffic_source": "ncu, same workload",
+                            "peak_source": pk["source"], "ms_per_launch": ms_b}
         line["kernels"] = {names[0]: {"ms": ms_f, "GB/s": ach_f, "frac": ach_f / pk["hbm_gbs"]},
                            names[1]: {"ms": ms_b, "GB/s": ach_b, "frac": ach_b / pk["hbm_gbs"]}}
     if op == "decode" and rank == 0:
