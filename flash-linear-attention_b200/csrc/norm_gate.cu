@@ -7,6 +7,8 @@
 // row layout as the L2 norm: rows of 16 bytes x 2^k lanes stay in registers, several rows per warp instruction.
 // dw is reduced per block (registers -> warp shuffles -> shared memory) into one partial row per block; the caller
 // sums the partial rows, like the reference sums its per-program partials (fused_norm_gate.py:385-386).
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace flab {
@@ -16,8 +18,13 @@ template <typename T> struct __align__(16) V16 {
   T v[N];
 };
 
-// hardware reciprocal for 16-bit element types (its 2^-22 is far below their rounding), IEEE division for fp32
+// sigmoid: tanh.approx for bf16, exponential + hardware reciprocal for fp16, exponential + IEEE division for fp32
 template <typename T> __device__ __forceinline__ float sigmoidf_(float x) {
+  if (std::is_same<T, bf16>::value) {  // one special-function instruction; its 5e-4 absolute error is below half a bf16 ulp of the product
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+    return fmaf(0.5f, t, 0.5f);
+  }
   return sizeof(T) == 2 ? __fdividef(1.f, 1.f + __expf(-x)) : 1.f / (1.f + __expf(-x));
 }
 
