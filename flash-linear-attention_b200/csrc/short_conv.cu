@@ -17,11 +17,13 @@ constexpr int SC_TT = 32;    // tokens per thread
 constexpr int SC_WMAX = 8;   // longest supported filter (decode step)
 constexpr int SC_UN = 4;     // tokens whose loads are in flight together
 
-// four channels per thread (8 bytes of a 16-bit type, 16 bytes of fp32): twice that costs the backward kernel its occupancy
-template <typename T> struct __align__(4 * sizeof(T)) CV {
-  static constexpr int N = 4;
+// EV channels per thread: four in the forward kernel (8 bytes of a 16-bit type, 16 bytes of fp32), two in the backward
+// kernel, whose register windows (inputs, dpre, dweight sums) otherwise leave two blocks per SM
+template <typename T, int EV> struct __align__(EV * sizeof(T)) CV {
+  static constexpr int N = EV;
   T v[N];
 };
+constexpr int SC_EVF = 4, SC_EVB = 2;
 
 // sigmoid: tanh.approx for bf16, exponential + hardware reciprocal for fp16, exponential + IEEE division for fp32
 template <typename T> __device__ __forceinline__ float sigm(float x) {
@@ -39,10 +41,10 @@ template <typename T> __device__ __forceinline__ float silu_grad_f(float x) {
 }
 
 // grid (ceil(T / TT), B, ceil(D / (EV * 256)))
-template <typename T, int W, bool ACT>
+template <typename T, int W, bool ACT, int EV>
 __global__ void __launch_bounds__(256, 3) short_conv_fwd_kernel(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                                                              T *__restrict__ y, int Tlen, int D) {
-  constexpr int EV = CV<T>::N;
+  using CVT = CV<T, EV>;
   const int c0 = (blockIdx.z * 256 + threadIdx.x) * EV;
   if (c0 >= D) return;
   const int t0 = blockIdx.x * SC_TT, b = blockIdx.y;
@@ -58,18 +60,18 @@ __global__ void __launch_bounds__(256, 3) short_conv_fwd_kernel(const T *__restr
 #pragma unroll
   for (int k = 0; k < W - 1; ++k) {  // win[k + 1] <- x[t0 - (W-1) + k]
     const int t = t0 - (W - 1) + k;
-    CV<T> v;
-    if (t >= 0) v = *reinterpret_cast<const CV<T> *>(xb + (size_t)t * D);
+    CVT v;
+    if (t >= 0) v = *reinterpret_cast<const CVT *>(xb + (size_t)t * D);
 #pragma unroll
     for (int j = 0; j < EV; ++j) win[k + 1][j] = t >= 0 ? Num<T>::f(v.v[j]) : 0.f;
   }
   const int tend = min(t0 + SC_TT, Tlen);
   constexpr int UNF = 2 * SC_UN;
   for (int tg = t0; tg < tend; tg += UNF) {
-    CV<T> vin[UNF];  // the group's loads are issued before any of them is used
+    CVT vin[UNF];  // the group's loads are issued before any of them is used
 #pragma unroll
     for (int u = 0; u < UNF; ++u)
-      if (tg + u < tend) vin[u] = *reinterpret_cast<const CV<T> *>(xb + (size_t)(tg + u) * D);
+      if (tg + u < tend) vin[u] = *reinterpret_cast<const CVT *>(xb + (size_t)(tg + u) * D);
 #pragma unroll
     for (int u = 0; u < UNF; ++u) {
       const int t = tg + u;
@@ -78,7 +80,7 @@ __global__ void __launch_bounds__(256, 3) short_conv_fwd_kernel(const T *__restr
       for (int k = 0; k < W - 1; ++k)
 #pragma unroll
         for (int j = 0; j < EV; ++j) win[k][j] = win[k + 1][j];
-      CV<T> out;
+      CVT out;
 #pragma unroll
       for (int j = 0; j < EV; ++j) {
         win[W - 1][j] = Num<T>::f(vin[u].v[j]);
@@ -87,18 +89,18 @@ __global__ void __launch_bounds__(256, 3) short_conv_fwd_kernel(const T *__restr
         for (int k = 0; k < W; ++k) pre = fmaf(wv[j][k], win[k][j], pre);
         out.v[j] = Num<T>::t(ACT ? silu_f<T>(pre) : pre);
       }
-      *reinterpret_cast<CV<T> *>(yb + (size_t)t * D) = out;
+      *reinterpret_cast<CVT *>(yb + (size_t)t * D) = out;
     }
   }
 }
 
 // grid (token-tile walkers, B, channel groups).  The thread recomputes pre over [t0, t0 + TT + W - 1) (the right halo
 // feeds dx of its last tokens).
-template <typename T, int W, bool ACT>
-__global__ void __launch_bounds__(256, 2) short_conv_bwd_kernel(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+template <typename T, int W, bool ACT, int EV>
+__global__ void __launch_bounds__(256, 3) short_conv_bwd_kernel(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                                                              const T *__restrict__ dy, T *__restrict__ dx, float *__restrict__ dw,
                                                              float *__restrict__ db, int Tlen, int D) {
-  constexpr int EV = CV<T>::N;
+  using CVT = CV<T, EV>;
   const int c0 = (blockIdx.z * 256 + threadIdx.x) * EV;
   if (c0 >= D) return;
   const int b = blockIdx.y;
@@ -122,8 +124,8 @@ __global__ void __launch_bounds__(256, 2) short_conv_bwd_kernel(const T *__restr
 #pragma unroll
   for (int k = 0; k < W - 1; ++k) {
     const int t = t0 - (W - 1) + k;
-    CV<T> v;
-    if (t >= 0) v = *reinterpret_cast<const CV<T> *>(xb + (size_t)t * D);
+    CVT v;
+    if (t >= 0) v = *reinterpret_cast<const CVT *>(xb + (size_t)t * D);
 #pragma unroll
     for (int j = 0; j < EV; ++j) xin[k + 1][j] = t >= 0 ? Num<T>::f(v.v[j]) : 0.f;
   }
@@ -131,12 +133,12 @@ __global__ void __launch_bounds__(256, 2) short_conv_bwd_kernel(const T *__restr
   // step s handles token t = t0 + s: computes dpre[t]; once W-1 further tokens are in, dx[t - (W-1)] is complete:
   // dx[u] = sum_w weight[w] dpre[u + (W-1) - w]  ->  with dp[k] = dpre[t - (W-1) + k]:  dx[t-(W-1)] = sum_w weight[w] dp[W-1-w]
   for (int tg = t0; tg < tend + (W - 1); tg += SC_UN) {
-    CV<T> vin[SC_UN], gin[SC_UN];
+    CVT vin[SC_UN], gin[SC_UN];
 #pragma unroll
     for (int u = 0; u < SC_UN; ++u)
       if (tg + u < Tlen && tg + u < tend + (W - 1)) {
-        vin[u] = *reinterpret_cast<const CV<T> *>(xb + (size_t)(tg + u) * D);
-        gin[u] = *reinterpret_cast<const CV<T> *>(gb + (size_t)(tg + u) * D);
+        vin[u] = *reinterpret_cast<const CVT *>(xb + (size_t)(tg + u) * D);
+        gin[u] = *reinterpret_cast<const CVT *>(gb + (size_t)(tg + u) * D);
       }
 #pragma unroll
     for (int u = 0; u < SC_UN; ++u) {
@@ -167,7 +169,7 @@ __global__ void __launch_bounds__(256, 2) short_conv_bwd_kernel(const T *__restr
       }
       const int uo = t - (W - 1);
       if (uo >= t0 && uo < tend) {
-        CV<T> out;
+        CVT out;
 #pragma unroll
         for (int j = 0; j < EV; ++j) {
           float a = 0.f;
@@ -175,7 +177,7 @@ __global__ void __launch_bounds__(256, 2) short_conv_bwd_kernel(const T *__restr
           for (int k = 0; k < W; ++k) a = fmaf(wv[j][k], dp[W - 1 - k][j], a);
           out.v[j] = Num<T>::t(a);
         }
-        *reinterpret_cast<CV<T> *>(ob + (size_t)uo * D) = out;
+        *reinterpret_cast<CVT *>(ob + (size_t)uo * D) = out;
       }
     }
   }
@@ -211,24 +213,24 @@ __global__ void __launch_bounds__(256) short_conv_update_kernel(const T *__restr
 template <typename T, int W>
 static int launch_short_conv(bool bwd, bool act, const void *x, const float *w, const float *bias, const void *dy, void *out, float *dw, float *db,
                              int B, int Tlen, int D, cudaStream_t st) {
-  constexpr int EV = CV<T>::N;
+  const int EV = bwd ? SC_EVB : SC_EVF;
   dim3 grid(cdiv(Tlen, SC_TT), B, cdiv(D, EV * 256));
-  if (bwd) {  // about two waves of blocks (two resident blocks per SM), each walking several token tiles
+  if (bwd) {  // about two waves of blocks, each walking several token tiles
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int per_x = (int)(B * grid.z);
-    const int gx = (4 * sms + per_x - 1) / per_x;
+    const int gx = (6 * sms + per_x - 1) / per_x;  // two waves at three resident blocks per SM
     if ((int)grid.x > gx) grid.x = gx < 1 ? 1 : gx;
   }
   const T *xi = reinterpret_cast<const T *>(x), *gi = reinterpret_cast<const T *>(dy);
   T *o = reinterpret_cast<T *>(out);
   if (!bwd) {
-    if (act) short_conv_fwd_kernel<T, W, true><<<grid, 256, 0, st>>>(xi, w, bias, o, Tlen, D);
-    else short_conv_fwd_kernel<T, W, false><<<grid, 256, 0, st>>>(xi, w, bias, o, Tlen, D);
+    if (act) short_conv_fwd_kernel<T, W, true, SC_EVF><<<grid, 256, 0, st>>>(xi, w, bias, o, Tlen, D);
+    else short_conv_fwd_kernel<T, W, false, SC_EVF><<<grid, 256, 0, st>>>(xi, w, bias, o, Tlen, D);
   } else {
-    if (act) short_conv_bwd_kernel<T, W, true><<<grid, 256, 0, st>>>(xi, w, bias, gi, o, dw, db, Tlen, D);
-    else short_conv_bwd_kernel<T, W, false><<<grid, 256, 0, st>>>(xi, w, bias, gi, o, dw, db, Tlen, D);
+    if (act) short_conv_bwd_kernel<T, W, true, SC_EVB><<<grid, 256, 0, st>>>(xi, w, bias, gi, o, dw, db, Tlen, D);
+    else short_conv_bwd_kernel<T, W, false, SC_EVB><<<grid, 256, 0, st>>>(xi, w, bias, gi, o, dw, db, Tlen, D);
   }
   return check_launch(bwd ? "short_conv_bwd" : "short_conv_fwd");
 }
