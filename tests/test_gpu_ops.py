@@ -801,3 +801,43 @@ def test_short_conv_reference_module_vectors():
                 yt, cache = conv(g["step_x"][:, t:t + 1].to(DEV), cache=cache)
                 assert_close(f"{case} step {t}", g["step_y"][:, t:t + 1], yt, 1e-6)
         assert torch.equal(cache.cpu(), g["step_cache"])
+
+
+@pytest.mark.gpu
+def test_layer_pipeline_conv_norm_op_gate_matches_oracle_chain():
+    """The data path of the reference's GatedDeltaNet layer around the op (fla/layers/gated_deltanet.py:205-282):
+    short convolution + SiLU on q, k, v -> L2 norm of q, k -> chunk_gated_delta_rule -> RMS norm x swish gate, with this
+    package's kernels end to end against the same chain of oracles, forward and the gradient of every input."""
+    from fla_b200.modules import FusedRMSNormSwishGate, ShortConvolution, l2_norm
+    from fla_b200.ops import chunk_gated_delta_rule
+    B, T, H, D, W = 2, 200, 2, 128, 4
+    dt = torch.bfloat16
+    g0 = torch.Generator().manual_seed(77)
+    xq, xk, xv, gate = (torch.randn(B, T, H * D, generator=g0).to(dt) for _ in range(4))
+    wq, wk, wv = (torch.randn(H * D, W, generator=g0) * 0.5 for _ in range(3))
+    gl = F.logsigmoid(torch.randn(B, T, H, generator=g0))
+    beta = torch.rand(B, T, H, generator=g0).sigmoid().to(dt)
+    wn = 1 + 0.1 * torch.randn(D, generator=g0)
+    dout = torch.randn(B, T, H, D, generator=g0).to(dt)
+
+    # this package
+    convs = [_short_conv_module(H * D, W, False, "silu", w, None, dt) for w in (wq, wk, wv)]
+    norm = FusedRMSNormSwishGate(D, eps=1e-5).to(DEV)
+    with torch.no_grad():
+        norm.weight.copy_(wn)
+    ins = [t_.to(DEV).requires_grad_(True) for t_ in (xq, xk, xv, gate)]
+    q, k, v = (c(x)[0].view(B, T, H, D) for c, x in zip(convs, ins[:3]))
+    o, _ = chunk_gated_delta_rule(l2_norm(q), l2_norm(k), v, gl.to(DEV), beta.to(DEV), head_first=False)
+    y = norm(o, ins[3].view(B, T, H, D))
+    y.backward(dout.to(DEV))
+
+    # the oracles, fp32 on the same bf16 inputs, rounding to bf16 where the kernels hand a tensor on
+    rins = [t_.float().requires_grad_(True) for t_ in (xq, xk, xv, gate)]
+    rq, rk, rv = (oracle.short_conv(x, w, None, True)[0].view(B, T, H, D) for x, w in zip(rins[:3], (wq, wk, wv)))
+    ro, _ = oracle.gated_delta_rule(oracle.l2_norm(rq), oracle.l2_norm(rk), rv, beta.float(), g=gl, head_first=False)
+    ry = oracle.rms_norm_swish_gate(ro, rins[3].view(B, T, H, D), wn, 1e-5)
+    ry.backward(dout.float())
+
+    print("layer pipeline y: %.2e" % assert_close("y", ry, y, 1e-2))
+    for n, a, b in zip(("dxq", "dxk", "dxv", "dgate"), rins, ins):
+        print("layer pipeline %s: %.2e" % (n, assert_close(n, a.grad, b.grad, 2e-2)))
