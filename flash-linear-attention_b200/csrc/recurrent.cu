@@ -588,6 +588,8 @@ int flab_recurrent_fwd(const flab_args *a, void *stream) {
   if (int e = check_common(a)) return e;
   FLAB_REQUIRE(a->q && a->k && a->v && a->o, FLAB_E_BADARG, "recurrent_fwd needs q, k, v and o");
   FLAB_REQUIRE(a->K <= 256, FLAB_E_UNSUPPORTED, "recurrent_fwd: K = %d > 256", a->K);
+  FLAB_REQUIRE(!a->ht || a->ht != a->h0 || (a->flags & FLAB_F_INPLACE_STATE), FLAB_E_BADARG,
+               "recurrent_fwd: ht aliases h0; pass FLAB_F_INPLACE_STATE to update the state in place");
   FLAB_DISPATCH_ALL(a->dtype, T, return (launch_recurrent_fwd<T, false>(a, (cudaStream_t)stream)));
   return FLAB_OK;
 }
@@ -598,6 +600,10 @@ int flab_recurrent_delta_fwd(const flab_args *a, void *stream) {
   FLAB_REQUIRE(a->q && a->k && a->v && a->o, FLAB_E_BADARG, "recurrent_delta_fwd needs q, k, v and o");
   FLAB_REQUIRE(!a->gk && !a->gv, FLAB_E_UNSUPPORTED, "recurrent_delta_fwd: only the scalar gate g is supported");
   FLAB_REQUIRE(a->K <= 256, FLAB_E_UNSUPPORTED, "recurrent_delta_fwd: K = %d > 256", a->K);
+  // every (sequence, head, value slab) tile of the state is read in full by the one CTA that later writes it, so an
+  // in-place update is safe; the caller has to say that it means it
+  FLAB_REQUIRE(!a->ht || a->ht != a->h0 || (a->flags & FLAB_F_INPLACE_STATE), FLAB_E_BADARG,
+               "recurrent_delta_fwd: ht aliases h0; pass FLAB_F_INPLACE_STATE to update the state in place");
   FLAB_DISPATCH_ALL(a->dtype, T, return (launch_recurrent_fwd<T, true>(a, (cudaStream_t)stream)));
   return FLAB_OK;
 }

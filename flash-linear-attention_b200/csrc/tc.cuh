@@ -55,6 +55,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   }
 }
 
+// The same wait with a caller-chosen limit in clock ticks (the wait self-test uses a short one).
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t *bar, uint32_t parity, long long limit_ticks) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > limit_ticks) return false;
+  }
+}
+
 // ---- TMA -----------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
   asm volatile(
@@ -226,7 +236,7 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 
 // Each translation unit with tcgen05 kernels defines its own device error word with this macro; a
 // kernel whose bounded wait ran out stores an id of the wait there, and flab_tc_error_state() reads
-// every unit's word through the generated host getter.
+// every unit's word through the generated host getter; getter##_clear() zeroes the word again.
 #define FLAB_TC_DEFINE_ERROR_WORD(getter)                                            \
   namespace {                                                                        \
   __device__ int tu_tc_error = 0;                                                    \
@@ -236,6 +246,10 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
     int v = 0;                                                                       \
     if (cudaMemcpyFromSymbol(&v, tu_tc_error, sizeof(int)) != cudaSuccess) return -1000; \
     return v;                                                                        \
+  }                                                                                  \
+  int getter##_clear() {                                                             \
+    const int v = 0;                                                                 \
+    return cudaMemcpyToSymbol(tu_tc_error, &v, sizeof(int)) == cudaSuccess ? 0 : -1000; \
   }                                                                                  \
   }
 

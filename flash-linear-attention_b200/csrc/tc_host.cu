@@ -27,10 +27,12 @@ int make_tensor_map_bf16(CUtensorMap *map, const void *base, int rank, const uin
                          const uint32_t *box, int elem_fp16) {
   EncodeTiledFn fn = encode_fn();
   // A driver-API call needs a current context; a thread that has only used the runtime lazily (an
-  // autograd worker thread, say) may not have bound the primary context yet.
+  // autograd worker thread, say) may not have bound the primary context yet.  cudaSetDevice binds it
+  // without touching the allocator, so this is legal while a stream is being captured.
   static thread_local bool bound = false;
   if (!bound) {
-    cudaFree(0);
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
     bound = true;
   }
   FLAB_REQUIRE(fn != nullptr, FLAB_E_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
@@ -73,20 +75,32 @@ int make_state_map(CUtensorMap *map, const void *base, const flab_args *a, int b
   return make_tensor_map_bf16(map, base, 2, dims, str, box, a->dtype == FLAB_FP16);
 }
 
-int tc_chunk_o_error();
-int recurrent_error();
-int tc_delta_h_error();
-int tc_dqkwg_error();
-int tc_wy_bwd_error();
-int tc_wy_fwd_error();
+#define FLAB_ERROR_UNITS(X) X(tc_chunk_o_error) X(recurrent_error) X(tc_delta_h_error) X(tc_dqkwg_error) X(tc_wy_bwd_error) X(tc_wy_fwd_error) X(tc_selftest_error)
+#define FLAB_DECLARE_UNIT(name) \
+  int name();                   \
+  int name##_clear();
+FLAB_ERROR_UNITS(FLAB_DECLARE_UNIT)
 
 }  // namespace flab
 
 extern "C" int flab_tc_error_state(void) {
-  int e = flab::tc_chunk_o_error();
-  if (!e) e = flab::recurrent_error();
-  if (!e) e = flab::tc_delta_h_error();
-  if (!e) e = flab::tc_dqkwg_error();
-  if (!e) e = flab::tc_wy_bwd_error();
-  return e ? e : flab::tc_wy_fwd_error();
+  int e = 0;
+#define FLAB_READ_UNIT(name) \
+  if (!e) e = flab::name();
+  FLAB_ERROR_UNITS(FLAB_READ_UNIT)
+  return e;
+}
+
+extern "C" int flab_tc_error_clear(void) {
+  int e = 0;
+#define FLAB_CLEAR_UNIT(name) e |= flab::name##_clear();
+  FLAB_ERROR_UNITS(FLAB_CLEAR_UNIT)
+  return e ? FLAB_E_LAUNCH : FLAB_OK;
+}
+
+extern "C" int flab_tc_check(void) {
+  const int e = flab_tc_error_state();
+  if (e == 0) return FLAB_OK;
+  flab::set_error("a bounded device-side wait ran out (wait id %d): the results of the kernels launched since the last check are invalid", e);
+  return FLAB_E_TIMEOUT;
 }

@@ -3,7 +3,28 @@
 // operand), read back with the fragment loads.  Single CTA; every wait is bounded.
 #include "tc.cuh"
 
+FLAB_TC_DEFINE_ERROR_WORD(tc_selftest_error)
+
 namespace flab {
+
+// A wait that is meant to run out: one warp waits, with a caller-chosen short limit, on an mbarrier that nothing
+// ever arrives at.  It takes the same way out as a production kernel whose wait gave up: the id of the wait goes
+// to the unit's error word (and to *status), the kernel returns normally and the context stays usable.
+constexpr int WAIT_SELFTEST_ID = 99;
+__global__ void __launch_bounds__(32) tc_wait_selftest_kernel(long long limit_ticks, int *status) {
+  using namespace tc;
+  __shared__ uint64_t never;
+  if (threadIdx.x == 0) {
+    mbar_init(&never, 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+  const bool ok = mbar_wait_limit(&never, 0, limit_ticks);
+  if (threadIdx.x == 0) {
+    if (!ok) atomicCAS(&tu_tc_error, 0, WAIT_SELFTEST_ID);
+    *status = ok ? 0 : WAIT_SELFTEST_ID;
+  }
+}
 
 __global__ void __launch_bounds__(128) tc_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                                           const __grid_constant__ CUtensorMap mapH, const __grid_constant__ CUtensorMap mapV,
@@ -118,6 +139,15 @@ __global__ void __launch_bounds__(128) tc_selftest_kernel(const __grid_constant_
 }
 
 }  // namespace flab
+
+extern "C" int flab_tc_wait_selftest(long long limit_ticks, int *status, void *stream) {
+  using namespace flab;
+  FLAB_REQUIRE(status != nullptr, FLAB_E_BADARG, "tc_wait_selftest: NULL status");
+  FLAB_REQUIRE(limit_ticks > 0 && limit_ticks <= (1ll << 28), FLAB_E_BADARG,
+               "tc_wait_selftest: the limit must be between 1 and 2^28 clock ticks (a fraction of a second)");
+  tc_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit_ticks, status);
+  return check_launch("tc_wait_selftest");
+}
 
 extern "C" int flab_tc_selftest(const void *a, const void *b, const void *h, const void *v, float *out, int *status, void *stream) {
   using namespace flab;

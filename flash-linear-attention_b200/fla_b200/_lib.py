@@ -22,6 +22,7 @@ F_REVERSE = 1 << 0
 F_BETA_VECTOR = 1 << 1
 F_INPLACE_STATE = 1 << 2
 F_STATE_ONLY = 1 << 4
+F_TRANSPOSE = 1 << 5
 
 _PTR_FIELDS = [
     "q", "k", "v", "g", "gk", "gv", "beta", "w", "u", "aw", "au", "h", "h0", "ht", "v_new", "o",
@@ -54,6 +55,9 @@ ENTRY_POINTS = [
 
 _lib = None
 LAUNCHES = 0  # kernels launched through this module (one per successful call)
+# FLA_B200_CHECK=1: synchronise after every call and turn a device-side wait that ran out into an exception
+# (FLAB_E_TIMEOUT). Off by default: the check costs a device synchronisation per launch.
+CHECK_EVERY_CALL = os.environ.get("FLA_B200_CHECK", "0") == "1"
 
 
 def load() -> ctypes.CDLL:
@@ -74,7 +78,11 @@ def load() -> ctypes.CDLL:
         fn.argtypes = [ctypes.POINTER(FlabArgs), ctypes.c_void_p]
     lib.flab_gated_delta_rule_fwd_workspace.restype = ctypes.c_size_t
     lib.flab_gated_delta_rule_fwd_workspace.argtypes = [ctypes.POINTER(FlabArgs)]
-    lib.flab_tc_error_state.restype = ctypes.c_int
+    for name in ("flab_tc_error_state", "flab_tc_check", "flab_tc_error_clear"):
+        getattr(lib, name).restype = ctypes.c_int
+        getattr(lib, name).argtypes = []
+    lib.flab_tc_wait_selftest.restype = ctypes.c_int
+    lib.flab_tc_wait_selftest.argtypes = [ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
     lib.flab_l2norm_fwd.restype = ctypes.c_int
     lib.flab_l2norm_fwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                     ctypes.c_float, ctypes.c_void_p]
@@ -94,6 +102,8 @@ def load() -> ctypes.CDLL:
     lib.flab_l2norm_bwd.restype = ctypes.c_int
     lib.flab_l2norm_bwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
                                     ctypes.c_float, ctypes.c_void_p]
+    lib.flab_state_chain.restype = ci
+    lib.flab_state_chain.argtypes = [vp, vp, ll, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]
     _lib = lib
     return lib
 
@@ -148,3 +158,41 @@ def call(entry: str, ref: torch.Tensor, **kw):
         raise RuntimeError(f"{entry} failed ({rc}): {lib.flab_last_error().decode()}")
     global LAUNCHES
     LAUNCHES += 1
+    if CHECK_EVERY_CALL:
+        check_device_waits(entry)
+
+
+def check_device_waits(what: str = "flab200") -> None:
+    """Synchronise and raise if a bounded wait inside one of the library's kernels has run out since the last
+    check (the kernel returned normally, but its outputs are invalid). Clears the record."""
+    lib = load()
+    rc = lib.flab_tc_check()
+    if rc != 0:
+        msg = lib.flab_last_error().decode()
+        lib.flab_tc_error_clear()
+        raise RuntimeError(f"{what} failed ({rc}): {msg}")
+
+
+def state_chain(M: torch.Tensor, b: torch.Tensor, s0: Optional[torch.Tensor], *, want_s_in: bool = True, want_last: bool = False,
+                reverse: bool = False, transpose: bool = False):
+    """`flab_state_chain`: M `[B,S,H,K,K]`, b `[B,S,H,K,V]` (may be a column slice of a wider contiguous buffer), s0
+    `[B,H,K,V]` or None, all fp32 CUDA. Returns (s_in `[B,S,H,K,V]` or None, s_last `[B,H,K,V]` or None)."""
+    lib = load()
+    B, S, H, K, _ = M.shape
+    V = b.shape[-1]
+    assert M.is_cuda and M.dtype == b.dtype == torch.float32 and M.is_contiguous()
+    assert b.stride(-1) == 1 and b.stride(-3) == K * b.stride(-2) and b.stride(-4) == H * b.stride(-3) and b.stride(0) == S * b.stride(1), \
+        "b must be a column slice of a contiguous [B,S,H,K,ldb] buffer"
+    s0 = None if s0 is None else s0.float().contiguous()
+    s_in = torch.empty(B, S, H, K, V, dtype=torch.float32, device=M.device) if want_s_in else None
+    s_last = torch.empty(B, H, K, V, dtype=torch.float32, device=M.device) if want_last else None
+    flags = (F_REVERSE if reverse else 0) | (F_TRANSPOSE if transpose else 0)
+    with torch.cuda.device(M.device):
+        rc = lib.flab_state_chain(M.data_ptr(), b.data_ptr(), b.stride(-2), None if s0 is None else s0.data_ptr(),
+                                  None if s_in is None else s_in.data_ptr(), None if s_last is None else s_last.data_ptr(),
+                                  B, S, H, K, V, flags, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"flab_state_chain failed ({rc}): {lib.flab_last_error().decode()}")
+    global LAUNCHES
+    LAUNCHES += 1
+    return s_in, s_last

@@ -59,7 +59,7 @@ class GatedDeltaRuleDecoder:
             self.state.copy_(keep)  # capture does not run the kernel, but keep the contract obvious
 
     def _launch(self):
-        _lib.call("flab_recurrent_delta_fwd", self.q, **self._geo.kw(), scale=self.scale, flags=0, q=self.q, k=self.k,
+        _lib.call("flab_recurrent_delta_fwd", self.q, **self._geo.kw(), scale=self.scale, flags=_lib.F_INPLACE_STATE, q=self.q, k=self.k,
                   v=self.v, beta=self.beta, g=self.g, h0=self.state, o=self.o, u=None, ht=self.state)
 
     @torch.no_grad()
@@ -70,10 +70,15 @@ class GatedDeltaRuleDecoder:
         self.q.copy_(q.view_as(self.q))
         self.k.copy_(k.view_as(self.k))
         self.v.copy_(v.view_as(self.v))
+        # an omitted gate / beta means "none" for THIS step (g = 0: no decay, beta = 1), never the previous step's values
         if g is not None:
             self.g.copy_(g.view_as(self.g))
+        else:
+            self.g.zero_()
         if beta is not None:
             self.beta.copy_(beta.view_as(self.beta))
+        else:
+            self.beta.fill_(1)
         if self._graph is not None:
             self._graph.replay()
         else:

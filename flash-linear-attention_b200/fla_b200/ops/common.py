@@ -225,13 +225,8 @@ def slab_delta_fwd_h(plan: SlabPlan, geo: Geometry, k, w, u, g=None, h0=None, ou
     del h0_ext
     ht_ext = ht_ext.view(B, S, H, K, V + K)
     b_, M = ht_ext[..., :V], ht_ext[..., V:].contiguous()
-    # true initial state of every slab
-    S_in = torch.empty(B, S, H, K, V, dtype=torch.float32, device=dev)
-    cur = torch.zeros(B, H, K, V, dtype=torch.float32, device=dev) if h0 is None else h0.float()
-    for s_ in range(S):
-        S_in[:, s_] = cur
-        if s_ + 1 < S:
-            cur = torch.matmul(M[:, s_], cur) + b_[:, s_]
+    # true initial state of every slab: the chain S <- M_s S + b_s, one launch
+    S_in, _ = _lib.state_chain(M, b_, h0)
     # pass 2
     gs = plan.geometry(k, u)
     h = torch.empty(geo.NT, H, K, V, dtype=k.dtype, device=dev)
@@ -253,12 +248,8 @@ def slab_delta_bwd_dhu(plan: SlabPlan, geo: Geometry, M, q, k, w, do, dv, scale,
     c_ = torch.empty(B * S, H, K, V, dtype=torch.float32, device=dev)
     _lib.call("flab_delta_bwd_dhu", q, **gs.kw(), scale=scale, flags=F_STATE_ONLY, q=q, k=k, w=w, g=gv, d_o=do, dv=dv, dh0=c_)
     c_ = c_.view(B, S, H, K, V)
-    D_out = torch.empty(B, S, H, K, V, dtype=torch.float32, device=dev)
-    cur = torch.zeros(B, H, K, V, dtype=torch.float32, device=dev) if dht is None else dht.float()
-    for s_ in range(S - 1, -1, -1):
-        D_out[:, s_] = cur
-        if s_ > 0:
-            cur = torch.matmul(M[:, s_].transpose(-1, -2), cur) + c_[:, s_]
+    # the transposed chain, right to left: D_out[s] = gradient of the state leaving slab s
+    D_out, _ = _lib.state_chain(M, c_, dht, reverse=True, transpose=True)
     # pass 2
     dh = torch.empty(geo.NT, H, K, V, dtype=q.dtype, device=dev)
     dv2 = torch.empty_like(dv)

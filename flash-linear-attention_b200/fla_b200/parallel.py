@@ -23,6 +23,38 @@ import torch.distributed as dist
 
 
 # ---------------------------------------------------------------------------------------------
+# optional stage timing (CUDA events on the current stream), used by the benchmark
+# ---------------------------------------------------------------------------------------------
+STAGE_EVENTS = None  # set to {} to record (start, end) event pairs per stage name; None = off (the default)
+
+
+class _stage:
+    """`with _stage("name"):` brackets a stage with CUDA events when STAGE_EVENTS is a dict; free otherwise."""
+
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        if STAGE_EVENTS is not None and torch.cuda.is_available():
+            self.a, self.b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.a.record()
+
+    def __exit__(self, *exc):
+        if STAGE_EVENTS is not None and torch.cuda.is_available():
+            self.b.record()
+            STAGE_EVENTS.setdefault(self.name, []).append((self.a, self.b))
+
+
+def stage_times_ms():
+    """Total milliseconds per recorded stage (synchronises); clears the record."""
+    torch.cuda.synchronize()
+    out = {n: sum(a.elapsed_time(b) for a, b in evs) for n, evs in (STAGE_EVENTS or {}).items()}
+    if STAGE_EVENTS is not None:
+        STAGE_EVENTS.clear()
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
 # planners (pure host logic)
 # ---------------------------------------------------------------------------------------------
 def shard_batch_heads(B: int, H: int, world: int, rank: int) -> Tuple[slice, slice]:
@@ -84,7 +116,14 @@ def handoff_states(M: torch.Tensor, b: torch.Tensor, S0: Optional[torch.Tensor],
     else:
         S_in = torch.empty_like(b)
         dist.recv(S_in, src=dist.get_global_rank(group, prev) if group is not None else prev, group=group)
-    S_out = torch.baddbmm(b, M, S_in)
+    if b.is_cuda:
+        from . import _lib  # one launch of the library's own chain kernel (fp32 FFMA), no library GEMM on this path
+        H, K, V = b.shape
+        _, S_out = _lib.state_chain(M.contiguous().view(1, 1, H, K, K), b.contiguous().view(1, 1, H, K, V), S_in.view(1, H, K, V),
+                                    want_s_in=False, want_last=True)
+        S_out = S_out.view(H, K, V)
+    else:  # CPU tensors occur only in the gloo tests of this host logic
+        S_out = torch.baddbmm(b, M, S_in)
     if 0 <= nxt < world:
         dist.send(S_out, dst=dist.get_global_rank(group, nxt) if group is not None else nxt, group=group)
     return S_in, S_out
@@ -107,6 +146,8 @@ def _fwd_slab(q, k, v, g, beta, scale, S_in_of):
     # one widened scan: value columns [u | 0], initial state [0 | I]  ->  final state [b | M]
     h0_ext = torch.cat([torch.zeros(1, H, K, V, device=k.device), torch.eye(K, device=k.device).expand(1, H, K, K)], dim=-1).contiguous()
     import os
+    timer = _stage("state_pass_fwd")
+    timer.__enter__()
     if k.dtype in (torch.bfloat16, torch.float16) and K == 128 and V % 64 == 0 and not os.environ.get("FLA_B200_NO_TC"):
         # state-only scan: nothing but the final state is stored, u itself is read (columns past V are zero-filled)
         from . import _lib
@@ -119,7 +160,9 @@ def _fwd_slab(q, k, v, g, beta, scale, S_in_of):
         geo_ext = Geometry(k, u_ext, None, False)
         _, _, ht_ext = C.chunk_gated_delta_rule_fwd_h(geo_ext, k, w, u_ext, g=g_cum, h0=h0_ext, output_final_state=True)
     b, M = ht_ext[0, :, :, :V].contiguous(), ht_ext[0, :, :, V:].contiguous()
-    S_in, S_out = S_in_of(M, b)
+    timer.__exit__()
+    with _stage("handoff_fwd"):
+        S_in, S_out = S_in_of(M, b)
     # correction pass with the true initial state
     h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g_cum, h0=S_in.unsqueeze(0), output_final_state=False)
     o = C.chunk_fwd_o(geo, q, k, v_new, h, g=g_cum, scale=scale)
@@ -175,6 +218,8 @@ class SPChunkGatedDeltaRuleFunction(torch.autograd.Function):
         # what this slab's outputs alone contribute to the gradient of its initial state (dS_out = 0)
         dv = C.chunk_bwd_dv_local(geo, q, k, g_cum, do, scale)
         import os
+        timer = _stage("state_pass_bwd")
+        timer.__enter__()
         if k.dtype in (torch.bfloat16, torch.float16) and geo.K == 128 and geo.V % 64 == 0 and not os.environ.get("FLA_B200_NO_TC"):
             from . import _lib  # state-only scan: only the gradient handed to the predecessor is stored
             c = torch.empty(1, geo.H, geo.K, geo.V, dtype=torch.float32, device=k.device)
@@ -182,8 +227,10 @@ class SPChunkGatedDeltaRuleFunction(torch.autograd.Function):
         else:
             _, c, _ = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g_cum, dht=None, want_dh0=True)
         # the gradient of the whole-sequence final state enters at the last rank
+        timer.__exit__()
         ext = None if dht is None or rank != world - 1 else dht.float()[0]
-        dS_out, dS_in = handoff_states(M.transpose(1, 2).contiguous(), c[0], ext, group, reverse=True)
+        with _stage("handoff_bwd"):
+            dS_out, dS_in = handoff_states(M.transpose(1, 2).contiguous(), c[0], ext, group, reverse=True)
         dq, dk, dv, db, dg, _ = chunk_gated_delta_rule_bwd(geo, q, k, v, g_cum, beta, aw, au, scale, S_in.unsqueeze(0), do,
                                                           dS_out.unsqueeze(0), saved=(w, h, v_new, None))
         dh0 = dS_in.unsqueeze(0) if (ctx.has_h0 and rank == 0) else None

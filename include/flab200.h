@@ -41,15 +41,17 @@ enum {
   FLAB_E_BADARG = -1,      /* NULL / inconsistent argument                    */
   FLAB_E_UNSUPPORTED = -2, /* shape or dtype outside what the kernels handle  */
   FLAB_E_LAUNCH = -3,      /* CUDA reported an error at launch                */
-  FLAB_E_TIMEOUT = -4      /* a bounded device-side wait ran out              */
+  FLAB_E_TIMEOUT = -4      /* a bounded device-side wait ran out: returned by flab_tc_check() */
 };
 
 enum {
   FLAB_F_REVERSE = 1 << 0,       /* cumsum / recurrence run from the last token to the first */
   FLAB_F_BETA_VECTOR = 1 << 1,   /* fused_recurrent_delta_rule: beta is [.., V] not scalar    */
-  FLAB_F_INPLACE_STATE = 1 << 2, /* decode: ht may alias h0                                   */
+  FLAB_F_INPLACE_STATE = 1 << 2, /* flab_recurrent_fwd / _delta_fwd: the caller passes ht == h0 (state updated in place); without
+                                    the flag an aliased pair is rejected with FLAB_E_BADARG                 */
   FLAB_F_UPPER = 1 << 3,         /* reserved                                                  */
-  FLAB_F_STATE_ONLY = 1 << 4     /* delta scans: only the final state is wanted (h, v_new / dh, dv2 may be NULL) */
+  FLAB_F_STATE_ONLY = 1 << 4,    /* delta scans: only the final state is wanted (h, v_new / dh, dv2 may be NULL) */
+  FLAB_F_TRANSPOSE = 1 << 5      /* flab_state_chain: apply the transposed transitions (backward chain)         */
 };
 
 typedef struct flab_args {
@@ -185,6 +187,18 @@ int flab_delta_fwd_h(const flab_args *a, void *stream);
  * dh0 is written (dh and dv2 may be NULL), same domain as above. */
 int flab_delta_bwd_dhu(const flab_args *a, void *stream);
 
+/* ---- chain of slab transitions (scans cut along T) -------------------------------------------
+ * No single counterpart in the reference (its two-level scan, fla/ops/common/chunk_h_split.py:164-260, is
+ * unused and covers diagonal decay only). A slab of tokens maps the state entering it to the state leaving it
+ * as S_out = M S_in + b. Given the transitions of the S slabs of every (sequence, head) this walks the chain in
+ * one launch, fp32:   for s = 0 .. S-1:  s_in[s] = cur;  cur = op(M[s]) cur + b[s]      (cur starts at s0 or 0)
+ * and writes the last cur to s_last. FLAB_F_REVERSE walks s = S-1 .. 0, FLAB_F_TRANSPOSE uses M[s]^T (the two
+ * together are the backward chain dS_in = M^T dS_out + c).
+ * M: [B,S,H,K,K]; b: [B,S,H,K,ldb] of which the first V columns are read (ldb >= V lets b be a column slice of
+ * a wider buffer); s0: [B,H,K,V] or NULL; s_in: [B,S,H,K,V] or NULL; s_last: [B,H,K,V] or NULL. K <= 256. */
+int flab_state_chain(const float *M, const float *b, long long ldb, const float *s0, float *s_in, float *s_last, int B, int S, int H, int K,
+                     int V, int flags, void *stream);
+
 /* ---- GLA (per-channel gates) -----------------------------------------------------------------
  * Replaces chunk_gla_fwd_intra_gk (fla/ops/gla/chunk.py:840): reads q, k, gk; writes a (fp32). */
 int flab_gla_fwd_intra(const flab_args *a, void *stream);
@@ -232,22 +246,39 @@ int flab_gated_delta_rule_fwd(const flab_args *a, void *stream);
  *  - problems whose scratch exceeds the 16 MiB (B*T*H > 8192 token-heads at K = V = 128) are
  *    rejected with FLAB_E_UNSUPPORTED and a message, nothing is launched;
  *  - the first call on each device looks up the array's device address (no allocation, but a
- *    runtime query): make that first call before any stream capture begins;
+ *    runtime query), and the first call of each host thread binds that thread to the device's
+ *    context: make the first call per device and per calling thread before any stream capture
+ *    begins;
  *  - all calls share the one array and it keeps the previous call's contents; every call fully
  *    overwrites what it reads, so nothing needs clearing, but two calls that overlap on the GPU
  *    (different streams, or two threads) race on it: serialise them. */
 int flab_gated_delta_rule_fwd_noalloc(const flab_args *a, void *stream);
 
 /* ---- diagnostics -----------------------------------------------------------------------------
- * No counterpart in the reference. Runs four small bf16 products through the TMA + tcgen05 + TMEM
- * path (every shared-memory operand form the kernels use) and writes them to `out`
- * (fp32: [64x64] A B^T, [64x128] A H, [128x64] A^T V, [64x64] bf16(A B^T) V) for the caller to compare
- * with a plain matmul. a, b: [64x128], h: [128x128], v: [64x64], row-major bf16. *status = 0 on
- * success, else the index of the bounded wait that ran out. */
-/* No counterpart in the reference. 0 if no tcgen05 kernel of this process has had a bounded wait run
- * out so far (synchronises the device); otherwise the id of the first wait that did. */
+ * None of these has a counterpart in the reference.
+ *
+ * Every wait inside the tcgen05 / TMA kernels (on an mbarrier) is bounded: a wait that runs out makes its
+ * kernel record the id of the wait in a device-side error word and return normally, so the context stays
+ * usable but the outputs of that launch are invalid. The ordinary entry points do not synchronise and
+ * therefore cannot report this themselves; the three calls below do (each synchronises the device):
+ *   flab_tc_error_state()  0, or the id of the first wait that ran out since the last clear;
+ *   flab_tc_check()        FLAB_OK, or FLAB_E_TIMEOUT with the id in flab_last_error();
+ *   flab_tc_error_clear()  zeroes the error words.
+ * A host that wants every launch checked calls flab_tc_check() after synchronising (the ctypes binding does
+ * so after every call when FLA_B200_CHECK=1). */
 int flab_tc_error_state(void);
+int flab_tc_check(void);
+int flab_tc_error_clear(void);
+/* Runs four small bf16 products through the TMA + tcgen05 + TMEM path (every shared-memory operand form
+ * the kernels use) and writes them to `out` (fp32: [64x64] A B^T, [64x128] A H, [128x64] A^T V,
+ * [64x64] bf16(A B^T) V) for the caller to compare with a plain matmul. a, b: [64x128], h: [128x128],
+ * v: [64x64], row-major bf16. *status = 0 on success, else the index of the bounded wait that ran out. */
 int flab_tc_selftest(const void *a, const void *b, const void *h, const void *v, float *out, int *status, void *stream);
+/* Exercises the way out of a wait that gives up: one warp waits for `limit_ticks` clock ticks
+ * (1 .. 2^28, i.e. well under a second) on a barrier nothing arrives at, then writes the wait id (99) to
+ * *status (device int) and to the error word, and returns. Afterwards flab_tc_check() reports
+ * FLAB_E_TIMEOUT until flab_tc_error_clear(). */
+int flab_tc_wait_selftest(long long limit_ticks, int *status, void *stream);
 
 #ifdef __cplusplus
 }

@@ -237,3 +237,68 @@ def test_tc_channel_gate_scans_against_torch(dt, V, head_first, lens):
             assert _rel(dhs.view(-1, H, K, V)[c0:c0 + nt, hd], rdhs) < 1e-2
             assert _rel(dh0s[n, hd], rdh0s) < 1e-2
         c0 += nt
+
+
+# ---------------------------------------------------------------------------------------------
+# a bounded wait that runs out: the kernel returns, the host sees FLAB_E_TIMEOUT, the context stays usable
+# ---------------------------------------------------------------------------------------------
+def test_bounded_wait_runs_out_and_is_reported():
+    """A warp waits, with a short limit (2^20 clock ticks, about half a millisecond), on a barrier that nothing
+    arrives at. The kernel must come back by itself with the id of the wait; flab_tc_check() must then return
+    FLAB_E_TIMEOUT (-4) with the id in the message, the record must clear, and the next ordinary kernel must run."""
+    lib = _lib.load()
+    torch.cuda.synchronize()
+    assert lib.flab_tc_check() == 0, lib.flab_last_error().decode()
+    status = torch.full((1,), -7, dtype=torch.int32, device="cuda")
+    rc = lib.flab_tc_wait_selftest(1 << 20, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.flab_last_error().decode()
+    torch.cuda.synchronize()
+    assert status.item() == 99
+    assert lib.flab_tc_error_state() == 99
+    assert lib.flab_tc_check() == -4
+    assert b"wait id 99" in lib.flab_last_error()
+    with pytest.raises(RuntimeError, match="wait id 99"):
+        _lib.check_device_waits("selftest")          # raises and clears
+    assert lib.flab_tc_error_state() == 0
+    assert lib.flab_tc_wait_selftest(0, status.data_ptr(), None) == -1   # limits outside (0, 2^28] are refused
+    # the context is intact: an ordinary tcgen05 launch still works
+    test_tc_selftest()
+    assert lib.flab_tc_check() == 0
+
+
+# ---------------------------------------------------------------------------------------------
+# chain of slab transitions against the same chain written with torch.matmul
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("B,S,H,K,V,ld_extra", [(2, 5, 3, 128, 128, 128), (1, 1, 4, 128, 256, 0), (1, 3, 2, 100, 60, 0), (1, 16, 16, 128, 128, 128)])
+def test_state_chain_matches_matmul_loop(B, S, H, K, V, ld_extra):
+    g0 = torch.Generator(device="cuda").manual_seed(S * 7 + K)
+    M = torch.randn(B, S, H, K, K, device="cuda", generator=g0) / K ** 0.5
+    wide = torch.randn(B, S, H, K, V + ld_extra, device="cuda", generator=g0)
+    b = wide[..., :V]
+    s0 = torch.randn(B, H, K, V, device="cuda", generator=g0)
+    for reverse, transpose, start in ((False, False, s0), (True, True, s0), (False, False, None)):
+        s_in, s_last = _lib.state_chain(M, b, start, want_last=True, reverse=reverse, transpose=transpose)
+        cur = torch.zeros_like(s0).double() if start is None else start.double()
+        order = range(S - 1, -1, -1) if reverse else range(S)
+        for s in order:
+            ref_in = cur
+            assert torch.allclose(s_in[:, s].double(), ref_in, rtol=1e-4, atol=1e-4), (reverse, s)
+            Ms = M[:, s].double().transpose(-1, -2) if transpose else M[:, s].double()
+            cur = Ms @ cur + b[:, s].double()
+        assert torch.allclose(s_last.double(), cur, rtol=1e-4, atol=1e-4)
+
+
+def test_inplace_state_needs_the_flag():
+    """flab_recurrent_delta_fwd with ht == h0 is refused unless the caller sets FLAB_F_INPLACE_STATE."""
+    B, H, K, V = 2, 2, 128, 128
+    q = torch.randn(B, 1, H, K, device="cuda").bfloat16()
+    v = torch.randn(B, 1, H, V, device="cuda").bfloat16()
+    beta = torch.ones(B, 1, H, device="cuda").bfloat16()
+    g = torch.zeros(B, 1, H, device="cuda")
+    st = torch.zeros(B, H, K, V, device="cuda")
+    o = torch.empty_like(v)
+    kw = dict(B=B, T=1, H=H, K=K, V=V, N=B, NT=B, scale=1.0, q=q, k=q, v=v, beta=beta, g=g, h0=st, ht=st, o=o)
+    with pytest.raises(RuntimeError, match="FLAB_F_INPLACE_STATE"):
+        _lib.call("flab_recurrent_delta_fwd", q, flags=0, **kw)
+    _lib.call("flab_recurrent_delta_fwd", q, flags=_lib.F_INPLACE_STATE, **kw)
+    torch.cuda.synchronize()
