@@ -1,6 +1,9 @@
-// Inter-chunk state recurrence for diagonal decay (scalar gate g, per-key-channel gate gk, or none).
+// Inter-chunk state recurrence for diagonal decay (scalar gate g, per-key-channel gate gk, per-value-channel
+// gate gv, or none).
 //   forward : h[t] = S;  S <- decay(S) + k~^T v~          (fla/ops/common/chunk_h.py:29-137)
-//   backward: dh[t] = D; D <- decay(D) + q~^T do          (fla/ops/common/chunk_h.py:156-271)
+//   backward: dh[t] = D; D <- decay(D) + q~^T do~         (fla/ops/common/chunk_h.py:156-271)
+// gv decays the COLUMNS of the state (S <- S diag(e^{gv_L}), v~ = v e^{gv_L - gv}; backward do~ = do e^{gv}):
+// the path the reference's GSA op takes (fla/ops/gsa/chunk.py:664-675); it may be combined with gk.
 // One CTA owns a [64 x 64] tile of the [K x V] state of one (sequence, head) and walks the chunks
 // serially; K and V tiles are independent, so the grid is (K/64, V/64, N*H).  The state tile lives
 // in mma accumulator registers for the whole walk; k/v (q/do) tiles are double-buffered with cp.async.
@@ -10,7 +13,7 @@ namespace flab {
 
 constexpr int HB = 64;  // state tile edge
 
-template <typename T, int GATE /*0 none, 1 g, 2 gk*/, bool BWD>
+template <typename T, int GATE /*0 none, 1 g, 2 gk*/, bool BWD, bool GV = false>
 __global__ void __launch_bounds__(128) chunk_h_kernel(const flab_args a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LD = HB + Num<T>::pad;
@@ -20,6 +23,7 @@ __global__ void __launch_bounds__(128) chunk_h_kernel(const flab_args a) {
   float *sG = reinterpret_cast<float *>(sStage + HB * LD);  // [2][64]
   float *sGK = sG + 2 * C;                                  // [2][64][HB+4] (GATE == 2 only)
   constexpr int LDG = HB + 4;
+  float *sGV = sGK + (GATE == 2 ? 2 * C * LDG : 0);         // [2][64][HB+4] (GV only)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int k0 = blockIdx.x * HB, v0 = blockIdx.y * HB;
@@ -33,6 +37,7 @@ __global__ void __launch_bounds__(128) chunk_h_kernel(const flab_args a) {
   const float *G = GATE == 1 ? reinterpret_cast<const float *>(a.g) + tok_off(a, s, hd, 0, 1) : nullptr;
   const size_t gs = tok_stride(a, 1);
   const float *GK = GATE == 2 ? reinterpret_cast<const float *>(a.gk) + tok_off(a, s, hd, 0, a.K) + k0 : nullptr;
+  const float *GVp = GV ? reinterpret_cast<const float *>(a.gv) + tok_off(a, s, hd, 0, a.V) + v0 : nullptr;
   T *Hout = reinterpret_cast<T *>(BWD ? a.dh : a.h);
   const float *S0 = reinterpret_cast<const float *>(BWD ? a.dht : a.h0);
   float *S1 = reinterpret_cast<float *>(BWD ? a.dh0 : a.ht);
@@ -53,6 +58,7 @@ __global__ void __launch_bounds__(128) chunk_h_kernel(const flab_args a) {
     tile_load<T>(sX + buf * C * LD, LD, X + (size_t)t0 * xs, xs, rows, C, kw, HB, tid, 128);
     tile_load<T>(sY + buf * C * LD, LD, Y + (size_t)t0 * ys, ys, rows, C, vw, HB, tid, 128);
     if (GATE == 2) tile_load<float>(sGK + buf * C * LDG, LDG, GK + (size_t)t0 * xs, xs, rows, C, kw, HB, tid, 128);
+    if (GV) tile_load<float>(sGV + buf * C * LDG, LDG, GVp + (size_t)t0 * ys, ys, rows, C, vw, HB, tid, 128);
     cp_async_commit();
   };
 
@@ -118,6 +124,15 @@ __global__ void __launch_bounds__(128) chunk_h_kernel(const flab_args a) {
         }
       }
     }
+    if (GV) {
+      // value-channel gate: forward v~ = v e^{gv_L - gv}, backward do~ = do e^{gv}; rounded to the element type
+      const float *gv = sGV + cur * C * LDG;
+      for (int e = tid; e < C * HB; e += 128) {
+        int r_ = e / HB, c_ = e - r_ * HB;
+        const float f = BWD ? expf(gv[r_ * LDG + c_]) : expf(gv[last * LDG + c_] - gv[r_ * LDG + c_]);
+        y[r_ * LD + c_] = Num<T>::t(Num<T>::f(y[r_ * LD + c_]) * f);
+      }
+    }
     __syncthreads();
     {
       const size_t hoff = ((size_t)(s.c0 + it) * a.H + hd) * a.K * a.V + (size_t)k0 * a.V + v0;
@@ -141,6 +156,17 @@ __global__ void __launch_bounds__(128) chunk_h_kernel(const flab_args a) {
         acc[0][ni][3] *= d_hi;
       }
     }
+    if (GV) {
+      const float *gv = sGV + cur * C * LDG + last * LDG;
+#pragma unroll
+      for (int ni = 0; ni < 8; ++ni) {
+        const float d0 = expf(gv[8 * ni + 2 * (lane & 3)]), d1 = expf(gv[8 * ni + 2 * (lane & 3) + 1]);
+        acc[0][ni][0] *= d0;
+        acc[0][ni][1] *= d1;
+        acc[0][ni][2] *= d0;
+        acc[0][ni][3] *= d1;
+      }
+    }
     WarpGemm<1, 8, true, true, T>::run(acc, x, LD, m0, y, LD, 0, C);
   }
   if (S1) {
@@ -155,14 +181,19 @@ template <typename T, bool BWD> static int launch_chunk_h(const flab_args *a, cu
   const int gate = a->gk ? 2 : (a->g ? 1 : 0);
   size_t smem = (size_t)(5 * C * LD) * sizeof(T) + 2 * C * sizeof(float);
   if (gate == 2) smem += (size_t)2 * C * (HB + 4) * sizeof(float);
+  if (a->gv) smem += (size_t)2 * C * (HB + 4) * sizeof(float);
   dim3 grid(cdiv(a->K, HB), cdiv(a->V, HB), a->N * a->H);
-#define FLAB_LAUNCH_H(G)                                          \
+#define FLAB_LAUNCH_H(G, GVF)                                     \
   {                                                               \
-    auto kern = chunk_h_kernel<T, G, BWD>;                        \
+    auto kern = chunk_h_kernel<T, G, BWD, GVF>;                   \
     if (int e = set_smem(kern, smem)) return e;                   \
     kern<<<grid, 128, smem, stream>>>(*a);                        \
   }
-  if (gate == 0) FLAB_LAUNCH_H(0) else if (gate == 1) FLAB_LAUNCH_H(1) else FLAB_LAUNCH_H(2)
+  if (a->gv) {
+    if (gate == 0) FLAB_LAUNCH_H(0, true) else FLAB_LAUNCH_H(2, true)
+  } else {
+    if (gate == 0) FLAB_LAUNCH_H(0, false) else if (gate == 1) FLAB_LAUNCH_H(1, false) else FLAB_LAUNCH_H(2, false)
+  }
 #undef FLAB_LAUNCH_H
   return check_launch(BWD ? "chunk_bwd_dh" : "chunk_fwd_h");
 }
@@ -188,7 +219,7 @@ int flab_chunk_fwd_h(const flab_args *a, void *stream) {
   if (int e = check_common(a)) return e;
   FLAB_REQUIRE(a->k && a->v && a->h, FLAB_E_BADARG, "chunk_fwd_h needs k, v and h");
   FLAB_REQUIRE(!(a->g && a->gk), FLAB_E_UNSUPPORTED, "chunk_fwd_h: g and gk together are not supported");
-  FLAB_REQUIRE(!a->gv, FLAB_E_UNSUPPORTED, "chunk_fwd_h: gv is not supported");
+  FLAB_REQUIRE(!(a->g && a->gv), FLAB_E_UNSUPPORTED, "chunk_fwd_h: g and gv together are not supported");
   if (tc_scan_on()) {
     const int r = tc_chunk_fwd_h_try(a, (cudaStream_t)stream);
     if (r != 0) return r < 0 ? r : FLAB_OK;
@@ -202,7 +233,7 @@ int flab_chunk_bwd_dh(const flab_args *a, void *stream) {
   if (int e = check_common(a)) return e;
   FLAB_REQUIRE(a->q && a->d_o && a->dh, FLAB_E_BADARG, "chunk_bwd_dh needs q, d_o and dh");
   FLAB_REQUIRE(!(a->g && a->gk), FLAB_E_UNSUPPORTED, "chunk_bwd_dh: g and gk together are not supported");
-  FLAB_REQUIRE(!a->gv, FLAB_E_UNSUPPORTED, "chunk_bwd_dh: gv is not supported");
+  FLAB_REQUIRE(!(a->g && a->gv), FLAB_E_UNSUPPORTED, "chunk_bwd_dh: g and gv together are not supported");
   if (tc_scan_on()) {
     const int r = tc_chunk_bwd_dh_try(a, (cudaStream_t)stream);
     if (r != 0) return r < 0 ? r : FLAB_OK;

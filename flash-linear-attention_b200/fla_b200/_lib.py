@@ -50,7 +50,7 @@ ENTRY_POINTS = [
     "flab_wy_bwd", "flab_delta_fwd_h", "flab_delta_bwd_dhu", "flab_gla_fwd_intra", "flab_gla_fwd_o",
     "flab_gla_bwd_dav", "flab_gla_bwd_dqkg", "flab_recurrent_fwd", "flab_recurrent_bwd",
     "flab_recurrent_delta_fwd", "flab_recurrent_delta_bwd", "flab_gated_delta_rule_fwd",
-    "flab_gated_delta_rule_fwd_noalloc",
+    "flab_gated_delta_rule_fwd_noalloc", "flab_simple_gla_attn",
 ]
 
 _lib = None
@@ -102,6 +102,11 @@ def load() -> ctypes.CDLL:
     lib.flab_l2norm_bwd.restype = ctypes.c_int
     lib.flab_l2norm_bwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
                                     ctypes.c_float, ctypes.c_void_p]
+    ap = ctypes.POINTER(FlabArgs)
+    lib.flab_gdn_gate_fwd.restype = ci
+    lib.flab_gdn_gate_fwd.argtypes = [ap, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.flab_gdn_gate_bwd.restype = ci
+    lib.flab_gdn_gate_bwd.argtypes = [ap, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     lib.flab_state_chain.restype = ci
     lib.flab_state_chain.argtypes = [vp, vp, ll, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]
     _lib = lib

@@ -62,17 +62,19 @@ def _f32(x):
     return None if x is None else x.float().contiguous()
 
 
-def chunk_fwd_h(geo: Geometry, k, v, g=None, gk=None, h0=None, output_final_state=False):
-    """State at the start of every chunk (fla/ops/common/chunk_h.py:282). Returns (h, ht)."""
+def chunk_fwd_h(geo: Geometry, k, v, g=None, gk=None, gv=None, h0=None, output_final_state=False):
+    """State at the start of every chunk (fla/ops/common/chunk_h.py:282). Returns (h, ht). g, gk, gv are
+    chunk-local cumulative log gates (fp32): per token, per key channel, per value channel (the path of the
+    reference's GSA op, fla/ops/gsa/chunk.py:664-675)."""
     h, ht = _state_buffers(geo, k, output_final_state)
-    _lib.call("flab_chunk_fwd_h", k, **geo.kw(), k=k, v=v, g=g, gk=gk, h0=_f32(h0), h=h, ht=ht)
+    _lib.call("flab_chunk_fwd_h", k, **geo.kw(), k=k, v=v, g=g, gk=gk, gv=gv, h0=_f32(h0), h=h, ht=ht)
     return h, ht
 
 
-def chunk_bwd_dh(geo: Geometry, q, do, scale, g=None, gk=None, dht=None, want_dh0=False):
+def chunk_bwd_dh(geo: Geometry, q, do, scale, g=None, gk=None, gv=None, dht=None, want_dh0=False):
     """Reverse state-gradient scan (fla/ops/common/chunk_h.py:338). Returns (dh, dh0)."""
     dh, dh0 = _state_buffers(geo, q, want_dh0)
-    _lib.call("flab_chunk_bwd_dh", q, **geo.kw(), scale=scale, q=q, d_o=do, g=g, gk=gk, dht=_f32(dht), dh=dh, dh0=dh0)
+    _lib.call("flab_chunk_bwd_dh", q, **geo.kw(), scale=scale, q=q, d_o=do, g=g, gk=gk, gv=gv, dht=_f32(dht), dh=dh, dh0=dh0)
     return dh, dh0
 
 

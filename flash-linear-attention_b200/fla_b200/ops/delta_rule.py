@@ -115,3 +115,24 @@ def fused_recurrent_delta_rule(
         beta = torch.ones_like(q[..., 0])
     return FusedRecurrentDeltaRuleFunction.apply(q, k, v, beta, scale, initial_state, output_final_state, offsets,
                                                  head_first)
+
+
+def fused_chunk_delta_rule(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    beta: torch.Tensor,
+    scale: float = None,
+    initial_state: torch.Tensor = None,
+    output_final_state: bool = False,
+    head_first: bool = True,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """The reference's fused execution mode of the delta rule (fla/ops/delta_rule/fused_chunk.py:359): fixed-length
+    batches, chunks of 16 tokens walked by one kernel. The recurrence, the arguments and the gradients (including the
+    one of the initial state) are those of `chunk_delta_rule`, whose kernels compute it here."""
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    else:
+        assert scale > 0, "scale must be positive."
+    return chunk_delta_rule(q, k, v, beta, scale=scale, initial_state=initial_state, output_final_state=output_final_state,
+                            head_first=head_first)

@@ -13,9 +13,10 @@ from .recurrent import FusedRecurrentGatedDeltaRuleFunction
 from .simple_gla import check_varlen_args
 
 
-def chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta, scale, initial_state, output_final_state):
-    """Stage order of fla/ops/gated_delta_rule/chunk.py:20-73."""
-    g = C.chunk_local_cumsum(g, offsets=geo.offsets_tensor, head_first=geo.head_first)
+def chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta, scale, initial_state, output_final_state, g_cum=None):
+    """Stage order of fla/ops/gated_delta_rule/chunk.py:20-73. `g_cum`: the chunk-local cumsum of g when the caller
+    already has it (the gate prologue computes it in the pass that makes g)."""
+    g = g_cum if g_cum is not None else C.chunk_local_cumsum(g, offsets=geo.offsets_tensor, head_first=geo.head_first)
     aw, au, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta, g=g)
     plan, M = C.slab_plan(geo, k), None
     if plan is not None:  # a few long sequences: the scan runs over slabs of T side by side
@@ -73,11 +74,11 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     @contiguous
     @autocast_custom_fwd
-    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, offsets, head_first):
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, offsets, head_first, g_cum=None):
         geo = Geometry(k, v, offsets, head_first)
         beta_k = beta.to(k.dtype)
         g_cum, o, aw, au, ht, states = chunk_gated_delta_rule_fwd(geo, q, k, v, g, beta_k, scale, initial_state,
-                                                                  output_final_state)
+                                                                  output_final_state, g_cum=g_cum)
         ctx.n_saved_states = len(states) if SAVE_STATES else 0
         ctx.save_for_backward(q, k, v, g_cum, beta_k, aw, au, initial_state, *(states if SAVE_STATES else ()))
         ctx.geo, ctx.scale, ctx.g_dtype, ctx.beta_dtype = geo, scale, g.dtype, beta.dtype
@@ -91,7 +92,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(ctx.geo, q, k, v, g_cum, beta, aw, au, ctx.scale,
                                                             initial_state, do, dht, saved=states or None)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(ctx.g_dtype), db.to(ctx.beta_dtype),
-                None, dh0, None, None, None)
+                None, dh0, None, None, None, None)
 
 
 def chunk_gated_delta_rule(
@@ -128,8 +129,10 @@ def chunk_gated_delta_rule(
             return o.to(q.dtype), ht
         return chunk_gated_delta_rule_fwd_fused(geo, q, k, v, g, beta.to(k.dtype), scale, initial_state,
                                                 output_final_state)
+    from ..modules.gate_prologue import attached_cumsum
+    g_cum = attached_cumsum(g, offsets, head_first)  # made together with g by the gate prologue, if g is its output
     return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, offsets,
-                                             head_first)
+                                             head_first, g_cum)
 
 
 def fused_recurrent_gated_delta_rule(

@@ -113,3 +113,26 @@ def fused_recurrent_gla(
     return fused_recurrent(q=q, k=k, v=v, gk=gk, gv=gv, scale=scale, initial_state=initial_state,
                            output_final_state=output_final_state, reverse=reverse, offsets=offsets,
                            head_first=head_first)
+
+
+def fused_chunk_gla(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    scale: int = -1,
+    initial_state: torch.Tensor = None,
+    output_final_state: bool = False,
+    head_first: bool = True,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """The reference's fused execution mode of GLA (fla/ops/gla/fused_chunk.py:622): same recurrence and arguments
+    as `chunk_gla` with two differences in the contract, both kept: `scale=-1` means K^-0.5, and the initial state is
+    a constant (no gradient flows into it). The reference fuses the state walk and the output into one kernel per
+    (value tile, key tile); here the same result comes from the chunk kernels, which never hold more than one chunk of
+    the sequence per CTA either."""
+    if scale == -1:
+        scale = q.shape[-1] ** -0.5
+    if initial_state is not None:
+        initial_state = initial_state.detach()
+    return chunk_gla(q, k, v, g, scale=scale, initial_state=initial_state, output_final_state=output_final_state,
+                     head_first=head_first)

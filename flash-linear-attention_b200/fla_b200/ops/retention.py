@@ -18,6 +18,24 @@ def retention_decay(q: torch.Tensor, head_first: bool) -> torch.Tensor:
     return s[None, None, :].expand(q.shape[0], q.shape[1], q.shape[2]).contiguous()
 
 
+_DECAY_CACHE = {}  # (B, T, H, head_first, device, offsets id) -> (g, its chunk-local cumsum): constants of the shape
+
+
+def _cached_decay(q, head_first, offsets):
+    """The decay is a constant per head, so g and its chunk-local cumsum depend on the shape (and offsets) only: they are
+    built once per shape instead of by four elementwise launches and a cumsum per call."""
+    from . import common as C
+    key = (tuple(q.shape[:3]), bool(head_first), str(q.device), None if offsets is None else (id(offsets), offsets._version))
+    hit = _DECAY_CACHE.get(key)
+    if hit is None:
+        if len(_DECAY_CACHE) >= 8:
+            _DECAY_CACHE.clear()
+        g = retention_decay(q, head_first)
+        hit = (g, C.chunk_local_cumsum(g, offsets=offsets, head_first=head_first), offsets)
+        _DECAY_CACHE[key] = hit
+    return hit[0], hit[1]
+
+
 def chunk_retention(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -29,10 +47,14 @@ def chunk_retention(
     head_first: bool = True,
     cu_seqlens: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-    g = retention_decay(q, head_first)
+    from ..utils import resolve_offsets
+    from .simple_gla import check_varlen_args
+    offsets = resolve_offsets(offsets, cu_seqlens)
+    check_varlen_args(q, initial_state, offsets, head_first)
+    g, g_cum = _cached_decay(q, head_first, offsets)
     return chunk_simple_gla(q=q, k=k, v=v, scale=scale, g=g, initial_state=initial_state,
                             output_final_state=output_final_state, head_first=head_first, offsets=offsets,
-                            cu_seqlens=cu_seqlens)
+                            _g_cumsum=g_cum)
 
 
 def fused_recurrent_retention(
@@ -51,3 +73,21 @@ def fused_recurrent_retention(
     return fused_recurrent_simple_gla(q, k, v, g, scale=scale, initial_state=initial_state,
                                       output_final_state=output_final_state, reverse=reverse, offsets=offsets,
                                       head_first=head_first, cu_seqlens=cu_seqlens)
+
+
+def fused_chunk_retention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    scale: Optional[float] = None,
+    initial_state: Optional[torch.Tensor] = None,
+    output_final_state: bool = False,
+    head_first: bool = True,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """The reference's fused execution mode of retention (fla/ops/retention/fused_chunk.py:296): fixed-length batches
+    only, the initial state is a constant (its backward returns no gradient for it). Same decay and result as
+    `chunk_retention`."""
+    if initial_state is not None:
+        initial_state = initial_state.detach()
+    return chunk_retention(q, k, v, scale=scale, initial_state=initial_state, output_final_state=output_final_state,
+                           head_first=head_first)

@@ -138,12 +138,27 @@ int flab_short_conv_bwd(const void *x, const float *weight, const float *bias, c
 int flab_short_conv_update(const void *x, void *cache, const float *weight, const float *bias, void *y, int B, int D, int W, int silu, int dtype,
                            void *stream);
 
+/* ---- gate / beta prologue of the gated delta rule layer (the elementwise step right before the chunk op) ----
+ * Replaces the two lines of GatedDeltaNet.forward that make the op's gate and beta (fla/layers/gated_deltanet.py:236-237)
+ *   beta = sigmoid(b_proj(x)),   g = -exp(A_log) * softplus(a_proj(x) + dt_bias)
+ * and, in the same pass, the chunk-local cumulative sum of g that opens the chunk op (chunk_local_cumsum,
+ * fla/ops/gated_delta_rule/chunk.py:33). `geo` supplies B, T, H, N, NT, head_first, dtype (element type of a_proj, b_proj,
+ * beta and their gradients) and the variable-length tables; its tensor slots are ignored. a_proj, b_proj, beta: [B,T,H]
+ * (or [B,H,T]); A_log, dt_bias (may be NULL): fp32 [H]; g, g_cumsum (may be NULL), dg: fp32 [B,T,H].
+ * Backward: da, db as above; dA_log, ddt_bias (may be NULL) fp32 [H] are ADDED to with atomics: the caller zeroes them. */
+int flab_gdn_gate_fwd(const flab_args *geo, const void *a_proj, const void *b_proj, const float *A_log, const float *dt_bias, float *g,
+                      float *g_cumsum, void *beta, void *stream);
+int flab_gdn_gate_bwd(const flab_args *geo, const void *a_proj, const void *b_proj, const float *A_log, const float *dt_bias, const float *dg,
+                      const void *dbeta, void *da, void *db, float *dA_log, float *ddt_bias, void *stream);
+
 /* ---- inter-chunk state recurrence for diagonal decay ---------------------------------------
- * Replaces chunk_fwd_h (fla/ops/common/chunk_h.py:282): reads k, v, g or gk (either may be NULL),
- * h0 (optional); writes h (state at the start of every chunk) and ht (optional). */
+ * Replaces chunk_fwd_h (fla/ops/common/chunk_h.py:282): reads k, v, the gates g, gk, gv (each may be NULL;
+ * gv, fp32 [.., V], decays the value channels of the state as the reference's GSA op needs,
+ * fla/ops/gsa/chunk.py:664-675; g cannot be combined with gk or gv), h0 (optional); writes h (state at the
+ * start of every chunk) and ht (optional). */
 int flab_chunk_fwd_h(const flab_args *a, void *stream);
-/* Replaces chunk_bwd_dh (fla/ops/common/chunk_h.py:338): reads q, d_o, g or gk, dht (optional);
- * writes dh and dh0 (optional). */
+/* Replaces chunk_bwd_dh (fla/ops/common/chunk_h.py:338): reads q, d_o, g / gk / gv (as above), dht
+ * (optional); writes dh and dh0 (optional). */
 int flab_chunk_bwd_dh(const flab_args *a, void *stream);
 
 /* ---- intra-chunk output and its gradients ---------------------------------------------------
@@ -186,6 +201,13 @@ int flab_delta_fwd_h(const flab_args *a, void *stream);
  * g (optional), dht (optional), d_o, dv; writes dh, dv2, dh0 (optional). FLAB_F_STATE_ONLY: only
  * dh0 is written (dh and dv2 may be NULL), same domain as above. */
 int flab_delta_bwd_dhu(const flab_args *a, void *stream);
+
+/* ---- attention scores of simple GLA ----------------------------------------------------------
+ * Replaces the `attn` output of parallel_simple_gla_fwd (fla/ops/simple_gla/parallel.py:474-544, written by the
+ * kernel at :95-131): a[b,h,i,j] = scale <q_i, k_j> exp(g_i - g_j) for j <= i, else 0, with g the cumulative
+ * log decay over the whole sequence (fp32, NULL = no decay). Reads q, k, g; writes a ([B,H,T,T], element type
+ * dtype, every entry). Fixed-length batches only, like the reference. */
+int flab_simple_gla_attn(const flab_args *a, void *stream);
 
 /* ---- chain of slab transitions (scans cut along T) -------------------------------------------
  * No single counterpart in the reference (its two-level scan, fla/ops/common/chunk_h_split.py:164-260, is

@@ -17,5 +17,5 @@ from .indexing import chunk_indices_ref, chunk_offsets_ref  # noqa: F401
 from .l2norm import l2_norm, l2_norm_bwd  # noqa: F401
 from .short_conv import short_conv, short_conv_step  # noqa: F401
 from .norm_gate import rms_norm_swish_gate, rms_norm_swish_gate_bwd  # noqa: F401
-from .naive import (cumsum_global, cumsum_local, delta_rule, gated_delta_rule, gla, retention_log_decay,  # noqa: F401
-                    simple_gla)
+from .naive import (chunk_state_gradients, chunk_states, cumsum_global, cumsum_local, delta_rule, gated_delta_rule, gla,  # noqa: F401
+                    retention_log_decay, simple_gla, simple_gla_attention)

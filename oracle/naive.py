@@ -138,3 +138,65 @@ def cumsum_global(x, reverse=False, offsets=None, head_first=True):
         seg = x[:, a:b]
         y[:, a:b] = seg.flip(1).cumsum(1).flip(1) if reverse else seg.cumsum(1)
     return y.transpose(1, 2) if head_first else y
+
+
+def simple_gla_attention(q, k, g=None, scale=None, head_first=True, dtype=torch.float32):
+    """A[b,h,i,j] = scale <q_i, k_j> exp(G_i - G_j) for j <= i, else 0, G = cumsum of g over the sequence: the attention
+    matrix the reference's parallel form can return (fla/ops/simple_gla/parallel.py:95-131). Returns [B,H,T,T]."""
+    if not head_first:
+        q, k = q.transpose(1, 2), k.transpose(1, 2)
+        g = None if g is None else g.transpose(1, 2)
+    q, k = q.to(dtype), k.to(dtype)
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    A = torch.einsum("bhik,bhjk->bhij", q, k) * scale
+    if g is not None:
+        G = g.to(dtype).cumsum(-1)
+        A = A * (G[..., :, None] - G[..., None, :]).clamp(max=0).exp()
+    return A.tril()
+
+
+def _chunk_bounds(T, chunk_size):
+    return [(a, min(a + chunk_size, T)) for a in range(0, T, chunk_size)]
+
+
+def chunk_states(k, v, gk_cumsum=None, gv_cumsum=None, initial_state=None, chunk_size=64, dtype=torch.float32):
+    """State at the start of every chunk and the final state, for seq-first [B,T,H,*] inputs and chunk-local cumulative
+    log gates per key channel (gk) and / or value channel (gv): fla/ops/common/chunk_h.py:83-133 restated
+    (S <- diag(e^{gk_L}) S diag(e^{gv_L}) + (k e^{gk_L - gk})^T (v e^{gv_L - gv})). Returns (h [B,NT,H,K,V], ht)."""
+    B, T, H, K = k.shape
+    V = v.shape[-1]
+    S = torch.zeros(B, H, K, V, dtype=dtype) if initial_state is None else initial_state.to(dtype).clone()
+    hs = []
+    for a, b in _chunk_bounds(T, chunk_size):
+        hs.append(S.clone())
+        kc, vc = k[:, a:b].to(dtype), v[:, a:b].to(dtype)
+        if gk_cumsum is not None:
+            gl = gk_cumsum[:, b - 1].to(dtype)
+            S = S * gl.exp()[..., None]
+            kc = kc * (gl[:, None] - gk_cumsum[:, a:b].to(dtype)).exp()
+        if gv_cumsum is not None:
+            gl = gv_cumsum[:, b - 1].to(dtype)
+            S = S * gl.exp()[..., None, :]
+            vc = vc * (gl[:, None] - gv_cumsum[:, a:b].to(dtype)).exp()
+        S = S + torch.einsum("bthk,bthv->bhkv", kc, vc)
+    return torch.stack(hs, 1), S
+
+
+def chunk_state_gradients(q, do, scale, gk_cumsum=None, gv_cumsum=None, dht=None, chunk_size=64, dtype=torch.float32):
+    """Reverse walk of the same recurrence: gradient of the state after every chunk and of the initial state
+    (fla/ops/common/chunk_h.py:205-267). Returns (dh [B,NT,H,K,V], dh0)."""
+    B, T, H, K = q.shape
+    V = do.shape[-1]
+    D = torch.zeros(B, H, K, V, dtype=dtype) if dht is None else dht.to(dtype).clone()
+    dhs = []
+    for a, b in reversed(_chunk_bounds(T, chunk_size)):
+        dhs.append(D.clone())
+        qc, dc = q[:, a:b].to(dtype) * scale, do[:, a:b].to(dtype)
+        if gk_cumsum is not None:
+            D = D * gk_cumsum[:, b - 1].to(dtype).exp()[..., None]
+            qc = qc * gk_cumsum[:, a:b].to(dtype).exp()
+        if gv_cumsum is not None:
+            D = D * gv_cumsum[:, b - 1].to(dtype).exp()[..., None, :]
+            dc = dc * gv_cumsum[:, a:b].to(dtype).exp()
+        D = D + torch.einsum("bthk,bthv->bhkv", qc, dc)
+    return torch.stack(dhs[::-1], 1), D

@@ -14,22 +14,27 @@ sample of its units against the CPU oracle on identical bits:
 * decode (256 sequences x 16 heads, one token per call): every output and the states.
 
 Bars: relative L2 error (RMS(ref - out) / RMS(ref), the metric of the reference's tests/ops/utils.py:1-14)
-<= 5e-3 for outputs, states and every gradient except those in LOOSE: d beta and d g of the delta-rule families pass
-through the longest chains of bf16 intermediates, keep the reference's own bars (tests/ops/test_gated_delta.py:282-294)
-and print their value.
+<= 5e-3 for outputs, states and every gradient except those in LOOSE (d beta and d g of the gated rule, which pass
+through the longest chains of bf16 intermediates: 1e-2, half the reference's own bar; the gradients of the plain delta
+rule, whose state never decays: the reference's 8e-3). Every value is printed.
 """
 import pytest
 import torch
 import torch.nn.functional as F
 
 import oracle
-from util import assert_close
+from util import assert_close, err_ratio
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 BAR = 5e-3
-# per-gradient bars at these shapes; everything not listed is held to BAR
-LOOSE = {"dbeta": 2e-2, "dg": 2e-2}
+# per-gradient bars at these shapes; everything not listed is held to BAR. Measured on the B200 at these shapes
+# (bf16): o, ht, dq, dk, dv, dh0 of the gated rule 1.5e-3 .. 3.8e-3; its dg up to 5.8e-3 and dbeta up to 6.3e-3 (the
+# reference asserts 2e-2 for both, tests/ops/test_gated_delta.py:282-294). The plain delta rule has no decay, so the
+# rounding of 4096 tokens of bf16 intermediates accumulates in the state: dk 5.05e-3 (the reference asserts 8e-3,
+# tests/ops/test_delta.py:74-93).
+LOOSE = {"gated_delta": {"dbeta": 1e-2, "dg": 1e-2},
+         "delta": {"dbeta": 1e-2, "dq": 8e-3, "dk": 8e-3, "dv": 8e-3, "dh0": 8e-3}}
 
 
 def ops():
@@ -38,7 +43,7 @@ def ops():
 
 
 def _bar(kind, name):
-    return LOOSE.get(name, BAR) if kind != "simple_gla" else BAR
+    return LOOSE.get(kind, {}).get(name, BAR)
 
 
 def _oracle_chain(kind, x, S_in, do, dS_out, scale=None):
@@ -65,12 +70,10 @@ def _oracle_chain(kind, x, S_in, do, dS_out, scale=None):
 
 
 def _report(kind, tag, want, got, skip=()):
-    res = {}
-    for n, ref in want.items():
-        if n in skip or n not in got:
-            continue
-        res[n] = assert_close(f"{tag} {n}", ref, got[n], _bar(kind, n))
+    res = {n: err_ratio(ref, got[n]) for n, ref in want.items() if n not in skip and n in got}
     print(tag, {n: f"{e:.2e}" for n, e in res.items()})
+    bad = {n: (e, _bar(kind, n)) for n, e in res.items() if not e < _bar(kind, n)}
+    assert not bad, f"{tag}: relative L2 error over the bar (value, bar): {bad}"
     return res
 
 

@@ -73,9 +73,9 @@ def run_both(fn_gpu, fn_ref, d, names, head_first=False, tol=None, tol_over=None
         do = do.transpose(1, 2).contiguous()
     o, ht = fn_gpu(gi, head_first=head_first, **kw)
     o_ref, ht_ref = fn_ref(ri, head_first=head_first, **kw)
-    res = {"o": assert_close("o", o_ref, o, tol_over.get("o", tol))}
+    res = {"o": err_ratio(o_ref, o)}
     if ht_ref is not None:
-        res["ht"] = assert_close("ht", ht_ref, ht, tol_over.get("ht", tol))
+        res["ht"] = err_ratio(ht_ref, ht)
     if check_grads:
         loss = (o.float() * do.to(DEV).float()).sum()
         loss_ref = (o_ref * do.float()).sum()
@@ -85,8 +85,11 @@ def run_both(fn_gpu, fn_ref, d, names, head_first=False, tol=None, tol_over=None
         gg = torch.autograd.grad(loss, [gi[n] for n in names])
         gr = torch.autograd.grad(loss_ref, [ri[n] for n in names])
         for n, a, b in zip(names, gr, gg):
-            res["d" + n] = assert_close("d" + n, a, b, tol_over.get("d" + n, tol))
+            res["d" + n] = err_ratio(a, b)
+    # every ratio is printed (pytest -s) before any is judged, so one run shows the whole picture
     print({k_: f"{v_:.2e}" for k_, v_ in res.items()})
+    bad = {k_: (v_, tol_over.get(k_, tol)) for k_, v_ in res.items() if not v_ < tol_over.get(k_, tol)}
+    assert not bad, f"relative L2 error over the bar (value, bar): {bad}"
     return res
 
 

@@ -231,3 +231,60 @@ def test_short_conv_matches_reference_module():
                 yt, c = oracle.short_conv_step(g["step_x"][:, t:t + 1], c, w, b, silu)
                 assert_close(f"{case} step {t}", g["step_y"][:, t:t + 1], yt, 1e-6)
         assert torch.equal(c, g["step_cache"])
+
+
+# ------------------------------------------------------------------------------------------------
+# the remaining execution modes of the same recurrences (tests/golden/make_golden_f4.py: the reference's fused_chunk /
+# parallel kernels and the gv mode of its chunk_fwd_h, run under Triton's CPU interpreter)
+# ------------------------------------------------------------------------------------------------
+def _f4():
+    import os
+
+    import numpy as np
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "f4_vectors.npz"))
+
+
+def test_oracle_matches_reference_fused_chunk_and_parallel_kernels():
+    z = _f4()
+    f = lambda n: torch.from_numpy(z[n]).float()  # noqa: E731
+    # fused_chunk_gla (fp32): same recurrence as chunk_gla
+    q, k, v, g = (f(f"fused_chunk_gla.{n}").requires_grad_(True) for n in ("q", "k", "v", "g"))
+    o, ht = oracle.gla(q, k, v, gk=g, initial_state=f("fused_chunk_gla.h0"), output_final_state=True, head_first=False)
+    assert_close("fused_chunk_gla o", f("fused_chunk_gla.o"), o, 1e-5)
+    assert_close("fused_chunk_gla ht", f("fused_chunk_gla.ht"), ht, 1e-5)
+    # (the reference's fused backward ignores the gradient of the final state: fla/ops/gla/fused_chunk.py:497, fla/ops/retention/fused_chunk.py:265)
+    gr = _grads((o,), (f("fused_chunk_gla.do"),), (q, k, v, g))
+    for name, gx in zip(("dq", "dk", "dv", "dg"), gr):
+        assert_close("fused_chunk_gla " + name, f(f"fused_chunk_gla.{name}"), gx, 2e-5)
+    # fused_chunk_retention (fp16 inputs, fp32 accumulation inside the reference kernel)
+    q, k, v = (f(f"fused_chunk_retention.{n}").requires_grad_(True) for n in ("q", "k", "v"))
+    H = q.shape[2]
+    gr_ = oracle.retention_log_decay(H)[None, None, :].expand(q.shape[0], q.shape[1], H)
+    o, ht = oracle.simple_gla(q, k, v, gr_, initial_state=f("fused_chunk_retention.h0"), output_final_state=True, head_first=False)
+    assert_close("fused_chunk_retention o", f("fused_chunk_retention.o"), o, 2e-3)
+    assert_close("fused_chunk_retention ht", f("fused_chunk_retention.ht"), ht, 2e-3)
+    gr = _grads((o,), (f("fused_chunk_retention.do"),), (q, k, v))
+    for name, gx in zip(("dq", "dk", "dv"), gr):
+        assert_close("fused_chunk_retention " + name, f(f"fused_chunk_retention.{name}"), gx, 2e-3)
+    # parallel_simple_gla: o, gradients, and the attention matrix
+    q, k, v, g = (f(f"parallel_simple_gla.{n}").requires_grad_(True) for n in ("q", "k", "v", "g"))
+    o, _ = oracle.simple_gla(q, k, v, g, head_first=False)
+    assert_close("parallel_simple_gla o", f("parallel_simple_gla.o"), o, 2e-3)
+    gr = _grads((o,), (f("parallel_simple_gla.do"),), (q, k, v, g))
+    for name, gx in zip(("dq", "dk", "dv", "dg"), gr):
+        assert_close("parallel_simple_gla " + name, f(f"parallel_simple_gla.{name}"), gx, 2e-3)
+    attn = oracle.simple_gla_attention(q.detach(), k.detach(), g.detach(), head_first=False)
+    assert_close("parallel_simple_gla attn", f("parallel_simple_gla.attn"), attn, 2e-3)
+
+
+def test_oracle_matches_reference_value_gate_state_scan():
+    """chunk_fwd_h / chunk_bwd_dh with gv (the GSA path): chunk states and the final state from the token recurrence."""
+    z = _f4()
+    f = lambda n: torch.from_numpy(z[n]).float()  # noqa: E731
+    k, v, q, gv, h0 = f("chunk_h_gv.k"), f("chunk_h_gv.v"), f("chunk_h_gv.q"), f("chunk_h_gv.gv"), f("chunk_h_gv.h0")
+    h, ht = oracle.chunk_states(k, v, gv_cumsum=gv, initial_state=h0)
+    assert_close("h", f("chunk_h_gv.h"), h, 2e-3)
+    assert_close("ht", f("chunk_h_gv.ht"), ht, 2e-3)
+    dh, dh0 = oracle.chunk_state_gradients(q, f("chunk_h_gv.do"), scale=k.shape[-1] ** -0.5, gv_cumsum=gv, dht=f("chunk_h_gv.dht"))
+    assert_close("dh", f("chunk_h_gv.dh"), dh, 2e-3)
+    assert_close("dh0", f("chunk_h_gv.dh0"), dh0, 2e-3)
