@@ -188,8 +188,10 @@ __global__ void __launch_bounds__(RC_WARPS * 32, (RPW <= 8 ? 2 : 1)) recurrent_f
 // decode configuration).  Persistent CTAs, one per SM, two groups of 8 consumer warps (each group works on
 // alternate items, so that four warps per scheduler hide each other's latencies); no producer warp:
 //  * the 64 KB fp32 state tile of each (sequence, head) arrives through a 3-deep ring of bulk async
-//    copies (one cp.async.bulk per tile, completion on an mbarrier); a slot is refilled by one thread of the
-//    group that used it, right after the group barrier that follows the drain of the slot into registers;
+//    copies, one 8 KB piece (16 rows) per consumer warp with its own mbarrier: a warp waits for its piece only,
+//    drains it into registers and at once asks for the same piece of the tile three items ahead, so the
+//    copies in flight never wait for a barrier among warps; the loads carry an evict-first L2 hint and the
+//    state is stored with streaming stores (neither is read again by this kernel);
 //  * a consumer warp owns 16 state rows, a lane 4 columns; the k / q values of the warp's rows sit in
 //    one register per lane (lanes 0-15: k, lanes 16-31: q*scale) and are broadcast with shuffles; they
 //    and v, g, beta are fetched one token ahead, so no global-load latency is exposed;
@@ -204,17 +206,35 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
                "l"(src), "r"(bytes), "r"(tc::smem_u32(bar))
                : "memory");
 }
+// the same copy with an L2 eviction policy (made by createpolicy) for data that is read exactly once
+__device__ __forceinline__ void bulk_load_hint(void *dst, const void *src, uint32_t bytes, uint64_t *bar, uint64_t policy) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+                   tc::smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(tc::smem_u32(bar)), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void st_streaming(float *dst, float4 x) {
+  asm volatile("st.global.cs.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w) : "memory");
+}
 
-template <typename T>
+// VARIANT bits (the launcher picks; all on by default): 1 = per-warp pieces of the ring, 2 = evict-first loads,
+// 4 = streaming stores of the new state
+template <typename T, int VARIANT>
 __global__ void __launch_bounds__(512, 1) recurrent_stream_kernel(const flab_args a, int n_items) {
   using namespace tc;
   constexpr int RPW = 16;
+  constexpr bool PIECES = (VARIANT & 1) != 0, HINT = (VARIANT & 2) != 0, STREAM_ST = (VARIANT & 4) != 0;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   float *sState = reinterpret_cast<float *>(smem_raw);  // [RS_STAGES][128][128]
   __shared__ __align__(16) float sRedAll[2][2][2][8][RC_V];  // [group][parity][S^T q | S^T k][warp][column]
   __shared__ float sKQAll[2][2][8];
   __shared__ volatile int fail_snap[2][2];
-  __shared__ uint64_t full[RS_STAGES];
+  __shared__ uint64_t full[RS_STAGES][8];  // [slot][piece]; the whole-tile form uses piece 0 only
   __shared__ volatile int fail_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K = a.K, V = a.V;  // V == 128
@@ -226,18 +246,37 @@ __global__ void __launch_bounds__(512, 1) recurrent_stream_kernel(const flab_arg
   const T *beta = reinterpret_cast<const T *>(a.beta);
   const bool beta_vec = (a.flags & FLAB_F_BETA_VECTOR) != 0;
   const int n_local = n_items > (int)blockIdx.x ? (n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const uint64_t pol = HINT ? policy_evict_first() : 0;
+  auto copy_in = [&](void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    mbar_expect_tx(bar, bytes);
+    if (HINT) bulk_load_hint(dst, src, bytes, bar, pol);
+    else bulk_load(dst, src, bytes, bar);
+  };
   auto refill = [&](int i) {  // one thread: tile of local item i -> its slot
     if (i >= n_local) return;
     const int st = i % RS_STAGES;
-    mbar_expect_tx(&full[st], tile_bytes);
-    bulk_load(sState + (size_t)st * 128 * RC_V, h0 + (size_t)(blockIdx.x + i * gridDim.x) * K * V, tile_bytes, &full[st]);
+    copy_in(sState + (size_t)st * 128 * RC_V, h0 + (size_t)(blockIdx.x + i * gridDim.x) * K * V, tile_bytes, &full[st][0]);
+  };
+  auto refill_piece = [&](int i, int w) {  // one thread: rows 16 w .. 16 w + 15 of the tile of local item i
+    const int rows = min(RPW, K - w * RPW);
+    if (i >= n_local || rows <= 0) return;
+    const int st = i % RS_STAGES;
+    copy_in(sState + (size_t)st * 128 * RC_V + (size_t)w * RPW * RC_V,
+            h0 + (size_t)(blockIdx.x + i * gridDim.x) * K * V + (size_t)w * RPW * RC_V, (uint32_t)rows * RC_V * sizeof(float), &full[st][w]);
   };
   if (tid == 0) {
-    for (int i = 0; i < RS_STAGES; ++i) mbar_init(&full[i], 1);
+    for (int i = 0; i < RS_STAGES; ++i)
+      for (int w = 0; w < 8; ++w) mbar_init(&full[i][w], 1);
     fail_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
-    for (int i = 0; i < RS_STAGES; ++i) refill(i);
+    for (int i = 0; i < RS_STAGES; ++i) {
+      if (PIECES) {
+        for (int w = 0; w < 8; ++w) refill_piece(i, w);
+      } else {
+        refill(i);
+      }
+    }
   }
   __syncthreads();
   // ---------------------------------------------------------------------------------- consumers
@@ -271,7 +310,7 @@ __global__ void __launch_bounds__(512, 1) recurrent_stream_kernel(const flab_arg
     const int n = item / a.H, hd = item % a.H;
     const Seq s = seq_of(a, n);
     const int st = i % RS_STAGES;
-    if (!mbar_wait(&full[st], (i / RS_STAGES) & 1)) {
+    if ((!PIECES || r0 < K) && !mbar_wait(&full[st][PIECES ? gw : 0], (i / RS_STAGES) & 1)) {
       atomicCAS(&tu_tc_error, 0, 20);
       fail_flag = 1;
     }
@@ -285,12 +324,16 @@ __global__ void __launch_bounds__(512, 1) recurrent_stream_kernel(const flab_arg
       if (kk < K) x = *reinterpret_cast<const float4 *>(tile + (size_t)kk * RC_V + c0);
       S[r][0] = x.x, S[r][1] = x.y, S[r][2] = x.z, S[r][3] = x.w;
     }
-    // every warp of the group has drained the slot: refill it; the group leaves as one if a wait has run out (a
-    // thread of it samples the flag, everybody reads the sample after the barrier)
+    if (PIECES) {  // this warp's piece is in registers: ask for the same piece three items ahead, before any barrier
+      __syncwarp();
+      if (lane == 0) refill_piece(i + RS_STAGES, gw);
+    }
+    // the group leaves as one if a wait has run out (a thread of it samples the flag, everybody reads the sample after
+    // the barrier); in the whole-tile form the barrier also says that every warp has drained the slot
     if ((tid & 255) == 0) fail_snap[grp][(i >> 1) & 1] = fail_flag;
     named_barrier(1 + grp, 256);
     if (fail_snap[grp][(i >> 1) & 1]) break;
-    if ((tid & 255) == 0) refill(i + RS_STAGES);
+    if (!PIECES && (tid & 255) == 0) refill(i + RS_STAGES);
 
     for (int i_t = 0; i_t < s.len; ++i_t) {
       const size_t ov = tok_off(a, s, hd, i_t, V);
@@ -363,15 +406,29 @@ __global__ void __launch_bounds__(512, 1) recurrent_stream_kernel(const flab_arg
 #pragma unroll
       for (int r = 0; r < RPW; ++r) {
         const int kk = r0 + r;
-        if (kk < K) *reinterpret_cast<float4 *>(dst + (size_t)kk * V + c0) = make_float4(S[r][0], S[r][1], S[r][2], S[r][3]);
+        if (kk < K) {
+          const float4 x = make_float4(S[r][0], S[r][1], S[r][2], S[r][3]);
+          if (STREAM_ST) st_streaming(dst + (size_t)kk * V + c0, x);
+          else *reinterpret_cast<float4 *>(dst + (size_t)kk * V + c0) = x;
+        }
       }
     }
   }
 }
 
-template <typename T> static int launch_recurrent_stream(const flab_args *a, cudaStream_t stream) {
+// FLA_B200_DECODE_VARIANT (0..7, read once) selects the kernel's memory-path options for measurements; default 7
+static int decode_variant() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("FLA_B200_DECODE_VARIANT");
+    v = (e && e[0] >= '0' && e[0] <= '7') ? e[0] - '0' : 7;
+  }
+  return v;
+}
+
+template <typename T, int VARIANT> static int launch_recurrent_stream_v(const flab_args *a, cudaStream_t stream) {
   const size_t smem = (size_t)RS_STAGES * 128 * RC_V * sizeof(float);
-  auto kern = recurrent_stream_kernel<T>;
+  auto kern = recurrent_stream_kernel<T, VARIANT>;
   if (int e = set_smem(kern, smem)) return e;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -379,6 +436,19 @@ template <typename T> static int launch_recurrent_stream(const flab_args *a, cud
   const int n_items = a->N * a->H;
   kern<<<n_items < sms ? n_items : sms, 512, smem, stream>>>(*a, n_items);
   return check_launch("recurrent_delta_fwd(stream)");
+}
+
+template <typename T> static int launch_recurrent_stream(const flab_args *a, cudaStream_t stream) {
+  switch (decode_variant()) {
+    case 0: return launch_recurrent_stream_v<T, 0>(a, stream);
+    case 1: return launch_recurrent_stream_v<T, 1>(a, stream);
+    case 2: return launch_recurrent_stream_v<T, 2>(a, stream);
+    case 3: return launch_recurrent_stream_v<T, 3>(a, stream);
+    case 4: return launch_recurrent_stream_v<T, 4>(a, stream);
+    case 5: return launch_recurrent_stream_v<T, 5>(a, stream);
+    case 6: return launch_recurrent_stream_v<T, 6>(a, stream);
+    default: return launch_recurrent_stream_v<T, 7>(a, stream);
+  }
 }
 
 template <typename T, bool DELTA> static int launch_recurrent_fwd(const flab_args *a, cudaStream_t stream) {

@@ -10,12 +10,14 @@
 //             is fetched a whole item ahead; X2 is refilled as soon as the products against the states are done,
 //             Y as soon as the outputs (built over q, k, w) have been read by the tile store
 //   warp 17 : MMA issuer   - ds = do v^T; then the three products against the states; then the two
-//             intra-chunk products, accumulated onto dq and dk in TMEM
+//             intra-chunk products: ds k accumulated onto dq, ds^T q into columns of its own (the dg of a chunk's last
+//             row needs <k, dk_inter>, which is read from the untouched inter-chunk dk at the end of the item)
 //   warps 0-15 : epilogue, warp = (TMEM lane quadrant = 16 tokens, 32-column group)
 //   warp 18 : output     - tile stores of dq, dk, dw from the Y buffer, then hands the buffer back to the producer
 // The row factors of the inter-chunk terms are applied to the A operands in shared memory (do, v, dv are
 // rescaled in place after ds has been formed from the unscaled tiles), so that inter- and intra-chunk parts
-// add up in one accumulator and TMEM holds ds | dq | dk | dw = 448 columns.  dq, dk, dw are written over the
+// add up in one accumulator; TMEM holds dq | dk | dw | ds (448 columns), the intra-chunk dk reuses the ds columns
+// plus the last 64.  dq, dk, dw are written over the
 // q, k, w tiles (each element by the thread that read it for the dg dot) and leave through tile stores.
 // All waits are bounded; a timeout records an id in the unit's error word and the epilogue warps leave
 // together at their next common barrier.
@@ -40,7 +42,7 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
   using namespace tc;
   constexpr uint32_t T16 = 16384, T32 = 32768;
   constexpr uint32_t X1_BYTES = (USE_DW ? 3 : 2) * T16, X2_BYTES = 2 * T32, Y_BYTES = (USE_DW ? 3 : 2) * T16;
-  constexpr uint32_t TM_DS = 0, TM_DQ = 64, TM_DK = 192, TM_DW = 320;
+  constexpr uint32_t TM_DQ = 0, TM_DK = 128, TM_DW = 256, TM_DS = 384, TM_DK2 = 384;  // dk2 (128 columns) overlays ds
   constexpr int ET = 512;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -52,7 +54,7 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
   float *sG = reinterpret_cast<float *>(sDS + 8192);  // [2][64] gates
   float *sDG = sG + 2 * C;                            // [2][64] dg rows
   float *sRed = sDG + 2 * C;                          // [2][2]  <h, dh>, <k, dk_inter>
-  __shared__ uint64_t fullX1[2], emptyX1[2], fullX2, emptyX2, fullY, emptyY, ds_done, e1_done, dk_done, e1b_done, all_done, acc_free, out_ready;
+  __shared__ uint64_t fullX1[2], emptyX1[2], fullX2, emptyX2, fullY, emptyY, ds_done, e1_done, all_done, acc_free, out_ready;
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
   __shared__ volatile int abort_snap[2];
@@ -70,8 +72,6 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
     mbar_init(&emptyY, 1);
     mbar_init(&ds_done, 1);
     mbar_init(&e1_done, 16);
-    mbar_init(&dk_done, 1);
-    mbar_init(&e1b_done, 16);
     mbar_init(&all_done, 1);
     mbar_init(&acc_free, 16);
     mbar_init(&out_ready, 16);
@@ -155,17 +155,17 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
         const uint32_t x1 = smem_u32(sX1 + xb * X1_BYTES);
         const uint64_t d_do = desc_kmajor(x1, 0, 8192), d_v = desc_kmajor(x1 + T16, 0, 8192), d_dv = desc_kmajor(x1 + 2 * T16, 0, 8192);
         if (!mbar_wait(&fullX1[xb], xph)) { fail(63); break; }
+        // ds lands on columns the previous item's intra-chunk dk occupied: its accumulators must have been read
+        if (i > 0 && !mbar_wait(&acc_free, ph ^ 1)) { fail(65); break; }
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma(tmem + TM_DS, d_do + kx(k, 8192), d_v + kx(k, 8192), id_ds, k > 0);
         umma_commit(&ds_done);
         if (!mbar_wait(&e1_done, ph)) { fail(64); break; }
-        if (i > 0 && !mbar_wait(&acc_free, ph ^ 1)) { fail(65); break; }
         if (!mbar_wait(&fullX2, ph)) { fail(75); break; }
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma(tmem + TM_DK, d_v + kx(k, 8192), d_dh + kx(k, T16), id_st, k > 0);
-        umma_commit(&dk_done);  // the epilogue takes <k, dk_inter> from it while the other products run
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma(tmem + TM_DQ, d_do + kx(k, 8192), d_h + kx(k, T16), id_st, k > 0);
         if (USE_DW) {
@@ -176,12 +176,11 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
         umma_commit(&emptyX2);
         const uint64_t d_q = desc_mnmajor(smem_u32(sY), 0, 8192), d_k = desc_mnmajor(smem_u32(sY + T16), 0, 8192);
         if (!mbar_wait(&fullY, ph)) { fail(66); break; }
-        if (use_g && !mbar_wait(&e1b_done, ph)) { fail(67); break; }
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma(tmem + TM_DQ, d_dsk + kx(k, 8192), d_k + mx(k), id_dq, 1);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma(tmem + TM_DK, d_dsm + mx(k), d_q + mx(k), id_dk, 1);
+        for (int k = 0; k < 4; ++k) umma(tmem + TM_DK2, d_dsm + mx(k), d_q + mx(k), id_dk, k > 0);
         umma_commit(&all_done);
       }
     }
@@ -346,35 +345,34 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&emptyX2);
-      // ---- E1b: <k, dk_inter> from the inter-chunk dk before the intra-chunk product lands on it
+      // ---- E2: finished dq, dk, dw -> dg rows, outputs over the q, k, w tiles
       if (!mbar_wait(&fullY, ph)) fail(70);
-      if (use_g) {
-        if (!mbar_wait(&dk_done, ph)) fail(71);
-        fence_after_sync();
-        float dki[4][4];
-        tmem_ld_frag<4>(tmem + lane_base + TM_DK + 32 * cq, dki);
+      if (!mbar_wait(&all_done, ph)) fail(72);
+      fence_after_sync();
+      float dq[4][4], dk[4][4], dw[4][4];
+      {
+        // inter-chunk dk and intra-chunk dk sit in separate columns: <k, dk_inter> first, then their sum
+        float dk2[4][4];
+        tmem_ld_frag<4>(tmem + lane_base + TM_DK + 32 * cq, dk);
+        tmem_ld_frag<4>(tmem + lane_base + TM_DK2 + 32 * cq, dk2);
         tmem_ld_wait();
         float dkk = 0.f;
 #pragma unroll
         for (int ni = 0; ni < 4; ++ni) {
-          const int col = colb + 8 * ni;
-          const uint32_t o_lo = o_lo_[ni], o_hi = o_hi_[ni];
-          const float2 k_lo = ld2(sK + o_lo), k_hi = ld2(sK + o_hi);
-          if (row_lo < rows) dkk += dki[ni][0] * k_lo.x + dki[ni][1] * k_lo.y;
-          if (row_hi < rows) dkk += dki[ni][2] * k_hi.x + dki[ni][3] * k_hi.y;
+          if (use_g) {
+            const float2 k_lo = ld2(sK + o_lo_[ni]), k_hi = ld2(sK + o_hi_[ni]);
+            if (row_lo < rows) dkk += dk[ni][0] * k_lo.x + dk[ni][1] * k_lo.y;
+            if (row_hi < rows) dkk += dk[ni][2] * k_hi.x + dk[ni][3] * k_hi.y;
+          }
+#pragma unroll
+          for (int r = 0; r < 4; ++r) dk[ni][r] += dk2[ni][r];
         }
-        dkk = warp_sum(dkk);
-        if (lane == 0) atomicAdd(&red[1], dkk);
-        fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&e1b_done);
+        if (use_g) {
+          dkk = warp_sum(dkk);
+          if (lane == 0) atomicAdd(&red[1], dkk);
+        }
       }
-      // ---- E2: finished dq, dk, dw -> dg rows, outputs over the q, k, w tiles
-      if (!mbar_wait(&all_done, ph)) fail(72);
-      fence_after_sync();
-      float dq[4][4], dk[4][4], dw[4][4];
       tmem_ld_frag<4>(tmem + lane_base + TM_DQ + 32 * cq, dq);
-      tmem_ld_frag<4>(tmem + lane_base + TM_DK + 32 * cq, dk);
       if (USE_DW) tmem_ld_frag<4>(tmem + lane_base + TM_DW + 32 * cq, dw);
       tmem_ld_wait();
       fence_before_sync();
