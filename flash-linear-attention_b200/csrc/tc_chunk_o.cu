@@ -325,7 +325,7 @@ template <int MODE> int tc_chunk_o_try(const flab_args *a, cudaStream_t stream, 
   constexpr bool L = MODE == TMODE_DV_LOCAL;
   int rc;
   if (a->K == 64) {
-    rc = (a->V % 128 == 0) ? launch_tc_o<1, 2, MODE, 4>(a, stream, name) : launch_tc_o<1, 1, MODE, 4>(a, stream, name);
+    rc = (a->V % 128 == 0) ? launch_tc_o<1, 2, MODE, L ? 4 : 3>(a, stream, name) : launch_tc_o<1, 1, MODE, 4>(a, stream, name);  // (1, 2) with four stages and a state tile is 241 KB
   } else {
     rc = (a->V % 128 == 0) ? launch_tc_o<2, 2, MODE, L ? 3 : 2>(a, stream, name) : launch_tc_o<2, 1, MODE, L ? 4 : 3>(a, stream, name);
   }

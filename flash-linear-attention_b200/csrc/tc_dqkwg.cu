@@ -10,14 +10,15 @@
 //             is fetched a whole item ahead; X2 is refilled as soon as the products against the states are done,
 //             Y as soon as the outputs (built over q, k, w) have been read by the tile store
 //   warp 17 : MMA issuer   - ds = do v^T; then the three products against the states; then the two
-//             intra-chunk products: ds k accumulated onto dq, ds^T q into columns of its own (the dg of a chunk's last
-//             row needs <k, dk_inter>, which is read from the untouched inter-chunk dk at the end of the item)
+//             intra-chunk products, accumulated onto dq and dk in TMEM
 //   warps 0-15 : epilogue, warp = (TMEM lane quadrant = 16 tokens, 32-column group)
 //   warp 18 : output     - tile stores of dq, dk, dw from the Y buffer, then hands the buffer back to the producer
+//   warp 19 : scalars    - gates and row count of the coming item into shared memory, zeroed dg rows, and the finished
+//                          dg rows of past items out to global memory: the epilogue warps touch no global memory per
+//                          token and meet each other only through the mbarriers of the phases
 // The row factors of the inter-chunk terms are applied to the A operands in shared memory (do, v, dv are
 // rescaled in place after ds has been formed from the unscaled tiles), so that inter- and intra-chunk parts
-// add up in one accumulator; TMEM holds dq | dk | dw | ds (448 columns), the intra-chunk dk reuses the ds columns
-// plus the last 64.  dq, dk, dw are written over the
+// add up in one accumulator and TMEM holds ds | dq | dk | dw = 448 columns.  dq, dk, dw are written over the
 // q, k, w tiles (each element by the thread that read it for the dg dot) and leave through tile stores.
 // All waits are bounded; a timeout records an id in the unit's error word and the epilogue warps leave
 // together at their next common barrier.
@@ -38,11 +39,11 @@ struct TcDqMaps {
 };
 
 template <bool USE_DW>
-__global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant__ TcDqMaps m, const TcDqParams p) {
+__global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant__ TcDqMaps m, const TcDqParams p) {
   using namespace tc;
   constexpr uint32_t T16 = 16384, T32 = 32768;
   constexpr uint32_t X1_BYTES = (USE_DW ? 3 : 2) * T16, X2_BYTES = 2 * T32, Y_BYTES = (USE_DW ? 3 : 2) * T16;
-  constexpr uint32_t TM_DQ = 0, TM_DK = 128, TM_DW = 256, TM_DS = 384, TM_DK2 = 384;  // dk2 (128 columns) overlays ds
+  constexpr uint32_t TM_DS = 0, TM_DQ = 64, TM_DK = 192, TM_DW = 320;
   constexpr int ET = 512;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -54,10 +55,11 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
   float *sG = reinterpret_cast<float *>(sDS + 8192);  // [2][64] gates
   float *sDG = sG + 2 * C;                            // [2][64] dg rows
   float *sRed = sDG + 2 * C;                          // [2][2]  <h, dh>, <k, dk_inter>
-  __shared__ uint64_t fullX1[2], emptyX1[2], fullX2, emptyX2, fullY, emptyY, ds_done, e1_done, all_done, acc_free, out_ready;
+  __shared__ uint64_t fullX1[2], emptyX1[2], fullX2, emptyX2, fullY, emptyY, ds_done, e1_done, dk_done, e1b_done, all_done, acc_free, out_ready;
+  __shared__ uint64_t scal_full[2], rows_done[2], ragged_sync;
+  __shared__ int sRows[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
-  __shared__ volatile int abort_snap[2];
 
   const flab_args &a = p.a;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -72,9 +74,16 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
     mbar_init(&emptyY, 1);
     mbar_init(&ds_done, 1);
     mbar_init(&e1_done, 16);
+    mbar_init(&dk_done, 1);
+    mbar_init(&e1b_done, 16);
     mbar_init(&all_done, 1);
     mbar_init(&acc_free, 16);
     mbar_init(&out_ready, 16);
+    for (int j = 0; j < 2; ++j) {
+      mbar_init(&scal_full[j], 1);
+      mbar_init(&rows_done[j], 16);
+    }
+    mbar_init(&ragged_sync, 16);
     abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -155,17 +164,17 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
         const uint32_t x1 = smem_u32(sX1 + xb * X1_BYTES);
         const uint64_t d_do = desc_kmajor(x1, 0, 8192), d_v = desc_kmajor(x1 + T16, 0, 8192), d_dv = desc_kmajor(x1 + 2 * T16, 0, 8192);
         if (!mbar_wait(&fullX1[xb], xph)) { fail(63); break; }
-        // ds lands on columns the previous item's intra-chunk dk occupied: its accumulators must have been read
-        if (i > 0 && !mbar_wait(&acc_free, ph ^ 1)) { fail(65); break; }
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma(tmem + TM_DS, d_do + kx(k, 8192), d_v + kx(k, 8192), id_ds, k > 0);
         umma_commit(&ds_done);
         if (!mbar_wait(&e1_done, ph)) { fail(64); break; }
+        if (i > 0 && !mbar_wait(&acc_free, ph ^ 1)) { fail(65); break; }
         if (!mbar_wait(&fullX2, ph)) { fail(75); break; }
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma(tmem + TM_DK, d_v + kx(k, 8192), d_dh + kx(k, T16), id_st, k > 0);
+        umma_commit(&dk_done);  // the epilogue takes <k, dk_inter> from it while the other products run
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma(tmem + TM_DQ, d_do + kx(k, 8192), d_h + kx(k, T16), id_st, k > 0);
         if (USE_DW) {
@@ -176,11 +185,12 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
         umma_commit(&emptyX2);
         const uint64_t d_q = desc_mnmajor(smem_u32(sY), 0, 8192), d_k = desc_mnmajor(smem_u32(sY + T16), 0, 8192);
         if (!mbar_wait(&fullY, ph)) { fail(66); break; }
+        if (use_g && !mbar_wait(&e1b_done, ph)) { fail(67); break; }
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma(tmem + TM_DQ, d_dsk + kx(k, 8192), d_k + mx(k), id_dq, 1);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma(tmem + TM_DK2, d_dsm + mx(k), d_q + mx(k), id_dk, k > 0);
+        for (int k = 0; k < 4; ++k) umma(tmem + TM_DK, d_dsm + mx(k), d_q + mx(k), id_dk, 1);
         umma_commit(&all_done);
       }
     }
@@ -210,6 +220,59 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       }
       tma_store_wait_all();
     }
+  } else if (warp == 19) {
+    // ------------------------------------------------------------------ scalar warp
+    // Item i uses slot i & 1 of sG / sDG / sRed / sRows.  A slot is handed to item i once item i - 2 is finished with
+    // it (rows_done); its dg rows go to global memory from here, the chunk's last row with the two state terms added.
+    const float *Gbase = reinterpret_cast<const float *>(a.g);
+    auto where = [&](int j, Seq &s, int &hd, int &t0, int &rows) {
+      int c, n, it;
+      decode(j, c, hd);
+      chunk_of(a, c, n, it);
+      s = seq_of(a, n);
+      t0 = it * C;
+      rows = min(C, s.len - t0);
+    };
+    auto write_out = [&](int j) -> bool {
+      const int slot = j & 1;
+      if (!mbar_wait(&rows_done[slot], (j >> 1) & 1)) {
+        fail(77);
+        return false;
+      }
+      if (!use_g) return true;
+      Seq s;
+      int hd, t0, rows;
+      where(j, s, hd, t0, rows);
+      const float *gs = sG + slot * C, *dgs = sDG + slot * C, *red = sRed + slot * 2;
+      for (int t = lane; t < rows; t += 32) {
+        float x = dgs[t];
+        if (t == rows - 1) x += red[0] * __expf(gs[t]) + red[1];
+        reinterpret_cast<float *>(a.dg)[tok_off(a, s, hd, t0 + t, 1)] = x;
+      }
+      return true;
+    };
+    bool alive = true;
+    for (int i = 0; i < n_local && alive && !abort_flag; ++i) {
+      const int slot = i & 1;
+      if (i >= 2) alive = write_out(i - 2);
+      __syncwarp();
+      if (!alive) break;
+      Seq s;
+      int hd, t0, rows;
+      where(i, s, hd, t0, rows);
+      for (int t = lane; t < C; t += 32) {
+        sG[slot * C + t] = (use_g && t < rows) ? Gbase[tok_off(a, s, hd, t0 + t, 1)] : 0.f;
+        sDG[slot * C + t] = 0.f;
+      }
+      if (lane < 2) sRed[slot * 2 + lane] = 0.f;
+      if (lane == 0) sRows[slot] = rows;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&scal_full[slot]);
+    }
+    for (int j = n_local > 2 ? n_local - 2 : 0; j < n_local && alive && !abort_flag; ++j) {
+      alive = write_out(j);
+      __syncwarp();
+    }
   } else {
     // ------------------------------------------------------------------ epilogue warps 0-15
     const int wq = warp & 3, cq = warp >> 2, g8 = lane >> 2, t4 = lane & 3;
@@ -224,16 +287,6 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       o_lo_[ni] = (uint32_t)(col >> 6) * 8192u + sw128_offset(row_lo, col & 63);
       o_hi_[ni] = (uint32_t)(col >> 6) * 8192u + sw128_offset(row_hi, col & 63);
     }
-    const float *Gbase = reinterpret_cast<const float *>(a.g);
-    // gate of token `tid` of local item i (fetched one item ahead)
-    auto gate_of = [&](int i) -> float {
-      if (!use_g || tid >= C || i >= n_local) return 0.f;
-      int c, hd, n, it;
-      decode(i, c, hd);
-      chunk_of(a, c, n, it);
-      const Seq s = seq_of(a, n);
-      return it * C + tid < s.len ? Gbase[tok_off(a, s, hd, it * C + tid, 1)] : 0.f;
-    };
     // packed 16-bit pair <-> floats in the kernel's element format
     auto ld2 = [&](const unsigned char *ptr) -> float2 {
       return p.ab_fmt ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(ptr))
@@ -243,28 +296,16 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       if (p.ab_fmt) *reinterpret_cast<__nv_bfloat162 *>(ptr) = __floats2bfloat162_rn(x, y);
       else *reinterpret_cast<__half2 *>(ptr) = __floats2half2_rn(x, y);
     };
-    float g_pf = gate_of(0);
-    float pend_val = 0.f, *pend_ptr = nullptr;  // dg of the previous item, not yet written
-    for (int i = 0; i < n_local; ++i) {
+    int n_ragged = 0;
+    for (int i = 0; i < n_local && !abort_flag; ++i) {
       const int ph = i & 1;
-      int c, hd, n, it;
-      decode(i, c, hd);
-      chunk_of(a, c, n, it);
-      const Seq s = seq_of(a, n);
-      const int t0 = it * C, rows = min(C, s.len - t0), last = rows - 1;
-      float *gs = sG + ph * C, *dgs = sDG + ph * C, *red = sRed + ph * 2;
       const int xb = i & 1, xph = (i >> 1) & 1;
+      // gates, row count and the zeroed dg rows / state terms of this item, from the scalar warp
+      if (!mbar_wait(&scal_full[ph], xph)) fail(78);
+      const int rows = sRows[ph], last = rows - 1;
+      float *gs = sG + ph * C, *dgs = sDG + ph * C, *red = sRed + ph * 2;
       unsigned char *sDo = sX1 + xb * X1_BYTES, *sV = sDo + T16, *sDv = sV + T16;
       unsigned char *sQ = sY, *sK = sQ + T16, *sW = sK + T16;
-      if (tid < C) {
-        gs[tid] = g_pf;
-        dgs[tid] = 0.f;
-      }
-      if (tid < 2) red[tid] = 0.f;
-      if (tid == 0) abort_snap[0] = abort_flag;
-      named_barrier(1, ET);
-      if (abort_snap[0]) break;
-      g_pf = gate_of(i + 1);
       const float g_lo = gs[row_lo], g_hi = gs[row_hi], gl = gs[last];
       const float e_lo = use_g ? __expf(g_lo) : 1.f, e_hi = use_g ? __expf(g_hi) : 1.f;
       const float f_lo = use_g ? __expf(fminf(gl - g_lo, 0.f)) : 1.f, f_hi = use_g ? __expf(fminf(gl - g_hi, 0.f)) : 1.f;
@@ -321,10 +362,6 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&e1_done);
-      if (pend_ptr) {
-        *pend_ptr = pend_val;
-        pend_ptr = nullptr;
-      }
       // <h, dh> while the tensor core works; then this warp is done with the state tiles
       if (use_g) {
         if (!mbar_wait(&fullX2, ph)) fail(76);
@@ -345,34 +382,35 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&emptyX2);
-      // ---- E2: finished dq, dk, dw -> dg rows, outputs over the q, k, w tiles
+      // ---- E1b: <k, dk_inter> from the inter-chunk dk before the intra-chunk product lands on it
       if (!mbar_wait(&fullY, ph)) fail(70);
-      if (!mbar_wait(&all_done, ph)) fail(72);
-      fence_after_sync();
-      float dq[4][4], dk[4][4], dw[4][4];
-      {
-        // inter-chunk dk and intra-chunk dk sit in separate columns: <k, dk_inter> first, then their sum
-        float dk2[4][4];
-        tmem_ld_frag<4>(tmem + lane_base + TM_DK + 32 * cq, dk);
-        tmem_ld_frag<4>(tmem + lane_base + TM_DK2 + 32 * cq, dk2);
+      if (use_g) {
+        if (!mbar_wait(&dk_done, ph)) fail(71);
+        fence_after_sync();
+        float dki[4][4];
+        tmem_ld_frag<4>(tmem + lane_base + TM_DK + 32 * cq, dki);
         tmem_ld_wait();
         float dkk = 0.f;
 #pragma unroll
         for (int ni = 0; ni < 4; ++ni) {
-          if (use_g) {
-            const float2 k_lo = ld2(sK + o_lo_[ni]), k_hi = ld2(sK + o_hi_[ni]);
-            if (row_lo < rows) dkk += dk[ni][0] * k_lo.x + dk[ni][1] * k_lo.y;
-            if (row_hi < rows) dkk += dk[ni][2] * k_hi.x + dk[ni][3] * k_hi.y;
-          }
-#pragma unroll
-          for (int r = 0; r < 4; ++r) dk[ni][r] += dk2[ni][r];
+          const int col = colb + 8 * ni;
+          const uint32_t o_lo = o_lo_[ni], o_hi = o_hi_[ni];
+          const float2 k_lo = ld2(sK + o_lo), k_hi = ld2(sK + o_hi);
+          if (row_lo < rows) dkk += dki[ni][0] * k_lo.x + dki[ni][1] * k_lo.y;
+          if (row_hi < rows) dkk += dki[ni][2] * k_hi.x + dki[ni][3] * k_hi.y;
         }
-        if (use_g) {
-          dkk = warp_sum(dkk);
-          if (lane == 0) atomicAdd(&red[1], dkk);
-        }
+        dkk = warp_sum(dkk);
+        if (lane == 0) atomicAdd(&red[1], dkk);
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&e1b_done);
       }
+      // ---- E2: finished dq, dk, dw -> dg rows, outputs over the q, k, w tiles
+      if (!mbar_wait(&all_done, ph)) fail(72);
+      fence_after_sync();
+      float dq[4][4], dk[4][4], dw[4][4];
       tmem_ld_frag<4>(tmem + lane_base + TM_DQ + 32 * cq, dq);
+      tmem_ld_frag<4>(tmem + lane_base + TM_DK + 32 * cq, dk);
       if (USE_DW) tmem_ld_frag<4>(tmem + lane_base + TM_DW + 32 * cq, dw);
       tmem_ld_wait();
       fence_before_sync();
@@ -413,18 +451,19 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
         }
       }
       fence_proxy_async();
-      if (tid == 0) abort_snap[1] = abort_flag;
-      named_barrier(1, ET);  // output tiles and dg rows complete
-      if (abort_snap[1]) break;
-      if (use_g && tid < rows) {
-        // held back until after the next fence.proxy.async: that fence waits for the thread's outstanding global
-        // stores, and it sits on the critical chain of the next item
-        pend_val = dgs[tid];
-        if (tid == last) pend_val += red[0] * __expf(gl) + red[1];
-        pend_ptr = reinterpret_cast<float *>(a.dg) + tok_off(a, s, hd, t0 + tid, 1);
-      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&rows_done[ph]);  // this warp's share of the dg rows and state terms is in shared memory
       if (rows < C) {
-        // ragged last chunk of a sequence: a tile store would write past its end
+        // ragged last chunk of a sequence: a tile store would write past its end, so the epilogue warps copy the valid
+        // rows themselves once every warp has finished its part of the output tiles
+        if (lane == 0) mbar_arrive(&ragged_sync);
+        if (!mbar_wait(&ragged_sync, n_ragged & 1)) fail(79);
+        ++n_ragged;
+        int c, hd, n, it;
+        decode(i, c, hd);
+        chunk_of(a, c, n, it);
+        const Seq s = seq_of(a, n);
+        const int t0 = it * C;
         const size_t ks = tok_stride(a, a.K), off0 = tok_off(a, s, hd, t0, a.K);
         for (int e = tid; e < rows * 16; e += ET) {
           const int r_ = e >> 4, c_ = (e & 15) * 8;
@@ -438,7 +477,6 @@ __global__ void __launch_bounds__(608, 1) tc_dqkwg_kernel(const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&out_ready);  // this warp is done with the Y buffer
     }
-    if (pend_ptr) *pend_ptr = pend_val;
   }
   fence_before_sync();
   __syncthreads();
@@ -469,7 +507,7 @@ template <bool USE_DW> static int launch_tc_dqkwg(const flab_args *a, cudaStream
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = p.n_items < sms ? p.n_items : sms;
-  kern<<<grid, 608, smem, stream>>>(m, p);
+  kern<<<grid, 640, smem, stream>>>(m, p);
   return check_launch("chunk_bwd_dqkwg(tc)");
 }
 

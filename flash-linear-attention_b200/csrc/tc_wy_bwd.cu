@@ -6,11 +6,15 @@
 //   dk = (A_w^T dw) beta + (dA k) beta + (diag(beta) dA)^T k [+ dk of the preceding stage];
 //   dbeta += rowsum((dA k) * k);   dg = rowsum(P) - colsum(P),  P = dA_u e^{b_i-b_j} * (diag(beta) k k^T)
 //   (fla/ops/delta_rule/wy_fast.py:325-433, fla/ops/gated_delta_rule/wy_fast.py:440-562)
-// Persistent kernel, one CTA per SM, work item = (chunk, head).  Nineteen warps:
+// Persistent kernel, one CTA per SM, work item = (chunk, head).  Twenty warps:
 //   warp 16 : TMA producer - k, v, dw, du, dk_in, A_w, A_u of an item (96 KB), two buffers
 //   warp 17 : MMA issuer   - four batches of products per item, accumulators in TMEM (512 columns, re-used)
 //   warp 18 : output       - tile stores of dk and dv, which the epilogue builds over the dw and du tiles
-//   warps 0-15 : epilogue, warp = (TMEM lane quadrant = 16 tokens, column group)
+//   warp 19 : scalars      - beta, gate and row count of the coming item into shared memory, zeroed dbeta / dg rows,
+//                            and the finished dbeta / dg rows of past items out to global memory: every global load,
+//                            global store and index computation per token is kept off the epilogue warps
+//   warps 0-15 : epilogue, warp = (TMEM lane quadrant = 16 tokens, column group); the warps are tied to each other
+//                            only through the mbarriers of the phases, never through a CTA-wide barrier
 // Batches:  B1: dw k^T, A_w^T dw, du v^T, A_u^T du      E1: mask / beta / round -> dA operands; dv; dbeta
 //           B2: dA_w A_w^T, dA_u A_u^T                  E2: round -> operands
 //           B3: A_w^T (.), A_u^T (.)                    E3: sign, mask, decay, sum -> dA, diag(beta) dA
@@ -34,7 +38,7 @@ struct TcWyMaps {
 };
 
 template <bool GATED>
-__global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant__ TcWyMaps m, const TcWyParams p) {
+__global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant__ TcWyMaps m, const TcWyParams p) {
   using namespace tc;
   constexpr uint32_t T16 = 16384, T8 = 8192;
   constexpr uint32_t IN_BYTES = 5 * T16 + 2 * T8;  // one item's tiles
@@ -53,9 +57,10 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
   float *sDB = sG + 2 * C;                             // [2][64] dbeta rows
   float *sDG = sDB + 2 * C;                            // [2][64] dg rows
   __shared__ uint64_t full[2], empty[2], zero_done, b1_done, e1_done, b2_done, e2_done, b3_done, e3_done, b4_done, acc_free, out_ready;
+  __shared__ uint64_t scal_full[2], rows_done[2], ragged_sync;
+  __shared__ int sRows[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
-  __shared__ volatile int abort_snap[2];
 
   const flab_args &a = p.a;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -74,6 +79,11 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
     mbar_init(&b4_done, 1);
     mbar_init(&acc_free, 16);
     mbar_init(&out_ready, 16);
+    for (int j = 0; j < 2; ++j) {
+      mbar_init(&scal_full[j], 1);
+      mbar_init(&rows_done[j], 16);
+    }
+    mbar_init(&ragged_sync, 16);
     abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -223,6 +233,57 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
       }
       tma_store_wait_all();
     }
+  } else if (warp == 19) {
+    // ------------------------------------------------------------------ scalar warp
+    // Item i uses slot i & 1 of sBeta / sG / sDB / sDG / sRows.  Before a slot is handed to item i its previous user
+    // (item i - 2) must be finished with it: the epilogue warps say so on rows_done, and their dbeta / dg rows are
+    // written to global memory from here.
+    float *dbeta_out = reinterpret_cast<float *>(a.dbeta), *dg_out = reinterpret_cast<float *>(a.dg);
+    auto write_out = [&](int j) -> bool {
+      const int slot = j & 1;
+      if (!mbar_wait(&rows_done[slot], (j >> 1) & 1)) {
+        fail(95);
+        return false;
+      }
+      Seq s;
+      int hd, t0, rows;
+      locate(j, s, hd, t0, rows);
+      for (int t = lane; t < rows; t += 32) {
+        const size_t o = tok_off(a, s, hd, t0 + t, 1);
+        dbeta_out[o] = sDB[slot * C + t];
+        if (GATED) dg_out[o] = sDG[slot * C + t];
+      }
+      return true;
+    };
+    bool alive = true;
+    for (int i = 0; i < n_local && alive && !abort_flag; ++i) {
+      const int slot = i & 1;
+      if (i >= 2) alive = write_out(i - 2);
+      __syncwarp();
+      if (!alive) break;
+      Seq s;
+      int hd, t0, rows;
+      locate(i, s, hd, t0, rows);
+      for (int t = lane; t < C; t += 32) {
+        float bt = 0.f, gt = 0.f;
+        if (t < rows) {
+          const size_t o = tok_off(a, s, hd, t0 + t, 1);
+          bt = p.ab_fmt ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.beta)[o]) : __half2float(reinterpret_cast<const __half *>(a.beta)[o]);
+          if (GATED) gt = reinterpret_cast<const float *>(a.g)[o];
+        }
+        sBeta[slot * C + t] = bt;
+        sG[slot * C + t] = gt;
+        sDB[slot * C + t] = 0.f;
+        sDG[slot * C + t] = 0.f;
+      }
+      if (lane == 0) sRows[slot] = rows;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&scal_full[slot]);
+    }
+    for (int j = n_local > 2 ? n_local - 2 : 0; j < n_local && alive && !abort_flag; ++j) {
+      alive = write_out(j);
+      __syncwarp();
+    }
   } else {
     // ------------------------------------------------------------------ epilogue warps 0-15
     const int wq = warp & 3, cq = warp >> 2, g8 = lane >> 2, t4 = lane & 3;
@@ -251,49 +312,12 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
       else *reinterpret_cast<__half2 *>(ptr) = __floats2half2_rn(x, y);
     };
     auto rnd1 = [&](float x) -> float { return p.ab_fmt ? __bfloat162float(__float2bfloat16_rn(x)) : __half2float(__float2half_rn(x)); };
-    // beta and gate of token `tid` of local item i (fetched one item ahead)
-    auto scalars_of = [&](int i, float &bt, float &gt) {
-      bt = 0.f, gt = 0.f;
-      if (tid >= C || i >= n_local) return;
-      Seq s;
-      int hd, t0, rows;
-      locate(i, s, hd, t0, rows);
-      if (tid < rows) {
-        const size_t o = tok_off(a, s, hd, t0 + tid, 1);
-        bt = p.ab_fmt ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.beta)[o]) : __half2float(reinterpret_cast<const __half *>(a.beta)[o]);
-        if (GATED) gt = reinterpret_cast<const float *>(a.g)[o];
-      }
-    };
-    float b_pf, g_pf;
-    scalars_of(0, b_pf, g_pf);
-    // beta, gate and the zeroed dbeta / dg rows of item i live in slot i & 1; they are published by the barrier at
-    // the end of item i - 1 (item 0: the barrier below)
-    auto publish = [&](int slot) {
-      if (tid < C) {
-        sBeta[slot * C + tid] = b_pf;
-        sG[slot * C + tid] = g_pf;
-        sDB[slot * C + tid] = 0.f;
-        sDG[slot * C + tid] = 0.f;
-      }
-    };
-    publish(0);
-    scalars_of(1, b_pf, g_pf);
-    if (tid == 0) abort_snap[0] = abort_flag;
-    named_barrier(1, ET);
-    bool live = !abort_snap[0];
-    long long pend_off = -1;  // dbeta / dg of the previous item, not yet written
-    float pend_db = 0.f, pend_dg = 0.f;
-    auto flush_pending = [&]() {
-      if (pend_off < 0) return;
-      reinterpret_cast<float *>(a.dbeta)[pend_off] = pend_db;
-      if (GATED) reinterpret_cast<float *>(a.dg)[pend_off] = pend_dg;
-      pend_off = -1;
-    };
-    for (int i = 0; i < n_local && live; ++i) {
+    int n_ragged = 0;
+    for (int i = 0; i < n_local && !abort_flag; ++i) {
       const int b = i & 1, ph = (i >> 1) & 1, ip = i & 1;
-      Seq s;
-      int hd, t0, rows;
-      locate(i, s, hd, t0, rows);
+      // beta, gate, row count and the zeroed dbeta / dg rows of this item, from the scalar warp
+      if (!mbar_wait(&scal_full[ip], ph)) fail(96);
+      const int rows = sRows[ip];
       unsigned char *in = sIn + b * IN_BYTES;
       unsigned char *tK = in, *tV = in + T16, *tDW = in + 2 * T16, *tDU = in + 3 * T16, *tDKI = in + 4 * T16;
       float *bs = sBeta + ip * C, *gs = sG + ip * C, *dbs = sDB + ip * C, *dgs = sDG + ip * C;
@@ -341,7 +365,6 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&e1_done);
-      flush_pending();
       // ---- E2: first product of the transform, rounded, becomes the operand of the second
       if (!mbar_wait(&b2_done, ip)) fail(91);
       fence_after_sync();
@@ -482,20 +505,17 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
         }
       }
       fence_proxy_async();
-      publish(ip ^ 1);  // scalars of the next item
-      if (tid == 0) abort_snap[ip] = abort_flag;
-      named_barrier(1, ET);  // dk, dv tiles and the dbeta / dg rows are complete
-      if (abort_snap[ip]) live = false;
-      scalars_of(i + 2, b_pf, g_pf);
-      if (tid < rows) {
-        // held back until after the next fence.proxy.async (it waits for the thread's outstanding global stores
-        // and sits on the critical chain of the next item)
-        pend_off = (long long)tok_off(a, s, hd, t0 + tid, 1);
-        pend_db = dbs[tid];
-        if (GATED) pend_dg = dgs[tid];
-      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&rows_done[ip]);  // this warp's share of the dbeta / dg rows is in shared memory
       if (rows < C) {
-        // ragged last chunk of a sequence: a tile store would write past its end
+        // ragged last chunk of a sequence: a tile store would write past its end, so the epilogue warps copy the valid
+        // rows themselves once every warp has finished its part of the dk / dv tiles
+        if (lane == 0) mbar_arrive(&ragged_sync);
+        if (!mbar_wait(&ragged_sync, n_ragged & 1)) fail(97);
+        ++n_ragged;
+        Seq s;
+        int hd, t0, rows_;
+        locate(i, s, hd, t0, rows_);
         const size_t ks = tok_stride(a, a.K), vs = tok_stride(a, a.V);
         const size_t offk = tok_off(a, s, hd, t0, a.K), offv = tok_off(a, s, hd, t0, a.V);
         for (int e = tid; e < rows * 16; e += ET) {
@@ -508,7 +528,6 @@ __global__ void __launch_bounds__(608, 1) tc_wy_bwd_kernel(const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&out_ready);  // this warp is done with the item's tiles
     }
-    flush_pending();
   }
   fence_before_sync();
   __syncthreads();
@@ -537,7 +556,7 @@ template <bool GATED> static int launch_tc_wy_bwd(const flab_args *a, cudaStream
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = p.n_items < sms ? p.n_items : sms;
-  kern<<<grid, 608, smem, stream>>>(m, p);
+  kern<<<grid, 640, smem, stream>>>(m, p);
   return check_launch("wy_bwd(tc)");
 }
 

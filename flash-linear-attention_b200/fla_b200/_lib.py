@@ -21,6 +21,7 @@ _DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 F_REVERSE = 1 << 0
 F_BETA_VECTOR = 1 << 1
 F_INPLACE_STATE = 1 << 2
+F_DESCENDING = 1 << 3
 F_STATE_ONLY = 1 << 4
 F_TRANSPOSE = 1 << 5
 

@@ -43,6 +43,7 @@ class GatedDeltaRuleDecoder:
             self.state.copy_(initial_state)
         self._geo = Geometry(self.k, self.v, None, False)
         self._graph = None
+        self._graphs, self._steps = None, 0
         if use_graph:
             # capture on a side stream; the launch itself neither allocates nor synchronises
             keep = self.state.clone()
@@ -52,15 +53,28 @@ class GatedDeltaRuleDecoder:
                 self._launch()  # warm-up outside capture (module load, attribute setting)
             torch.cuda.current_stream(dev).wait_stream(side)
             self.state.copy_(keep)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self._launch()
-            self._graph = graph
+            # two captures of the same step, one per direction of the walk over the state tiles: replays alternate, so a step
+            # starts on the tiles its predecessor wrote last (still in L2)
+            graphs = []
+            for descending in (False, True):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._launch(descending)
+                graphs.append(graph)
+            self._graph, self._graphs = graphs[0], graphs
             self.state.copy_(keep)  # capture does not run the kernel, but keep the contract obvious
 
-    def _launch(self):
-        _lib.call("flab_recurrent_delta_fwd", self.q, **self._geo.kw(), scale=self.scale, flags=_lib.F_INPLACE_STATE, q=self.q, k=self.k,
+    def _launch(self, descending: bool = False):
+        flags = _lib.F_INPLACE_STATE | (_lib.F_DESCENDING if descending else 0)
+        _lib.call("flab_recurrent_delta_fwd", self.q, **self._geo.kw(), scale=self.scale, flags=flags, q=self.q, k=self.k,
                   v=self.v, beta=self.beta, g=self.g, h0=self.state, o=self.o, u=None, ht=self.state)
+
+    def _run(self):
+        self._steps += 1
+        if self._graphs is not None:
+            self._graphs[self._steps & 1].replay()
+        else:
+            self._launch(bool(self._steps & 1))
 
     @torch.no_grad()
     def step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: Optional[torch.Tensor] = None,
@@ -79,17 +93,11 @@ class GatedDeltaRuleDecoder:
             self.beta.copy_(beta.view_as(self.beta))
         else:
             self.beta.fill_(1)
-        if self._graph is not None:
-            self._graph.replay()
-        else:
-            self._launch()
+        self._run()
         return self.o
 
     @torch.no_grad()
     def replay(self) -> torch.Tensor:
         """Run the step on whatever the input buffers (`.q .k .v .g .beta`) hold: for callers that write them in place."""
-        if self._graph is not None:
-            self._graph.replay()
-        else:
-            self._launch()
+        self._run()
         return self.o

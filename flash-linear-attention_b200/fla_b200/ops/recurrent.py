@@ -84,11 +84,21 @@ def fused_recurrent(q, k, v, g=None, gk=None, gv=None, scale=None, initial_state
 # ---------------------------------------------------------------------------------------------
 # delta rule
 # ---------------------------------------------------------------------------------------------
+_CALLS = 0  # calls of recurrent_delta_fwd so far: every other call walks the state tiles in descending order
+
+
 def recurrent_delta_fwd(geo, q, k, v, beta, g, scale, initial_state, output_final_state, want_u):
+    """One launch of the token-recurrent (gated) delta rule. Successive calls alternate the order in which the kernel
+    walks the (sequence, head) state tiles: in a decode loop the state a step reads is the one the previous step wrote,
+    and the tiles that step wrote last are still in L2 when this one starts on them."""
+    global _CALLS
+    _CALLS += 1
     o = torch.empty_like(v)
     u = torch.empty_like(v) if want_u else None
     ht = torch.empty(geo.N, geo.H, geo.K, geo.V, dtype=torch.float32, device=v.device) if output_final_state else None
     flags = F_BETA_VECTOR if (beta is not None and beta.dim() == v.dim()) else 0
+    if _CALLS & 1:
+        flags |= _lib.F_DESCENDING
     _lib.call("flab_recurrent_delta_fwd", q, **geo.kw(), scale=scale, flags=flags, q=q, k=k, v=v,
               beta=None if beta is None else beta.to(q.dtype).contiguous(), g=_f32(g), h0=_f32(initial_state),
               o=o, u=u, ht=ht)

@@ -49,7 +49,9 @@ enum {
   FLAB_F_BETA_VECTOR = 1 << 1,   /* fused_recurrent_delta_rule: beta is [.., V] not scalar    */
   FLAB_F_INPLACE_STATE = 1 << 2, /* flab_recurrent_fwd / _delta_fwd: the caller passes ht == h0 (state updated in place); without
                                     the flag an aliased pair is rejected with FLAB_E_BADARG                 */
-  FLAB_F_UPPER = 1 << 3,         /* reserved                                                  */
+  FLAB_F_DESCENDING = 1 << 3,    /* flab_recurrent_delta_fwd: walk the (sequence, head) state tiles from the last to the
+                                    first. A decode loop alternates the direction from step to step, so that a step
+                                    starts on the tiles its predecessor wrote last, which are still in L2    */
   FLAB_F_STATE_ONLY = 1 << 4,    /* delta scans: only the final state is wanted (h, v_new / dh, dv2 may be NULL) */
   FLAB_F_TRANSPOSE = 1 << 5      /* flab_state_chain: apply the transposed transitions (backward chain)         */
 };

@@ -15,8 +15,8 @@ sample of its units against the CPU oracle on identical bits:
 
 Bars: relative L2 error (RMS(ref - out) / RMS(ref), the metric of the reference's tests/ops/utils.py:1-14)
 <= 5e-3 for outputs, states and every gradient except those in LOOSE (d beta and d g of the gated rule, which pass
-through the longest chains of bf16 intermediates: 1e-2, half the reference's own bar; the gradients of the plain delta
-rule, whose state never decays: the reference's 8e-3). Every value is printed.
+through the longest chains of bf16 intermediates: 1e-2, half the reference's own bar; d k of the plain delta rule,
+whose state never decays: 6e-3). Every value is printed.
 """
 import pytest
 import torch
@@ -31,10 +31,9 @@ BAR = 5e-3
 # per-gradient bars at these shapes; everything not listed is held to BAR. Measured on the B200 at these shapes
 # (bf16): o, ht, dq, dk, dv, dh0 of the gated rule 1.5e-3 .. 3.8e-3; its dg up to 5.8e-3 and dbeta up to 6.3e-3 (the
 # reference asserts 2e-2 for both, tests/ops/test_gated_delta.py:282-294). The plain delta rule has no decay, so the
-# rounding of 4096 tokens of bf16 intermediates accumulates in the state: dk 5.05e-3 (the reference asserts 8e-3,
-# tests/ops/test_delta.py:74-93).
-LOOSE = {"gated_delta": {"dbeta": 1e-2, "dg": 1e-2},
-         "delta": {"dbeta": 1e-2, "dq": 8e-3, "dk": 8e-3, "dv": 8e-3, "dh0": 8e-3}}
+# rounding of 4096 tokens of bf16 intermediates accumulates in the state: o 4.1e-3, dq 4.4e-3, dk 5.1e-3 (bar 6e-3; the
+# reference asserts 8e-3, tests/ops/test_delta.py:74-93).
+LOOSE = {"gated_delta": {"dbeta": 1e-2, "dg": 1e-2}, "delta": {"dk": 6e-3}}
 
 
 def ops():

@@ -260,9 +260,13 @@ def _gdelta_ref(i, scale=None, offsets=None, head_first=False, **kw):
                                    output_final_state=True, offsets=offsets, head_first=head_first)
 
 
-# the reference's own bars for these two families (tests/ops/test_delta.py:74-93,
-# tests/ops/test_gated_delta.py:282-294): o/ht 5e-3, dq/dk/dv/dh0 7e-3..8e-3, dbeta/dg 2e-2
-DELTA_TOL = {"dq": 8e-3, "dk": 8e-3, "dv": 8e-3, "dh0": 8e-3, "dbeta": 2e-2, "dg": 2e-2}
+# Bars of the two delta-rule families against the fp32 oracle: 5e-3 for o, ht, dq, dv, dh0 like every other op; the
+# three gradients that pass through the longest chains of 16-bit intermediates (A, w, u, v_new, the inverse) get
+# dk 6e-3, dbeta and dg 1e-2. Measured over all cases of this file on the B200: dq <= 4.4e-3, dk <= 5.2e-3,
+# dv <= 3.7e-3, dh0 <= 3.7e-3, dg <= 5.8e-3, dbeta <= 6.3e-3. The reference's own bars for these quantities
+# (tests/ops/test_delta.py:74-93, tests/ops/test_gated_delta.py:282-294) are 7e-3..8e-3 and 2e-2; its Triton kernels
+# sit at the same distance from the oracle (bench.py prints ours-vs-Triton on the same bf16 inputs: <= 4e-3).
+DELTA_TOL = {"dk": 6e-3, "dbeta": 1e-2, "dg": 1e-2}
 
 
 @pytest.mark.parametrize("B,T,H,K,V,dtype,head_first", [
