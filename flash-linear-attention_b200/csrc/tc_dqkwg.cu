@@ -16,7 +16,7 @@
 //   warp 19 : scalars    - gates and row count of the coming item into shared memory, zeroed dg rows, and the finished
 //                          dg rows of past items out to global memory: the epilogue warps touch no global memory per
 //                          token and meet each other only through the mbarriers of the phases
-// The row factors of the inter-chunk terms are applied to the A operands in shared memory (do, v, dv are
+// The row factors of the inter-chunk terms of dq and dk are applied to the A operands in shared memory (do and v are
 // rescaled in place after ds has been formed from the unscaled tiles), so that inter- and intra-chunk parts
 // add up in one accumulator and TMEM holds ds | dq | dk | dw = 448 columns.  dq, dk, dw are written over the
 // q, k, w tiles (each element by the thread that read it for the dg dot) and leave through tile stores.
@@ -53,8 +53,10 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
   unsigned char *sY = sDH + T32;                   // [q | k | w]
   unsigned char *sDS = sY + Y_BYTES;               // [64][128 B]
   float *sG = reinterpret_cast<float *>(sDS + 8192);  // [2][64] gates
-  float *sDG = sG + 2 * C;                            // [2][64] dg rows
-  float *sRed = sDG + 2 * C;                          // [2][2]  <h, dh>, <k, dk_inter>
+  // partial sums of the epilogue warps: plain stores into a slot per (item parity, column group or warp), no atomics;
+  // the scalar warp adds them up when it writes the rows out
+  float *sDG = sG + 2 * C;                            // [2][4][64] dg rows per column group
+  float *sRed = sDG + 8 * C;                          // [2][2][16] <h, dh>, <k, dk_inter> per epilogue warp
   __shared__ uint64_t fullX1[2], emptyX1[2], fullX2, emptyX2, fullY, emptyY, ds_done, e1_done, dk_done, e1b_done, all_done, acc_free, out_ready;
   __shared__ uint64_t scal_full[2], rows_done[2], ragged_sync;
   __shared__ int sRows[2];
@@ -243,10 +245,13 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
       Seq s;
       int hd, t0, rows;
       where(j, s, hd, t0, rows);
-      const float *gs = sG + slot * C, *dgs = sDG + slot * C, *red = sRed + slot * 2;
+      const float *gs = sG + slot * C, *dgs = sDG + slot * 4 * C, *red = sRed + slot * 32;
+      float r0 = lane < 16 ? red[lane] : 0.f, r1 = lane < 16 ? red[16 + lane] : 0.f;  // the 16 warps' shares of the two state terms
+      r0 = warp_sum(r0);
+      r1 = warp_sum(r1);
       for (int t = lane; t < rows; t += 32) {
-        float x = dgs[t];
-        if (t == rows - 1) x += red[0] * __expf(gs[t]) + red[1];
+        float x = (dgs[t] + dgs[C + t]) + (dgs[2 * C + t] + dgs[3 * C + t]);
+        if (t == rows - 1) x += r0 * __expf(gs[t]) + r1;
         reinterpret_cast<float *>(a.dg)[tok_off(a, s, hd, t0 + t, 1)] = x;
       }
       return true;
@@ -262,9 +267,7 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
       where(i, s, hd, t0, rows);
       for (int t = lane; t < C; t += 32) {
         sG[slot * C + t] = (use_g && t < rows) ? Gbase[tok_off(a, s, hd, t0 + t, 1)] : 0.f;
-        sDG[slot * C + t] = 0.f;
       }
-      if (lane < 2) sRed[slot * 2 + lane] = 0.f;
       if (lane == 0) sRows[slot] = rows;
       __syncwarp();
       if (lane == 0) mbar_arrive(&scal_full[slot]);
@@ -303,7 +306,7 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
       // gates, row count and the zeroed dg rows / state terms of this item, from the scalar warp
       if (!mbar_wait(&scal_full[ph], xph)) fail(78);
       const int rows = sRows[ph], last = rows - 1;
-      float *gs = sG + ph * C, *dgs = sDG + ph * C, *red = sRed + ph * 2;
+      float *gs = sG + ph * C, *dgs = sDG + (ph * 4 + cq) * C, *red = sRed + ph * 32;
       unsigned char *sDo = sX1 + xb * X1_BYTES, *sV = sDo + T16, *sDv = sV + T16;
       unsigned char *sQ = sY, *sK = sQ + T16, *sW = sK + T16;
       const float g_lo = gs[row_lo], g_hi = gs[row_hi], gl = gs[last];
@@ -313,13 +316,14 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
       if (!mbar_wait(&fullX1[xb], xph)) fail(68);
       if (!mbar_wait(&ds_done, ph)) fail(69);
       fence_after_sync();
-      if (cq < 2) {
-        float sc[4][4];
-        tmem_ld_frag<4>(tmem + lane_base + TM_DS + 32 * cq, sc);
+      {
+        // ds: all sixteen warps, 16 columns each
+        float sc[2][4];
+        tmem_ld_frag<2>(tmem + lane_base + TM_DS + 16 * cq, sc);
         tmem_ld_wait();
 #pragma unroll
-        for (int ni = 0; ni < 4; ++ni) {
-          const int col = colb + 8 * ni;
+        for (int ni = 0; ni < 2; ++ni) {
+          const int col = 16 * cq + 8 * ni + 2 * t4;
           const float gc0 = gs[col], gc1 = gs[col + 1];
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
@@ -334,29 +338,28 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
         }
       }
       {
-        // do' = scale e^{b} do; v' = e^{b_L-b} v; dv' = -e^{b} dv (all in place; ds was formed from the unscaled tiles)
-        const float sd_lo = e_lo * a.scale, sd_hi = e_hi * a.scale;
+        // do' = scale e^{b} do and v' = e^{b_L-b} v, in place (ds was formed from the unscaled tiles); a row factor does
+        // not care about the swizzle, so every thread rescales two whole 16-byte pieces of one token row per tile
+        // (the factor of dw, -e^{b}, is applied to the fp32 accumulator at the end of the item instead)
+        const int pr = tid >> 3;  // token row of this thread's pieces (one in each 64-column box)
+        const float gp = gs[pr];
+        const float sd = (use_g ? __expf(gp) : 1.f) * a.scale, fv = use_g ? __expf(fminf(gl - gp, 0.f)) : 1.f;
+        auto rescale = [&](unsigned char *tile, float f) {
 #pragma unroll
-        for (int ni = 0; ni < 4; ++ni) {
-          const int col = colb + 8 * ni;
+          for (int bx = 0; bx < 2; ++bx) {
+            int4 *ptr = reinterpret_cast<int4 *>(tile + bx * 8192 + tid * 16);
+            int4 x = *ptr;
+            uint32_t *u = reinterpret_cast<uint32_t *>(&x);
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            const uint32_t off = hf ? o_hi_[ni] : o_lo_[ni];
-            float2 x = ld2(sDo + off);
-            const float sd = hf ? sd_hi : sd_lo;
-            st2(sDo + off, x.x * sd, x.y * sd);
-            if (use_g) {
-              const float fv = hf ? f_hi : f_lo;
-              x = ld2(sV + off);
-              st2(sV + off, x.x * fv, x.y * fv);
+            for (int e = 0; e < 4; ++e) {
+              const float2 f2 = ld2(reinterpret_cast<const unsigned char *>(&u[e]));
+              st2(reinterpret_cast<unsigned char *>(&u[e]), f2.x * f, f2.y * f);
             }
-            if (USE_DW) {
-              const float fd = hf ? -e_hi : -e_lo;
-              x = ld2(sDv + off);
-              st2(sDv + off, x.x * fd, x.y * fd);
-            }
+            *ptr = x;
           }
-        }
+        };
+        rescale(sDo, sd);
+        if (use_g) rescale(sV, fv);
       }
       fence_proxy_async();
       fence_before_sync();
@@ -378,7 +381,7 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
           }
         }
         hd_ = warp_sum(hd_);
-        if (lane == 0) atomicAdd(&red[0], hd_);
+        if (lane == 0) red[warp] = hd_;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&emptyX2);
@@ -400,7 +403,7 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
           if (row_hi < rows) dkk += dki[ni][2] * k_hi.x + dki[ni][3] * k_hi.y;
         }
         dkk = warp_sum(dkk);
-        if (lane == 0) atomicAdd(&red[1], dkk);
+        if (lane == 0) red[16 + warp] = dkk;
         fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&e1b_done);
@@ -431,6 +434,8 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
         st2(sK + o_lo, dk[ni][0], dk[ni][1]);
         st2(sK + o_hi, dk[ni][2], dk[ni][3]);
         if (USE_DW) {
+          // dw = -e^{b} (dv h^T): the row factor goes onto the fp32 product here (dv itself was left as loaded)
+          dw[ni][0] *= -e_lo, dw[ni][1] *= -e_lo, dw[ni][2] *= -e_hi, dw[ni][3] *= -e_hi;
           if (use_g) {
             const float2 w_lo = ld2(sW + o_lo), w_hi = ld2(sW + o_hi);
             dg_lo += dw[ni][0] * w_lo.x + dw[ni][1] * w_lo.y;
@@ -446,8 +451,8 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
         dg_hi += __shfl_xor_sync(0xffffffffu, dg_hi, 1);
         dg_hi += __shfl_xor_sync(0xffffffffu, dg_hi, 2);
         if (t4 == 0) {
-          atomicAdd(&dgs[row_lo], dg_lo);
-          atomicAdd(&dgs[row_hi], dg_hi);
+          dgs[row_lo] = dg_lo;
+          dgs[row_hi] = dg_hi;
         }
       }
       fence_proxy_async();
@@ -500,7 +505,7 @@ template <bool USE_DW> static int launch_tc_dqkwg(const flab_args *a, cudaStream
   p.a = *a;
   p.n_items = a->NT * a->H;
   p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
-  const size_t smem = 1024 + (size_t)(USE_DW ? 9 : 6) * 16384 + 2 * 32768 + 8192 + (4 * C + 4) * sizeof(float);
+  const size_t smem = 1024 + (size_t)(USE_DW ? 9 : 6) * 16384 + 2 * 32768 + 8192 + (10 * C + 64) * sizeof(float);
   auto kern = tc_dqkwg_kernel<USE_DW>;
   if (int e = set_smem(kern, smem)) return e;
   int dev = 0, sms = 148;

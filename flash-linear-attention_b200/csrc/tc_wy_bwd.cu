@@ -54,8 +54,11 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
   unsigned char *sM1 = sM0 + T8;                  // [64][128 B]: dA_u operand, then its first product, then diag(beta) dA
   float *sBeta = reinterpret_cast<float *>(sM1 + T8);  // [2][64]
   float *sG = sBeta + 2 * C;                           // [2][64]
-  float *sDB = sG + 2 * C;                             // [2][64] dbeta rows
-  float *sDG = sDB + 2 * C;                            // [2][64] dg rows
+  // partial sums of the epilogue warps, one slot per (item parity, warp column group or lane quadrant, token): plain
+  // stores, no atomics, every entry rewritten by exactly one lane per item; the scalar warp adds the four partials
+  float *sDB = sG + 2 * C;                             // [2][4][64] dbeta rows per column group
+  float *sDG = sDB + 8 * C;                            // [2][4][64] dg row sums per column group
+  float *sDGC = sDG + 8 * C;                           // [2][4][64] dg column sums per lane quadrant
   __shared__ uint64_t full[2], empty[2], zero_done, b1_done, e1_done, b2_done, e2_done, b3_done, e3_done, b4_done, acc_free, out_ready;
   __shared__ uint64_t scal_full[2], rows_done[2], ragged_sync;
   __shared__ int sRows[2];
@@ -248,10 +251,11 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       Seq s;
       int hd, t0, rows;
       locate(j, s, hd, t0, rows);
+      const float *db = sDB + slot * 4 * C, *dgr = sDG + slot * 4 * C, *dgc = sDGC + slot * 4 * C;
       for (int t = lane; t < rows; t += 32) {
         const size_t o = tok_off(a, s, hd, t0 + t, 1);
-        dbeta_out[o] = sDB[slot * C + t];
-        if (GATED) dg_out[o] = sDG[slot * C + t];
+        dbeta_out[o] = (db[t] + db[C + t]) + (db[2 * C + t] + db[3 * C + t]);
+        if (GATED) dg_out[o] = ((dgr[t] + dgr[C + t]) + (dgr[2 * C + t] + dgr[3 * C + t])) - ((dgc[t] + dgc[C + t]) + (dgc[2 * C + t] + dgc[3 * C + t]));
       }
       return true;
     };
@@ -273,8 +277,6 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
         }
         sBeta[slot * C + t] = bt;
         sG[slot * C + t] = gt;
-        sDB[slot * C + t] = 0.f;
-        sDG[slot * C + t] = 0.f;
       }
       if (lane == 0) sRows[slot] = rows;
       __syncwarp();
@@ -320,7 +322,8 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       const int rows = sRows[ip];
       unsigned char *in = sIn + b * IN_BYTES;
       unsigned char *tK = in, *tV = in + T16, *tDW = in + 2 * T16, *tDU = in + 3 * T16, *tDKI = in + 4 * T16;
-      float *bs = sBeta + ip * C, *gs = sG + ip * C, *dbs = sDB + ip * C, *dgs = sDG + ip * C;
+      float *bs = sBeta + ip * C, *gs = sG + ip * C;
+      float *dbs = sDB + (ip * 4 + cq) * C, *dgs = sDG + (ip * 4 + cq) * C, *dgc = sDGC + (ip * 4 + wq) * C;
       const float b_lo = bs[row_lo], b_hi = bs[row_hi], g_lo = gs[row_lo], g_hi = gs[row_hi];
       if (!mbar_wait(&full[b], ph)) fail(89);
       if (rows < C) {
@@ -471,8 +474,8 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
         db_hi += __shfl_xor_sync(0xffffffffu, db_hi, 1);
         db_hi += __shfl_xor_sync(0xffffffffu, db_hi, 2);
         if (t4 == 0) {
-          atomicAdd(&dbs[row_lo], db_lo);
-          atomicAdd(&dbs[row_hi], db_hi);
+          dbs[row_lo] = db_lo;
+          dbs[row_hi] = db_hi;
         }
         if (GATED) {
           float r_lo = 0.f, r_hi = 0.f;
@@ -490,8 +493,8 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
             c1 += __shfl_xor_sync(0xffffffffu, c1, 8);
             c1 += __shfl_xor_sync(0xffffffffu, c1, 16);
             if (g8 == 0) {
-              atomicAdd(&dgs[c64 + 8 * ni], -c0);
-              atomicAdd(&dgs[c64 + 8 * ni + 1], -c1);
+              dgc[c64 + 8 * ni] = c0;
+              dgc[c64 + 8 * ni + 1] = c1;
             }
           }
           r_lo += __shfl_xor_sync(0xffffffffu, r_lo, 1);
@@ -499,8 +502,8 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
           r_hi += __shfl_xor_sync(0xffffffffu, r_hi, 1);
           r_hi += __shfl_xor_sync(0xffffffffu, r_hi, 2);
           if (t4 == 0) {
-            atomicAdd(&dgs[row_lo], r_lo);
-            atomicAdd(&dgs[row_hi], r_hi);
+            dgs[row_lo] = r_lo;
+            dgs[row_hi] = r_hi;
           }
         }
       }
@@ -549,7 +552,7 @@ template <bool GATED> static int launch_tc_wy_bwd(const flab_args *a, cudaStream
   p.a = *a;
   p.n_items = a->NT * a->H;
   p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
-  const size_t smem = 1024 + 2 * (size_t)(5 * 16384 + 2 * 8192) + 2 * 8192 + 8 * C * sizeof(float);
+  const size_t smem = 1024 + 2 * (size_t)(5 * 16384 + 2 * 8192) + 2 * 8192 + 28 * C * sizeof(float);
   auto kern = tc_wy_bwd_kernel<GATED>;
   if (int e = set_smem(kern, smem)) return e;
   int dev = 0, sms = 148;
