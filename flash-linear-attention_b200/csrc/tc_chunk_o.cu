@@ -3,12 +3,18 @@
 //   bwd_dv   : dv = (k dh) * e^{b_L-b_j} + triu(k q^T * e^{b_i-b_j}) * scale do  (fla/ops/common/chunk_o.py:289-364)
 //   dv_local : second term of bwd_dv only                                         (fla/ops/common/chunk_o.py:379-441)
 //
-// Persistent kernel, one CTA per SM, work item = (chunk, head, 128-wide V tile).  Eighteen warps:
+// Persistent kernel, one CTA per SM, work item = (chunk, head, 128-wide V tile).  Twenty warps:
 //   warp 16 : TMA producer  - streams the item's tiles (x1, x2, y, state) into a ring of stages
 //   warp 17 : MMA issuer    - S = x1 x2^T and O = x1 state into TMEM, later O = P y
 //   warps 0-7 / 8-15: two epilogue groups working on even / odd items (ping-pong); inside a group
 //                     warp = (TMEM lane quadrant = 16 token rows, column half)
 //                           - S -> mask / decay -> P (bf16, swizzled shared memory); O -> gate -> out
+//   warp 18 : scalars       - gates and row count of the coming items into a ring of four shared-memory slots, so that no
+//                             epilogue warp ever waits for a global load
+//   warp 19 : output       - lanes 0 and 1, one per group: tile store of the group's finished output tile, then the
+//                             tile goes back to the group
+// The epilogue warps meet each other only through the mbarriers of the phases (one arrival per warp), never through a
+// barrier of the group.
 // The epilogue arithmetic (one exponential per score element, packing, swizzled stores) is what
 // bounds the kernel, hence 16 epilogue warps for one MMA-issuing thread.
 // TMEM holds two stages of [S: 64 columns | O: 128 columns] (M = 64 rows = lanes 0-15 of each warp's
@@ -33,7 +39,7 @@ struct TcOParams {
 };
 
 template <int KB /*K/64*/, int VB /*BV/64*/, int MODE, int NS /*smem stages*/>
-__global__ void __launch_bounds__(576, 1)
+__global__ void __launch_bounds__(640, 1)
 tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_constant__ CUtensorMap mapX2,
                   const __grid_constant__ CUtensorMap mapY, const __grid_constant__ CUtensorMap mapH,
                   const __grid_constant__ CUtensorMap mapOut, const TcOParams p) {
@@ -49,11 +55,12 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
   unsigned char *sStage = base;                         // [NS][STAGE_BYTES]
   unsigned char *sP = sStage + NS * STAGE_BYTES;         // [2][8192] score tiles (swizzled K-major)
   unsigned char *sOutAll = sP + 2 * 8192;                   // [2][VB][64][128 B] output tiles (swizzled, source of the tile store)
-  float *sG = reinterpret_cast<float *>(sOutAll + 2 * Y_BYTES);  // [2][64]
+  float *sG = reinterpret_cast<float *>(sOutAll + 2 * Y_BYTES);  // [4][64]: gates of item i in slot i & 3
   __shared__ uint64_t full[NS], empty[NS], s_done[2], p_ready[2], o_done[2], t_free[2];
+  __shared__ uint64_t gates_full[4], gates_free[4], out_ready[2], out_free[2], copy_done[2];
+  __shared__ int sRows[4];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
-  __shared__ volatile int abort_snap[2];
 
   const flab_args &a = p.a;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -64,9 +71,16 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_done[i], 1);
-      mbar_init(&p_ready[i], 256);
+      mbar_init(&p_ready[i], 8);
       mbar_init(&o_done[i], 1);
-      mbar_init(&t_free[i], 256);
+      mbar_init(&t_free[i], 8);
+      mbar_init(&out_ready[i], 8);
+      mbar_init(&out_free[i], 1);
+      mbar_init(&copy_done[i], 8);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&gates_full[i], 1);
+      mbar_init(&gates_free[i], 8);
     }
     abort_flag = 0;
     fence_barrier_init();
@@ -154,6 +168,50 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
         umma_commit(&empty[st]);
       }
     }
+  } else if (warp == 18) {
+    // ------------------------------------------------------------------ scalar warp
+    for (int i = 0; i < n_local && !abort_flag; ++i) {
+      const int slot = i & 3;
+      if (i >= 4 && !mbar_wait(&gates_free[slot], ((i - 4) >> 2) & 1)) { fail(9); break; }  // item i - 4 has read the slot
+      int c, hd, vt, n, it;
+      decode(blockIdx.x + i * gridDim.x, c, hd, vt);
+      chunk_of(a, c, n, it);
+      const Seq s = seq_of(a, n);
+      const int t0 = it * C, rows = min(C, s.len - t0);
+      for (int t = lane; t < C; t += 32)
+        sG[slot * C + t] = (use_g && t < rows) ? reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + t, 1)] : 0.f;
+      if (lane == 0) sRows[slot] = rows;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&gates_full[slot]);
+    }
+  } else if (warp == 19) {
+    // ------------------------------------------------------------------ output warp (one lane per group)
+    if (lane < 2) {
+      const int g = lane;
+      int n_ragged = 0;
+      for (int i = g; i < n_local && !abort_flag; i += 2) {
+        const int k = i >> 1;
+        int c, hd, vt, n, it;
+        decode(blockIdx.x + i * gridDim.x, c, hd, vt);
+        chunk_of(a, c, n, it);
+        const Seq s = seq_of(a, n);
+        const int t0 = it * C, rows = min(C, s.len - t0);
+        if (!mbar_wait(&out_ready[g], k & 1)) { fail(10); break; }
+        if (rows == C) {  // one tile store per 64-column box
+          unsigned char *sOut = sOutAll + g * Y_BYTES;
+          const int tt = s.bos + t0, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
+#pragma unroll
+          for (int j = 0; j < VB; ++j) tma_store_4d(&mapOut, sOut + j * 8192, vt * BV + 64 * j, c1, c2, s.b);
+          tma_store_commit();
+          tma_store_wait_read();
+        } else {  // a ragged chunk is copied out by the epilogue warps themselves
+          if (!mbar_wait(&copy_done[g], n_ragged & 1)) { fail(11); break; }
+          ++n_ragged;
+        }
+        mbar_arrive(&out_free[g]);
+      }
+      tma_store_wait_all();
+    }
   } else {
     // ------------------------------------------------------------------ epilogue groups (warps 0-7, 8-15)
     const int grp = warp >> 3, gw = warp & 7, wq = gw & 3, chh = gw >> 2, etid = tid & 255;
@@ -163,18 +221,13 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
     constexpr int NIO = 4 * VB;  // accumulator n-tiles of this warp's half of the O columns
     unsigned char *sOut = sOutAll + grp * Y_BYTES;
     const int row_lo = m0 + g8, row_hi = row_lo + 8;
-    for (int i = grp; i < n_local; i += 2) {
-      const int st = grp, ph = (i >> 1) & 1;
-      int c, hd, vt, n, it;
-      decode(blockIdx.x + i * gridDim.x, c, hd, vt);
-      chunk_of(a, c, n, it);
-      const Seq s = seq_of(a, n);
-      const int t0 = it * C, rows = min(C, s.len - t0), last = rows - 1;
-      float *gs = sG + st * C;
-      if (etid < C) gs[etid] = (use_g && etid < rows) ? reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + etid, 1)] : 0.f;
-      if (etid == 0) abort_snap[grp] = abort_flag;  // one thread samples the flag so that the whole group leaves together
-      named_barrier(1 + grp, 256);
-      if (abort_snap[grp]) break;
+    int n_ragged = 0;
+    for (int i = grp; i < n_local && !abort_flag; i += 2) {
+      const int st = grp, ph = (i >> 1) & 1, k = i >> 1, slot = i & 3;
+      // gates and row count of this item, from the scalar warp
+      if (!mbar_wait(&gates_full[slot], (i >> 2) & 1)) { fail(7); break; }
+      const int rows = sRows[slot], last = rows - 1;
+      float *gs = sG + slot * C;
       if (!mbar_wait(&s_done[st], ph)) { fail(5); break; }
       fence_after_sync();
       const uint32_t t = tmem + st * TM_STAGE + lane_base;
@@ -232,7 +285,11 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
       }
       fence_proxy_async();
       fence_before_sync();
-      mbar_arrive(&p_ready[st]);
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&p_ready[st]);
+        mbar_arrive(&gates_free[slot]);  // this warp has read the item's gates for the last time
+      }
       // ---- O2 = P y
       if (!mbar_wait(&o_done[st], ph)) { fail(6); break; }
       fence_after_sync();
@@ -240,9 +297,9 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
       tmem_ld_frag<NIO>(t + TM_O + (BV / 2) * chh, o2);
       tmem_ld_wait();
       fence_before_sync();
-      mbar_arrive(&t_free[st]);
-      if (etid == 0) tma_store_wait_read();  // this group's previous tile store has read sOut
-      named_barrier(1 + grp, 256);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&t_free[st]);
+      if (k >= 1 && !mbar_wait(&out_free[grp], (k - 1) & 1)) { fail(8); break; }  // the group's previous tile has left sOut
       const float osc = MODE == TMODE_O ? a.scale : 1.f;
 #pragma unroll
       for (int ni = 0; ni < NIO; ++ni)
@@ -256,25 +313,28 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
           else *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(x0, x1);
         }
       fence_proxy_async();
-      named_barrier(1 + grp, 256);
-      if (rows == C) {
-        if (etid == 0) {  // one tile store per 64-column box; ordinary global stores would stall the next fence.proxy.async
-          const int tt = s.bos + t0, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
-#pragma unroll
-          for (int j = 0; j < VB; ++j) tma_store_4d(&mapOut, sOut + j * 8192, vt * BV + 64 * j, c1, c2, s.b);
-          tma_store_commit();
-        }
-      } else {
-        // ragged last chunk of a sequence: a tile store would write past its end
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&out_ready[grp]);  // this warp's part of the output tile is written
+      if (rows < C) {
+        // ragged last chunk of a sequence: a tile store would write past its end; once the whole tile is there the
+        // group's warps copy the valid rows out with ordinary stores
+        if (!mbar_wait(&out_ready[grp], k & 1)) { fail(12); break; }
+        int c, hd, vt, n, it;
+        decode(blockIdx.x + i * gridDim.x, c, hd, vt);
+        chunk_of(a, c, n, it);
+        const Seq s = seq_of(a, n);
+        const int t0 = it * C;
         bf16 *out = reinterpret_cast<bf16 *>(MODE == TMODE_O ? a.o : a.dv) + tok_off(a, s, hd, t0, a.V) + vt * BV;
         const size_t vs = tok_stride(a, a.V);
         for (int e = etid; e < rows * (BV / 8); e += 256) {
           const int r_ = e / (BV / 8), c_ = (e - r_ * (BV / 8)) * 8;
           *reinterpret_cast<int4 *>(out + (size_t)r_ * vs + c_) = *reinterpret_cast<const int4 *>(sOut + (c_ >> 6) * 8192 + sw128_offset(r_, c_ & 63));
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&copy_done[grp]);
+        ++n_ragged;
       }
     }
-    if (etid == 0) tma_store_wait_all();
   }
   fence_before_sync();
   __syncthreads();
@@ -301,14 +361,14 @@ template <int KB, int VB, int MODE, int NS> static int launch_tc_o(const flab_ar
   p.n_items = a->NT * a->H * p.v_tiles;
   p.ab_fmt = a->dtype == FLAB_BF16 ? 1 : 0;
   constexpr uint32_t STAGE = 2 * KB * 8192 + VB * 8192 + (MODE != TMODE_DV_LOCAL ? VB * K * 128 : 0);
-  const size_t smem = 1024 + NS * (size_t)STAGE + 2 * 8192 + 2 * (size_t)VB * 8192 + 2 * C * sizeof(float);
+  const size_t smem = 1024 + NS * (size_t)STAGE + 2 * 8192 + 2 * (size_t)VB * 8192 + 4 * C * sizeof(float);
   auto kern = tc_chunk_o_kernel<KB, VB, MODE, NS>;
   if (int e = set_smem(kern, smem)) return e;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = p.n_items < sms ? p.n_items : sms;
-  kern<<<grid, 576, smem, stream>>>(mX1, mX2, mY, mH, mOut, p);
+  kern<<<grid, 640, smem, stream>>>(mX1, mX2, mY, mH, mOut, p);
   return check_launch(name);
 }
 

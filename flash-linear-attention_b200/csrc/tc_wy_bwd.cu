@@ -368,6 +368,21 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&e1_done);
+      // dv and its part of dbeta, while the tensor core runs the first product of the transform
+      float db_lo = 0.f, db_hi = 0.f;
+      {
+        float vb[4][4];
+        tmem_ld_frag<4>(tmem + lane_base + TM_VB + 32 * cq, vb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni) {
+          const float2 v_lo = ld2(tV + o128_lo[ni]), v_hi = ld2(tV + o128_hi[ni]);
+          db_lo += vb[ni][0] * v_lo.x + vb[ni][1] * v_lo.y;
+          db_hi += vb[ni][2] * v_hi.x + vb[ni][3] * v_hi.y;
+          st2(tDU + o128_lo[ni], vb[ni][0] * b_lo, vb[ni][1] * b_lo);  // dv, over du (the tensor core is done with it)
+          st2(tDU + o128_hi[ni], vb[ni][2] * b_hi, vb[ni][3] * b_hi);
+        }
+      }
       // ---- E2: first product of the transform, rounded, becomes the operand of the second
       if (!mbar_wait(&b2_done, ip)) fail(91);
       fence_after_sync();
@@ -390,23 +405,17 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&e2_done);
-      // dv, the first part of dk and of dbeta, while the tensor core runs the second product of the transform
-      float db_lo = 0.f, db_hi = 0.f;
+      // the first part of dk and of dbeta, while the tensor core runs the second product of the transform
       float dk1[4][4];
       {
-        float vb[4][4];
         tmem_ld_frag<4>(tmem + lane_base + TM_KB + 32 * cq, dk1);
-        tmem_ld_frag<4>(tmem + lane_base + TM_VB + 32 * cq, vb);
         tmem_ld_wait();
 #pragma unroll
         for (int ni = 0; ni < 4; ++ni) {
           const float2 k_lo = ld2(tK + o128_lo[ni]), k_hi = ld2(tK + o128_hi[ni]);
-          const float2 v_lo = ld2(tV + o128_lo[ni]), v_hi = ld2(tV + o128_hi[ni]);
-          db_lo += dk1[ni][0] * k_lo.x + dk1[ni][1] * k_lo.y + vb[ni][0] * v_lo.x + vb[ni][1] * v_lo.y;
-          db_hi += dk1[ni][2] * k_hi.x + dk1[ni][3] * k_hi.y + vb[ni][2] * v_hi.x + vb[ni][3] * v_hi.y;
+          db_lo += dk1[ni][0] * k_lo.x + dk1[ni][1] * k_lo.y;
+          db_hi += dk1[ni][2] * k_hi.x + dk1[ni][3] * k_hi.y;
           dk1[ni][0] *= b_lo, dk1[ni][1] *= b_lo, dk1[ni][2] *= b_hi, dk1[ni][3] *= b_hi;
-          st2(tDU + o128_lo[ni], vb[ni][0] * b_lo, vb[ni][1] * b_lo);  // dv, over du (the tensor core is done with it)
-          st2(tDU + o128_hi[ni], vb[ni][2] * b_hi, vb[ni][3] * b_hi);
         }
       }
       // ---- E3: dA = -strict_lower(.) (+ decayed dA_u), and diag(beta) dA
