@@ -3,7 +3,7 @@
 //   bwd_dv   : dv = (k dh) * e^{b_L-b_j} + triu(k q^T * e^{b_i-b_j}) * scale do  (fla/ops/common/chunk_o.py:289-364)
 //   dv_local : second term of bwd_dv only                                         (fla/ops/common/chunk_o.py:379-441)
 //
-// Persistent kernel, one CTA per SM, work item = (chunk, head, 128-wide V tile).  Twenty warps:
+// Persistent kernel, one CTA per SM, work item = (chunk, head, 128-wide V tile).  Nineteen warps:
 //   warp 16 : TMA producer  - streams the item's tiles (x1, x2, y, state) into a ring of stages
 //   warp 17 : MMA issuer    - S = x1 x2^T and O = x1 state into TMEM, later O = P y
 //   warps 0-7 / 8-15: two epilogue groups working on even / odd items (ping-pong); inside a group
@@ -11,8 +11,6 @@
 //                           - S -> mask / decay -> P (bf16, swizzled shared memory); O -> gate -> out
 //   warp 18 : scalars       - gates and row count of the coming items into a ring of four shared-memory slots, so that no
 //                             epilogue warp ever waits for a global load
-//   warp 19 : output       - lanes 0 and 1, one per group: tile store of the group's finished output tile, then the
-//                             tile goes back to the group
 // The epilogue warps meet each other only through the mbarriers of the phases (one arrival per warp), never through a
 // barrier of the group.
 // The epilogue arithmetic (one exponential per score element, packing, swizzled stores) is what
@@ -39,7 +37,7 @@ struct TcOParams {
 };
 
 template <int KB /*K/64*/, int VB /*BV/64*/, int MODE, int NS /*smem stages*/>
-__global__ void __launch_bounds__(640, 1)
+__global__ void __launch_bounds__(608, 1)
 tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_constant__ CUtensorMap mapX2,
                   const __grid_constant__ CUtensorMap mapY, const __grid_constant__ CUtensorMap mapH,
                   const __grid_constant__ CUtensorMap mapOut, const TcOParams p) {
@@ -170,47 +168,37 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
     }
   } else if (warp == 18) {
     // ------------------------------------------------------------------ scalar warp
-    for (int i = 0; i < n_local && !abort_flag; ++i) {
-      const int slot = i & 3;
-      if (i >= 4 && !mbar_wait(&gates_free[slot], ((i - 4) >> 2) & 1)) { fail(9); break; }  // item i - 4 has read the slot
+    // The gates of item i + 1 are fetched into registers before item i is published, so that the latency of the global
+    // loads never limits how fast slots are filled (a short item lasts about as long as one such load).
+    auto fetch = [&](int i, float &g0, float &g1, int &rows) {
+      g0 = g1 = 0.f;
+      rows = 0;
+      if (i >= n_local) return;
       int c, hd, vt, n, it;
       decode(blockIdx.x + i * gridDim.x, c, hd, vt);
       chunk_of(a, c, n, it);
       const Seq s = seq_of(a, n);
-      const int t0 = it * C, rows = min(C, s.len - t0);
-      for (int t = lane; t < C; t += 32)
-        sG[slot * C + t] = (use_g && t < rows) ? reinterpret_cast<const float *>(a.g)[tok_off(a, s, hd, t0 + t, 1)] : 0.f;
-      if (lane == 0) sRows[slot] = rows;
+      const int t0 = it * C;
+      rows = min(C, s.len - t0);
+      if (use_g) {
+        const float *G = reinterpret_cast<const float *>(a.g);
+        if (lane < rows) g0 = G[tok_off(a, s, hd, t0 + lane, 1)];
+        if (lane + 32 < rows) g1 = G[tok_off(a, s, hd, t0 + lane + 32, 1)];
+      }
+    };
+    float c0, c1, n0, n1;
+    int crows, nrows;
+    fetch(0, c0, c1, crows);
+    for (int i = 0; i < n_local && !abort_flag; ++i) {
+      const int slot = i & 3;
+      fetch(i + 1, n0, n1, nrows);
+      if (i >= 4 && !mbar_wait(&gates_free[slot], ((i - 4) >> 2) & 1)) { fail(9); break; }  // item i - 4 has read the slot
+      sG[slot * C + lane] = c0;
+      sG[slot * C + lane + 32] = c1;
+      if (lane == 0) sRows[slot] = crows;
       __syncwarp();
       if (lane == 0) mbar_arrive(&gates_full[slot]);
-    }
-  } else if (warp == 19) {
-    // ------------------------------------------------------------------ output warp (one lane per group)
-    if (lane < 2) {
-      const int g = lane;
-      int n_ragged = 0;
-      for (int i = g; i < n_local && !abort_flag; i += 2) {
-        const int k = i >> 1;
-        int c, hd, vt, n, it;
-        decode(blockIdx.x + i * gridDim.x, c, hd, vt);
-        chunk_of(a, c, n, it);
-        const Seq s = seq_of(a, n);
-        const int t0 = it * C, rows = min(C, s.len - t0);
-        if (!mbar_wait(&out_ready[g], k & 1)) { fail(10); break; }
-        if (rows == C) {  // one tile store per 64-column box
-          unsigned char *sOut = sOutAll + g * Y_BYTES;
-          const int tt = s.bos + t0, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
-#pragma unroll
-          for (int j = 0; j < VB; ++j) tma_store_4d(&mapOut, sOut + j * 8192, vt * BV + 64 * j, c1, c2, s.b);
-          tma_store_commit();
-          tma_store_wait_read();
-        } else {  // a ragged chunk is copied out by the epilogue warps themselves
-          if (!mbar_wait(&copy_done[g], n_ragged & 1)) { fail(11); break; }
-          ++n_ragged;
-        }
-        mbar_arrive(&out_free[g]);
-      }
-      tma_store_wait_all();
+      c0 = n0, c1 = n1, crows = nrows;
     }
   } else {
     // ------------------------------------------------------------------ epilogue groups (warps 0-7, 8-15)
@@ -222,6 +210,7 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
     unsigned char *sOut = sOutAll + grp * Y_BYTES;
     const int row_lo = m0 + g8, row_hi = row_lo + 8;
     int n_ragged = 0;
+    bool prev_ragged = false;
     for (int i = grp; i < n_local && !abort_flag; i += 2) {
       const int st = grp, ph = (i >> 1) & 1, k = i >> 1, slot = i & 3;
       // gates and row count of this item, from the scalar warp
@@ -299,7 +288,19 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&t_free[st]);
-      if (k >= 1 && !mbar_wait(&out_free[grp], (k - 1) & 1)) { fail(8); break; }  // the group's previous tile has left sOut
+      if (k >= 1) {
+        // the group's previous tile has left sOut: the thread that stored it says so once the copy engine has read it
+        // (or, after a ragged chunk, once every warp has copied its rows out)
+        if (gw == 0 && lane == 0) {
+          if (prev_ragged) {
+            if (!mbar_wait(&copy_done[grp], (n_ragged - 1) & 1)) fail(11);
+          } else {
+            tma_store_wait_read();
+          }
+          mbar_arrive(&out_free[grp]);
+        }
+        if (!mbar_wait(&out_free[grp], (k - 1) & 1)) { fail(8); break; }
+      }
       const float osc = MODE == TMODE_O ? a.scale : 1.f;
 #pragma unroll
       for (int ni = 0; ni < NIO; ++ni)
@@ -315,7 +316,20 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&out_ready[grp]);  // this warp's part of the output tile is written
-      if (rows < C) {
+      prev_ragged = rows < C;
+      if (rows == C) {
+        if (gw == 0 && lane == 0) {  // the whole tile is there: one tile store per 64-column box
+          if (!mbar_wait(&out_ready[grp], k & 1)) fail(10);  // (no early exit of a single lane: the warp stays together)
+          int c, hd, vt, n, it;
+          decode(blockIdx.x + i * gridDim.x, c, hd, vt);
+          chunk_of(a, c, n, it);
+          const Seq s = seq_of(a, n);
+          const int tt = s.bos + it * C, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
+#pragma unroll
+          for (int j = 0; j < VB; ++j) tma_store_4d(&mapOut, sOut + j * 8192, vt * BV + 64 * j, c1, c2, s.b);
+          tma_store_commit();
+        }
+      } else {
         // ragged last chunk of a sequence: a tile store would write past its end; once the whole tile is there the
         // group's warps copy the valid rows out with ordinary stores
         if (!mbar_wait(&out_ready[grp], k & 1)) { fail(12); break; }
@@ -335,6 +349,7 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
         ++n_ragged;
       }
     }
+    if (gw == 0 && lane == 0) tma_store_wait_all();
   }
   fence_before_sync();
   __syncthreads();
@@ -368,7 +383,7 @@ template <int KB, int VB, int MODE, int NS> static int launch_tc_o(const flab_ar
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = p.n_items < sms ? p.n_items : sms;
-  kern<<<grid, 640, smem, stream>>>(mX1, mX2, mY, mH, mOut, p);
+  kern<<<grid, 608, smem, stream>>>(mX1, mX2, mY, mH, mOut, p);
   return check_launch(name);
 }
 

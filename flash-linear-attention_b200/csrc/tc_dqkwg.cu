@@ -256,21 +256,37 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
       }
       return true;
     };
+    // the gates of item i + 1 are fetched into registers before item i is published and before the wait for item i - 2:
+    // the latency of these global loads is never exposed
+    auto fetch = [&](int i, float (&gt)[2], int &rows) {
+      gt[0] = gt[1] = 0.f;
+      rows = 0;
+      if (i >= n_local) return;
+      Seq s;
+      int hd, t0;
+      where(i, s, hd, t0, rows);
+      if (use_g) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          if (lane + 32 * h < rows) gt[h] = Gbase[tok_off(a, s, hd, t0 + lane + 32 * h, 1)];
+      }
+    };
+    float cg[2], ng[2];
+    int crows, nrows;
+    fetch(0, cg, crows);
     bool alive = true;
     for (int i = 0; i < n_local && alive && !abort_flag; ++i) {
       const int slot = i & 1;
+      fetch(i + 1, ng, nrows);
       if (i >= 2) alive = write_out(i - 2);
       __syncwarp();
       if (!alive) break;
-      Seq s;
-      int hd, t0, rows;
-      where(i, s, hd, t0, rows);
-      for (int t = lane; t < C; t += 32) {
-        sG[slot * C + t] = (use_g && t < rows) ? Gbase[tok_off(a, s, hd, t0 + t, 1)] : 0.f;
-      }
-      if (lane == 0) sRows[slot] = rows;
+      sG[slot * C + lane] = cg[0];
+      sG[slot * C + lane + 32] = cg[1];
+      if (lane == 0) sRows[slot] = crows;
       __syncwarp();
       if (lane == 0) mbar_arrive(&scal_full[slot]);
+      cg[0] = ng[0], cg[1] = ng[1], crows = nrows;
     }
     for (int j = n_local > 2 ? n_local - 2 : 0; j < n_local && alive && !abort_flag; ++j) {
       alive = write_out(j);

@@ -259,28 +259,46 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       }
       return true;
     };
+    // beta / gate of item i + 1 are fetched into registers before item i is published and before the wait for item i - 2:
+    // the latency of these global loads is never exposed
+    auto fetch = [&](int i, float (&bt)[2], float (&gt)[2], int &rows) {
+      bt[0] = bt[1] = gt[0] = gt[1] = 0.f;
+      rows = 0;
+      if (i >= n_local) return;
+      Seq s;
+      int hd, t0;
+      locate(i, s, hd, t0, rows);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int t = lane + 32 * h;
+        if (t < rows) {
+          const size_t o = tok_off(a, s, hd, t0 + t, 1);
+          bt[h] = p.ab_fmt ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.beta)[o]) : __half2float(reinterpret_cast<const __half *>(a.beta)[o]);
+          if (GATED) gt[h] = reinterpret_cast<const float *>(a.g)[o];
+        }
+      }
+    };
+    float cb[2], cg[2], nb[2], ng[2];
+    int crows, nrows;
+    fetch(0, cb, cg, crows);
     bool alive = true;
     for (int i = 0; i < n_local && alive && !abort_flag; ++i) {
       const int slot = i & 1;
+      fetch(i + 1, nb, ng, nrows);
       if (i >= 2) alive = write_out(i - 2);
       __syncwarp();
       if (!alive) break;
-      Seq s;
-      int hd, t0, rows;
-      locate(i, s, hd, t0, rows);
-      for (int t = lane; t < C; t += 32) {
-        float bt = 0.f, gt = 0.f;
-        if (t < rows) {
-          const size_t o = tok_off(a, s, hd, t0 + t, 1);
-          bt = p.ab_fmt ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.beta)[o]) : __half2float(reinterpret_cast<const __half *>(a.beta)[o]);
-          if (GATED) gt = reinterpret_cast<const float *>(a.g)[o];
-        }
-        sBeta[slot * C + t] = bt;
-        sG[slot * C + t] = gt;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        sBeta[slot * C + lane + 32 * h] = cb[h];
+        sG[slot * C + lane + 32 * h] = cg[h];
       }
-      if (lane == 0) sRows[slot] = rows;
+      if (lane == 0) sRows[slot] = crows;
       __syncwarp();
       if (lane == 0) mbar_arrive(&scal_full[slot]);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) cb[h] = nb[h], cg[h] = ng[h];
+      crows = nrows;
     }
     for (int j = n_local > 2 ? n_local - 2 : 0; j < n_local && alive && !abort_flag; ++j) {
       alive = write_out(j);
