@@ -110,10 +110,10 @@ def stage_table(op):
         "dv_local": (3 * X + gb + X, 2 * CK + 2 * CV, 1),                   # q, k, do, b -> dv
         "delta_bwd_dhu": (5 * X + gb + ST + X, 6 * KV, 1),                  # q, k, w, do, dv, b -> dh, dv2
         "dqkwg": (6 * X + gb + 2 * ST + 3 * X + gb, 6 * KV + 2 * CV + 6 * CK, 1),   # q, k, w, v_new, do, dv2, b, h, dh -> dq, dk, dw, dg
-        "wy_bwd": (5 * X + na * A64 + 2 + gb + 2 * X + 4 + gb, 8 * CK + 4 * CV + 8 * CC, 1),  # k, v, dw, dv2, dk, Aw, Au, beta, b -> dk, dv, dbeta, dg
+        "wy_bwd": (5 * X + na * A64 + 2 + 2 * gb + 2 * X + 4 + gb, 8 * CK + 4 * CV + 8 * CC, 1),  # k, v, dw, dv2, dk, Aw, Au, beta, b, dg(dqkwg) -> dk, dv, dbeta, dg
     }
     if gated:
-        t["cumsum"] = (8, 0, 2)
+        t["cumsum"] = (8, 0, 1)  # forward only: the reverse cumsum of dg is done by the last backward kernel
     return t
 
 
@@ -402,7 +402,7 @@ def stage_breakdown(op, i):
             "dv_local": lambda: C.chunk_bwd_dv_local(geo, q, k, gc, do, scale),
             "delta_bwd_dhu": lambda: C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=gc, dht=dht, want_dh0=True),
             "dqkwg": lambda: C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=gc, w=w, dv=dv2),
-            "wy_bwd": lambda: C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv2, g=gc, au=au, dk_in=dk),
+            "wy_bwd": lambda: C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv2, g=gc, au=au, dk_in=dk, dg_in=dg if gated else None),
         }
         if gated:
             g = i["g"].detach()

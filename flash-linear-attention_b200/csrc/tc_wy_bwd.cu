@@ -242,6 +242,7 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
     // (item i - 2) must be finished with it: the epilogue warps say so on rows_done, and their dbeta / dg rows are
     // written to global memory from here.
     float *dbeta_out = reinterpret_cast<float *>(a.dbeta), *dg_out = reinterpret_cast<float *>(a.dg);
+    const float *dg_prev = reinterpret_cast<const float *>(a.dgk);  // dg of the preceding stage (optional): see flab_wy_bwd
     auto write_out = [&](int j) -> bool {
       const int slot = j & 1;
       if (!mbar_wait(&rows_done[slot], (j >> 1) & 1)) {
@@ -252,10 +253,37 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       int hd, t0, rows;
       locate(j, s, hd, t0, rows);
       const float *db = sDB + slot * 4 * C, *dgr = sDG + slot * 4 * C, *dgc = sDGC + slot * 4 * C;
-      for (int t = lane; t < rows; t += 32) {
-        const size_t o = tok_off(a, s, hd, t0 + t, 1);
-        dbeta_out[o] = (db[t] + db[C + t]) + (db[2 * C + t] + db[3 * C + t]);
-        if (GATED) dg_out[o] = ((dgr[t] + dgr[C + t]) + (dgr[2 * C + t] + dgr[3 * C + t])) - ((dgc[t] + dgc[C + t]) + (dgc[2 * C + t] + dgc[3 * C + t]));
+      float x[2] = {0.f, 0.f};
+      size_t o[2] = {0, 0};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int t = lane + 32 * h;
+        if (t < rows) {
+          o[h] = tok_off(a, s, hd, t0 + t, 1);
+          dbeta_out[o[h]] = (db[t] + db[C + t]) + (db[2 * C + t] + db[3 * C + t]);
+          if (GATED) {
+            x[h] = ((dgr[t] + dgr[C + t]) + (dgr[2 * C + t] + dgr[3 * C + t])) - ((dgc[t] + dgc[C + t]) + (dgc[2 * C + t] + dgc[3 * C + t]));
+            if (dg_prev) x[h] += dg_prev[o[h]];
+          }
+        }
+      }
+      if (GATED) {
+        if (dg_prev) {
+          // gradient w.r.t. the raw gate: suffix sums over the chunk's tokens (the reverse chunk-local cumsum the reference
+          // applies at the end, fla/ops/gated_delta_rule/chunk.py:173-176); tokens lane + 32 first, then tokens lane
+#pragma unroll
+          for (int h = 1; h >= 0; --h) {
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+              const float y = __shfl_down_sync(0xffffffffu, x[h], off);
+              if (lane + off < 32) x[h] += y;
+            }
+          }
+          x[0] += __shfl_sync(0xffffffffu, x[1], 0);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          if (lane + 32 * h < rows) dg_out[o[h]] = x[h];
       }
       return true;
     };

@@ -755,6 +755,13 @@ static bool tc_wy_enabled() {
 
 }  // namespace flab
 
+namespace flab {
+__global__ void add_inplace_kernel(float *__restrict__ x, const float *__restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] += y[i];
+}
+}  // namespace flab
+
 extern "C" {
 
 int flab_wy_fwd(const flab_args *a, void *stream) {
@@ -795,10 +802,22 @@ int flab_wy_bwd(const flab_args *a, void *stream) {
     const int r = tc_wy_bwd_try(a, (cudaStream_t)stream);
     if (r != 0) return r < 0 ? r : FLAB_OK;
   }
+  int rc = FLAB_OK;
   FLAB_DISPATCH_16(a->dtype, T, {
-    if (gated) return (launch_wy_bwd<T, true>(a, (cudaStream_t)stream));
-    return (launch_wy_bwd<T, false>(a, (cudaStream_t)stream));
+    rc = gated ? launch_wy_bwd<T, true>(a, (cudaStream_t)stream) : launch_wy_bwd<T, false>(a, (cudaStream_t)stream);
   });
-  return FLAB_OK;
+  if (rc != FLAB_OK || !gated || !a->dgk) return rc;
+  // these kernels leave dg w.r.t. the cumulative gate; the optional last step (add the dg of the preceding stage, reverse
+  // chunk-local cumsum) follows as two small launches: an in-place add, then the cumsum kernel in place
+  const long long n = (long long)a->B * a->T * a->H;
+  add_inplace_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<float *>(a->dg),
+                                                                                  reinterpret_cast<const float *>(a->dgk), n);
+  if (int e = check_launch("wy_bwd(dg add)")) return e;
+  flab_args c = *a;
+  c.dtype = FLAB_FP32;
+  c.flags = FLAB_F_REVERSE;
+  c.x = a->dg;
+  c.y = a->dg;
+  return flab_chunk_local_cumsum_scalar(&c, stream);
 }
 }

@@ -127,15 +127,17 @@ def fwd_recompute_w_u(geo: Geometry, k, v, beta, aw, au=None):
     return w, u
 
 
-def bwd_prepare_wy_repr(geo: Geometry, k, v, beta, aw, dw, du, g=None, au=None, dk_in=None):
+def bwd_prepare_wy_repr(geo: Geometry, k, v, beta, aw, dw, du, g=None, au=None, dk_in=None, dg_in=None):
     """Backward of the WY transform (fla/ops/delta_rule/wy_fast.py:619,
     fla/ops/gated_delta_rule/wy_fast.py:565). Returns (dk, dv, dbeta, dg). `dk_in` (optional, same dtype as
-    k) is added to the returned dk inside the kernel, in fp32, before the single rounding."""
+    k) is added to the returned dk inside the kernel, in fp32, before the single rounding. `dg_in` (optional, gated:
+    the fp32 dg of chunk_bwd_dqkwg): the returned dg is then the finished gradient of the raw gate, the reverse
+    chunk-local cumsum of (dg_in + this stage's dg), formed inside the same kernel."""
     dk, dv = torch.empty_like(k), torch.empty_like(v)
     dbeta = torch.empty(beta.shape, dtype=torch.float32, device=k.device)
     dg = torch.empty(beta.shape, dtype=torch.float32, device=k.device) if g is not None else None
     _lib.call("flab_wy_bwd", k, **geo.kw(), k=k, v=v, beta=beta, g=g, aw=aw, au=au, dw=dw, du=du, dk=dk, dv=dv,
-              dbeta=dbeta, dg=dg, x=dk_in)
+              dbeta=dbeta, dg=dg, x=dk_in, dgk=dg_in if g is not None else None)
     return dk, dv, dbeta, dg
 
 
@@ -210,26 +212,31 @@ def slab_plan(geo: Geometry, k: torch.Tensor) -> Optional[SlabPlan]:
     return SlabPlan(geo.B, geo.T, -(-nts // per), per, k.device)
 
 
-def slab_delta_fwd_h(plan: SlabPlan, geo: Geometry, k, w, u, g=None, h0=None, output_final_state=False):
-    """`chunk_gated_delta_rule_fwd_h` over slabs. Returns (h, v_new, ht, M) with M `[B, S, H, K, K]` fp32, the slabs'
-    state transitions (kept for the backward scan)."""
+def slab_delta_fwd_pass1(plan: SlabPlan, geo: Geometry, k, w, u, g=None):
+    """First pass of the forward scan over slabs: every slab's transition. Returns `bm` `[B, S, H, K, V + K]` fp32, the
+    final state of each slab started from `[0 | I]` over the value columns `[u | 0]`: columns `[:V]` are the slab's
+    offset b, columns `[V:]` its matrix M (S_out = M S_in + b)."""
     from .._lib import F_STATE_ONLY
     B, S, H, K, V = plan.B, plan.S, geo.H, geo.K, geo.V
     dev = k.device
     gv = None if g is None else g.view(1, -1, H)
-    # pass 1: [b | M] of every slab
     h0_ext = torch.zeros(B * S, H, K, V + K, dtype=torch.float32, device=dev)
     h0_ext[..., V:] = torch.eye(K, dtype=torch.float32, device=dev)
     ht_ext = torch.empty_like(h0_ext)
     ge = plan.geometry(k, u)
     ge.V = V + K  # the state is V + K columns wide; u supplies the first V (S = V), the rest read as zero
     _lib.call("flab_delta_fwd_h", k, **ge.kw(), flags=F_STATE_ONLY, S=V, k=k, w=w, u=u, g=gv, h0=h0_ext, ht=ht_ext)
-    del h0_ext
-    ht_ext = ht_ext.view(B, S, H, K, V + K)
-    b_, M = ht_ext[..., :V], ht_ext[..., V:].contiguous()
-    # true initial state of every slab: the chain S <- M_s S + b_s, one launch
+    return ht_ext.view(B, S, H, K, V + K)
+
+
+def slab_delta_fwd_pass2(plan: SlabPlan, geo: Geometry, bm, k, w, u, g=None, h0=None, output_final_state=False):
+    """Second pass: the slabs' true initial states from the chain S <- M_s S + b_s (one launch), then the scan proper.
+    Returns (h, v_new, ht, M) with M `[B, S, H, K, K]` fp32 kept for the backward scan."""
+    B, S, H, K, V = plan.B, plan.S, geo.H, geo.K, geo.V
+    dev = k.device
+    gv = None if g is None else g.view(1, -1, H)
+    b_, M = bm[..., :V], bm[..., V:].contiguous()
     S_in, _ = _lib.state_chain(M, b_, h0)
-    # pass 2
     gs = plan.geometry(k, u)
     h = torch.empty(geo.NT, H, K, V, dtype=k.dtype, device=dev)
     v_new = torch.empty_like(u)
@@ -239,17 +246,44 @@ def slab_delta_fwd_h(plan: SlabPlan, geo: Geometry, k, w, u, g=None, h0=None, ou
     return h, v_new, ht, M
 
 
-def slab_delta_bwd_dhu(plan: SlabPlan, geo: Geometry, M, q, k, w, do, dv, scale, g=None, dht=None, want_dh0=False):
-    """`chunk_gated_delta_rule_bwd_dhu` over slabs, with the transitions M of the forward. Returns (dh, dh0, dv2)."""
+def slab_delta_fwd_h(plan: SlabPlan, geo: Geometry, k, w, u, g=None, h0=None, output_final_state=False):
+    """`chunk_gated_delta_rule_fwd_h` over slabs. Returns (h, v_new, ht, M) with M `[B, S, H, K, K]` fp32, the slabs'
+    state transitions (kept for the backward scan)."""
+    bm = slab_delta_fwd_pass1(plan, geo, k, w, u, g=g)
+    return slab_delta_fwd_pass2(plan, geo, bm, k, w, u, g=g, h0=h0, output_final_state=output_final_state)
+
+
+def slab_total_transition(bm: torch.Tensor, V: int):
+    """The transition of the WHOLE sequence from those of its slabs: the chain started from `[0 | I]`. bm: `[B, S, H, K,
+    V + K]` from `slab_delta_fwd_pass1`. Returns (b `[B, H, K, V]`, M `[B, H, K, K]`)."""
+    B, S, H, K, W = bm.shape
+    ext0 = torch.zeros(B, H, K, W, dtype=torch.float32, device=bm.device)
+    ext0[..., V:] = torch.eye(K, dtype=torch.float32, device=bm.device)
+    _, tot = _lib.state_chain(bm[..., V:].contiguous(), bm, ext0, want_s_in=False, want_last=True)
+    return tot[..., :V].contiguous(), tot[..., V:].contiguous()
+
+
+def slab_delta_bwd_pass1(plan: SlabPlan, geo: Geometry, q, k, w, do, dv, scale, g=None):
+    """First pass of the reverse scan over slabs: c `[B, S, H, K, V]` fp32, the state gradient every slab hands to its
+    predecessor when it receives zero."""
     from .._lib import F_STATE_ONLY
+    B, S, H, K, V = plan.B, plan.S, geo.H, geo.K, geo.V
+    gv = None if g is None else g.view(1, -1, H)
+    gs = plan.geometry(k, dv)
+    c_ = torch.empty(B * S, H, K, V, dtype=torch.float32, device=q.device)
+    _lib.call("flab_delta_bwd_dhu", q, **gs.kw(), scale=scale, flags=F_STATE_ONLY, q=q, k=k, w=w, g=gv, d_o=do, dv=dv, dh0=c_)
+    return c_.view(B, S, H, K, V)
+
+
+def slab_delta_bwd_dhu(plan: SlabPlan, geo: Geometry, M, q, k, w, do, dv, scale, g=None, dht=None, want_dh0=False, c_=None):
+    """`chunk_gated_delta_rule_bwd_dhu` over slabs, with the transitions M of the forward (`c_`: the result of
+    `slab_delta_bwd_pass1` when the caller already has it). Returns (dh, dh0, dv2)."""
     B, S, H, K, V = plan.B, plan.S, geo.H, geo.K, geo.V
     dev = q.device
     gv = None if g is None else g.view(1, -1, H)
     gs = plan.geometry(k, dv)
-    # pass 1: c of every slab (the state gradient a slab hands to its predecessor when it receives zero)
-    c_ = torch.empty(B * S, H, K, V, dtype=torch.float32, device=dev)
-    _lib.call("flab_delta_bwd_dhu", q, **gs.kw(), scale=scale, flags=F_STATE_ONLY, q=q, k=k, w=w, g=gv, d_o=do, dv=dv, dh0=c_)
-    c_ = c_.view(B, S, H, K, V)
+    if c_ is None:
+        c_ = slab_delta_bwd_pass1(plan, geo, q, k, w, do, dv, scale, g=g)
     # the transposed chain, right to left: D_out[s] = gradient of the state leaving slab s
     D_out, _ = _lib.state_chain(M, c_, dht, reverse=True, transpose=True)
     # pass 2

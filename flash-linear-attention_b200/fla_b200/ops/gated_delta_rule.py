@@ -43,9 +43,11 @@ def chunk_gated_delta_rule_fwd_fused(geo, q, k, v, g, beta, scale, initial_state
     return o, ht
 
 
-def chunk_gated_delta_rule_bwd(geo, q, k, v, g, beta, aw, au, scale, initial_state, do, dht, saved=None):
+def chunk_gated_delta_rule_bwd(geo, q, k, v, g, beta, aw, au, scale, initial_state, do, dht, saved=None, dv_local=None, slab_c=None):
     """Stage order of fla/ops/gated_delta_rule/chunk.py:76-177; `g` is the chunk-local cumsum.
-    `saved` = (w, h, v_new, M) kept from forward (M: slab transitions of a split scan, else None); None recomputes them like the reference."""
+    `saved` = (w, h, v_new, M) kept from forward (M: slab transitions of a split scan, else None); None recomputes them like the
+    reference. `dv_local` / `slab_c`: the local dv and the first pass of a split reverse scan when the caller (the
+    sequence-parallel backward) has computed them already."""
     if saved is not None:
         w, h, v_new, M = saved
         plan = C.slab_plan(geo, k) if M is not None else None  # split the reverse scan iff the forward one was
@@ -56,16 +58,16 @@ def chunk_gated_delta_rule_bwd(geo, q, k, v, g, beta, aw, au, scale, initial_sta
             h, v_new, _, M = C.slab_delta_fwd_h(plan, geo, k, w, u, g=g, h0=initial_state, output_final_state=False)
         else:
             h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g, h0=initial_state, output_final_state=False)
-    dv = C.chunk_bwd_dv_local(geo, q, k, g, do, scale)
+    dv = dv_local if dv_local is not None else C.chunk_bwd_dv_local(geo, q, k, g, do, scale)
     if plan is not None:
-        dh, dh0, dv = C.slab_delta_bwd_dhu(plan, geo, M, q, k, w, do, dv, scale, g=g, dht=dht, want_dh0=initial_state is not None)
+        dh, dh0, dv = C.slab_delta_bwd_dhu(plan, geo, M, q, k, w, do, dv, scale, g=g, dht=dht, want_dh0=initial_state is not None,
+                                           c_=slab_c)
     else:
         dh, dh0, dv = C.chunk_gated_delta_rule_bwd_dhu(geo, q, k, w, do, dv, scale, g=g, dht=dht,
                                                        want_dh0=initial_state is not None)
     dq, dk, dw, dg = C.chunk_bwd_dqkwg(geo, q, k, v_new, h, dh, do, scale, g=g, w=w, dv=dv)
-    dk, dv, db, dg2 = C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv, g=g, au=au, dk_in=dk)
-    dg.add_(dg2)
-    dg = C.chunk_local_cumsum(dg, reverse=True, offsets=geo.offsets_tensor, head_first=geo.head_first)
+    # the last stage also finishes the gate gradient: dg(dqkwg) + its own share, reverse chunk-local cumsum
+    dk, dv, db, dg = C.bwd_prepare_wy_repr(geo, k, v, beta, aw, dw, dv, g=g, au=au, dk_in=dk, dg_in=dg)
     return dq, dk, dv, db, dg, dh0
 
 

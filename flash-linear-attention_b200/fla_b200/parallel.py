@@ -136,37 +136,52 @@ def broadcast_from(x: torch.Tensor, src_rank: int, group=None) -> torch.Tensor:
 
 def _fwd_slab(q, k, v, g, beta, scale, S_in_of):
     """Forward of one rank's slab. `S_in_of(M, b)` maps the slab's transition to its true initial state (this is
-    where the communication happens). Returns (o, S_out, saved tensors for backward)."""
+    where the communication happens). Returns (o, S_out, saved tensors for backward).
+
+    A rank's slab is itself a few long chains, so when it is long enough its two scans run split into sub-slabs over the
+    SMs (`ops.common.slab_*`): the first pass gives every sub-slab's transition, their composition (one launch of the
+    chain kernel) is the rank's (M, b), and the second pass starts from the state received from the previous rank."""
     from .ops import common as C
     from .utils import Geometry
     geo = Geometry(k, v, None, False)
     H, K, V = geo.H, geo.K, geo.V
     g_cum = C.chunk_local_cumsum(g, head_first=False)
     aw, au, w, u = C.fwd_prepare_wy_repr(geo, k, v, beta, g=g_cum)
-    # one widened scan: value columns [u | 0], initial state [0 | I]  ->  final state [b | M]
-    h0_ext = torch.cat([torch.zeros(1, H, K, V, device=k.device), torch.eye(K, device=k.device).expand(1, H, K, K)], dim=-1).contiguous()
     import os
+    plan = C.slab_plan(geo, k)
     timer = _stage("state_pass_fwd")
     timer.__enter__()
-    if k.dtype in (torch.bfloat16, torch.float16) and K == 128 and V % 64 == 0 and not os.environ.get("FLA_B200_NO_TC"):
-        # state-only scan: nothing but the final state is stored, u itself is read (columns past V are zero-filled)
-        from . import _lib
-        geo_ext = Geometry(k, u, None, False)
-        geo_ext.V = V + K
-        ht_ext = torch.empty_like(h0_ext)
-        _lib.call("flab_delta_fwd_h", k, **geo_ext.kw(), flags=_lib.F_STATE_ONLY, S=V, k=k, w=w, u=u, g=g_cum, h0=h0_ext, ht=ht_ext)
+    bm = None
+    if plan is not None:
+        bm = C.slab_delta_fwd_pass1(plan, geo, k, w, u, g=g_cum)
+        b, M = C.slab_total_transition(bm, V)
+        b, M = b[0], M[0]
     else:
-        u_ext = torch.cat([u, torch.zeros_like(k)], dim=-1)
-        geo_ext = Geometry(k, u_ext, None, False)
-        _, _, ht_ext = C.chunk_gated_delta_rule_fwd_h(geo_ext, k, w, u_ext, g=g_cum, h0=h0_ext, output_final_state=True)
-    b, M = ht_ext[0, :, :, :V].contiguous(), ht_ext[0, :, :, V:].contiguous()
+        # one widened scan: value columns [u | 0], initial state [0 | I]  ->  final state [b | M]
+        h0_ext = torch.cat([torch.zeros(1, H, K, V, device=k.device), torch.eye(K, device=k.device).expand(1, H, K, K)], dim=-1).contiguous()
+        if k.dtype in (torch.bfloat16, torch.float16) and K == 128 and V % 64 == 0 and not os.environ.get("FLA_B200_NO_TC"):
+            # state-only scan: nothing but the final state is stored, u itself is read (columns past V are zero-filled)
+            from . import _lib
+            geo_ext = Geometry(k, u, None, False)
+            geo_ext.V = V + K
+            ht_ext = torch.empty_like(h0_ext)
+            _lib.call("flab_delta_fwd_h", k, **geo_ext.kw(), flags=_lib.F_STATE_ONLY, S=V, k=k, w=w, u=u, g=g_cum, h0=h0_ext, ht=ht_ext)
+        else:
+            u_ext = torch.cat([u, torch.zeros_like(k)], dim=-1)
+            geo_ext = Geometry(k, u_ext, None, False)
+            _, _, ht_ext = C.chunk_gated_delta_rule_fwd_h(geo_ext, k, w, u_ext, g=g_cum, h0=h0_ext, output_final_state=True)
+        b, M = ht_ext[0, :, :, :V].contiguous(), ht_ext[0, :, :, V:].contiguous()
     timer.__exit__()
     with _stage("handoff_fwd"):
         S_in, S_out = S_in_of(M, b)
     # correction pass with the true initial state
-    h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g_cum, h0=S_in.unsqueeze(0), output_final_state=False)
+    M_sub = None
+    if plan is not None:
+        h, v_new, _, M_sub = C.slab_delta_fwd_pass2(plan, geo, bm, k, w, u, g=g_cum, h0=S_in.unsqueeze(0), output_final_state=False)
+    else:
+        h, v_new, _ = C.chunk_gated_delta_rule_fwd_h(geo, k, w, u, g=g_cum, h0=S_in.unsqueeze(0), output_final_state=False)
     o = C.chunk_fwd_o(geo, q, k, v_new, h, g=g_cum, scale=scale)
-    return o, S_out, (g_cum, aw, au, w, h, v_new, geo, M, S_in)
+    return o, S_out, (g_cum, aw, au, w, h, v_new, geo, M, S_in, M_sub)
 
 
 def sp_chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, group=None):
@@ -200,9 +215,9 @@ class SPChunkGatedDeltaRuleFunction(torch.autograd.Function):
         beta_k = beta.to(k.dtype)
         S0 = None if initial_state is None else initial_state.float()[0]
         o, S_out, saved = _fwd_slab(q, k, v, g.float(), beta_k, scale, lambda M, b: handoff_states(M, b, S0, group))
-        g_cum, aw, au, w, h, v_new, geo, M, S_in = saved
+        g_cum, aw, au, w, h, v_new, geo, M, S_in, M_sub = saved
         ht = broadcast_from(S_out.clone(), world - 1, group).unsqueeze(0) if output_final_state else None
-        ctx.save_for_backward(q, k, v, g_cum, beta_k, aw, au, w, h, v_new, M, S_in)
+        ctx.save_for_backward(q, k, v, g_cum, beta_k, aw, au, w, h, v_new, M, S_in, M_sub)
         ctx.geo, ctx.scale, ctx.group, ctx.g_dtype, ctx.beta_dtype = geo, scale, group, g.dtype, beta.dtype
         ctx.has_h0 = initial_state is not None
         return o, ht
@@ -211,7 +226,7 @@ class SPChunkGatedDeltaRuleFunction(torch.autograd.Function):
     def backward(ctx, do, dht):
         from .ops import common as C
         from .ops.gated_delta_rule import chunk_gated_delta_rule_bwd
-        q, k, v, g_cum, beta, aw, au, w, h, v_new, M, S_in = ctx.saved_tensors
+        q, k, v, g_cum, beta, aw, au, w, h, v_new, M, S_in, M_sub = ctx.saved_tensors
         geo, scale, group = ctx.geo, ctx.scale, ctx.group
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         do = do.contiguous()
@@ -220,7 +235,14 @@ class SPChunkGatedDeltaRuleFunction(torch.autograd.Function):
         import os
         timer = _stage("state_pass_bwd")
         timer.__enter__()
-        if k.dtype in (torch.bfloat16, torch.float16) and geo.K == 128 and geo.V % 64 == 0 and not os.environ.get("FLA_B200_NO_TC"):
+        plan = C.slab_plan(geo, k) if M_sub is not None else None
+        slab_c = None
+        if plan is not None:
+            # split reverse scan: every sub-slab's contribution, composed right to left from zero (one launch)
+            from . import _lib
+            slab_c = C.slab_delta_bwd_pass1(plan, geo, q, k, w, do, dv, scale, g=g_cum)
+            _, c = _lib.state_chain(M_sub, slab_c, None, want_s_in=False, want_last=True, reverse=True, transpose=True)
+        elif k.dtype in (torch.bfloat16, torch.float16) and geo.K == 128 and geo.V % 64 == 0 and not os.environ.get("FLA_B200_NO_TC"):
             from . import _lib  # state-only scan: only the gradient handed to the predecessor is stored
             c = torch.empty(1, geo.H, geo.K, geo.V, dtype=torch.float32, device=k.device)
             _lib.call("flab_delta_bwd_dhu", q, **geo.kw(), scale=scale, flags=_lib.F_STATE_ONLY, q=q, k=k, w=w, g=g_cum, d_o=do, dv=dv, dh0=c)
@@ -232,7 +254,7 @@ class SPChunkGatedDeltaRuleFunction(torch.autograd.Function):
         with _stage("handoff_bwd"):
             dS_out, dS_in = handoff_states(M.transpose(1, 2).contiguous(), c[0], ext, group, reverse=True)
         dq, dk, dv, db, dg, _ = chunk_gated_delta_rule_bwd(geo, q, k, v, g_cum, beta, aw, au, scale, S_in.unsqueeze(0), do,
-                                                          dS_out.unsqueeze(0), saved=(w, h, v_new, None))
+                                                          dS_out.unsqueeze(0), saved=(w, h, v_new, M_sub), dv_local=dv, slab_c=slab_c)
         dh0 = dS_in.unsqueeze(0) if (ctx.has_h0 and rank == 0) else None
         if ctx.has_h0 and rank != 0:
             dh0 = torch.zeros_like(dS_in).unsqueeze(0)

@@ -188,7 +188,10 @@ int flab_wy_recompute(const flab_args *a, void *stream);
  * fla/ops/gated_delta_rule/wy_fast.py:565): reads k, v, beta, g (gated only), aw, au (gated only),
  * dw, du; writes dk, dv, dbeta (fp32) and dg (fp32, gated only). Optional x: a dk of the element type
  * to accumulate onto (the reference adds the dk of chunk_bwd_dqkwg afterwards, chunk.py:168); the sum
- * is formed in fp32 and rounded once. */
+ * is formed in fp32 and rounded once. Optional dgk (gated only; fp32 [B,T,H], used here as "the dg of the
+ * preceding stage"): when given, dg is not this stage's share but the finished gradient of the raw gate,
+ * dg = reverse chunk-local cumsum of (dgk + this stage's dg), which the reference forms with an add and a
+ * cumsum launch (fla/ops/gated_delta_rule/chunk.py:173-176). */
 int flab_wy_bwd(const flab_args *a, void *stream);
 
 /* ---- state recurrence of the (gated) delta rule ----------------------------------------------
