@@ -560,7 +560,51 @@ def configs_record(dev, tri, deadline):
         out[name] = rec
         del i
         torch.cuda.empty_cache()
+    out["layer_path"] = layer_path_record(dev)
+    torch.cuda.empty_cache()
     return out
+
+
+def layer_path_record(dev):
+    """The data path of the reference's Gated DeltaNet layer around the op (fla/layers/gated_deltanet.py:205-282), forward
+    + backward at the headline shape: short convolution + SiLU on q, k, v -> L2 norm of q, k -> gate / beta prologue ->
+    chunk_gated_delta_rule -> RMS norm x swish gate.  Timed twice: with the prologue as the reference writes it (five
+    elementwise PyTorch kernels, the op's own cumsum launch) and with this library's fused prologue kernel."""
+    from fla_b200.modules import ShortConvolution, gdn_gate_beta, l2_norm, rms_norm_swish_gate_fn
+    from fla_b200.ops import chunk_gated_delta_rule
+    B, T, H, D = 8, 4096, 16, 128
+    g0 = torch.Generator(device=dev).manual_seed(11)
+    rn = lambda *s: torch.randn(*s, generator=g0, device=dev)  # noqa: E731
+    xs = {n: rn(B, T, H * D).bfloat16().requires_grad_(True) for n in ("q", "k", "v")}
+    a, b = rn(B, T, H).bfloat16().requires_grad_(True), rn(B, T, H).bfloat16().requires_grad_(True)
+    gate = rn(B, T, H, D).bfloat16().requires_grad_(True)
+    A_log, dt_bias = torch.zeros(H, device=dev, requires_grad=True), torch.zeros(H, device=dev, requires_grad=True)
+    w_norm = torch.ones(D, device=dev, requires_grad=True)
+    convs = {n: ShortConvolution(H * D, 4, activation="silu").to(dev).bfloat16() for n in xs}
+    do = rn(B, T, H, D).bfloat16()
+    leaves = list(xs.values()) + [a, b, gate, A_log, dt_bias, w_norm] + [c.weight for c in convs.values()]
+
+    def step(fused):
+        for t_ in leaves:
+            t_.grad = None
+        q, k, v = (convs[n](xs[n])[0].view(B, T, H, D) for n in ("q", "k", "v"))
+        q, k = l2_norm(q), l2_norm(k)
+        if fused:
+            g, beta = gdn_gate_beta(a, b, A_log, dt_bias)
+        else:
+            beta = b.sigmoid()
+            g = -A_log.float().exp() * F.softplus(a.float() + dt_bias)
+        o, _ = chunk_gated_delta_rule(q, k, v, g, beta, head_first=False)
+        y = rms_norm_swish_gate_fn(o, gate, w_norm, eps=1e-5)
+        torch.autograd.backward([y], [do])
+    rec = {"shape": f"B={B} T={T} H={H} D={D} bf16, conv W=4"}
+    try:
+        rec["ms_reference_style_prologue"] = time_stage(lambda: step(False), reps=10, warm=3)
+        rec["ms_fused_prologue"] = time_stage(lambda: step(True), reps=10, warm=3)
+        rec["tokens_per_s"] = B * T / (rec["ms_fused_prologue"] * 1e-3)
+    except Exception as e:
+        rec["error"] = repr(e)[:400]
+    return rec
 
 
 # ------------------------------------------------------------------------------------------------
