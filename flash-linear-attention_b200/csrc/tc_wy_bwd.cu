@@ -18,7 +18,7 @@
 // Batches:  B1: dw k^T, A_w^T dw, du v^T, A_u^T du      E1: mask / beta / round -> dA operands; dv; dbeta
 //           B2: dA_w A_w^T, dA_u A_u^T                  E2: round -> operands
 //           B3: A_w^T (.), A_u^T (.)                    E3: sign, mask, decay, sum -> dA, diag(beta) dA
-//           B4: dA k, (diag(beta) dA)^T k, k k^T        E4: dk, dbeta, dg
+//           B4: (beta dA) k + (beta dA)^T k, k k^T      E4: dk, dbeta, dg
 // All waits are bounded; a timeout records an id in the unit's error word and the epilogue warps leave
 // together at their next common barrier.
 #include "tc.cuh"
@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char *sIn = base;                      // [2][k | v | dw | du | dk_in | A_w | A_u]
-  unsigned char *sM0 = sIn + 2 * IN_BYTES;        // [64][128 B]: dA_w operand, then its first product, then dA
+  unsigned char *sM0 = sIn + 2 * IN_BYTES;        // [64][128 B]: dA_w operand, then its first product
   unsigned char *sM1 = sM0 + T8;                  // [64][128 B]: dA_u operand, then its first product, then diag(beta) dA
   float *sBeta = reinterpret_cast<float *>(sM1 + T8);  // [2][64]
   float *sG = sBeta + 2 * C;                           // [2][64]
@@ -198,17 +198,16 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
           for (int k = 0; k < 4; ++k) umma(tmem + TM_T2V, dau_m + mx(k), dm1m + mx(k), id_mm64, k > 0);
         }
         umma_commit(&b3_done);
-        // ---- B4: dA k, (diag(beta) dA)^T k, k k^T
+        // ---- B4: (diag(beta) dA) k + (diag(beta) dA)^T k in ONE accumulator (both are dk terms: beta_i (dA k)_i and
+        //          ((beta dA)^T k)_i); k k^T (dbeta needs rowsum(dA * k k^T) = <(dA k)_i, k_i>, dg the same of dA_u)
         if (!mbar_wait(&e3_done, ip)) { fail(87); break; }
         fence_after_sync();
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma(tmem + TM_X, dm0k + kx(k), dk_m + mx(k), id_km128, k > 0);
+        for (int k = 0; k < 4; ++k) umma(tmem + TM_X, dm1k + kx(k), dk_m + mx(k), id_km128, k > 0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma(tmem + TM_Y, dm1m + mx(k), dk_m + mx(k), id_mm128, k > 0);
-        if (GATED) {
+        for (int k = 0; k < 4; ++k) umma(tmem + TM_X, dm1m + mx(k), dk_m + mx(k), id_mm128, 1);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma(tmem + TM_GR, dk_k + kx(k), dk_k + kx(k), id_kk64, k > 0);
-        }
+        for (int k = 0; k < 8; ++k) umma(tmem + TM_GR, dk_k + kx(k), dk_k + kx(k), id_kk64, k > 0);
         umma_commit(&b4_done);
       }
     }
@@ -468,6 +467,7 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       if (!mbar_wait(&b3_done, ip)) fail(92);
       fence_after_sync();
       float dA2[2][4];  // decayed dA_u (gated), for dg
+      float dAt[2][4];  // dA, for dbeta
       {
         float t2k[2][4], t2v[2][4];
         tmem_ld_frag<2>(tmem + lane_base + TM_T2K + 16 * cq, t2k);
@@ -487,9 +487,8 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
               x = rnd1(x + x2);
             }
             d[r] = x;
+            dAt[ni][r] = x;
           }
-          st2(sM0 + o64_lo[ni], d[0], d[1]);
-          st2(sM0 + o64_hi[ni], d[2], d[3]);
           st2(sM1 + o64_lo[ni], d[0] * b_lo, d[1] * b_lo);
           st2(sM1 + o64_hi[ni], d[2] * b_hi, d[3] * b_hi);
         }
@@ -502,21 +501,22 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       if (!mbar_wait(&b4_done, ip)) fail(93);
       fence_after_sync();
       {
-        float x[4][4], y[4][4], gr[2][4];
-        tmem_ld_frag<4>(tmem + lane_base + TM_X + 32 * cq, x);
-        tmem_ld_frag<4>(tmem + lane_base + TM_Y + 32 * cq, y);
-        if (GATED) tmem_ld_frag<2>(tmem + lane_base + TM_GR + 16 * cq, gr);
+        float xy[4][4], gr[2][4];
+        tmem_ld_frag<4>(tmem + lane_base + TM_X + 32 * cq, xy);
+        tmem_ld_frag<2>(tmem + lane_base + TM_GR + 16 * cq, gr);
         tmem_ld_wait();
         fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_free);
 #pragma unroll
+        for (int ni = 0; ni < 2; ++ni) {  // <(dA k)_i, k_i> = sum_j dA_ij (k k^T)_ij
+          db_lo += dAt[ni][0] * gr[ni][0] + dAt[ni][1] * gr[ni][1];
+          db_hi += dAt[ni][2] * gr[ni][2] + dAt[ni][3] * gr[ni][3];
+        }
+#pragma unroll
         for (int ni = 0; ni < 4; ++ni) {
-          const float2 k_lo = ld2(tK + o128_lo[ni]), k_hi = ld2(tK + o128_hi[ni]);
-          db_lo += x[ni][0] * k_lo.x + x[ni][1] * k_lo.y;
-          db_hi += x[ni][2] * k_hi.x + x[ni][3] * k_hi.y;
-          float o0 = dk1[ni][0] + x[ni][0] * b_lo + y[ni][0], o1 = dk1[ni][1] + x[ni][1] * b_lo + y[ni][1];
-          float o2 = dk1[ni][2] + x[ni][2] * b_hi + y[ni][2], o3 = dk1[ni][3] + x[ni][3] * b_hi + y[ni][3];
+          float o0 = dk1[ni][0] + xy[ni][0], o1 = dk1[ni][1] + xy[ni][1];
+          float o2 = dk1[ni][2] + xy[ni][2], o3 = dk1[ni][3] + xy[ni][3];
           if (has_dkin) {
             const float2 i_lo = ld2(tDKI + o128_lo[ni]), i_hi = ld2(tDKI + o128_hi[ni]);
             o0 += i_lo.x, o1 += i_lo.y, o2 += i_hi.x, o3 += i_hi.y;
