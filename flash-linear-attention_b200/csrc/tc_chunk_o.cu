@@ -4,7 +4,10 @@
 //   dv_local : second term of bwd_dv only                                         (fla/ops/common/chunk_o.py:379-441)
 //
 // Persistent kernel, one CTA per SM, work item = (chunk, head, 128-wide V tile).  Nineteen warps:
-//   warp 16 : TMA producer  - streams the item's tiles (x1, x2, y, state) into a ring of stages
+//   warp 16 : TMA producer  - streams the item's tiles (x1, x2, y, state) into a ring of stages; a stage has two halves
+//                             with barriers of their own: x1 | x2 | state is dead as soon as the first two products have
+//                             run, so it is refilled for a later item while the epilogue still works on this one and only
+//                             y waits for the item's last product
 //   warp 17 : MMA issuer    - S = x1 x2^T and O = x1 state into TMEM, later O = P y
 //   warps 0-7 / 8-15: two epilogue groups working on even / odd items (ping-pong); inside a group
 //                     warp = (TMEM lane quadrant = 16 token rows, column half)
@@ -54,7 +57,7 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
   unsigned char *sP = sStage + NS * STAGE_BYTES;         // [2][8192] score tiles (swizzled K-major)
   unsigned char *sOutAll = sP + 2 * 8192;                   // [2][VB][64][128 B] output tiles (swizzled, source of the tile store)
   float *sG = reinterpret_cast<float *>(sOutAll + 2 * Y_BYTES);  // [4][64]: gates of item i in slot i & 3
-  __shared__ uint64_t full[NS], empty[NS], s_done[2], p_ready[2], o_done[2], t_free[2];
+  __shared__ uint64_t full[NS], empty[NS], fullY[NS], emptyY[NS], s_done[2], p_ready[2], o_done[2], t_free[2];
   __shared__ uint64_t gates_full[4], gates_free[4], out_ready[2], out_free[2], copy_done[2];
   __shared__ int sRows[4];
   __shared__ uint32_t tmem_base_s;
@@ -66,6 +69,8 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
     for (int i = 0; i < NS; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
+      mbar_init(&fullY[i], 1);
+      mbar_init(&emptyY[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_done[i], 1);
@@ -109,25 +114,28 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
     if (lane == 0) {
       for (int i = 0; i < n_local && !abort_flag; ++i) {
         const int st = i % NS, ph = (i / NS) & 1;
-        if (!mbar_wait(&empty[st], ph ^ 1)) { fail(1); break; }
+        if (!mbar_wait(&empty[st], ph ^ 1)) { fail(1); break; }  // x1 | x2 | state of the stage's previous item are dead
         int c, hd, vt, n, it;
         decode(blockIdx.x + i * gridDim.x, c, hd, vt);
         chunk_of(a, c, n, it);
         const Seq s = seq_of(a, n);
         const int t0 = s.bos + it * C;
         unsigned char *x1 = sStage + st * STAGE_BYTES, *x2 = x1 + X_BYTES, *y = x2 + X_BYTES, *hh = y + Y_BYTES;
-        mbar_expect_tx(&full[st], STAGE_BYTES);
+        mbar_expect_tx(&full[st], STAGE_BYTES - Y_BYTES);
         const int c1 = a.head_first ? t0 : hd, c2 = a.head_first ? hd : t0;
 #pragma unroll
         for (int j = 0; j < KB; ++j) {
           tma_load_4d(x1 + j * 8192, &mapX1, &full[st], 64 * j, c1, c2, s.b);
           tma_load_4d(x2 + j * 8192, &mapX2, &full[st], 64 * j, c1, c2, s.b);
         }
+        if (HAS_H) {
 #pragma unroll
-        for (int j = 0; j < VB; ++j) {
-          tma_load_4d(y + j * 8192, &mapY, &full[st], vt * BV + 64 * j, c1, c2, s.b);
-          if (HAS_H) tma_load_2d(hh + j * (K * 128), &mapH, &full[st], vt * BV + 64 * j, ((s.c0 + it) * a.H + hd) * K);
+          for (int j = 0; j < VB; ++j) tma_load_2d(hh + j * (K * 128), &mapH, &full[st], vt * BV + 64 * j, ((s.c0 + it) * a.H + hd) * K);
         }
+        if (!mbar_wait(&emptyY[st], ph ^ 1)) { fail(13); break; }  // the last product of the stage's previous item has read y
+        mbar_expect_tx(&fullY[st], Y_BYTES);
+#pragma unroll
+        for (int j = 0; j < VB; ++j) tma_load_4d(y + j * 8192, &mapY, &fullY[st], vt * BV + 64 * j, c1, c2, s.b);
       }
     }
   } else if (warp == 17) {
@@ -149,6 +157,7 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
           for (int s = 0; s < 4 * KB; ++s) umma(t + TM_O, desc_kmajor(x1, s, 8192), desc_mnmajor(hh, s, K * 128), idesc_h, s > 0);
         }
         umma_commit(&s_done[ts]);
+        umma_commit(&empty[st]);  // x1 | x2 | state may be refilled
         return true;
       };
       bool ok = n_local > 0 ? issue12(0) : true;
@@ -157,13 +166,14 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
         if (i + 1 < n_local) ok = issue12(i + 1);
         if (!ok) break;
         if (!mbar_wait(&p_ready[ts], tph)) { fail(4); break; }
+        if (!mbar_wait(&fullY[st], (i / NS) & 1)) { fail(14); break; }
         fence_after_sync();
         const uint32_t y = smem_u32(sStage + st * STAGE_BYTES) + 2 * X_BYTES, pp = smem_u32(sP + ts * 8192);
         const uint32_t t = tmem + ts * TM_STAGE;
 #pragma unroll
         for (int s = 0; s < 4; ++s) umma(t + TM_O, desc_kmajor(pp, s, 8192), desc_mnmajor(y, s, 8192), idesc_h, s > 0);
         umma_commit(&o_done[ts]);
-        umma_commit(&empty[st]);
+        umma_commit(&emptyY[st]);
       }
     }
   } else if (warp == 18) {

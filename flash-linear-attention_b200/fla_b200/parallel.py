@@ -111,11 +111,23 @@ def handoff_states(M: torch.Tensor, b: torch.Tensor, S0: Optional[torch.Tensor],
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     first, step = (world - 1, -1) if reverse else (0, 1)
     prev, nxt = rank - step, rank + step
+
+    def _finish(work, what, peer):
+        # A peer that has left, or a link error, surfaces here: on the host, as an exception that names the hop, after the
+        # process group's timeout at the latest, and before any kernel of this rank has consumed the buffer.
+        try:
+            work.wait()
+        except Exception as e:  # noqa: BLE001 - whatever the backend raises
+            raise RuntimeError(f"sequence-parallel state hand-off: {what} rank {peer} failed on rank {rank}: {e}") from e
+        if hasattr(work, "is_success") and work.is_completed() and not work.is_success():
+            raise RuntimeError(f"sequence-parallel state hand-off: {what} rank {peer} did not succeed on rank {rank}")
+
     if rank == first:
         S_in = torch.zeros_like(b) if S0 is None else S0.to(b.dtype).reshape(b.shape).contiguous()
     else:
         S_in = torch.empty_like(b)
-        dist.recv(S_in, src=dist.get_global_rank(group, prev) if group is not None else prev, group=group)
+        src = dist.get_global_rank(group, prev) if group is not None else prev
+        _finish(dist.irecv(S_in, src=src, group=group), "receive from", prev)
     if b.is_cuda:
         from . import _lib  # one launch of the library's own chain kernel (fp32 FFMA), no library GEMM on this path
         H, K, V = b.shape
@@ -125,7 +137,8 @@ def handoff_states(M: torch.Tensor, b: torch.Tensor, S0: Optional[torch.Tensor],
     else:  # CPU tensors occur only in the gloo tests of this host logic
         S_out = torch.baddbmm(b, M, S_in)
     if 0 <= nxt < world:
-        dist.send(S_out, dst=dist.get_global_rank(group, nxt) if group is not None else nxt, group=group)
+        dst = dist.get_global_rank(group, nxt) if group is not None else nxt
+        _finish(dist.isend(S_out, dst=dst, group=group), "send to", nxt)
     return S_in, S_out
 
 

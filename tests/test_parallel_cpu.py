@@ -111,3 +111,34 @@ def test_sequence_parallel_chain_reproduces_one_shot_gloo():
         ret = mgr.dict()
         mp.spawn(_sp_worker, args=(world, 29650, ret), nprocs=world, join=True)
         assert all(ret.get(r) for r in range(world))
+
+
+def _worker_missing_peer(rank, world, port, ret):
+    """Rank 0 never takes part in the hand-off (it leaves between steps, nothing of its own in flight); rank 1, which
+    waits for rank 0's state, must get an exception that names the hop within the process group's timeout."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        if rank == 0:
+            ret[rank] = "left"
+            return
+        H, K, V = 1, 4, 4
+        try:
+            handoff_states(torch.eye(K).expand(H, K, K).contiguous(), torch.zeros(H, K, V), None)
+            ret[rank] = "no error"
+        except RuntimeError as e:
+            ret[rank] = str(e)
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # the group is already broken on the surviving rank
+            pass
+
+
+def test_handoff_reports_a_peer_that_left():
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_missing_peer, args=(2, 29651, ret), nprocs=2, join=True)
+        assert ret[0] == "left"
+        assert "receive from rank 0 failed on rank 1" in ret[1], ret[1]
