@@ -8,18 +8,20 @@
 //   warp 16 : TMA producer - X1 = {do, v, dv} (48 KB, two buffers), X2 = {h, dh} (64 KB, one buffer) and
 //             Y = {q, k, w} (48 KB, one buffer).  The item starts on X1 (ds, row factors), so X1 of the next item
 //             is fetched a whole item ahead; X2 is refilled as soon as the products against the states are done,
-//             Y as soon as the outputs (built over q, k, w) have been read by the tile store
+//             Y as soon as the last phase has read q, k, w.  The outputs are built over the item's own do, v, dv tiles
+//             (dead once the products against the states have run), so the tile store holds up only a buffer that is
+//             not needed again for a whole item
 //   warp 17 : MMA issuer   - ds = do v^T; then the three products against the states; then the two
 //             intra-chunk products, accumulated onto dq and dk in TMEM
 //   warps 0-15 : epilogue, warp = (TMEM lane quadrant = 16 tokens, 32-column group)
-//   warp 18 : output     - tile stores of dq, dk, dw from the Y buffer, then hands the buffer back to the producer
+//   warp 18 : output     - tile stores of dq, dk, dw from the item's X1 buffer, then hands the buffer back to the producer
 //   warp 19 : scalars    - gates and row count of the coming item into shared memory, zeroed dg rows, and the finished
 //                          dg rows of past items out to global memory: the epilogue warps touch no global memory per
 //                          token and meet each other only through the mbarriers of the phases
 // The row factors of the inter-chunk terms of dq and dk are applied to the A operands in shared memory (do and v are
 // rescaled in place after ds has been formed from the unscaled tiles), so that inter- and intra-chunk parts
 // add up in one accumulator and TMEM holds ds | dq | dk | dw = 448 columns.  dq, dk, dw are written over the
-// q, k, w tiles (each element by the thread that read it for the dg dot) and leave through tile stores.
+// item's do, v, dv tiles and leave through tile stores.
 // All waits are bounded; a timeout records an id in the unit's error word and the epilogue warps leave
 // together at their next common barrier.
 #include "tc.cuh"
@@ -73,7 +75,7 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
     mbar_init(&fullX2, 1);
     mbar_init(&emptyX2, 17);  // the products against the states have completed + every epilogue warp is done with h, dh
     mbar_init(&fullY, 1);
-    mbar_init(&emptyY, 1);
+    mbar_init(&emptyY, 16);  // every epilogue warp has read q, k, w for the last time
     mbar_init(&ds_done, 1);
     mbar_init(&e1_done, 16);
     mbar_init(&dk_done, 1);
@@ -183,7 +185,6 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma(tmem + TM_DW, d_dv + kx(k, 8192), d_h + kx(k, T16), id_st, k > 0);
         }
-        umma_commit(&emptyX1[xb]);
         umma_commit(&emptyX2);
         const uint64_t d_q = desc_mnmajor(smem_u32(sY), 0, 8192), d_k = desc_mnmajor(smem_u32(sY + T16), 0, 8192);
         if (!mbar_wait(&fullY, ph)) { fail(66); break; }
@@ -205,20 +206,21 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
         chunk_of(a, c, n, it);
         const Seq s = seq_of(a, n);
         const int t0 = it * C, rows = min(C, s.len - t0);
-        unsigned char *sQ = sY, *sK = sQ + T16, *sW = sK + T16;
+        const int xb = i & 1;
+        unsigned char *oQ = sX1 + xb * X1_BYTES, *oK = oQ + T16, *oW = oK + T16;  // dq over do, dk over v, dw over dv
         if (!mbar_wait(&out_ready, i & 1)) { fail(73); break; }
         if (rows == C) {  // (a ragged chunk was written out by the epilogue warps themselves)
           const int tt = s.bos + t0, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            tma_store_4d(&m.dq, sQ + j * 8192, 64 * j, c1, c2, s.b);
-            tma_store_4d(&m.dk, sK + j * 8192, 64 * j, c1, c2, s.b);
-            if (USE_DW) tma_store_4d(&m.dw, sW + j * 8192, 64 * j, c1, c2, s.b);
+            tma_store_4d(&m.dq, oQ + j * 8192, 64 * j, c1, c2, s.b);
+            tma_store_4d(&m.dk, oK + j * 8192, 64 * j, c1, c2, s.b);
+            if (USE_DW) tma_store_4d(&m.dw, oW + j * 8192, 64 * j, c1, c2, s.b);
           }
           tma_store_commit();
           tma_store_wait_read();
         }
-        mbar_arrive(&emptyY);
+        mbar_arrive(&emptyX1[xb]);
       }
       tma_store_wait_all();
     }
@@ -424,7 +426,7 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&e1b_done);
       }
-      // ---- E2: finished dq, dk, dw -> dg rows, outputs over the q, k, w tiles
+      // ---- E2: finished dq, dk, dw -> dg rows (dots with q, k, w), outputs over the item's do, v, dv tiles
       if (!mbar_wait(&all_done, ph)) fail(72);
       fence_after_sync();
       float dq[4][4], dk[4][4], dw[4][4];
@@ -445,10 +447,10 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
           dg_lo += dq[ni][0] * q_lo.x + dq[ni][1] * q_lo.y - dk[ni][0] * k_lo.x - dk[ni][1] * k_lo.y;
           dg_hi += dq[ni][2] * q_hi.x + dq[ni][3] * q_hi.y - dk[ni][2] * k_hi.x - dk[ni][3] * k_hi.y;
         }
-        st2(sQ + o_lo, dq[ni][0], dq[ni][1]);
-        st2(sQ + o_hi, dq[ni][2], dq[ni][3]);
-        st2(sK + o_lo, dk[ni][0], dk[ni][1]);
-        st2(sK + o_hi, dk[ni][2], dk[ni][3]);
+        st2(sDo + o_lo, dq[ni][0], dq[ni][1]);
+        st2(sDo + o_hi, dq[ni][2], dq[ni][3]);
+        st2(sV + o_lo, dk[ni][0], dk[ni][1]);
+        st2(sV + o_hi, dk[ni][2], dk[ni][3]);
         if (USE_DW) {
           // dw = -e^{b} (dv h^T): the row factor goes onto the fp32 product here (dv itself was left as loaded)
           dw[ni][0] *= -e_lo, dw[ni][1] *= -e_lo, dw[ni][2] *= -e_hi, dw[ni][3] *= -e_hi;
@@ -457,10 +459,12 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
             dg_lo += dw[ni][0] * w_lo.x + dw[ni][1] * w_lo.y;
             dg_hi += dw[ni][2] * w_hi.x + dw[ni][3] * w_hi.y;
           }
-          st2(sW + o_lo, dw[ni][0], dw[ni][1]);
-          st2(sW + o_hi, dw[ni][2], dw[ni][3]);
+          st2(sDv + o_lo, dw[ni][0], dw[ni][1]);
+          st2(sDv + o_hi, dw[ni][2], dw[ni][3]);
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&emptyY);  // q, k, w have been read for the last time: the producer may fetch the next item's
       if (use_g) {
         dg_lo += __shfl_xor_sync(0xffffffffu, dg_lo, 1);
         dg_lo += __shfl_xor_sync(0xffffffffu, dg_lo, 2);
@@ -490,13 +494,13 @@ __global__ void __launch_bounds__(640, 1) tc_dqkwg_kernel(const __grid_constant_
           const int r_ = e >> 4, c_ = (e & 15) * 8;
           const uint32_t so = (uint32_t)(c_ >> 6) * 8192u + sw128_offset(r_, c_ & 63);
           const size_t go = off0 + (size_t)r_ * ks + c_;
-          *reinterpret_cast<int4 *>(reinterpret_cast<bf16 *>(a.dq) + go) = *reinterpret_cast<const int4 *>(sQ + so);
-          *reinterpret_cast<int4 *>(reinterpret_cast<bf16 *>(a.dk) + go) = *reinterpret_cast<const int4 *>(sK + so);
-          if (USE_DW) *reinterpret_cast<int4 *>(reinterpret_cast<bf16 *>(a.dw) + go) = *reinterpret_cast<const int4 *>(sW + so);
+          *reinterpret_cast<int4 *>(reinterpret_cast<bf16 *>(a.dq) + go) = *reinterpret_cast<const int4 *>(sDo + so);
+          *reinterpret_cast<int4 *>(reinterpret_cast<bf16 *>(a.dk) + go) = *reinterpret_cast<const int4 *>(sV + so);
+          if (USE_DW) *reinterpret_cast<int4 *>(reinterpret_cast<bf16 *>(a.dw) + go) = *reinterpret_cast<const int4 *>(sDv + so);
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&out_ready);  // this warp is done with the Y buffer
+      if (lane == 0) mbar_arrive(&out_ready);  // this warp's part of the output tiles is complete
     }
   }
   fence_before_sync();
