@@ -18,7 +18,8 @@
 // Batches:  B1: dw k^T, A_w^T dw, du v^T, A_u^T du      E1: mask / beta / round -> dA operands; dv; dbeta
 //           B2: dA_w A_w^T, dA_u A_u^T                  E2: round -> operands
 //           B3: A_w^T (.), A_u^T (.)                    E3: sign, mask, decay, sum -> dA, diag(beta) dA
-//           B4: (beta dA) k + (beta dA)^T k, k k^T      E4: dk, dbeta, dg
+//           (k k^T behind B3)                           dbeta / dg sums over dA * k k^T
+//           B4: (beta dA) k + (beta dA)^T k             E4: dk, dbeta
 // All waits are bounded; a timeout records an id in the unit's error word and the epilogue warps leave
 // together at their next common barrier.
 #include "tc.cuh"
@@ -59,7 +60,7 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
   float *sDB = sG + 2 * C;                             // [2][4][64] dbeta rows per column group
   float *sDG = sDB + 8 * C;                            // [2][4][64] dg row sums per column group
   float *sDGC = sDG + 8 * C;                           // [2][4][64] dg column sums per lane quadrant
-  __shared__ uint64_t full[2], empty[2], zero_done, b1_done, e1_done, b2_done, e2_done, b3_done, e3_done, b4_done, acc_free, out_ready;
+  __shared__ uint64_t full[2], empty[2], zero_done, b1_done, e1_done, b2_done, e2_done, b3_done, gr_done, e3_done, b4_done, acc_free, out_ready;
   __shared__ uint64_t scal_full[2], rows_done[2], ragged_sync;
   __shared__ int sRows[2];
   __shared__ uint32_t tmem_base_s;
@@ -78,6 +79,7 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
     mbar_init(&b2_done, 1);
     mbar_init(&e2_done, 16);
     mbar_init(&b3_done, 1);
+    mbar_init(&gr_done, 1);
     mbar_init(&e3_done, 16);
     mbar_init(&b4_done, 1);
     mbar_init(&acc_free, 16);
@@ -198,16 +200,20 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
           for (int k = 0; k < 4; ++k) umma(tmem + TM_T2V, dau_m + mx(k), dm1m + mx(k), id_mm64, k > 0);
         }
         umma_commit(&b3_done);
+        // k k^T (dbeta needs rowsum(dA * k k^T) = <(dA k)_i, k_i>, dg the same of dA_u) depends on nothing the epilogue
+        // makes: it runs behind B3, in the columns the first product of the transform has left, and the epilogue turns
+        // it into the dbeta / dg sums while B4 runs
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma(tmem + TM_GR, dk_k + kx(k), dk_k + kx(k), id_kk64, k > 0);
+        umma_commit(&gr_done);
         // ---- B4: (diag(beta) dA) k + (diag(beta) dA)^T k in ONE accumulator (both are dk terms: beta_i (dA k)_i and
-        //          ((beta dA)^T k)_i); k k^T (dbeta needs rowsum(dA * k k^T) = <(dA k)_i, k_i>, dg the same of dA_u)
+        //          ((beta dA)^T k)_i)
         if (!mbar_wait(&e3_done, ip)) { fail(87); break; }
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma(tmem + TM_X, dm1k + kx(k), dk_m + mx(k), id_km128, k > 0);
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma(tmem + TM_X, dm1m + mx(k), dk_m + mx(k), id_mm128, 1);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma(tmem + TM_GR, dk_k + kx(k), dk_k + kx(k), id_kk64, k > 0);
         umma_commit(&b4_done);
       }
     }
@@ -370,6 +376,18 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       float *bs = sBeta + ip * C, *gs = sG + ip * C;
       float *dbs = sDB + (ip * 4 + cq) * C, *dgs = sDG + (ip * 4 + cq) * C, *dgc = sDGC + (ip * 4 + wq) * C;
       const float b_lo = bs[row_lo], b_hi = bs[row_hi], g_lo = gs[row_lo], g_hi = gs[row_hi];
+      // decay e^{g_i - g_j} of this thread's eight entries of the 64x64 blocks (strict lower triangle), computed here,
+      // ahead of the first wait, so that E3, which sits on the chain between two products, only multiplies
+      float dec[2][4];
+      if (GATED) {
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int row = (r >> 1) ? row_hi : row_lo, cc = c64 + 8 * ni + (r & 1);
+            dec[ni][r] = row > cc ? __expf(fminf(((r >> 1) ? g_hi : g_lo) - gs[cc], 0.f)) : 0.f;
+          }
+      }
       if (!mbar_wait(&full[b], ph)) fail(89);
       if (rows < C) {
         // ragged last chunk: the rows of dw, du past the end of the sequence hold another sequence's data
@@ -482,7 +500,7 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
             const int row = (r >> 1) ? row_hi : row_lo, cc = col + (r & 1);
             float x = row > cc ? rnd1(-t2k[ni][r]) : 0.f;
             if (GATED) {
-              const float x2 = row > cc ? rnd1(-t2v[ni][r]) * __expf(fminf(((r >> 1) ? g_hi : g_lo) - gs[cc], 0.f)) : 0.f;
+              const float x2 = rnd1(-t2v[ni][r]) * dec[ni][r];
               dA2[ni][r] = x2;
               x = rnd1(x + x2);
             }
@@ -497,40 +515,17 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&e3_done);
-      // ---- E4: dk, dbeta, dg
-      if (!mbar_wait(&b4_done, ip)) fail(93);
+      // ---- the dbeta / dg sums that need k k^T, while the tensor core runs B4
+      if (!mbar_wait(&gr_done, ip)) fail(98);
       fence_after_sync();
       {
-        float xy[4][4], gr[2][4];
-        tmem_ld_frag<4>(tmem + lane_base + TM_X + 32 * cq, xy);
+        float gr[2][4];
         tmem_ld_frag<2>(tmem + lane_base + TM_GR + 16 * cq, gr);
         tmem_ld_wait();
-        fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_free);
 #pragma unroll
         for (int ni = 0; ni < 2; ++ni) {  // <(dA k)_i, k_i> = sum_j dA_ij (k k^T)_ij
           db_lo += dAt[ni][0] * gr[ni][0] + dAt[ni][1] * gr[ni][1];
           db_hi += dAt[ni][2] * gr[ni][2] + dAt[ni][3] * gr[ni][3];
-        }
-#pragma unroll
-        for (int ni = 0; ni < 4; ++ni) {
-          float o0 = dk1[ni][0] + xy[ni][0], o1 = dk1[ni][1] + xy[ni][1];
-          float o2 = dk1[ni][2] + xy[ni][2], o3 = dk1[ni][3] + xy[ni][3];
-          if (has_dkin) {
-            const float2 i_lo = ld2(tDKI + o128_lo[ni]), i_hi = ld2(tDKI + o128_hi[ni]);
-            o0 += i_lo.x, o1 += i_lo.y, o2 += i_hi.x, o3 += i_hi.y;
-          }
-          st2(tDW + o128_lo[ni], o0, o1);  // dk, over dw
-          st2(tDW + o128_hi[ni], o2, o3);
-        }
-        db_lo += __shfl_xor_sync(0xffffffffu, db_lo, 1);
-        db_lo += __shfl_xor_sync(0xffffffffu, db_lo, 2);
-        db_hi += __shfl_xor_sync(0xffffffffu, db_hi, 1);
-        db_hi += __shfl_xor_sync(0xffffffffu, db_hi, 2);
-        if (t4 == 0) {
-          dbs[row_lo] = db_lo;
-          dbs[row_hi] = db_hi;
         }
         if (GATED) {
           float r_lo = 0.f, r_hi = 0.f;
@@ -560,6 +555,36 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
             dgs[row_lo] = r_lo;
             dgs[row_hi] = r_hi;
           }
+        }
+      }
+      // ---- E4: dk, dbeta
+      if (!mbar_wait(&b4_done, ip)) fail(93);
+      fence_after_sync();
+      {
+        float xy[4][4];
+        tmem_ld_frag<4>(tmem + lane_base + TM_X + 32 * cq, xy);
+        tmem_ld_wait();
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_free);
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni) {
+          float o0 = dk1[ni][0] + xy[ni][0], o1 = dk1[ni][1] + xy[ni][1];
+          float o2 = dk1[ni][2] + xy[ni][2], o3 = dk1[ni][3] + xy[ni][3];
+          if (has_dkin) {
+            const float2 i_lo = ld2(tDKI + o128_lo[ni]), i_hi = ld2(tDKI + o128_hi[ni]);
+            o0 += i_lo.x, o1 += i_lo.y, o2 += i_hi.x, o3 += i_hi.y;
+          }
+          st2(tDW + o128_lo[ni], o0, o1);  // dk, over dw
+          st2(tDW + o128_hi[ni], o2, o3);
+        }
+        db_lo += __shfl_xor_sync(0xffffffffu, db_lo, 1);
+        db_lo += __shfl_xor_sync(0xffffffffu, db_lo, 2);
+        db_hi += __shfl_xor_sync(0xffffffffu, db_hi, 1);
+        db_hi += __shfl_xor_sync(0xffffffffu, db_hi, 2);
+        if (t4 == 0) {
+          dbs[row_lo] = db_lo;
+          dbs[row_hi] = db_hi;
         }
       }
       fence_proxy_async();
