@@ -879,7 +879,7 @@ def main():
         nbytes = B * H * (2 * K * V * 4 + (2 * K + 2 * V) * 2 + 8)
         ach = nbytes / (ms_k * 1e-3) / 1e9
         line["roofline"] = {"kernel": "recurrent_stream_kernel (decode)", "bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"],
-                            "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": 485e6,
+                            "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": 484e6,
                             "traffic_source": "ncu, same workload (profiles/decode_stream_kernel_ncu_full.md)", "peak_source": pk["source"],
                             "ms_per_launch": ms_k}
         # the same step replayed from a CUDA graph (fla_b200.decode): fixed buffers, state updated in place
@@ -1024,8 +1024,8 @@ def main():
 # DRAM bytes per token-head of each stage's kernel, from the ncu capture summarised in
 # profiles/gdn_kernels_ncu_full_T2048.md (dram__bytes_read.sum + dram__bytes_write.sum at T=2048, 262 144
 # token-heads; the traffic of these kernels is proportional to the number of tokens)
-NCU_BYTES_PER_TOKENHEAD = {"wy_fwd": 1074, "delta_fwd_h": 1415, "chunk_fwd_o": 1499, "dv_local": 941,
-                           "delta_bwd_dhu": 1953, "dqkwg": 3240, "wy_bwd": 1966}
+NCU_BYTES_PER_TOKENHEAD = {"wy_fwd": 1071, "delta_fwd_h": 1413, "chunk_fwd_o": 1478, "dv_local": 941,
+                           "delta_bwd_dhu": 1973, "dqkwg": 3255, "wy_bwd": 1972}
 
 
 if __name__ == "__main__":

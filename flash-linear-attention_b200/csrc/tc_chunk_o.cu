@@ -196,10 +196,48 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
         if (lane + 32 < rows) g1 = G[tok_off(a, s, hd, t0 + lane + 32, 1)];
       }
     };
+    // Lane 0 also sends the finished output tiles on their way, three items behind the gates it publishes: it waits for
+    // the eight warps of the item's group, issues the tile stores and, once the copy engine has read the PREVIOUS item's
+    // tile (or, after a ragged chunk, once that group's warps have copied their rows out), tells the other group that
+    // its output buffer is free.  No epilogue warp issues a store or waits for one.
+    int n_rag0 = 0, n_rag1 = 0;  // ragged items seen per group
+    int prev_rows = C;  // row count of the item before the one being stored
+    auto store_out = [&](int j) -> bool {
+      const int grp = j & 1, kk = j >> 1;
+      if (!mbar_wait(&out_ready[grp], kk & 1)) { fail(10); return false; }
+      int c, hd, vt, n, it;
+      decode(blockIdx.x + j * gridDim.x, c, hd, vt);
+      chunk_of(a, c, n, it);
+      const Seq s = seq_of(a, n);
+      const int rows = min(C, s.len - it * C);
+      if (rows == C) {
+        const int tt = s.bos + it * C, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
+        unsigned char *src = sOutAll + grp * Y_BYTES;
+#pragma unroll
+        for (int jj = 0; jj < VB; ++jj) tma_store_4d(&mapOut, src + jj * 8192, vt * BV + 64 * jj, c1, c2, s.b);
+        tma_store_commit();
+      }
+      if (j >= 1) {
+        const int og = grp ^ 1;
+        if (prev_rows < C) {
+          if (!mbar_wait(&copy_done[og], (og ? n_rag1 : n_rag0) & 1)) { fail(11); return false; }
+          if (og) ++n_rag1;
+          else ++n_rag0;
+        } else if (rows == C) {
+          tma_store_wait_read_but_one();
+        } else {
+          tma_store_wait_read();
+        }
+        mbar_arrive(&out_free[og]);
+      }
+      prev_rows = rows;
+      return true;
+    };
     float c0, c1, n0, n1;
     int crows, nrows;
     fetch(0, c0, c1, crows);
-    for (int i = 0; i < n_local && !abort_flag; ++i) {
+    bool alive = true;
+    for (int i = 0; i < n_local && alive && !abort_flag; ++i) {
       const int slot = i & 3;
       fetch(i + 1, n0, n1, nrows);
       if (i >= 4 && !mbar_wait(&gates_free[slot], ((i - 4) >> 2) & 1)) { fail(9); break; }  // item i - 4 has read the slot
@@ -207,8 +245,16 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
       sG[slot * C + lane + 32] = c1;
       if (lane == 0) sRows[slot] = crows;
       __syncwarp();
-      if (lane == 0) mbar_arrive(&gates_full[slot]);
+      if (lane == 0) {
+        mbar_arrive(&gates_full[slot]);
+        if (i >= 3) alive = store_out(i - 3);
+      }
+      alive = __shfl_sync(0xffffffffu, alive, 0);
       c0 = n0, c1 = n1, crows = nrows;
+    }
+    if (lane == 0) {
+      for (int j = n_local > 3 ? n_local - 3 : 0; j < n_local && alive && !abort_flag; ++j) alive = store_out(j);
+      tma_store_wait_all();
     }
   } else {
     // ------------------------------------------------------------------ epilogue groups (warps 0-7, 8-15)
@@ -219,8 +265,6 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
     constexpr int NIO = 4 * VB;  // accumulator n-tiles of this warp's half of the O columns
     unsigned char *sOut = sOutAll + grp * Y_BYTES;
     const int row_lo = m0 + g8, row_hi = row_lo + 8;
-    int n_ragged = 0;
-    bool prev_ragged = false;
     for (int i = grp; i < n_local && !abort_flag; i += 2) {
       const int st = grp, ph = (i >> 1) & 1, k = i >> 1, slot = i & 3;
       // gates and row count of this item, from the scalar warp
@@ -298,19 +342,8 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&t_free[st]);
-      if (k >= 1) {
-        // the group's previous tile has left sOut: the thread that stored it says so once the copy engine has read it
-        // (or, after a ragged chunk, once every warp has copied its rows out)
-        if (gw == 0 && lane == 0) {
-          if (prev_ragged) {
-            if (!mbar_wait(&copy_done[grp], (n_ragged - 1) & 1)) fail(11);
-          } else {
-            tma_store_wait_read();
-          }
-          mbar_arrive(&out_free[grp]);
-        }
-        if (!mbar_wait(&out_free[grp], (k - 1) & 1)) { fail(8); break; }
-      }
+      // the group's previous tile has left sOut (the scalar warp says so)
+      if (k >= 1 && !mbar_wait(&out_free[grp], (k - 1) & 1)) { fail(8); break; }
       const float osc = MODE == TMODE_O ? a.scale : 1.f;
 #pragma unroll
       for (int ni = 0; ni < NIO; ++ni)
@@ -326,20 +359,7 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&out_ready[grp]);  // this warp's part of the output tile is written
-      prev_ragged = rows < C;
-      if (rows == C) {
-        if (gw == 0 && lane == 0) {  // the whole tile is there: one tile store per 64-column box
-          if (!mbar_wait(&out_ready[grp], k & 1)) fail(10);  // (no early exit of a single lane: the warp stays together)
-          int c, hd, vt, n, it;
-          decode(blockIdx.x + i * gridDim.x, c, hd, vt);
-          chunk_of(a, c, n, it);
-          const Seq s = seq_of(a, n);
-          const int tt = s.bos + it * C, c1 = a.head_first ? tt : hd, c2 = a.head_first ? hd : tt;
-#pragma unroll
-          for (int j = 0; j < VB; ++j) tma_store_4d(&mapOut, sOut + j * 8192, vt * BV + 64 * j, c1, c2, s.b);
-          tma_store_commit();
-        }
-      } else {
+      if (rows < C) {
         // ragged last chunk of a sequence: a tile store would write past its end; once the whole tile is there the
         // group's warps copy the valid rows out with ordinary stores
         if (!mbar_wait(&out_ready[grp], k & 1)) { fail(12); break; }
@@ -356,10 +376,8 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&copy_done[grp]);
-        ++n_ragged;
       }
     }
-    if (gw == 0 && lane == 0) tma_store_wait_all();
   }
   fence_before_sync();
   __syncthreads();
