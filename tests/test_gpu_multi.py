@@ -1,6 +1,7 @@
 """GPU (needs >= 2 devices): sequence-parallel forward and backward over NCCL, first against the CPU oracle run over
 the whole sequence, then against the single-GPU result."""
 import os
+from datetime import timedelta
 
 import pytest
 import torch
@@ -11,13 +12,14 @@ import torch.nn.functional as F
 import oracle
 from util import err_ratio
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.timeout(300)]
 
 
 def _worker(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    # a short process-group timeout: a rank that fails must end its peers' collectives with an error, not leave them waiting
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=timedelta(seconds=120))
     try:
         from fla_b200.ops import chunk_gated_delta_rule
         from fla_b200.parallel import sp_chunk_gated_delta_rule_fwd
@@ -60,7 +62,8 @@ def test_sequence_parallel_forward_matches_single_gpu():
 def _worker_bwd(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    # a short process-group timeout: a rank that fails must end its peers' collectives with an error, not leave them waiting
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=timedelta(seconds=120))
     try:
         from fla_b200.ops import chunk_gated_delta_rule
         from fla_b200.parallel import sp_chunk_gated_delta_rule
