@@ -740,7 +740,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        from datetime import timedelta
+        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=300))  # a failed rank ends the others' collectives soon
     from fla_b200 import _lib
 
     host = make_inputs(op, B, T, H, K, V, 1000 + rank, dtype)
