@@ -1025,8 +1025,8 @@ def main():
 # DRAM bytes per token-head of each stage's kernel, from the ncu capture summarised in
 # profiles/gdn_kernels_ncu_full_T2048.md (dram__bytes_read.sum + dram__bytes_write.sum at T=2048, 262 144
 # token-heads; the traffic of these kernels is proportional to the number of tokens)
-NCU_BYTES_PER_TOKENHEAD = {"wy_fwd": 1071, "delta_fwd_h": 1413, "chunk_fwd_o": 1478, "dv_local": 941,
-                           "delta_bwd_dhu": 1973, "dqkwg": 3255, "wy_bwd": 1972}
+NCU_BYTES_PER_TOKENHEAD = {"wy_fwd": 1076, "delta_fwd_h": 1412, "chunk_fwd_o": 1476, "dv_local": 925,
+                           "delta_bwd_dhu": 1960, "dqkwg": 3241, "wy_bwd": 1970}
 
 
 if __name__ == "__main__":
