@@ -13,7 +13,9 @@
 //                     warp = (TMEM lane quadrant = 16 token rows, column half)
 //                           - S -> mask / decay -> P (bf16, swizzled shared memory); O -> gate -> out
 //   warp 18 : scalars       - gates and row count of the coming items into a ring of four shared-memory slots, so that no
-//                             epilogue warp ever waits for a global load
+//                             epilogue warp ever waits for a global load; its first lane also issues the tile stores of
+//                             the finished output tiles (three items behind the gates) and frees the groups' output
+//                             buffers, so that no epilogue warp issues a store or waits for one either
 // The epilogue warps meet each other only through the mbarriers of the phases (one arrival per warp), never through a
 // barrier of the group.
 // The epilogue arithmetic (one exponential per score element, packing, swizzled stores) is what

@@ -4,7 +4,7 @@
 //   dw = -e^{b_i} (dv h^T)                         (delta-rule families only)
 //   dg_i = <q_i, dq_i> - <k_i, dk_i> + <w_i, dw_i>;  dg_last += e^{b_L} <h, dh> + <k, dk_inter>
 //   (fla/ops/common/chunk_o.py:444-600)
-// Persistent kernel, one CTA per SM, work item = (chunk, head).  Eighteen warps:
+// Persistent kernel, one CTA per SM, work item = (chunk, head).  Twenty warps:
 //   warp 16 : TMA producer - X1 = {do, v, dv} (48 KB, two buffers), X2 = {h, dh} (64 KB, one buffer) and
 //             Y = {q, k, w} (48 KB, one buffer).  The item starts on X1 (ds, row factors), so X1 of the next item
 //             is fetched a whole item ahead; X2 is refilled as soon as the products against the states are done,
