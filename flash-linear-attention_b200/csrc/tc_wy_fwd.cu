@@ -221,27 +221,28 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
       if (p.ab_fmt) *reinterpret_cast<__nv_bfloat162 *>(ptr) = __floats2bfloat162_rn(x, y);
       else *reinterpret_cast<__half2 *>(ptr) = __floats2half2_rn(x, y);
     };
-    // beta and gate of token `gtid` of local item i (fetched one of the group's items ahead)
-    auto scalars_of = [&](int i, float &bt, float &gt) {
-      bt = 0.f, gt = 0.f;
-      if (gtid >= C || i >= n_local) return;
-      Seq s;
-      int hd, t0, rows;
-      locate(i, s, hd, t0, rows);
-      if (gtid < rows) {
-        const size_t o = tok_off(a, s, hd, t0 + gtid, 1);
-        bt = p.ab_fmt ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.beta)[o]) : __half2float(reinterpret_cast<const __half *>(a.beta)[o]);
-        if (GATED) gt = reinterpret_cast<const float *>(a.g)[o];
+    // Where the group's next item lies, and beta and gate of its token `gtid`: worked out one of the group's items ahead,
+    // while the tensor core runs the current item's products, so that neither the index arithmetic (integer divisions)
+    // nor the global loads sit on the group's chain
+    Seq s_n;
+    int hd_n = 0, t0_n = 0, rows_n = 0;
+    float b_pf = 0.f, g_pf = 0.f;
+    auto fetch = [&](int i) {
+      b_pf = 0.f, g_pf = 0.f, rows_n = 0;
+      if (i >= n_local) return;
+      locate(i, s_n, hd_n, t0_n, rows_n);
+      if (gtid < rows_n) {  // (rows_n <= 64)
+        const size_t o = tok_off(a, s_n, hd_n, t0_n + gtid, 1);
+        b_pf = p.ab_fmt ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.beta)[o]) : __half2float(reinterpret_cast<const __half *>(a.beta)[o]);
+        if (GATED) g_pf = reinterpret_cast<const float *>(a.g)[o];
       }
     };
-    float b_pf, g_pf;
-    scalars_of(g, b_pf, g_pf);
+    fetch(g);
     for (int i = g; i < n_local; i += 2) {
       const int ph = (i >> 1) & 1;
       unsigned char *tK = sbuf(i % NS), *tV = tK + T16;
-      Seq s;
-      int hd, t0, rows;
-      locate(i, s, hd, t0, rows);
+      const Seq s = s_n;
+      const int hd = hd_n, t0 = t0_n, rows = rows_n;
       if (gtid < C) {
         bs[gtid] = b_pf;
         gs[gtid] = g_pf;
@@ -249,7 +250,6 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
       if (gtid == 0) abort_snap[g][ph] = abort_flag;
       grp_sync();
       if (abort_snap[g][ph]) break;
-      scalars_of(i + 2, b_pf, g_pf);
       // ---- E1: Gram block -> fp32 work matrix -> inverse -> A (stored), A diag(beta) (operands)
       if (!mbar_wait(&g1_done[g], ph)) fail(107);
       fence_after_sync();
@@ -309,6 +309,7 @@ __global__ void __launch_bounds__(640, 1) tc_wy_fwd_kernel(const __grid_constant
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&e1_done[g]);
+      fetch(i + 2);
       // ---- E2: w, u -> rounded, over the k and v tiles
       if (!mbar_wait(&g23_done[g], ph)) fail(108);
       fence_after_sync();
