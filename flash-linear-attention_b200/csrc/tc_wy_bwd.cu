@@ -151,11 +151,20 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
       const uint64_t dm0k = desc_kmajor(smem_u32(sM0), 0, 8192), dm1k = desc_kmajor(smem_u32(sM1), 0, 8192);
       const uint64_t dm0m = desc_mnmajor(smem_u32(sM0), 0, 8192), dm1m = desc_mnmajor(smem_u32(sM1), 0, 8192);
       int n_ragged = 0;
-      for (int i = 0; i < n_local && !abort_flag; ++i) {
-        const int b = i & 1, ph = (i >> 1) & 1, ip = i & 1;
+      // Only the row count of an item matters here (a ragged item waits for its zeroed rows). Its index arithmetic
+      // (integer divisions) is done an item ahead, while this thread waits for the epilogue anyway: at the top of an
+      // item it would delay the first batch, which the epilogue is waiting for.
+      auto rows_of = [&](int i) -> int {
+        if (i >= n_local) return C;
         Seq s;
         int hd, t0, rows;
         locate(i, s, hd, t0, rows);
+        return rows;
+      };
+      int rows_next = rows_of(0);
+      for (int i = 0; i < n_local && !abort_flag; ++i) {
+        const int b = i & 1, ph = (i >> 1) & 1, ip = i & 1;
+        const int rows = rows_next;
         const uint32_t in = smem_u32(sIn + b * IN_BYTES);
         const uint32_t tk = in, tv = in + T16, tdw = in + 2 * T16, tdu = in + 3 * T16, taw = in + 5 * T16, tau = GATED ? taw + T8 : taw;
         const uint64_t dk_k = desc_kmajor(tk, 0, 8192), dv_k = desc_kmajor(tv, 0, 8192), dk_m = desc_mnmajor(tk, 0, 8192);
@@ -190,6 +199,7 @@ __global__ void __launch_bounds__(640, 1) tc_wy_bwd_kernel(const __grid_constant
           for (int k = 0; k < 4; ++k) umma(tmem + TM_T1V, dm1k + kx(k), dau_k + kx(k), id_kk64, k > 0);
         }
         umma_commit(&b2_done);
+        rows_next = rows_of(i + 1);
         // ---- B3: A^T (.)
         if (!mbar_wait(&e2_done, ip)) { fail(86); break; }
         fence_after_sync();
