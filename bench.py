@@ -83,7 +83,7 @@ WORKLOADS = {
 # THE byte / flop table (per token-head, 16-bit elements, K = V = 128, chunk of 64 tokens).  X = one [B,T,H,128] tensor
 # = 256 B per token-head; a pass over the chunk states h or dh is K*V*2/64 = 512 B = 2X; A = one [B,T,H,64] tensor = 128 B.
 # bytes = what the stage must read and write once (its inputs and outputs, nothing re-read); flops = dense-tile count,
-# 1 MAC = 2 flops.  DESIGN.md section 3 quotes this table; nothing else in the repository defines these numbers.
+# 1 MAC = 2 flops.  The design document quotes this table; nothing else in the repository defines these numbers.
 # ------------------------------------------------------------------------------------------------
 X, ST, A64 = 256, 512, 128
 KV, CK, CV, CC = 128 * 128, 64 * 128, 64 * 128, 64 * 64
