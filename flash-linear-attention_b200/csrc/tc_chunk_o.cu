@@ -116,12 +116,13 @@ tc_chunk_o_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_consta
     if (lane == 0) {
       for (int i = 0; i < n_local && !abort_flag; ++i) {
         const int st = i % NS, ph = (i / NS) & 1;
-        if (!mbar_wait(&empty[st], ph ^ 1)) { fail(1); break; }  // x1 | x2 | state of the stage's previous item are dead
+        // (where the item lies is worked out before the wait: the loads go out the moment the stage is free)
         int c, hd, vt, n, it;
         decode(blockIdx.x + i * gridDim.x, c, hd, vt);
         chunk_of(a, c, n, it);
         const Seq s = seq_of(a, n);
         const int t0 = s.bos + it * C;
+        if (!mbar_wait(&empty[st], ph ^ 1)) { fail(1); break; }  // x1 | x2 | state of the stage's previous item are dead
         unsigned char *x1 = sStage + st * STAGE_BYTES, *x2 = x1 + X_BYTES, *y = x2 + X_BYTES, *hh = y + Y_BYTES;
         mbar_expect_tx(&full[st], STAGE_BYTES - Y_BYTES);
         const int c1 = a.head_first ? t0 : hd, c2 = a.head_first ? hd : t0;
